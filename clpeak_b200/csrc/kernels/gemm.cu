@@ -1,0 +1,360 @@
+// C[M][N] = A[M][K] * B[N][K]^T on tcgen05.mma, the in-house replacement for the
+// cuBLASLt call the reference makes for its "GEMM peak" rows.
+//
+// Shape of the kernel
+//  * Persistent: one 2-CTA cluster per SM pair, tiles handed out round-robin.
+//  * A cluster computes a 256x256 tile with 2-SM MMAs (cta_group::2, M=256,
+//    N=256): CTA r of the pair owns rows [128r, 128r+128) of the tile and holds
+//    that half of the accumulator in its own tensor memory; it loads its 128
+//    rows of A and its 128-row half of B, and the MMA reads both CTAs' shared
+//    memory.  No TMA multicast anywhere: each CTA fetches what it needs itself.
+//  * Warp roles (192 threads): warp 0 TMA producer, warp 1 MMA issuer (leader
+//    CTA only) and TMEM owner, warps 2-5 epilogue (TMEM -> registers -> bf16 ->
+//    global).  TMEM holds two 256-column accumulators so the epilogue of tile
+//    i overlaps the main loop of tile i+1.
+//  * K is consumed in blocks of 128 bytes per row (64 x 16-bit, 128 x 8-bit),
+//    the width of one 128-byte-swizzled TMA box; a stage is 16 KiB of A and
+//    16 KiB of B per CTA.  Both CTAs' loads signal the leader's "full"
+//    barrier; tcgen05.commit releases a stage in both CTAs at once.
+//  * Every mbarrier wait is bounded; on expiry the status word is set and all
+//    roles fall through to the common exit, which frees tensor memory.
+//
+// Algorithmic work: 2*M*N*K flop per call; HBM traffic at least
+// (M*K + N*K)*elem + M*N*2 bytes (each operand read once, C written once).
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "../clpk_internal.h"
+#include "../clpk_ptx.cuh"
+
+namespace clpk {
+
+constexpr int kGemmStages = 6;
+constexpr uint32_t kRowBytesK = 128;                        // K bytes per row per stage
+constexpr uint32_t kHalfTileBytes = 128 * kRowBytesK;       // 16 KiB: 128 rows x 128 B
+constexpr uint32_t kStageBytes = 2 * kHalfTileBytes;        // A half + B half
+constexpr uint32_t kTileMN = 256;
+constexpr int kGemmThreads = 192;
+constexpr int kGroupN = 8;                                  // tile columns per raster group
+
+struct GemmParams {
+    uint32_t m, n, k;
+    uint32_t k_blocks;          // K / (elements per 128 B)
+    uint32_t k_block_elems;
+    __nv_bfloat16 *c;
+    float alpha;
+    uint32_t *status;
+};
+
+struct GemmSmem {
+    uint64_t full[kGemmStages];
+    uint64_t empty[kGemmStages];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+};
+
+__device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uint32_t tiles_n,
+                                            uint32_t &mb, uint32_t &nb)
+{
+    const uint32_t per_group = kGroupN * tiles_m;
+    const uint32_t g = tile / per_group;
+    const uint32_t within = tile - g * per_group;
+    const uint32_t first_n = g * kGroupN;
+    const uint32_t width = (tiles_n - first_n) < (uint32_t)kGroupN ? (tiles_n - first_n) : (uint32_t)kGroupN;
+    mb = within / width;
+    nb = first_n + within % width;
+}
+
+// 2-D tile load whose completion bytes go to the barrier at the same offset in
+// the pair's leader CTA (cluster rank 0).
+__device__ __forceinline__ void tma_load_pair(void *smem_dst, const CUtensorMap *tmap, int32_t x,
+                                              int32_t y, uint64_t *bar)
+{
+    uint32_t leader_bar;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(leader_bar) : "r"(smem_u32(bar)));
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(smem_dst)),
+        "l"(tmap), "r"(leader_bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+// KIND: CLPK_DT_BF16 / CLPK_DT_F16 -> kind::f16 (K=16); CLPK_DT_E4M3 -> kind::f8f6f4 (K=32).
+template <int DT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
+    gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                GemmParams p)
+{
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // The runtime only guarantees 16-byte alignment of dynamic shared memory;
+    // the swizzled tiles need 1024.
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    GemmSmem *sh = reinterpret_cast<GemmSmem *>(smem + (size_t)kGemmStages * kStageBytes);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const uint32_t cluster_id = blockIdx.x >> 1;
+    const uint32_t n_clusters = gridDim.x >> 1;
+    const uint32_t tiles_m = p.m / kTileMN, tiles_n = p.n / kTileMN;
+    const uint32_t n_tiles = tiles_m * tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kGemmStages; s++) {
+            mbar_init(&sh->full[s], 1);
+            mbar_init(&sh->empty[s], 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&sh->tmem_full[b], 1);
+            mbar_init(&sh->tmem_empty[b], 8);    // 4 epilogue warps x 2 CTAs
+        }
+        mbar_fence_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+    }
+    if (warp == 1)
+        tmem_alloc<2>(&sh->tmem_base, 512);
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync();
+    tc_fence_after_sync();
+    const uint32_t tmem = sh->tmem_base;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters) {
+                uint32_t mb, nb;
+                tile_coords(tile, tiles_m, tiles_n, mb, nb);
+                const int32_t row_a = (int32_t)(mb * kTileMN + rank * 128);
+                const int32_t row_b = (int32_t)(nb * kTileMN + rank * 128);
+                for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
+                    const uint32_t s = it % kGemmStages, round = it / kGemmStages;
+                    if (round > 0 && !mbar_wait(&sh->empty[s], (round - 1) & 1)) {
+                        atomicCAS(p.status, 0u, 0x201u);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t *st = smem + (size_t)s * kStageBytes;
+                    if (rank == 0)
+                        mbar_expect_tx(&sh->full[s], 2 * kStageBytes);
+                    const int32_t x = (int32_t)(kb * p.k_block_elems);
+                    tma_load_pair(st, &tmap_a, x, row_a, &sh->full[s]);
+                    tma_load_pair(st + kHalfTileBytes, &tmap_b, x, row_b, &sh->full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader CTA) ----------------
+        if (rank == 0 && lane == 0) {
+            constexpr uint32_t kAFmt = (DT == CLPK_DT_BF16) ? kFmtBF16 : (DT == CLPK_DT_F16 ? kFmtF16 : kFmtE4M3);
+            const uint32_t idesc = make_idesc(256, 256, kAFmt, kAFmt, kAccF32);
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters, tcount++) {
+                const uint32_t b = tcount & 1, use = tcount >> 1;
+                if (use > 0 && !mbar_wait(&sh->tmem_empty[b], (use - 1) & 1)) {
+                    atomicCAS(p.status, 0u, 0x202u);
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t d = tmem + b * 256;
+                for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
+                    const uint32_t s = it % kGemmStages, round = it / kGemmStages;
+                    if (!mbar_wait(&sh->full[s], round & 1)) {
+                        atomicCAS(p.status, 0u, 0x203u);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(smem + (size_t)s * kStageBytes);
+                    const uint64_t ad = make_smem_desc(a_addr, 16, 1024, kSwizzle128B);
+                    const uint64_t bd = make_smem_desc(a_addr + kHalfTileBytes, 16, 1024, kSwizzle128B);
+#pragma unroll
+                    for (uint32_t kk = 0; kk < 4; kk++) {
+                        // +32 bytes of K per instruction: +2 in the (>>4) address field
+                        if constexpr (DT == CLPK_DT_E4M3)
+                            mma2_f8f6f4_ss(d, ad + 2 * kk, bd + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
+                        else
+                            mma2_f16_ss(d, ad + 2 * kk, bd + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
+                    }
+                    tc_commit_pair(&sh->empty[s], 3);
+                }
+                if (ok)
+                    tc_commit_pair(&sh->tmem_full[b], 3);
+            }
+        }
+    } else {
+        // ---------------- epilogue warps ----------------
+        const uint32_t q = (uint32_t)(warp & 3);        // TMEM lane quarter this warp may read
+        uint32_t tcount = 0;
+        for (uint32_t tile = cluster_id; tile < n_tiles; tile += n_clusters, tcount++) {
+            uint32_t mb, nb;
+            tile_coords(tile, tiles_m, tiles_n, mb, nb);
+            const uint32_t b = tcount & 1, use = tcount >> 1;
+            if (!mbar_wait(&sh->tmem_full[b], use & 1)) {
+                if (lane == 0)
+                    atomicCAS(p.status, 0u, 0x204u);
+                break;
+            }
+            tc_fence_after_sync();
+            const size_t row = (size_t)mb * kTileMN + rank * 128 + q * 32 + lane;
+            __nv_bfloat16 *crow = p.c + row * p.n + (size_t)nb * kTileMN;
+            const uint32_t taddr = tmem + b * 256 + ((q * 32) << 16);
+#pragma unroll 2
+            for (uint32_t c = 0; c < kTileMN / 32; c++) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(taddr + c * 32, r);
+                tmem_ld_wait();
+                uint32_t w[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    const float lo = __uint_as_float(r[2 * i]) * p.alpha;
+                    const float hi = __uint_as_float(r[2 * i + 1]) * p.alpha;
+                    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+                    w[i] = *reinterpret_cast<uint32_t *>(&v);
+                }
+                uint4 *dst = reinterpret_cast<uint4 *>(crow + c * 32);
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                    dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive_cluster(&sh->tmem_empty[b], 0);
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync();
+    if (warp == 1)
+        tmem_dealloc<2>(tmem, 512);
+}
+
+// ---- host side -----------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static int get_encode_fn(EncodeTiledFn *out)
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        CLPK_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres));
+        if (qres != cudaDriverEntryPointSuccess || !sym) {
+            set_error("cuTensorMapEncodeTiled is not available from this driver");
+            return CLPK_ERR_CUDA;
+        }
+        fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    *out = fn;
+    return CLPK_OK;
+}
+
+// Row-major [rows][row_bytes] operand, box = 128 rows x 128 bytes, 128-byte swizzle.
+static int make_operand_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t row_bytes)
+{
+    EncodeTiledFn enc;
+    int rc = get_encode_fn(&enc);
+    if (rc != CLPK_OK)
+        return rc;
+    const cuuint64_t dims[2] = {row_bytes, rows};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {kRowBytesK, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+        return CLPK_ERR_CUDA;
+    }
+    return CLPK_OK;
+}
+
+constexpr size_t kGemmSmemBytes = (size_t)kGemmStages * kStageBytes + sizeof(GemmSmem) + 1024;
+
+template <int DT>
+static int launch_gemm(const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, cudaStream_t s)
+{
+    CLPK_CUDA(cudaFuncSetAttribute(gemm_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)kGemmSmemBytes));
+    const int grid = (num_sms() / 2) * 2;
+    gemm_kernel<DT><<<grid, kGemmThreads, kGemmSmemBytes, s>>>(ta, tb, p);
+    CLPK_LAUNCH_CHECK("gemm");
+    return CLPK_OK;
+}
+
+} // namespace clpk
+
+using namespace clpk;
+
+extern "C" {
+
+int clpk_gemm_workspace_bytes(int dtype, uint32_t m, uint32_t n, uint32_t k, size_t *bytes)
+{
+    CLPK_REQUIRE(bytes, "bytes is NULL");
+    *bytes = 0;
+    if (dtype == CLPK_DT_NVF4)
+        *bytes = ((size_t)m + n) * (k / 16);
+    return CLPK_OK;
+}
+
+int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
+{
+    int rc = require_sm100();
+    if (rc != CLPK_OK)
+        return rc;
+    CLPK_REQUIRE(a, "args is NULL");
+    CLPK_REQUIRE(a->d_a && a->d_b && a->d_c && a->d_status, "NULL buffer");
+    CLPK_REQUIRE(a->m % 256 == 0 && a->n % 256 == 0 && a->m > 0 && a->n > 0,
+                 "M and N must be positive multiples of 256 (got %u, %u)", a->m, a->n);
+    CLPK_REQUIRE(a->k % 128 == 0 && a->k > 0, "K must be a positive multiple of 128 (got %u)", a->k);
+    CLPK_REQUIRE(((uintptr_t)a->d_a % 16) == 0 && ((uintptr_t)a->d_b % 16) == 0 && ((uintptr_t)a->d_c % 16) == 0,
+                 "operands must be 16-byte aligned");
+    uint32_t elem_bits;
+    switch (a->dtype) {
+    case CLPK_DT_BF16:
+    case CLPK_DT_F16:  elem_bits = 16; break;
+    case CLPK_DT_E4M3: elem_bits = 8; break;
+    default:
+        set_error("clpk_gemm: dtype %d is not available in this build", a->dtype);
+        return CLPK_ERR_UNSUPPORTED;
+    }
+    cudaStream_t s = as_stream(stream);
+    CLPK_CUDA(cudaMemsetAsync(a->d_status, 0, sizeof(uint32_t), s));
+
+    const uint64_t row_bytes = (uint64_t)a->k * elem_bits / 8;
+    CUtensorMap ta, tb;
+    rc = make_operand_map(&ta, a->d_a, a->m, row_bytes);
+    if (rc != CLPK_OK)
+        return rc;
+    rc = make_operand_map(&tb, a->d_b, a->n, row_bytes);
+    if (rc != CLPK_OK)
+        return rc;
+
+    GemmParams p;
+    p.m = a->m;
+    p.n = a->n;
+    p.k = a->k;
+    p.k_block_elems = kRowBytesK;          // x coordinate is in bytes: the maps are typed UINT8
+    p.k_blocks = (uint32_t)(row_bytes / kRowBytesK);
+    p.c = static_cast<__nv_bfloat16 *>(a->d_c);
+    p.alpha = a->alpha;
+    p.status = a->d_status;
+    switch (a->dtype) {
+    case CLPK_DT_BF16: return launch_gemm<CLPK_DT_BF16>(ta, tb, p, s);
+    case CLPK_DT_F16:  return launch_gemm<CLPK_DT_F16>(ta, tb, p, s);
+    default:           return launch_gemm<CLPK_DT_E4M3>(ta, tb, p, s);
+    }
+}
+
+} // extern "C"

@@ -1,0 +1,306 @@
+// Tensor-core peak probes on tcgen05.mma.
+//
+// One CTA = 128 threads.  It stages an A tile [128][K] and a B tile [256][K]
+// (K contiguous) into shared memory, allocates tensor memory for a 128x256
+// 32-bit accumulator and lets one thread issue n_mma instructions of shape
+// M128 N256 K that all accumulate into that tile; a tcgen05.commit arrives on
+// an mbarrier when the last one has retired.  The four warps then read the
+// accumulator back with tcgen05.ld (warp w owns TMEM lanes 32w..32w+31),
+// XOR it into a per-CTA checksum and, for the first n_out_tiles CTAs, store it.
+//
+// Shared-memory operand layout (no swizzle, K-major): every dense kind has
+// 32 bytes of K per row per instruction (16 x 16-bit, 32 x 8-bit, 64 x 4-bit),
+// i.e. two 16-byte chunks.  An 8-row x 16-byte "core matrix" is 128
+// contiguous bytes; the two K chunks of a row group sit side by side (leading
+// offset 128 B) and row groups follow each other (stride offset 256 B):
+//     byte(r, kc) = (r / 8) * 256 + kc * 128 + (r % 8) * 16
+//
+// Block-scaled kinds keep their scale factors in tensor memory: row r of A has
+// one 32-bit word (up to four 8-bit factors along K) at lane r % 32, column
+// r / 32 of the scale area, replicated in all four 32-lane quarters; B's 256
+// rows take 8 columns the same way.  The probes write them with tcgen05.st.
+//
+// Residency: dense kinds take 256 TMEM columns, so two CTAs fit one SM; the
+// launch asks for enough dynamic shared memory that a third never becomes
+// resident (tcgen05.alloc would otherwise block on it).  Kinds with scale
+// factors or metadata take all 512 columns: one CTA per SM.
+#include "../clpk_internal.h"
+#include "../clpk_ptx.cuh"
+
+namespace clpk {
+
+constexpr int kTileM = 128;
+constexpr int kTileN = 256;
+constexpr int kRowBytes = 32;                       // K bytes per row per instruction
+constexpr int kATileBytes = kTileM * kRowBytes;     // 4 KiB
+constexpr int kBTileBytes = kTileN * kRowBytes;     // 8 KiB
+
+struct PeakParams {
+    const uint8_t *a;
+    const uint8_t *b;
+    const uint8_t *sfa;
+    const uint8_t *sfb;
+    const uint8_t *meta;
+    uint32_t n_mma;
+    uint32_t n_out_tiles;
+    uint32_t *out;
+    uint32_t *checksum;
+    uint32_t *status;
+};
+
+// Copy a [rows][32 B] row-major tile into the core-matrix layout.
+__device__ __forceinline__ void stage_tile(uint8_t *smem_tile, const uint8_t *g, int rows)
+{
+    const int chunks = rows * 2;
+    for (int i = threadIdx.x; i < chunks; i += blockDim.x) {
+        const int r = i >> 1, kc = i & 1;
+        const uint4 v = *reinterpret_cast<const uint4 *>(g + (size_t)r * kRowBytes + kc * 16);
+        *reinterpret_cast<uint4 *>(smem_tile + (r >> 3) * 256 + kc * 128 + (r & 7) * 16) = v;
+    }
+}
+
+template <int KIND>
+struct KindTraits;
+template <> struct KindTraits<CLPK_MMA_F16>  { static constexpr bool scaled = false; static constexpr int sf_per_row = 0; };
+template <> struct KindTraits<CLPK_MMA_BF16> { static constexpr bool scaled = false; static constexpr int sf_per_row = 0; };
+template <> struct KindTraits<CLPK_MMA_E4M3> { static constexpr bool scaled = false; static constexpr int sf_per_row = 0; };
+template <> struct KindTraits<CLPK_MMA_E5M2> { static constexpr bool scaled = false; static constexpr int sf_per_row = 0; };
+template <> struct KindTraits<CLPK_MMA_I8>   { static constexpr bool scaled = false; static constexpr int sf_per_row = 0; };
+template <> struct KindTraits<CLPK_MMA_MXF4> { static constexpr bool scaled = true;  static constexpr int sf_per_row = 2; };
+template <> struct KindTraits<CLPK_MMA_NVF4> { static constexpr bool scaled = true;  static constexpr int sf_per_row = 4; };
+
+template <int KIND>
+__device__ __forceinline__ void issue_mma(uint32_t d, uint64_t ad, uint64_t bd, uint32_t sfa,
+                                          uint32_t sfb, uint32_t acc)
+{
+    if constexpr (KIND == CLPK_MMA_F16) {
+        mma_f16_ss(d, ad, bd, make_idesc(kTileM, kTileN, kFmtF16, kFmtF16, kAccF32), acc);
+    } else if constexpr (KIND == CLPK_MMA_BF16) {
+        mma_f16_ss(d, ad, bd, make_idesc(kTileM, kTileN, kFmtBF16, kFmtBF16, kAccF32), acc);
+    } else if constexpr (KIND == CLPK_MMA_E4M3) {
+        mma_f8f6f4_ss(d, ad, bd, make_idesc(kTileM, kTileN, kFmtE4M3, kFmtE4M3, kAccF32), acc);
+    } else if constexpr (KIND == CLPK_MMA_E5M2) {
+        mma_f8f6f4_ss(d, ad, bd, make_idesc(kTileM, kTileN, kFmtE5M2, kFmtE5M2, kAccF32), acc);
+    } else if constexpr (KIND == CLPK_MMA_I8) {
+        mma_i8_ss(d, ad, bd, make_idesc(kTileM, kTileN, kFmtS8, kFmtS8, kAccS32), acc);
+    } else if constexpr (KIND == CLPK_MMA_MXF4) {
+        mma_mxf4_bs(d, ad, bd,
+                    make_idesc_block_scaled(kTileM, kTileN, kFmtE2M1, kFmtE2M1, /*ue8m0*/ 1, 0, 0),
+                    sfa, sfb, acc);
+    } else if constexpr (KIND == CLPK_MMA_NVF4) {
+        mma_nvf4_bs(d, ad, bd,
+                    make_idesc_block_scaled(kTileM, kTileN, kFmtE2M1, kFmtE2M1, /*ue4m3*/ 0, 0, 0),
+                    sfa, sfb, acc);
+    }
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(128) mma_peak_kernel(PeakParams p)
+{
+    using T = KindTraits<KIND>;
+    constexpr uint32_t kCols = T::scaled ? 512u : 256u;
+    constexpr uint32_t kSfaCol = 256, kSfbCol = 260;
+
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t *sA = smem;
+    uint8_t *sB = smem + kATileBytes;
+    uint64_t *bar = reinterpret_cast<uint64_t *>(smem + kATileBytes + kBTileBytes);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    stage_tile(sA, p.a, kTileM);
+    stage_tile(sB, p.b, kTileN);
+    if (threadIdx.x == 0) {
+        mbar_init(bar, 1);
+        mbar_fence_init();
+    }
+    fence_proxy_async_smem();
+    if (warp == 0)
+        tmem_alloc<1>(tmem_slot, kCols);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if constexpr (T::scaled) {
+        // Scale factors: one 32-bit word per row, factors along K in byte order.
+        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+        for (int c = 0; c < 4; c++) {
+            const int r = c * 32 + lane;
+            uint32_t w = 0;
+            for (int k = 0; k < T::sf_per_row; k++)
+                w |= (uint32_t)p.sfa[r * T::sf_per_row + k] << (8 * k);
+            tmem_st_32x32b_x1(lane_base + kSfaCol + c, w);
+        }
+        for (int c = 0; c < 8; c++) {
+            const int r = c * 32 + lane;
+            uint32_t w = 0;
+            for (int k = 0; k < T::sf_per_row; k++)
+                w |= (uint32_t)p.sfb[r * T::sf_per_row + k] << (8 * k);
+            tmem_st_32x32b_x1(lane_base + kSfbCol + c, w);
+        }
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncthreads();
+        tc_fence_after_sync();
+    }
+
+    if (threadIdx.x == 0) {
+        const uint64_t ad = make_smem_desc(smem_u32(sA), 128, 256, kSwizzleNone);
+        const uint64_t bd = make_smem_desc(smem_u32(sB), 128, 256, kSwizzleNone);
+        const uint32_t sfa = tmem + kSfaCol, sfb = tmem + kSfbCol;
+        issue_mma<KIND>(tmem, ad, bd, sfa, sfb, 0u);
+        for (uint32_t i = 1; i < p.n_mma; i++)
+            issue_mma<KIND>(tmem, ad, bd, sfa, sfb, 1u);
+        tc_commit(bar);
+    }
+    __syncwarp();
+
+    const bool done = mbar_wait(bar, 0);
+    tc_fence_after_sync();
+    if (!done && lane == 0)
+        atomicCAS(p.status, 0u, 0x100u + (uint32_t)KIND);
+
+    if (done) {
+        uint32_t x = 0;
+        const int row = warp * 32 + lane;
+        uint32_t *out_row = (blockIdx.x < p.n_out_tiles)
+                                ? p.out + ((size_t)blockIdx.x * kTileM + row) * kTileN
+                                : nullptr;
+        for (int c = 0; c < kTileN / 32; c++) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(tmem + ((uint32_t)(warp * 32) << 16) + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; i++)
+                x ^= r[i];
+            if (out_row) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 4)
+                    *reinterpret_cast<uint4 *>(out_row + c * 32 + i) =
+                        make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
+            }
+        }
+        if (p.checksum) {
+            __shared__ uint32_t wx[4];
+            for (int o = 16; o > 0; o >>= 1)
+                x ^= __shfl_xor_sync(0xffffffffu, x, o);
+            if (lane == 0)
+                wx[warp] = x;
+            __syncthreads();
+            if (threadIdx.x == 0)
+                p.checksum[blockIdx.x] = wx[0] ^ wx[1] ^ wx[2] ^ wx[3];
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0)
+        tmem_dealloc<1>(tmem, kCols);
+}
+
+struct KindInfo {
+    int k;              // logical K per instruction
+    bool scaled;
+    bool sparse;
+};
+
+static bool kind_info(int kind, KindInfo *ki)
+{
+    switch (kind) {
+    case CLPK_MMA_F16:     *ki = {16, false, false}; return true;
+    case CLPK_MMA_BF16:    *ki = {16, false, false}; return true;
+    case CLPK_MMA_E4M3:    *ki = {32, false, false}; return true;
+    case CLPK_MMA_E5M2:    *ki = {32, false, false}; return true;
+    case CLPK_MMA_I8:      *ki = {32, false, false}; return true;
+    case CLPK_MMA_MXF4:    *ki = {64, true, false};  return true;
+    case CLPK_MMA_NVF4:    *ki = {64, true, false};  return true;
+    case CLPK_MMA_E4M3_SP: *ki = {64, false, true};  return true;
+    case CLPK_MMA_I8_SP:   *ki = {64, false, true};  return true;
+    case CLPK_MMA_MXF4_SP: *ki = {128, true, true};  return true;
+    case CLPK_MMA_NVF4_SP: *ki = {128, true, true};  return true;
+    default: return false;
+    }
+}
+
+template <int KIND>
+static int launch_peak(const PeakParams &p, uint32_t grid, cudaStream_t s)
+{
+    // Dense: ~100 KiB so that exactly two CTAs fit one SM; scaled: one CTA.
+    const int optin = smem_optin_bytes();
+    const size_t smem = KindTraits<KIND>::scaled ? (size_t)(optin * 3 / 5) : (size_t)(optin * 2 / 5);
+    CLPK_CUDA(cudaFuncSetAttribute(mma_peak_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)smem));
+    mma_peak_kernel<KIND><<<grid, 128, smem, s>>>(p);
+    CLPK_LAUNCH_CHECK("mma_peak");
+    return CLPK_OK;
+}
+
+} // namespace clpk
+
+using namespace clpk;
+
+extern "C" {
+
+int clpk_mma_kind_k(int kind)
+{
+    KindInfo ki;
+    return kind_info(kind, &ki) ? ki.k : 0;
+}
+
+double clpk_mma_flops_per_instr(int kind)
+{
+    KindInfo ki;
+    if (!kind_info(kind, &ki))
+        return 0.0;
+    return 2.0 * kTileM * kTileN * (double)ki.k;
+}
+
+int clpk_mma_peak(const clpk_mma_peak_args_t *a, void *stream)
+{
+    int rc = require_sm100();
+    if (rc != CLPK_OK)
+        return rc;
+    CLPK_REQUIRE(a, "args is NULL");
+    KindInfo ki;
+    CLPK_REQUIRE(kind_info(a->kind, &ki), "unknown kind %d", a->kind);
+    CLPK_REQUIRE(a->d_a && a->d_b && a->d_status, "NULL buffer");
+    CLPK_REQUIRE(((uintptr_t)a->d_a % 16) == 0 && ((uintptr_t)a->d_b % 16) == 0, "tiles must be 16-byte aligned");
+    CLPK_REQUIRE(a->n_mma >= 1 && a->grid >= 1, "n_mma and grid must be >= 1");
+    CLPK_REQUIRE(a->n_out_tiles <= a->grid, "n_out_tiles exceeds grid");
+    CLPK_REQUIRE(a->n_out_tiles == 0 || (a->d_out && ((uintptr_t)a->d_out % 16) == 0), "d_out missing or misaligned");
+    if (ki.scaled)
+        CLPK_REQUIRE(a->d_sfa && a->d_sfb, "block-scaled kinds need d_sfa and d_sfb");
+    if (ki.sparse) {
+        set_error("sparse kind %d is not available in this build", a->kind);
+        return CLPK_ERR_UNSUPPORTED;
+    }
+    cudaStream_t s = as_stream(stream);
+    CLPK_CUDA(cudaMemsetAsync(a->d_status, 0, sizeof(uint32_t), s));
+    PeakParams p;
+    p.a = static_cast<const uint8_t *>(a->d_a);
+    p.b = static_cast<const uint8_t *>(a->d_b);
+    p.sfa = static_cast<const uint8_t *>(a->d_sfa);
+    p.sfb = static_cast<const uint8_t *>(a->d_sfb);
+    p.meta = static_cast<const uint8_t *>(a->d_meta);
+    p.n_mma = a->n_mma;
+    p.n_out_tiles = a->n_out_tiles;
+    p.out = static_cast<uint32_t *>(a->d_out);
+    p.checksum = a->d_checksum;
+    p.status = a->d_status;
+    switch (a->kind) {
+    case CLPK_MMA_F16:  return launch_peak<CLPK_MMA_F16>(p, a->grid, s);
+    case CLPK_MMA_BF16: return launch_peak<CLPK_MMA_BF16>(p, a->grid, s);
+    case CLPK_MMA_E4M3: return launch_peak<CLPK_MMA_E4M3>(p, a->grid, s);
+    case CLPK_MMA_E5M2: return launch_peak<CLPK_MMA_E5M2>(p, a->grid, s);
+    case CLPK_MMA_I8:   return launch_peak<CLPK_MMA_I8>(p, a->grid, s);
+    case CLPK_MMA_MXF4: return launch_peak<CLPK_MMA_MXF4>(p, a->grid, s);
+    case CLPK_MMA_NVF4: return launch_peak<CLPK_MMA_NVF4>(p, a->grid, s);
+    default: break;
+    }
+    set_error("kind %d not handled", a->kind);
+    return CLPK_ERR_BAD_ARG;
+}
+
+} // extern "C"

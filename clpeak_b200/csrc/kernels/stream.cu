@@ -1,0 +1,550 @@
+// Global-memory bandwidth kernels.
+//
+//  * global_bandwidth_v<W>: the reference read-and-sum test with its exact
+//    per-thread order (16 fetches at a 256-element stride inside a block-owned
+//    region), widened to 64-bit indexing so buffers beyond 4 Gi elements work.
+//  * stream read / copy / triad in two flavours:
+//      LDG - persistent grid, four independent 128-bit loads per thread per
+//            step (streaming cache hints), registers in between;
+//      TMA - one elected thread per CTA moves 32 KiB tiles with
+//            cp.async.bulk through a ring of shared-memory stages; copy never
+//            touches registers, triad computes in place in shared memory.
+//
+// HBM traffic per pass (the algorithmic bytes the roofline is computed from):
+// read n, copy 2n, triad 3n bytes for n-byte arrays; GPUs do not
+// write-allocate, so these are the true DRAM bytes.
+#include "../clpk_internal.h"
+#include "../clpk_ptx.cuh"
+
+namespace clpk {
+
+constexpr int kFetchPerWI = 16;   // FETCH_PER_WI of the reference (include/common/common.h:56)
+
+template <typename V>
+__device__ __forceinline__ float lane_sum(const V &v);
+template <>
+__device__ __forceinline__ float lane_sum<float>(const float &v) { return v; }
+template <>
+__device__ __forceinline__ float lane_sum<float2>(const float2 &v) { return v.x + v.y; }
+template <>
+__device__ __forceinline__ float lane_sum<float4>(const float4 &v)
+{
+    return v.x + v.y + v.z + v.w;   // ((x + y) + z) + w
+}
+
+__device__ __forceinline__ void vadd(float &a, const float &b) { a += b; }
+__device__ __forceinline__ void vadd(float2 &a, const float2 &b) { a.x += b.x; a.y += b.y; }
+__device__ __forceinline__ void vadd(float4 &a, const float4 &b)
+{
+    a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+}
+
+template <typename V>
+__global__ void __launch_bounds__(256) global_bandwidth_kernel(const V *__restrict__ in,
+                                                               float *__restrict__ out)
+{
+    const uint64_t gid = (uint64_t)blockIdx.x * 256 + threadIdx.x;
+    uint64_t offset = (uint64_t)blockIdx.x * 256 * kFetchPerWI + threadIdx.x;
+    V vals[kFetchPerWI];
+#pragma unroll
+    for (int i = 0; i < kFetchPerWI; i++)
+        vals[i] = __ldg(in + offset + (uint64_t)i * 256);
+    V sum{};
+#pragma unroll
+    for (int i = 0; i < kFetchPerWI; i++)
+        vadd(sum, vals[i]);
+    out[gid] = lane_sum(sum);
+}
+
+// ---- LDG flavour ---------------------------------------------------------------------
+
+constexpr int kLdgThreads = 512;
+constexpr int kLdgUnroll = 4;
+constexpr int kLdgCtasPerSm = 4;
+
+__device__ __forceinline__ uint32_t xor4(const uint4 &v) { return v.x ^ v.y ^ v.z ^ v.w; }
+
+__device__ __forceinline__ void cta_xor_store(uint32_t x, uint32_t *slot)
+{
+    __shared__ uint32_t warp_x[32];
+    for (int o = 16; o > 0; o >>= 1)
+        x ^= __shfl_xor_sync(0xffffffffu, x, o);
+    if ((threadIdx.x & 31) == 0)
+        warp_x[threadIdx.x >> 5] = x;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        uint32_t y = threadIdx.x < (blockDim.x >> 5) ? warp_x[threadIdx.x] : 0u;
+        for (int o = 16; o > 0; o >>= 1)
+            y ^= __shfl_xor_sync(0xffffffffu, y, o);
+        if (threadIdx.x == 0)
+            *slot = y;
+    }
+}
+
+__global__ void __launch_bounds__(kLdgThreads) stream_read_ldg(const uint4 *__restrict__ src,
+                                                               uint64_t n16,
+                                                               uint32_t *__restrict__ partials)
+{
+    constexpr uint64_t kTile = (uint64_t)kLdgThreads * kLdgUnroll;
+    uint32_t acc = 0;
+    const uint64_t n_full = n16 / kTile;
+    for (uint64_t t = blockIdx.x; t < n_full; t += gridDim.x) {
+        const uint4 *p = src + t * kTile + threadIdx.x;
+        uint4 v[kLdgUnroll];
+#pragma unroll
+        for (int u = 0; u < kLdgUnroll; u++)
+            v[u] = __ldcs(p + u * kLdgThreads);
+#pragma unroll
+        for (int u = 0; u < kLdgUnroll; u++)
+            acc ^= xor4(v[u]);
+    }
+    if (blockIdx.x == 0) {
+        for (uint64_t i = n_full * kTile + threadIdx.x; i < n16; i += kLdgThreads)
+            acc ^= xor4(__ldcs(src + i));
+    }
+    cta_xor_store(acc, partials + blockIdx.x);
+}
+
+__global__ void __launch_bounds__(kLdgThreads) stream_copy_ldg(uint4 *__restrict__ dst,
+                                                               const uint4 *__restrict__ src,
+                                                               uint64_t n16)
+{
+    constexpr uint64_t kTile = (uint64_t)kLdgThreads * kLdgUnroll;
+    const uint64_t n_full = n16 / kTile;
+    for (uint64_t t = blockIdx.x; t < n_full; t += gridDim.x) {
+        const uint64_t base = t * kTile + threadIdx.x;
+        uint4 v[kLdgUnroll];
+#pragma unroll
+        for (int u = 0; u < kLdgUnroll; u++)
+            v[u] = __ldcs(src + base + u * kLdgThreads);
+#pragma unroll
+        for (int u = 0; u < kLdgUnroll; u++)
+            __stcs(dst + base + u * kLdgThreads, v[u]);
+    }
+    if (blockIdx.x == 0) {
+        for (uint64_t i = n_full * kTile + threadIdx.x; i < n16; i += kLdgThreads)
+            __stcs(dst + i, __ldcs(src + i));
+    }
+}
+
+__device__ __forceinline__ float4 triad4(const float4 &b, const float4 &c, float s)
+{
+    // b + s*c as two roundings (multiply, then add): no FMA contraction, so the
+    // host check can use plain C arithmetic.
+    return make_float4(__fadd_rn(b.x, __fmul_rn(s, c.x)), __fadd_rn(b.y, __fmul_rn(s, c.y)),
+                       __fadd_rn(b.z, __fmul_rn(s, c.z)), __fadd_rn(b.w, __fmul_rn(s, c.w)));
+}
+
+__global__ void __launch_bounds__(kLdgThreads) stream_triad_ldg(float4 *__restrict__ a,
+                                                                const float4 *__restrict__ b,
+                                                                const float4 *__restrict__ c,
+                                                                float s, uint64_t n4,
+                                                                uint64_t n_tail_floats)
+{
+    constexpr int kU = 2;   // two b + two c loads in flight per thread
+    constexpr uint64_t kTile = (uint64_t)kLdgThreads * kU;
+    const uint64_t n_full = n4 / kTile;
+    for (uint64_t t = blockIdx.x; t < n_full; t += gridDim.x) {
+        const uint64_t base = t * kTile + threadIdx.x;
+        float4 vb[kU], vc[kU];
+#pragma unroll
+        for (int u = 0; u < kU; u++) {
+            vb[u] = __ldcs(b + base + u * kLdgThreads);
+            vc[u] = __ldcs(c + base + u * kLdgThreads);
+        }
+#pragma unroll
+        for (int u = 0; u < kU; u++)
+            __stcs(a + base + u * kLdgThreads, triad4(vb[u], vc[u], s));
+    }
+    if (blockIdx.x == 0) {
+        for (uint64_t i = n_full * kTile + threadIdx.x; i < n4; i += kLdgThreads)
+            __stcs(a + i, triad4(__ldcs(b + i), __ldcs(c + i), s));
+        // floats beyond the last whole float4
+        const float *bf = reinterpret_cast<const float *>(b) + n4 * 4;
+        const float *cf = reinterpret_cast<const float *>(c) + n4 * 4;
+        float *af = reinterpret_cast<float *>(a) + n4 * 4;
+        if (threadIdx.x < n_tail_floats)
+            af[threadIdx.x] = __fadd_rn(bf[threadIdx.x], __fmul_rn(s, cf[threadIdx.x]));
+    }
+}
+
+// ---- TMA (cp.async.bulk) flavour ------------------------------------------------------------
+//
+// Shared memory: kTmaStages stages of kTmaTile bytes (triad: two tiles per
+// stage), then the barriers.  Tiles are handed out round-robin:
+// CTA b owns tiles b, b+grid, b+2*grid, ...
+
+constexpr uint32_t kTmaTile = 32768;
+constexpr int kTmaStages = 6;
+constexpr int kTmaTriadStages = 3;
+constexpr uint32_t kTmaTriadTile = 32768;
+
+__device__ __forceinline__ uint32_t tile_bytes(uint64_t tile, uint64_t n_bytes, uint32_t tile_sz)
+{
+    const uint64_t off = tile * tile_sz;
+    const uint64_t left = n_bytes - off;
+    return left < tile_sz ? (uint32_t)left : tile_sz;
+}
+
+// status word: 0 ok, otherwise 1 + id of the wait that expired.
+__device__ __forceinline__ void report_timeout(uint32_t *status, uint32_t where)
+{
+    atomicCAS(status, 0u, 1u + where);
+}
+
+__global__ void __launch_bounds__(160) stream_read_tma(const uint8_t *__restrict__ src,
+                                                       uint64_t n_bytes,
+                                                       uint32_t *__restrict__ partials,
+                                                       uint32_t *__restrict__ status)
+{
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + (size_t)kTmaStages * kTmaTile);
+    uint64_t *empty = full + kTmaStages;
+    const uint64_t n_tiles = (n_bytes + kTmaTile - 1) / kTmaTile;
+    const int warp = threadIdx.x >> 5;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kTmaStages; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 4);   // one arrive per consumer warp
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    uint32_t acc = 0;
+    if (warp == 0) {
+        if (threadIdx.x == 0) {
+            uint32_t j = 0;
+            for (uint64_t t = blockIdx.x; t < n_tiles; t += gridDim.x, j++) {
+                const int s = j % kTmaStages;
+                const uint32_t round = j / kTmaStages;
+                if (round > 0 && !mbar_wait(&empty[s], (round - 1) & 1)) {
+                    report_timeout(status, 0);
+                    break;
+                }
+                const uint32_t bytes = tile_bytes(t, n_bytes, kTmaTile);
+                mbar_expect_tx(&full[s], bytes);
+                bulk_g2s(smem + (size_t)s * kTmaTile, src + t * kTmaTile, bytes, &full[s]);
+            }
+        }
+    } else {
+        const int ctid = threadIdx.x - 32;   // 0..127
+        uint32_t j = 0;
+        for (uint64_t t = blockIdx.x; t < n_tiles; t += gridDim.x, j++) {
+            const int s = j % kTmaStages;
+            const uint32_t round = j / kTmaStages;
+            if (!mbar_wait(&full[s], round & 1)) {
+                report_timeout(status, 1);
+                break;
+            }
+            const uint32_t n16 = tile_bytes(t, n_bytes, kTmaTile) / 16;
+            const uint4 *p = reinterpret_cast<const uint4 *>(smem + (size_t)s * kTmaTile);
+            for (uint32_t i = ctid; i < n16; i += 128)
+                acc ^= xor4(p[i]);
+            __syncwarp();
+            if ((threadIdx.x & 31) == 0)
+                mbar_arrive(&empty[s]);
+        }
+    }
+    cta_xor_store(acc, partials + blockIdx.x);
+}
+
+__global__ void __launch_bounds__(32) stream_copy_tma(uint8_t *__restrict__ dst,
+                                                      const uint8_t *__restrict__ src,
+                                                      uint64_t n_bytes,
+                                                      uint32_t *__restrict__ status)
+{
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + (size_t)kTmaStages * kTmaTile);
+    const uint64_t n_tiles = (n_bytes + kTmaTile - 1) / kTmaTile;
+    if (threadIdx.x != 0)
+        return;
+    for (int s = 0; s < kTmaStages; s++)
+        mbar_init(&full[s], 1);
+    mbar_fence_init();
+
+    // Number of tiles this CTA owns.
+    const uint64_t mine = blockIdx.x < n_tiles ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    auto issue_load = [&](uint64_t j) {
+        const uint64_t t = blockIdx.x + j * gridDim.x;
+        const int s = (int)(j % kTmaStages);
+        const uint32_t bytes = tile_bytes(t, n_bytes, kTmaTile);
+        mbar_expect_tx(&full[s], bytes);
+        bulk_g2s(smem + (size_t)s * kTmaTile, src + t * kTmaTile, bytes, &full[s]);
+    };
+    const uint64_t prologue = mine < (uint64_t)kTmaStages ? mine : (uint64_t)kTmaStages;
+    for (uint64_t j = 0; j < prologue; j++)
+        issue_load(j);
+    for (uint64_t j = 0; j < mine; j++) {
+        const uint64_t t = blockIdx.x + j * gridDim.x;
+        const int s = (int)(j % kTmaStages);
+        if (!mbar_wait(&full[s], (uint32_t)(j / kTmaStages) & 1)) {
+            report_timeout(status, 2);
+            break;
+        }
+        bulk_s2g(dst + t * kTmaTile, smem + (size_t)s * kTmaTile, tile_bytes(t, n_bytes, kTmaTile));
+        bulk_commit();
+        // Store j-1 has finished reading its stage once at most one group is
+        // still pending; that stage can take tile j-1+stages.
+        bulk_wait_read<1>();
+        if (j >= 1 && j - 1 + kTmaStages < mine)
+            issue_load(j - 1 + kTmaStages);
+    }
+    bulk_wait<0>();
+}
+
+// Triad: warp 0 loads b and c tiles, warps 1-4 compute a = b + s*c in place
+// (over the b tile), warp 5 stores the result.
+__global__ void __launch_bounds__(192) stream_triad_tma(float *__restrict__ a,
+                                                        const float *__restrict__ b,
+                                                        const float *__restrict__ c, float s,
+                                                        uint64_t n_bytes,
+                                                        uint32_t *__restrict__ status)
+{
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr uint32_t kStage = 2 * kTmaTriadTile;
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + (size_t)kTmaTriadStages * kStage);
+    uint64_t *done = full + kTmaTriadStages;
+    uint64_t *empty = done + kTmaTriadStages;
+    const uint64_t n_tiles = (n_bytes + kTmaTriadTile - 1) / kTmaTriadTile;
+    const int warp = threadIdx.x >> 5;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kTmaTriadStages; i++) {
+            mbar_init(&full[i], 1);
+            mbar_init(&done[i], 4);
+            mbar_init(&empty[i], 1);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    const uint8_t *bb = reinterpret_cast<const uint8_t *>(b);
+    const uint8_t *cb = reinterpret_cast<const uint8_t *>(c);
+    uint8_t *ab = reinterpret_cast<uint8_t *>(a);
+
+    if (warp == 0) {
+        if (threadIdx.x == 0) {
+            uint32_t j = 0;
+            for (uint64_t t = blockIdx.x; t < n_tiles; t += gridDim.x, j++) {
+                const int st = j % kTmaTriadStages;
+                const uint32_t round = j / kTmaTriadStages;
+                if (round > 0 && !mbar_wait(&empty[st], (round - 1) & 1)) {
+                    report_timeout(status, 3);
+                    break;
+                }
+                const uint32_t bytes = tile_bytes(t, n_bytes, kTmaTriadTile);
+                uint8_t *sb = smem + (size_t)st * kStage;
+                mbar_expect_tx(&full[st], 2 * bytes);
+                bulk_g2s(sb, bb + t * kTmaTriadTile, bytes, &full[st]);
+                bulk_g2s(sb + kTmaTriadTile, cb + t * kTmaTriadTile, bytes, &full[st]);
+            }
+        }
+    } else if (warp <= 4) {
+        const int ctid = threadIdx.x - 32;
+        uint32_t j = 0;
+        for (uint64_t t = blockIdx.x; t < n_tiles; t += gridDim.x, j++) {
+            const int st = j % kTmaTriadStages;
+            if (!mbar_wait(&full[st], (j / kTmaTriadStages) & 1)) {
+                report_timeout(status, 4);
+                break;
+            }
+            const uint32_t n4 = tile_bytes(t, n_bytes, kTmaTriadTile) / 16;
+            float4 *pb = reinterpret_cast<float4 *>(smem + (size_t)st * kStage);
+            const float4 *pc = reinterpret_cast<const float4 *>(smem + (size_t)st * kStage + kTmaTriadTile);
+            for (uint32_t i = ctid; i < n4; i += 128)
+                pb[i] = triad4(pb[i], pc[i], s);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if ((threadIdx.x & 31) == 0)
+                mbar_arrive(&done[st]);
+        }
+    } else {
+        if (threadIdx.x == 160) {
+            uint32_t j = 0;
+            for (uint64_t t = blockIdx.x; t < n_tiles; t += gridDim.x, j++) {
+                const int st = j % kTmaTriadStages;
+                if (!mbar_wait(&done[st], (j / kTmaTriadStages) & 1)) {
+                    report_timeout(status, 5);
+                    break;
+                }
+                bulk_s2g(ab + t * kTmaTriadTile, smem + (size_t)st * kStage,
+                         tile_bytes(t, n_bytes, kTmaTriadTile));
+                bulk_commit();
+                bulk_wait_read<0>();
+                mbar_arrive(&empty[st]);
+            }
+            bulk_wait<0>();
+        }
+    }
+}
+
+// Per-device status word for the TMA kernels (timeouts are reported through
+// the return code of the *next* synchronising call via clpk_stream_status()).
+static uint32_t *g_status[64] = {nullptr};
+
+static int status_word(uint32_t **out)
+{
+    int dev = 0;
+    CLPK_CUDA(cudaGetDevice(&dev));
+    if (!g_status[dev]) {
+        CLPK_CUDA(cudaMalloc(&g_status[dev], sizeof(uint32_t)));
+        CLPK_CUDA(cudaMemset(g_status[dev], 0, sizeof(uint32_t)));
+    }
+    *out = g_status[dev];
+    return CLPK_OK;
+}
+
+static int read_grid(int variant)
+{
+    return variant == CLPK_STREAM_TMA ? num_sms() : num_sms() * kLdgCtasPerSm;
+}
+
+constexpr size_t kTmaSmem = (size_t)kTmaStages * kTmaTile + 2 * kTmaStages * sizeof(uint64_t);
+constexpr size_t kTmaTriadSmem =
+    (size_t)kTmaTriadStages * 2 * kTmaTriadTile + 3 * kTmaTriadStages * sizeof(uint64_t);
+
+} // namespace clpk
+
+using namespace clpk;
+
+extern "C" {
+
+int clpk_global_bandwidth(int width, const float *d_in, float *d_out, uint64_t n_floats, void *stream)
+{
+    int rc = require_sm100();
+    if (rc != CLPK_OK)
+        return rc;
+    CLPK_REQUIRE(width == 1 || width == 2 || width == 4, "width must be 1, 2 or 4 (got %d)", width);
+    CLPK_REQUIRE(d_in && d_out, "NULL buffer");
+    const uint64_t per_block = 256ull * kFetchPerWI * (uint64_t)width;
+    CLPK_REQUIRE(n_floats > 0 && n_floats % per_block == 0,
+                 "n_floats (%llu) must be a positive multiple of %llu",
+                 (unsigned long long)n_floats, (unsigned long long)per_block);
+    const uint64_t blocks = n_floats / per_block;
+    CLPK_REQUIRE(blocks <= 0x7FFFFFFFull, "too many blocks (%llu)", (unsigned long long)blocks);
+    cudaStream_t s = as_stream(stream);
+    if (width == 1)
+        global_bandwidth_kernel<float><<<(unsigned)blocks, 256, 0, s>>>(d_in, d_out);
+    else if (width == 2)
+        global_bandwidth_kernel<float2>
+            <<<(unsigned)blocks, 256, 0, s>>>(reinterpret_cast<const float2 *>(d_in), d_out);
+    else
+        global_bandwidth_kernel<float4>
+            <<<(unsigned)blocks, 256, 0, s>>>(reinterpret_cast<const float4 *>(d_in), d_out);
+    CLPK_LAUNCH_CHECK("global_bandwidth");
+    return CLPK_OK;
+}
+
+int clpk_stream_read_grid(int variant, int *grid)
+{
+    int rc = require_sm100();
+    if (rc != CLPK_OK)
+        return rc;
+    CLPK_REQUIRE(grid, "grid is NULL");
+    CLPK_REQUIRE(variant == CLPK_STREAM_LDG || variant == CLPK_STREAM_TMA, "unknown variant %d", variant);
+    *grid = read_grid(variant);
+    return CLPK_OK;
+}
+
+int clpk_stream_read(int variant, const void *d_src, uint64_t n_bytes, uint32_t *d_partials, void *stream)
+{
+    int rc = require_sm100();
+    if (rc != CLPK_OK)
+        return rc;
+    CLPK_REQUIRE(variant == CLPK_STREAM_LDG || variant == CLPK_STREAM_TMA, "unknown variant %d", variant);
+    CLPK_REQUIRE(d_src && d_partials, "NULL buffer");
+    CLPK_REQUIRE(n_bytes % 16 == 0 && ((uintptr_t)d_src % 16) == 0, "n_bytes and d_src must be 16-byte aligned");
+    cudaStream_t s = as_stream(stream);
+    const int grid = read_grid(variant);
+    if (variant == CLPK_STREAM_LDG) {
+        stream_read_ldg<<<grid, kLdgThreads, 0, s>>>(reinterpret_cast<const uint4 *>(d_src), n_bytes / 16,
+                                                     d_partials);
+    } else {
+        uint32_t *st;
+        rc = status_word(&st);
+        if (rc != CLPK_OK)
+            return rc;
+        CLPK_CUDA(cudaFuncSetAttribute(stream_read_tma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTmaSmem));
+        stream_read_tma<<<grid, 160, kTmaSmem, s>>>(reinterpret_cast<const uint8_t *>(d_src), n_bytes,
+                                                    d_partials, st);
+    }
+    CLPK_LAUNCH_CHECK("stream_read");
+    return CLPK_OK;
+}
+
+int clpk_stream_copy(int variant, void *d_dst, const void *d_src, uint64_t n_bytes, void *stream)
+{
+    int rc = require_sm100();
+    if (rc != CLPK_OK)
+        return rc;
+    CLPK_REQUIRE(variant == CLPK_STREAM_LDG || variant == CLPK_STREAM_TMA, "unknown variant %d", variant);
+    CLPK_REQUIRE(d_dst && d_src, "NULL buffer");
+    CLPK_REQUIRE(n_bytes % 16 == 0 && ((uintptr_t)d_src % 16) == 0 && ((uintptr_t)d_dst % 16) == 0,
+                 "n_bytes and both pointers must be 16-byte aligned");
+    cudaStream_t s = as_stream(stream);
+    if (variant == CLPK_STREAM_LDG) {
+        stream_copy_ldg<<<num_sms() * kLdgCtasPerSm, kLdgThreads, 0, s>>>(
+            reinterpret_cast<uint4 *>(d_dst), reinterpret_cast<const uint4 *>(d_src), n_bytes / 16);
+    } else {
+        uint32_t *st;
+        rc = status_word(&st);
+        if (rc != CLPK_OK)
+            return rc;
+        CLPK_CUDA(cudaFuncSetAttribute(stream_copy_tma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTmaSmem));
+        stream_copy_tma<<<num_sms(), 32, kTmaSmem, s>>>(reinterpret_cast<uint8_t *>(d_dst),
+                                                        reinterpret_cast<const uint8_t *>(d_src), n_bytes, st);
+    }
+    CLPK_LAUNCH_CHECK("stream_copy");
+    return CLPK_OK;
+}
+
+int clpk_stream_triad(int variant, float *d_a, const float *d_b, const float *d_c, float sc,
+                      uint64_t n_floats, void *stream)
+{
+    int rc = require_sm100();
+    if (rc != CLPK_OK)
+        return rc;
+    CLPK_REQUIRE(variant == CLPK_STREAM_LDG || variant == CLPK_STREAM_TMA, "unknown variant %d", variant);
+    CLPK_REQUIRE(d_a && d_b && d_c, "NULL buffer");
+    CLPK_REQUIRE(((uintptr_t)d_a % 16) == 0 && ((uintptr_t)d_b % 16) == 0 && ((uintptr_t)d_c % 16) == 0,
+                 "pointers must be 16-byte aligned");
+    cudaStream_t s = as_stream(stream);
+    if (variant == CLPK_STREAM_LDG) {
+        stream_triad_ldg<<<num_sms() * kLdgCtasPerSm, kLdgThreads, 0, s>>>(
+            reinterpret_cast<float4 *>(d_a), reinterpret_cast<const float4 *>(d_b),
+            reinterpret_cast<const float4 *>(d_c), sc, n_floats / 4, n_floats % 4);
+    } else {
+        CLPK_REQUIRE(n_floats % 4 == 0, "the TMA variant needs n_floats to be a multiple of 4");
+        uint32_t *st;
+        rc = status_word(&st);
+        if (rc != CLPK_OK)
+            return rc;
+        CLPK_CUDA(cudaFuncSetAttribute(stream_triad_tma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTmaTriadSmem));
+        stream_triad_tma<<<num_sms(), 192, kTmaTriadSmem, s>>>(d_a, d_b, d_c, sc, n_floats * 4, st);
+    }
+    CLPK_LAUNCH_CHECK("stream_triad");
+    return CLPK_OK;
+}
+
+/* Reads and clears the device-side status word of the TMA streaming kernels
+ * (0 = no wait expired).  Synchronises the stream. */
+int clpk_stream_status(uint32_t *h_status, void *stream)
+{
+    CLPK_REQUIRE(h_status, "h_status is NULL");
+    uint32_t *st;
+    int rc = status_word(&st);
+    if (rc != CLPK_OK)
+        return rc;
+    CLPK_CUDA(cudaMemcpyAsync(h_status, st, sizeof(uint32_t), cudaMemcpyDeviceToHost, as_stream(stream)));
+    CLPK_CUDA(cudaStreamSynchronize(as_stream(stream)));
+    if (*h_status) {
+        CLPK_CUDA(cudaMemsetAsync(st, 0, sizeof(uint32_t), as_stream(stream)));
+        set_error("a TMA streaming kernel gave up waiting (code %u)", *h_status);
+        return CLPK_ERR_TIMEOUT;
+    }
+    return CLPK_OK;
+}
+
+} // extern "C"

@@ -1,0 +1,285 @@
+/* clpeak_b200 kernel shim -- the C ABI between clpeak's C++ host code and the
+ * sm_100a kernels.
+ *
+ * In the reference project the CUDA backend reaches its kernels through three
+ * pieces: fatbin blobs embedded in the binary (cuda_kernels::Blob,
+ * include/cuda/cuda_peak.h:214-248), CudaDevice::getKernel, which loads a blob
+ * with cuModuleLoadData (src/cuda/cuda_device.cpp:140-173), and
+ * cuLaunchKernel inside CudaPeak::runKernel (src/cuda/cuda_peak.cpp:64-107).
+ * This header replaces that trio: one plain C function per kernel, POD
+ * arguments and a stream, an int status back.  Each entry point names the
+ * reference kernel or host routine whose job it takes over.
+ *
+ * Conventions
+ *  - Every function returns CLPK_OK (0) or a CLPK_ERR_* code; clpk_last_error()
+ *    gives a thread-local human-readable detail string.  No C++ exceptions
+ *    cross this boundary.
+ *  - Pointers named d_* are device pointers of the current device, h_* are
+ *    host pointers.  Buffers are allocated and freed by the caller
+ *    (clpk_malloc/clpk_free or any other CUDA allocator in the same context).
+ *  - `stream` is a cudaStream_t passed as void* (NULL = the legacy default
+ *    stream).  Calls are asynchronous unless stated otherwise.
+ *  - Callable from any host thread that has made the target device current
+ *    (clpk_set_device).  No global state except per-device lazily created
+ *    handles.
+ *  - There is no CPU fallback: on a machine without an sm_100 GPU every
+ *    compute entry point fails with CLPK_ERR_NO_DEVICE / CLPK_ERR_UNSUPPORTED.
+ */
+#ifndef CLPEAK_B200_KERNELS_H
+#define CLPEAK_B200_KERNELS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(_WIN32)
+#define CLPK_API __declspec(dllexport)
+#else
+#define CLPK_API __attribute__((visibility("default")))
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------- */
+#define CLPK_OK               0
+#define CLPK_ERR_CUDA         1   /* a CUDA runtime/driver call failed            */
+#define CLPK_ERR_BAD_ARG      2   /* size/alignment/enum rejected before launch   */
+#define CLPK_ERR_TIMEOUT      3   /* a bounded device-side wait expired           */
+#define CLPK_ERR_UNSUPPORTED  4   /* device is not compute capability 10.x        */
+#define CLPK_ERR_NO_DEVICE    5   /* no CUDA device / driver                      */
+#define CLPK_ERR_TOO_LARGE    6   /* request exceeds a documented fixed capacity  */
+
+CLPK_API const char *clpk_last_error(void);
+CLPK_API const char *clpk_version(void);
+
+/* ---- device / memory / stream plumbing ------------------------------------
+ * Replaces CudaDevice::init and the cuMemAlloc / cuMemcpy / cuEvent calls
+ * scattered through src/cuda/ (cuda_device.cpp:40-120, cuda_peak.cpp:69-83). */
+typedef struct clpk_device_info {
+    char     name[256];
+    int      cc_major, cc_minor;
+    int      num_sms;
+    uint64_t total_mem_bytes;
+    int      driver_version;      /* e.g. 12090 */
+    int      runtime_version;
+    int      sm_clock_khz;        /* max */
+    int      mem_clock_khz;       /* max */
+    int      mem_bus_bits;
+    int      l2_bytes;
+    int      smem_optin_bytes;    /* max dynamic shared memory per block */
+} clpk_device_info_t;
+
+CLPK_API int clpk_device_count(int *count);
+CLPK_API int clpk_device_info(int device, clpk_device_info_t *out);
+CLPK_API int clpk_set_device(int device);
+CLPK_API int clpk_malloc(void **d_ptr, size_t bytes);
+CLPK_API int clpk_free(void *d_ptr);
+CLPK_API int clpk_malloc_host(void **h_ptr, size_t bytes);      /* pinned */
+CLPK_API int clpk_free_host(void *h_ptr);
+CLPK_API int clpk_memset(void *d_ptr, int byte, size_t bytes, void *stream);
+CLPK_API int clpk_memcpy_h2d(void *d_dst, const void *h_src, size_t bytes, void *stream);
+CLPK_API int clpk_memcpy_d2h(void *h_dst, const void *d_src, size_t bytes, void *stream);
+CLPK_API int clpk_memcpy_d2d(void *d_dst, const void *d_src, size_t bytes, void *stream);
+CLPK_API int clpk_stream_create(void **stream);                 /* non-blocking */
+CLPK_API int clpk_stream_destroy(void *stream);
+CLPK_API int clpk_stream_sync(void *stream);
+CLPK_API int clpk_event_create(void **event);
+CLPK_API int clpk_event_destroy(void *event);
+CLPK_API int clpk_event_record(void *event, void *stream);
+CLPK_API int clpk_event_sync(void *event);
+CLPK_API int clpk_event_elapsed_ms(void *start, void *stop, float *ms);
+/* Writes `bytes` (rounded down to 16) of a throw-away buffer so that the L2
+ * holds none of the previous kernel's data.  d_scratch must hold `bytes`. */
+CLPK_API int clpk_flush_l2(void *d_scratch, size_t bytes, void *stream);
+
+/* ---- seeded operand generation ----------------------------------------------
+ * Replaces populate() (src/common/common.cpp:76-95, a sequential xorshift32
+ * fill on the host) with counter-based device fills: element i of stream
+ * `seed` is a pure function of (seed, i); see clpk_rng.h for the definition. */
+#define CLPK_DIST_UNIFORM01   0   /* [0,1)               */
+#define CLPK_DIST_UNIFORM_PM1 1   /* [-1,1)              */
+#define CLPK_DIST_NORMAL      2   /* mean + std * N(0,1) */
+CLPK_API int clpk_fill_f32(float *d_dst, uint64_t n, uint64_t seed, int dist,
+                           float mean, float std, void *stream);
+/* int8 uniform in [-8,7]. */
+CLPK_API int clpk_fill_i8(int8_t *d_dst, uint64_t n, uint64_t seed, void *stream);
+
+/* Element formats for conversion, tensor-core peak tests and GEMM. */
+#define CLPK_DT_F32   0
+#define CLPK_DT_F16   1
+#define CLPK_DT_BF16  2
+#define CLPK_DT_E4M3  3
+#define CLPK_DT_E5M2  4
+#define CLPK_DT_I8    5
+#define CLPK_DT_MXF4  6   /* e2m1 pairs + one ue8m0 scale per 32 elements            */
+#define CLPK_DT_NVF4  7   /* e2m1 pairs + one ue4m3 scale per 16 elements + fp32 scale */
+
+/* Round-to-nearest-even conversion of n floats to a plain (unscaled) format:
+ * F16, BF16, E4M3 / E5M2 (saturating to the largest finite value), I8
+ * (round-to-nearest-even, saturating). */
+CLPK_API int clpk_convert_f32(void *d_dst, const float *d_src, uint64_t n, int dtype, void *stream);
+
+/* max |x| over n floats -> *d_absmax (a float the call overwrites). */
+CLPK_API int clpk_absmax_f32(float *d_absmax, const float *d_src, uint64_t n, void *stream);
+
+/* Block-scaled FP4 quantisation of a row-major [rows][cols] float matrix
+ * (cols a multiple of 64; blocks run along a row).
+ *   d_packed : rows*cols/2 bytes, element 2j in the low nibble of byte j
+ *   d_scales : one byte per block, row-major [rows][cols/block]
+ *              (block = 32, ue8m0 for MXF4; block = 16, ue4m3 for NVF4)
+ *   tensor_scale : NVF4 only; values are divided by it before the block scale
+ *              is chosen.  Pass absmax/(6*448) for the usual recipe, 1.0f for MXF4. */
+CLPK_API int clpk_quantize_fp4(uint8_t *d_packed, uint8_t *d_scales, const float *d_src,
+                               uint64_t rows, uint64_t cols, int dtype, float tensor_scale,
+                               void *stream);
+
+/* ---- global-memory bandwidth ------------------------------------------------------
+ * clpk_global_bandwidth: the reference's read-and-sum test, same per-thread
+ * order (global_bandwidth_v{1,2,4}, src/cuda/cuda_kernels/global_bandwidth.cu:14-71;
+ * host side src/cuda/global_bandwidth.cpp:6-92) with 64-bit indexing.
+ * `width` is 1, 2 or 4 floats per fetch; n_floats must be a multiple of
+ * 256*16*width.  d_out receives n_floats/(16*width) sums. */
+CLPK_API int clpk_global_bandwidth(int width, const float *d_in, float *d_out,
+                                   uint64_t n_floats, void *stream);
+
+/* STREAM-style kernels over large buffers; definitions follow the reference's
+ * CPU backend (read / copy / triad with s = 1.5f, src/cpu/bandwidth.cpp:325-352)
+ * -- its CUDA backend has read only.  `variant`:
+ *   CLPK_STREAM_LDG : 128-bit loads/stores from registers
+ *   CLPK_STREAM_TMA : cp.async.bulk global->shared->global staging
+ * n_bytes must be a multiple of 16.
+ * read  : d_partials[grid] receives per-CTA XOR of all 32-bit words read
+ *         (clpk_stream_read_grid() gives the grid size to allocate for).
+ * copy  : dst = src.           triad : a = b + s*c (no FMA contraction). */
+#define CLPK_STREAM_LDG 0
+#define CLPK_STREAM_TMA 1
+CLPK_API int clpk_stream_read_grid(int variant, int *grid);
+CLPK_API int clpk_stream_read(int variant, const void *d_src, uint64_t n_bytes,
+                              uint32_t *d_partials, void *stream);
+CLPK_API int clpk_stream_copy(int variant, void *d_dst, const void *d_src, uint64_t n_bytes,
+                              void *stream);
+CLPK_API int clpk_stream_triad(int variant, float *d_a, const float *d_b, const float *d_c,
+                               float s, uint64_t n_floats, void *stream);
+/* The TMA variants bound every device-side wait; a wait that expired is
+ * recorded in a per-device status word.  This call synchronises the stream,
+ * returns CLPK_ERR_TIMEOUT (and clears the word) if one did, and stores the
+ * raw code in *h_status. */
+CLPK_API int clpk_stream_status(uint32_t *h_status, void *stream);
+
+/* ---- fp32 multiply-add chains ----------------------------------------------------------
+ * clpk_compute_sp: the reference chain x = fma(x,x,c), c = threadIdx.x,
+ * 128 x 16 FMAs (compute_sp, src/cuda/cuda_kernels/compute_sp.cu:12-24).
+ * grid blocks of 256 threads; d_out holds grid*256 floats. */
+CLPK_API int clpk_compute_sp(float *d_out, float a, uint32_t grid, void *stream);
+/* clpk_mad_chain: work-item i holds a float4 seeded uniform[-1,1) from
+ * (seed, 4i..4i+3) and runs `iters` steps of x = fma(x, y, x) per lane;
+ * d_out[i] = ((x0 + x1) + x2) + x3.  n_items must be a multiple of 256. */
+CLPK_API int clpk_mad_chain(float *d_out, uint64_t n_items, uint64_t seed, float y,
+                            uint32_t iters, void *stream);
+
+/* ---- latency -------------------------------------------------------------------------------
+ * clpk_pointer_chase: one thread follows next[] for `hops` dependent loads
+ * starting at `start` (the CUDA backend has no such test; the model is
+ * chaseLatencyNs, src/cpu/latency.cpp:42-87).  d_result[0] = final index,
+ * d_result[1] = XOR of all indices visited, d_result[2..3] = elapsed
+ * %globaltimer nanoseconds (low, high word). */
+CLPK_API int clpk_pointer_chase(const uint32_t *d_next, uint32_t start, uint64_t hops,
+                                uint32_t *d_result, void *stream);
+/* Host-side construction of the chase cycle (Sattolo shuffle of 0..n-1 with a
+ * seeded generator, then next[order[i]] = order[i+1]); h_next holds n entries. */
+CLPK_API int clpk_build_chase_cycle(uint32_t *h_next, uint64_t n, uint64_t seed);
+/* clpk_launch_noop: one empty 1x1 kernel (kernel_latency_noop,
+ * src/cuda/cuda_kernels/kernel_latency.cu:5-7).
+ * clpk_launch_latency: `iters` x (launch + stream synchronise), each timed on
+ * the host clock, after `warmup` untimed rounds; *mean_us is the mean
+ * (src/cuda/kernel_latency.cpp:44-75).  Synchronous. */
+CLPK_API int clpk_launch_noop(void *stream);
+CLPK_API int clpk_launch_latency(uint32_t iters, uint32_t warmup, double *mean_us, void *stream);
+
+/* ---- tensor-core peak (tcgen05.mma, accumulator in tensor memory) ------------------------------
+ * Takes over the sixteen wmma / mma.sync probes filled in by CudaPeak::runWmma
+ * (src/cuda/wmma.cpp:10-425, kernels src/cuda/cuda_kernels/wmma_*.cu).  Each
+ * CTA stages one A tile [128][K] and one B tile [256][K] (both K-contiguous,
+ * row-major in global memory) in shared memory and issues `n_mma`
+ * tcgen05.mma instructions of shape 128x256xK that accumulate into one
+ * 128x256 tile in tensor memory.
+ *   kind   K    A/B element        D
+ *   F16    16   fp16               f32      BF16  16  bf16  f32
+ *   E4M3   32   fp8 e4m3           f32      E5M2  32  e5m2  f32
+ *   I8     32   int8               s32
+ *   MXF4   64   e2m1 x2 per byte   f32   + ue8m0 scale per 32 (d_sfa [128][2], d_sfb [256][2])
+ *   NVF4   64   e2m1 x2 per byte   f32   + ue4m3 scale per 16 (d_sfa [128][4], d_sfb [256][4])
+ *   *_SP   2:4 sparse A: d_a holds the compressed tile [128][K/2] and d_meta
+ *          one byte per 4 logical-K positions... see DESIGN notes in mma_peak.cu
+ * d_out receives the first `n_out_tiles` CTAs' accumulator tiles, row-major
+ * [128][256] 32-bit words; d_checksum[grid] the XOR of every CTA's accumulator
+ * bits; *d_status is set non-zero if a device-side wait timed out. */
+#define CLPK_MMA_F16      0
+#define CLPK_MMA_BF16     1
+#define CLPK_MMA_E4M3     2
+#define CLPK_MMA_E5M2     3
+#define CLPK_MMA_I8       4
+#define CLPK_MMA_MXF4     5
+#define CLPK_MMA_NVF4     6
+#define CLPK_MMA_E4M3_SP  7
+#define CLPK_MMA_MXF4_SP  8
+#define CLPK_MMA_NVF4_SP  9
+#define CLPK_MMA_I8_SP    10
+#define CLPK_MMA_KIND_COUNT 11
+
+typedef struct clpk_mma_peak_args {
+    int         kind;
+    const void *d_a;          /* [128][K] (dense) or [128][K/2] (sparse), element type of kind */
+    const void *d_b;          /* [256][K]                                                     */
+    const void *d_sfa;        /* block-scaled kinds only                                      */
+    const void *d_sfb;
+    const void *d_meta;       /* sparse kinds only: [128][K/8] bytes, see mma_peak.cu         */
+    uint32_t    n_mma;        /* instructions per CTA (>= 1)                                  */
+    uint32_t    grid;         /* CTAs                                                         */
+    uint32_t    n_out_tiles;  /* how many CTAs store their tile to d_out (<= grid)            */
+    void       *d_out;        /* n_out_tiles * 128*256 * 4 bytes                              */
+    uint32_t   *d_checksum;   /* grid words, may be NULL                                      */
+    uint32_t   *d_status;     /* one word, zeroed by the call                                 */
+} clpk_mma_peak_args_t;
+
+CLPK_API int clpk_mma_peak(const clpk_mma_peak_args_t *args, void *stream);
+/* K (logical, per instruction) and flop count per instruction for a kind
+ * (2*128*256*K, counted at the logical K for sparse kinds, the reference's
+ * convention: src/cuda/cuda_kernels/wmma_int8_sparse.cu:29-34). */
+CLPK_API int clpk_mma_kind_k(int kind);
+CLPK_API double clpk_mma_flops_per_instr(int kind);
+
+/* ---- GEMM (takes the place of cuBLASLt in CudaPeak::runCublas) -----------------------------------
+ * C[M][N] = A[M][K] * B[N][K]^T: A row-major, B "column-major K x N" = N rows
+ * of K contiguous elements -- the reference's TN layout
+ * (src/cuda/cuda_blas.cpp:275-287).  fp32 accumulation in tensor memory, bf16
+ * output, no epilogue beyond the NVF4 tensor scale `alpha`.
+ * dtype: CLPK_DT_BF16, CLPK_DT_F16, CLPK_DT_E4M3, CLPK_DT_NVF4.
+ * M and N multiples of 256, K a multiple of 128.
+ * NVF4: d_a/d_b are packed e2m1 (K/2 bytes per row); d_sfa/d_sfb are ue4m3
+ * scales row-major [rows][K/16] as written by clpk_quantize_fp4; the call
+ * repacks them into the tensor-core tile order in d_workspace
+ * (clpk_gemm_workspace_bytes) before the main kernel. */
+typedef struct clpk_gemm_args {
+    int         dtype;
+    uint32_t    m, n, k;
+    const void *d_a;
+    const void *d_b;
+    void       *d_c;          /* bf16 [M][N] row-major */
+    const void *d_sfa;
+    const void *d_sfb;
+    float       alpha;        /* applied in the epilogue; pass 1.0f when unused */
+    void       *d_workspace;
+    size_t      workspace_bytes;
+    uint32_t   *d_status;     /* one word, zeroed by the call */
+} clpk_gemm_args_t;
+
+CLPK_API int clpk_gemm_workspace_bytes(int dtype, uint32_t m, uint32_t n, uint32_t k, size_t *bytes);
+CLPK_API int clpk_gemm(const clpk_gemm_args_t *args, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* CLPEAK_B200_KERNELS_H */

@@ -1,0 +1,85 @@
+"""Operand construction and checking for the tensor-core tests.
+
+Config (BASELINE): dense kinds draw uniform[-1,1) (ints uniform[-8,7]) from
+seed 2; block-scaled kinds draw N(0,1) from seed 3 and quantise per block.
+"""
+import numpy as np
+
+from clpeak_b200 import native as N
+
+DENSE_DT = {N.MMA_F16: N.DT_F16, N.MMA_BF16: N.DT_BF16, N.MMA_E4M3: N.DT_E4M3, N.MMA_E5M2: N.DT_E5M2}
+KIND_K = {N.MMA_F16: 16, N.MMA_BF16: 16, N.MMA_E4M3: 32, N.MMA_E5M2: 32, N.MMA_I8: 32, N.MMA_MXF4: 64,
+          N.MMA_NVF4: 64}
+
+
+def make_operands(orc, kind):
+    """Returns dict(a, b, sfa, sfb, tensor_scale) of numpy arrays in the kernel's input encoding."""
+    k = KIND_K[kind]
+    if kind == N.MMA_I8:
+        a = orc.fill_i8(128 * k, 2).reshape(128, k)
+        b = orc.fill_i8(256 * k, 2, first=128 * k).reshape(256, k)
+        return dict(a=a, b=b, sfa=None, sfb=None, tensor_scale=(1.0, 1.0))
+    if kind in DENSE_DT:
+        fa = orc.fill_f32(128 * k, 2, 1)
+        fb = orc.fill_f32(256 * k, 2, 1, first=128 * k)
+        a = orc.convert_f32(fa, DENSE_DT[kind]).reshape(128, k)
+        b = orc.convert_f32(fb, DENSE_DT[kind]).reshape(256, k)
+        return dict(a=a, b=b, sfa=None, sfb=None, tensor_scale=(1.0, 1.0))
+    dt = N.DT_MXF4 if kind == N.MMA_MXF4 else N.DT_NVF4
+    fa = orc.fill_f32(128 * k, 3, 2).reshape(128, k)
+    fb = orc.fill_f32(256 * k, 3, 2, first=128 * k).reshape(256, k)
+    if dt == N.DT_NVF4:
+        tsa = np.float32(np.abs(fa).max()) / np.float32(6.0 * 448.0)
+        tsb = np.float32(np.abs(fb).max()) / np.float32(6.0 * 448.0)
+    else:
+        tsa = tsb = np.float32(1.0)
+    a, sfa = orc.quantize_fp4(fa, dt, float(tsa))
+    b, sfb = orc.quantize_fp4(fb, dt, float(tsb))
+    return dict(a=a, b=b, sfa=sfa, sfb=sfb, tensor_scale=(float(tsa), float(tsb)))
+
+
+def expected_tile(orc, kind, ops, n_mma):
+    """(expected tile, tolerance tile).  int8: exact int32, tolerance None."""
+    if kind == N.MMA_I8:
+        return orc.mma_tile_i8(ops["a"], ops["b"], n_mma), None
+    p, s = orc.mma_tile(kind, ops["a"], ops["b"], ops["sfa"], ops["sfb"])
+    k = KIND_K[kind]
+    # fp32 accumulation: each of the n additions into the running sum, and each
+    # of the K product additions inside one instruction, may lose up to one
+    # unit in the last place of the running magnitude (2^-23 relative if the
+    # hardware truncates).  The running magnitude is at most n*S, S = sum|a||b|.
+    rel = (n_mma + 2 * k) * 2.0 ** -23
+    return p * n_mma, rel * n_mma * s + 1e-30
+
+
+def run_peak(K, cuda, kind, ops, n_mma, grid, n_out_tiles):
+    from tests.gpu_util import dev_empty, dev_from, stream_ptr, sync, to_np
+    import ctypes as C
+    d_a = dev_from(ops["a"].view(np.uint8))
+    d_b = dev_from(ops["b"].view(np.uint8))
+    d_sfa = dev_from(ops["sfa"]) if ops["sfa"] is not None else None
+    d_sfb = dev_from(ops["sfb"]) if ops["sfb"] is not None else None
+    d_out = dev_empty(max(n_out_tiles, 1) * 128 * 256, cuda.int32)
+    d_chk = dev_empty(grid, cuda.int32)
+    d_status = dev_empty(1, cuda.int32)
+    args = N.MmaPeakArgs(kind=kind, d_a=d_a.data_ptr(), d_b=d_b.data_ptr(),
+                         d_sfa=d_sfa.data_ptr() if d_sfa is not None else None,
+                         d_sfb=d_sfb.data_ptr() if d_sfb is not None else None,
+                         d_meta=None, n_mma=n_mma, grid=grid, n_out_tiles=n_out_tiles,
+                         d_out=d_out.data_ptr(), d_checksum=d_chk.data_ptr(), d_status=d_status.data_ptr())
+    K.clpk_mma_peak(C.byref(args), stream_ptr())
+    sync()
+    status = int(to_np(d_status)[0])
+    tiles = to_np(d_out).reshape(-1, 128, 256)[:n_out_tiles]
+    return status, tiles, to_np(d_chk).view(np.uint32)
+
+
+def check_tile(kind, got_i32, want, tol):
+    if kind == N.MMA_I8:
+        assert np.array_equal(got_i32, want), f"int8 tile differs in {(got_i32 != want).sum()} elements"
+        return 0.0
+    got = got_i32.view(np.float32).astype(np.float64)
+    err = np.abs(got - want)
+    worst = float((err / tol).max())
+    assert worst <= 1.0, f"kind {kind}: error is {worst:.3g}x the stated tolerance"
+    return worst
