@@ -1,0 +1,484 @@
+#!/usr/bin/env python
+"""Headline benchmark: HBM streaming bandwidth (BASELINE config 2a) on N B200s.
+
+A *step* is one pass of the three STREAM kernels over 8 GiB fp32 buffers:
+read (8 GiB), copy (16 GiB), triad a = b + 1.5*c (24 GiB) -> 48 GiB of
+algorithmic HBM traffic per step.  `value` is whole-job GB/s with the buffers
+resident in HBM; `e2e` is the same three kernels driven through the C ABI from
+pinned HOST buffers (H2D of b and c and a D2H of the read checksum inside the
+timed region).  The tensor-core and GEMM rows of the same backend are measured
+after the timed region and reported under "rows" (they explain the headline
+metric's "TFLOPS/TOPS per dtype" part; each carries its own roofline fraction).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Multi-GPU (launched by torch.distributed.run, one rank per GPU): every rank runs
+the identical, independent workload on its own buffers -- replicas only, no
+data-path collective; torch.distributed is used for the start barrier and the
+max-over-ranks of the device-timed duration.
+
+--impl reference times the reference project's own CPU implementation of the
+same metric (its native-CPU backend's global_memory_bandwidth read/copy/triad,
+built unchanged into oracle/_ref/clpeak_ref) on the host cores; when that
+binary is absent it falls back to the oracle's C port of the three passes.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import re
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+GIB = 1 << 30
+METRIC = "global_memory_bandwidth (HBM stream read+copy+triad)"
+UNIT = "GB/s"
+SPEC = {  # NVIDIA HGX B200 datasheet, per GPU, dense (the 8-GPU figures divided by 8)
+    "hbm_gbs": 8000.0, "bf16_tflops": 2250.0, "fp16_tflops": 2250.0, "fp8_tflops": 4500.0,
+    "int8_tops": 4500.0, "fp4_tflops": 9000.0,
+}
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def ncu_traffic(kernel: str):
+    """Per-launch DRAM bytes of `kernel` from the committed ncu summary (None if not captured)."""
+    p = ROOT / "profiles" / "dram_traffic.json"
+    if not p.exists():
+        return None
+    return json.loads(p.read_text()).get(kernel)
+
+
+# ---------------------------------------------------------------------------------
+# clock sampling during the timed region
+# ---------------------------------------------------------------------------------
+
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------------
+# reference arm / CPU baseline
+# ---------------------------------------------------------------------------------
+
+def harmonic_stream(read, copy, triad):
+    """Aggregate GB/s of one read+copy+triad pass over equal arrays (1:2:3 bytes)."""
+    return 6.0 / (1.0 / read + 2.0 / copy + 3.0 / triad)
+
+
+def run_reference_cpu(max_time_ms: int):
+    """The reference's own CPU backend (built unchanged by oracle/Makefile `ref`)."""
+    exe = ROOT / "oracle" / "_ref" / "clpeak_ref"
+    if not exe.exists():
+        return None
+    with tempfile.TemporaryDirectory() as td:
+        xml = Path(td) / "ref.xml"
+        t0 = time.time()
+        r = subprocess.run([str(exe), "--cpu", "--global-memory-bandwidth", "--max-time-cpu", str(max_time_ms),
+                            "--xml-file", str(xml)], capture_output=True, text=True, timeout=600)
+        wall = time.time() - t0
+        if r.returncode != 0 or not xml.exists():
+            return None
+        txt = xml.read_text()
+    vals = {}
+    for name in ("read", "copy", "triad"):
+        m = re.search(rf'<metric name="{name}"[^>]*>([0-9.]+)</metric>', txt)
+        if not m:
+            return None
+        vals[name] = float(m.group(1))
+    cores = re.search(r'<prop name="Cores" value="([^"]*)"', txt)
+    return {"rows": vals, "value": harmonic_stream(vals["read"], vals["copy"], vals["triad"]),
+            "cores": os.cpu_count(), "cores_prop": cores.group(1) if cores else "", "wall_s": wall,
+            "kind": "reference",
+            "sample": f"reference CPU backend global_memory_bandwidth read/copy/triad on its own array sizing "
+                      f"(<=512 MiB per array), all logical cores, --max-time-cpu {max_time_ms} ms, gcc build"}
+
+
+def run_port_cpu(seconds: float):
+    """Fallback: the oracle's C port of the three passes on 256 MiB arrays."""
+    import numpy as np
+    from oracle import binding as ob
+    n = (256 << 20) // 4
+    threads = os.cpu_count() or 1
+    a = np.zeros(n, dtype=np.float32)
+    b = ob.fill_f32(n, 101, 0)
+    c = ob.fill_f32(n, 102, 0)
+    rows = {}
+    t0 = time.time()
+    for kind, name, mult in ((0, "read", 1), (1, "copy", 2), (2, "triad", 3)):
+        sec = ob.lib().orc_stream_pass_mt(kind, ob.ptr(a), ob.ptr(b), ob.ptr(c), n, threads, 1, None)
+        passes = max(1, int(seconds / 3.0 / max(sec, 1e-6)))
+        sec = ob.lib().orc_stream_pass_mt(kind, ob.ptr(a), ob.ptr(b), ob.ptr(c), n, threads, passes, None)
+        rows[name] = mult * n * 4 / sec / 1e9
+    return {"rows": rows, "value": harmonic_stream(rows["read"], rows["copy"], rows["triad"]), "cores": threads,
+            "wall_s": time.time() - t0, "kind": "port",
+            "sample": "oracle C port of read/copy/triad, 256 MiB arrays, one pthread per logical core"}
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    per_step_ms = 400
+    vals, t_steps = [], []
+    res = None
+    for i in range(args.warmup + args.steps):
+        t0 = time.time()
+        res = run_reference_cpu(per_step_ms) or run_port_cpu(per_step_ms * 3 / 1000.0)
+        if i >= args.warmup:
+            vals.append(res["value"]); t_steps.append(time.time() - t0)
+    value = sum(vals) / len(vals)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(t_steps) / len(t_steps),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "hbm_stream_read_copy_triad (reference CPU backend arrays, host DRAM)",
+                   "note": "CPU run of the same metric; array size is the reference's own (<=512 MiB)"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": res["cores"], "kind": res["kind"],
+                         "sample": res["sample"]},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "rows_last_step": res["rows"],
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ---------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--size-gib", type=float, default=8.0, help="bytes per array (default: the 8 GiB of the config)")
+    ap.add_argument("--no-rows", action="store_true", help="skip the tensor-core / GEMM rows")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import numpy as np
+    import torch
+    from clpeak_b200 import native as N
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the kernels have no CPU fallback")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    K = N.kernels()                      # raises if the CUDA library is missing
+    K.clpk_set_device(local)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    n_bytes = int(args.size_gib * GIB) // 4096 * 4096
+    n_floats = n_bytes // 4
+    a, b, c = (torch.empty(n_floats, dtype=torch.float32, device="cuda") for _ in range(3))
+    for i, t in enumerate((a, b, c)):
+        K.clpk_fill_f32(t.data_ptr(), n_floats, 100 + i, N.DIST_UNIFORM01, 0.0, 1.0, stream)
+
+    grids = {}
+    for v in (N.STREAM_LDG, N.STREAM_TMA):
+        g = C.c_int(0)
+        K.clpk_stream_read_grid(v, C.byref(g))
+        grids[v] = g.value
+    parts = torch.empty(max(grids.values()), dtype=torch.int32, device="cuda")
+
+    ops = {
+        "read": lambda v: K.clpk_stream_read(v, b.data_ptr(), n_bytes, parts.data_ptr(), stream),
+        "copy": lambda v: K.clpk_stream_copy(v, a.data_ptr(), c.data_ptr(), n_bytes, stream),
+        "triad": lambda v: K.clpk_stream_triad(v, a.data_ptr(), b.data_ptr(), c.data_ptr(), 1.5, n_floats, stream),
+    }
+    alg_bytes = {"read": n_bytes, "copy": 2 * n_bytes, "triad": 3 * n_bytes}
+
+    def ev():
+        return torch.cuda.Event(enable_timing=True)
+
+    def time_once(fn, reps=3):
+        fn(); torch.cuda.synchronize()
+        e0, e1 = ev(), ev()
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    # pick the faster flavour of each kernel once, outside the timed region
+    variant = {}
+    for name, fn in ops.items():
+        t = {v: time_once(lambda v=v: fn(v)) for v in (N.STREAM_LDG, N.STREAM_TMA)}
+        variant[name] = min(t, key=t.get)
+    vname = {N.STREAM_LDG: "ldg", N.STREAM_TMA: "tma"}
+
+    def step(events=None):
+        for i, name in enumerate(("read", "copy", "triad")):
+            if events is not None:
+                events[i].record()
+            ops[name](variant[name])
+        if events is not None:
+            events[3].record()
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    st = C.c_uint32(0)
+    K.clpk_stream_status(C.byref(st), stream)
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    per_step_events = [[ev() for _ in range(4)] for _ in range(args.steps)]
+    if dist:
+        dist.barrier()
+    torch.cuda.synchronize()
+    for k in range(args.steps):
+        step(per_step_events[k])
+    torch.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    total_ms = per_step_events[0][0].elapsed_time(per_step_events[-1][3])
+    clocks = sampler.stop() if rank == 0 else None
+    K.clpk_stream_status(C.byref(st), stream)      # raises on a device-side timeout
+
+    kern_ms = {name: sum(e[i].elapsed_time(e[i + 1]) for e in per_step_events) / args.steps
+               for i, name in enumerate(("read", "copy", "triad"))}
+    if dist:
+        t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    bytes_per_step = sum(alg_bytes.values())
+    value = world * bytes_per_step / (ms_per_step * 1e6)
+
+    # checksum of the step's result vs a second, independent pass (copy then read-back XOR)
+    read_xor = int(np.bitwise_xor.reduce(parts[:grids[variant["read"]]].cpu().numpy().view(np.uint32)))
+
+    # ---- end to end: host buffers through the C ABI -------------------------------------------
+    e2e = None
+    if not args.no_e2e:
+        avail_kb = 0
+        for ln in open("/proc/meminfo"):
+            if ln.startswith("MemAvailable"):
+                avail_kb = int(ln.split()[1])
+        local_world = int(os.environ.get("LOCAL_WORLD_SIZE", str(world)))
+        budget = avail_kb * 1024 // (6 * max(local_world, 1))     # per pinned array, per rank
+        chunk = min(n_bytes, max(256 << 20, budget // (1 << 20) * (1 << 20)))
+        hb = torch.empty(chunk // 4, dtype=torch.float32).pin_memory()
+        hc = torch.empty(chunk // 4, dtype=torch.float32).pin_memory()
+        hb.copy_(b[:chunk // 4]); hc.copy_(c[:chunk // 4])
+        hparts = torch.empty(parts.numel(), dtype=torch.int32).pin_memory()
+
+        def e2e_step():
+            off = 0
+            while off < n_bytes:
+                m = min(chunk, n_bytes - off)
+                K.clpk_memcpy_h2d(b.data_ptr() + off, hb.data_ptr(), m, stream)
+                K.clpk_memcpy_h2d(c.data_ptr() + off, hc.data_ptr(), m, stream)
+                off += m
+            step()
+            K.clpk_memcpy_d2h(hparts.data_ptr(), parts.data_ptr(), parts.numel() * 4, stream)
+            K.clpk_stream_sync(stream)
+
+        e2e_steps = max(3, min(args.steps, 10))
+        e2e_step()
+        if dist:
+            dist.barrier()
+        e0, e1 = ev(), ev()
+        e0.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e1.record(); torch.cuda.synchronize()
+        e2e_ms = e0.elapsed_time(e1)
+        if dist:
+            t = torch.tensor([e2e_ms], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_ms = float(t.item())
+        e2e = {"value": world * bytes_per_step / (e2e_ms / e2e_steps * 1e6), "unit": UNIT,
+               "h2d_bytes_per_step": 2 * n_bytes, "d2h_bytes_per_step": parts.numel() * 4,
+               "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
+               "host_buffer": "pinned, full size" if chunk == n_bytes else f"pinned {chunk >> 20} MiB chunk reused"}
+        del hb, hc
+
+    # ---- the other rows of the metric (per-dtype tensor peaks, GEMM) -----------------------------
+    rows = None
+    if not args.no_rows and rank == 0:
+        del a, c
+        torch.cuda.empty_cache()
+        rows = measure_rows(K, N, torch, stream, time_once)
+
+    if rank != 0:
+        if dist:
+            dist.barrier(); dist.destroy_process_group()
+        return 0
+
+    peaks = measured_peaks()
+    dom = max(kern_ms, key=kern_ms.get)
+    kernel_symbol = f"stream_{dom}_{vname[variant[dom]]}"
+    achieved = alg_bytes[dom] / (kern_ms[dom] * 1e6)
+    cpu = run_reference_cpu(2000) or run_port_cpu(12.0)
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"hbm_stream_read_copy_triad_{args.size_gib:g}GiB_fp32 (BASELINE configs[1]a)",
+                   "bytes_per_array": n_bytes, "algorithmic_bytes_per_step": bytes_per_step,
+                   "variants": {k: vname[v] for k, v in variant.items()},
+                   "l2": "inputs (3 x %.0f GiB) far exceed the 126 MB L2; no flush needed" % args.size_gib,
+                   "parallelism": f"replicas x{world}, no collective"},
+        "kernels": {k: {"ms": kern_ms[k], "GBps": alg_bytes[k] / (kern_ms[k] * 1e6),
+                        "frac_of_spec_8TBps": alg_bytes[k] / (kern_ms[k] * 1e6) / SPEC["hbm_gbs"]} for k in kern_ms},
+        "roofline": {"bound": "hbm", "kernel": kernel_symbol, "achieved": achieved, "peak": peaks["hbm_gbs"],
+                     "peak_source": f"of {peaks['source']}", "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                     "frac_of_spec": achieved / SPEC["hbm_gbs"], "traffic": ncu_traffic(kernel_symbol)},
+        "cpu_baseline": {"value": cpu["value"], "unit": UNIT, "cores": cpu["cores"], "kind": cpu["kind"],
+                         "sample": cpu["sample"], "rows": cpu["rows"]},
+        "e2e": e2e, "gpu_launches": 3 * args.steps, "clocks": clocks, "read_checksum": read_xor,
+        "rows": rows, "spec_peaks_per_gpu": SPEC,
+    }
+    print(json.dumps(line), flush=True)
+    if dist:
+        dist.barrier(); dist.destroy_process_group()
+    return 0
+
+
+def measure_rows(K, N, torch, stream, time_once):
+    """Tensor-core peak per dtype (config 3/4) and GEMM (config 5) on this GPU, after the timed region."""
+    import numpy as np
+    peaks = measured_peaks()
+    sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    rows = {}
+    spec_of = {N.MMA_F16: "fp16_tflops", N.MMA_BF16: "bf16_tflops", N.MMA_E4M3: "fp8_tflops",
+               N.MMA_E5M2: "fp8_tflops", N.MMA_I8: "int8_tops", N.MMA_MXF4: "fp4_tflops", N.MMA_NVF4: "fp4_tflops"}
+    grid, n_mma = 4 * sms, 1 << 14
+    ta = torch.zeros(128 * 32, dtype=torch.uint8, device="cuda")
+    tb = torch.zeros(256 * 32, dtype=torch.uint8, device="cuda")
+    # operands: seeded values converted on the device (bit patterns do not change the rate check here;
+    # the parity tests own the numerics)
+    f = torch.empty(256 * 64, dtype=torch.float32, device="cuda")
+    sf = torch.full((256 * 4,), 0x38, dtype=torch.uint8, device="cuda")
+    chk = torch.empty(grid, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for kind, name in N.MMA_KIND_NAMES.items():
+        if kind not in spec_of:
+            continue
+        K.clpk_fill_f32(f.data_ptr(), f.numel(), 2, N.DIST_UNIFORM_PM1, 0.0, 1.0, stream)
+        if kind in (N.MMA_F16, N.MMA_BF16, N.MMA_E4M3, N.MMA_E5M2):
+            dt = {N.MMA_F16: N.DT_F16, N.MMA_BF16: N.DT_BF16, N.MMA_E4M3: N.DT_E4M3, N.MMA_E5M2: N.DT_E5M2}[kind]
+            K.clpk_convert_f32(ta.data_ptr(), f.data_ptr(), 128 * K.raw("clpk_mma_kind_k")(kind), dt, stream)
+            K.clpk_convert_f32(tb.data_ptr(), f.data_ptr(), 256 * K.raw("clpk_mma_kind_k")(kind), dt, stream)
+        elif kind == N.MMA_I8:
+            K.clpk_fill_i8(ta.data_ptr(), ta.numel(), 2, stream)
+            K.clpk_fill_i8(tb.data_ptr(), tb.numel(), 3, stream)
+        else:
+            dt = N.DT_MXF4 if kind == N.MMA_MXF4 else N.DT_NVF4
+            K.clpk_quantize_fp4(ta.data_ptr(), sf.data_ptr(), f.data_ptr(), 128, 64, dt, 1.0, stream)
+            K.clpk_quantize_fp4(tb.data_ptr(), sf.data_ptr(), f.data_ptr(), 256, 64, dt, 1.0, stream)
+        args = N.MmaPeakArgs(kind=kind, d_a=ta.data_ptr(), d_b=tb.data_ptr(), d_sfa=sf.data_ptr(),
+                             d_sfb=sf.data_ptr(), d_meta=None, n_mma=n_mma, grid=grid, n_out_tiles=0, d_out=None,
+                             d_checksum=chk.data_ptr(), d_status=status.data_ptr())
+        ms = time_once(lambda: K.clpk_mma_peak(C.byref(args), stream), reps=5)
+        if int(status.item()) != 0:
+            rows[f"mma_{name}"] = {"error": "device-side wait timed out"}
+            continue
+        same = bool((chk == chk[0]).all().item())
+        tf = K.raw("clpk_mma_flops_per_instr")(kind) * n_mma * grid / ms / 1e9
+        rows[f"mma_{name}"] = {"T(FL)OPS": tf, "ms": ms, "frac_of_spec": tf / SPEC[spec_of[kind]],
+                               "all_ctas_same_checksum": same}
+    # GEMM, 16384^3 (config 5), bf16 and fp8
+    for dt, name, spec in ((N.DT_BF16, "bf16", "bf16_tflops"), (N.DT_E4M3, "fp8_e4m3", "fp8_tflops")):
+        for m in (4096, 8192, 16384):
+            es = 2 if dt == N.DT_BF16 else 1
+            A = torch.empty(m * m * es, dtype=torch.uint8, device="cuda")
+            B = torch.empty(m * m * es, dtype=torch.uint8, device="cuda")
+            Cc = torch.empty(m * m, dtype=torch.int16, device="cuda")
+            tmp = torch.empty(m * m, dtype=torch.float32, device="cuda")
+            for buf, seed in ((A, 40), (B, 41)):
+                K.clpk_fill_f32(tmp.data_ptr(), m * m, seed, N.DIST_NORMAL, 0.0, 0.02, stream)
+                K.clpk_convert_f32(buf.data_ptr(), tmp.data_ptr(), m * m, dt, stream)
+            del tmp
+            ga = N.GemmArgs(dtype=dt, m=m, n=m, k=m, d_a=A.data_ptr(), d_b=B.data_ptr(), d_c=Cc.data_ptr(),
+                            alpha=1.0, d_status=status.data_ptr())
+            ms = time_once(lambda: K.clpk_gemm(C.byref(ga), stream), reps=5)
+            tf = 2.0 * m * m * m / ms / 1e9
+            row = {"TFLOPS": tf, "ms": ms, "frac_of_spec": tf / SPEC[spec], "status": int(status.item())}
+            if dt == N.DT_BF16:
+                row["frac_of_measured_cublas_burst"] = tf / peaks["bf16_tflops"]
+            rows[f"gemm_{name}_{m}"] = row
+            del A, B, Cc
+            torch.cuda.empty_cache()
+    return rows
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -194,7 +194,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
             uint32_t mb, nb;
             tile_coords(tile, tiles_m, tiles_n, mb, nb);
             const uint32_t b = tcount & 1, use = tcount >> 1;
-            if (!mbar_wait(&sh->tmem_full[b], use & 1)) {
+            // warp-uniform verdict: the tcgen05.ld below is warp-aligned
+            if (!__all_sync(0xffffffffu, mbar_wait(&sh->tmem_full[b], use & 1) ? 1 : 0)) {
                 if (lane == 0)
                     atomicCAS(p.status, 0u, 0x204u);
                 break;

@@ -116,8 +116,10 @@ __global__ void __launch_bounds__(128) mma_peak_kernel(PeakParams p)
         mbar_fence_init();
     }
     fence_proxy_async_smem();
-    if (warp == 0)
+    if (warp == 0) {
+        __syncwarp();
         tmem_alloc<1>(tmem_slot, kCols);
+    }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -157,13 +159,15 @@ __global__ void __launch_bounds__(128) mma_peak_kernel(PeakParams p)
     }
     __syncwarp();
 
-    const bool done = mbar_wait(bar, 0);
+    // The verdict must be uniform across the CTA: the tcgen05.ld below is a
+    // warp-aligned instruction and the checksum uses a CTA barrier.
+    const int done = __syncthreads_and(mbar_wait(bar, 0) ? 1 : 0);
     tc_fence_after_sync();
-    if (!done && lane == 0)
+    if (!done && threadIdx.x == 0)
         atomicCAS(p.status, 0u, 0x100u + (uint32_t)KIND);
 
+    uint32_t x = 0;
     if (done) {
-        uint32_t x = 0;
         const int row = warp * 32 + lane;
         uint32_t *out_row = (blockIdx.x < p.n_out_tiles)
                                 ? p.out + ((size_t)blockIdx.x * kTileM + row) * kTileN
@@ -182,17 +186,15 @@ __global__ void __launch_bounds__(128) mma_peak_kernel(PeakParams p)
                         make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
             }
         }
-        if (p.checksum) {
-            __shared__ uint32_t wx[4];
-            for (int o = 16; o > 0; o >>= 1)
-                x ^= __shfl_xor_sync(0xffffffffu, x, o);
-            if (lane == 0)
-                wx[warp] = x;
-            __syncthreads();
-            if (threadIdx.x == 0)
-                p.checksum[blockIdx.x] = wx[0] ^ wx[1] ^ wx[2] ^ wx[3];
-        }
     }
+    __shared__ uint32_t wx[4];
+    for (int o = 16; o > 0; o >>= 1)
+        x ^= __shfl_xor_sync(0xffffffffu, x, o);
+    if (lane == 0)
+        wx[warp] = x;
+    __syncthreads();
+    if (done && p.checksum && threadIdx.x == 0)
+        p.checksum[blockIdx.x] = wx[0] ^ wx[1] ^ wx[2] ^ wx[3];
 
     tc_fence_before_sync();
     __syncthreads();

@@ -164,8 +164,8 @@ def test_stream_triad_ldg_ragged_floats(K, orc, cuda):
     b = orc.fill_f32(n, 23, 0)
     c = orc.fill_f32(n, 24, 0)
     d_a = dev_empty(n, cuda.float32)
-    K.clpk_stream_triad(N.STREAM_LDG, d_a.data_ptr(), dev_from(b).data_ptr(), dev_from(c).data_ptr(), 1.5, n,
-                        stream_ptr())
+    d_b, d_c = dev_from(b), dev_from(c)
+    K.clpk_stream_triad(N.STREAM_LDG, d_a.data_ptr(), d_b.data_ptr(), d_c.data_ptr(), 1.5, n, stream_ptr())
     sync()
     assert_bits_equal(to_np(d_a), orc.triad(b, c, 1.5), "triad ragged")
     with pytest.raises(N.ClpkError):
