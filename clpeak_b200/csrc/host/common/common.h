@@ -1,0 +1,4 @@
+// Resolves the reference tree's <common/common.h> include path to the single
+// header this host library keeps its whole backend contract in.
+#pragma once
+#include "../clpeak_api.hpp"

@@ -37,3 +37,16 @@ def assert_bits_equal(got: np.ndarray, want: np.ndarray, what: str):
     if not np.array_equal(g, w):
         bad = np.flatnonzero(g != w)
         raise AssertionError(f"{what}: {bad.size} differing bytes, first at byte {bad[0]}")
+
+
+def assert_floats_equal_nan_aware(got: np.ndarray, want: np.ndarray, what: str):
+    """Bit-exact, except that any NaN matches any NaN: the payload and sign of a
+    generated NaN (inf - inf) differ between x86 and the GPU."""
+    g = np.ascontiguousarray(got, dtype=np.float32)
+    w = np.ascontiguousarray(want, dtype=np.float32)
+    assert g.shape == w.shape
+    both_nan = np.isnan(g) & np.isnan(w)
+    same = (g.view(np.uint32) == w.view(np.uint32)) | both_nan
+    if not same.all():
+        bad = np.flatnonzero(~same)
+        raise AssertionError(f"{what}: {bad.size} differing values, first at {bad[0]}: {g[bad[0]]!r} vs {w[bad[0]]!r}")

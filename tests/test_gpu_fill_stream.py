@@ -6,7 +6,8 @@ import numpy as np
 import pytest
 
 from clpeak_b200 import native as N
-from tests.gpu_util import (assert_bits_equal, dev_empty, dev_from, stream_ptr, sync, to_np)
+from tests.gpu_util import (assert_bits_equal, assert_floats_equal_nan_aware, dev_empty, dev_from, stream_ptr, sync,
+                            to_np)
 
 pytestmark = pytest.mark.gpu
 
@@ -187,9 +188,12 @@ def test_mad_chain(K, orc, cuda, iters):
     K.clpk_mad_chain(d.data_ptr(), n, 0, 0.999, iters, stream_ptr())
     sync()
     got = to_np(d)
-    assert_bits_equal(got, orc.mad_chain(n, 0, 0.999, iters), f"mad_chain iters={iters}")
-    if iters == 64:
+    # x roughly doubles per step, so past ~128 steps every lane is +-inf and a
+    # work-item whose lanes disagree in sign sums to NaN: compare NaN-aware.
+    assert_floats_equal_nan_aware(got, orc.mad_chain(n, 0, 0.999, iters), f"mad_chain iters={iters}")
+    if iters <= 64:
         assert np.all(np.isfinite(got))            # the finite-range prefix has real values
+        assert_bits_equal(got, orc.mad_chain(n, 0, 0.999, iters), "finite prefix")
 
 
 def test_mad_chain_full_config_sampled(K, orc, cuda):
@@ -200,7 +204,8 @@ def test_mad_chain_full_config_sampled(K, orc, cuda):
     sync()
     got = to_np(d)
     for first in (0, 123456, n - 512):
-        assert_bits_equal(got[first:first + 512], orc.mad_chain(512, 0, 0.999, 4096, first=first), "mad window")
+        assert_floats_equal_nan_aware(got[first:first + 512], orc.mad_chain(512, 0, 0.999, 4096, first=first),
+                                      "mad window")
 
 
 @pytest.mark.parametrize("n,hops", [(2, 7), (1000, 5000), (1 << 20, 1 << 16)])
