@@ -71,7 +71,7 @@ def build_kernels(force: bool = False) -> Path:
         list(ex.map(_run, jobs))
     so = LIB / "libclpeak_b200_kernels.so"
     if force or jobs or _stale(so, objs):
-        _run([nvcc, "-shared", "-o", str(so), *map(str, objs), "-cudart", "static"])
+        _run([nvcc, "-shared", "-o", str(so), *map(str, objs), "-cudart", "static", "-Xlinker", "--exclude-libs,ALL"])
     return so
 
 
@@ -98,13 +98,19 @@ def build_host(force: bool = False) -> list[Path]:
     ffi = LIB / "libclpeak_ffi.so"
     link_kernels = ["-L", str(LIB), "-lclpeak_b200_kernels", "-Wl,-rpath,$ORIGIN"]
     if force or jobs or _stale(ffi, objs):
-        _run([cxx, "-shared", "-pthread", "-o", str(ffi), *map(str, objs), *link_kernels, "-ldl"])
+        # --exclude-libs keeps a statically linked libstdc++ from leaking its symbols: the
+        # library exports the clpeak_* C symbols and nothing else.
+        _run([cxx, "-shared", "-pthread", "-Wl,--exclude-libs,ALL", "-o", str(ffi), *map(str, objs), *link_kernels,
+              "-ldl"])
     outs.append(ffi)
     cli_obj = OBJ / "host_cli_main.o"
     if cli_obj.exists():
         exe = LIB / "clpeak"
         if force or jobs or _stale(exe, [cli_obj, ffi]):
-            _run([cxx, "-pthread", "-o", str(exe), str(cli_obj), "-L", str(LIB), "-lclpeak_ffi",
+            # libclpeak_ffi.so exports only its six C symbols (like the reference's), so the CLI
+            # links the host objects themselves.
+            core = [o for o in objs if o.name != "host_ffi.o"]
+            _run([cxx, "-pthread", "-o", str(exe), str(cli_obj), *map(str, core), "-L", str(LIB),
                   "-lclpeak_b200_kernels", "-Wl,-rpath,$ORIGIN", "-ldl"])
         outs.append(exe)
     return outs

@@ -6,6 +6,7 @@
 // (backend, platform, device, driver), free text is folded to one line.
 #include <cassert>
 #include <cctype>
+#include <cmath>
 #include <iomanip>
 #include <sstream>
 
