@@ -106,6 +106,7 @@ KERNEL_API = {
     "clpk_stream_copy": [_i, _vp, _vp, _u64, _vp],
     "clpk_stream_triad": [_i, _vp, _vp, _vp, _f, _u64, _vp],
     "clpk_stream_status": [C.POINTER(_u32), _vp],
+    "clpk_stream_checksum_static": [_vp, _u64, _u32, _vp, _vp],
     "clpk_compute_sp": [_vp, _f, _u32, _vp],
     "clpk_mad_chain": [_vp, _u64, _u64, _f, _u32, _vp],
     "clpk_pointer_chase": [_vp, _u32, _u64, _vp, _vp],

@@ -167,6 +167,25 @@ CLPK_API int clpk_stream_triad(int variant, float *d_a, const float *d_b, const 
  * raw code in *h_status. */
 CLPK_API int clpk_stream_status(uint32_t *h_status, void *stream);
 
+/* clpk_stream_checksum_static: no counterpart in the reference.  The same
+ * streaming read as clpk_stream_read(CLPK_STREAM_LDG), for callers that must
+ * not allocate device memory when they need the checksum (inside a region where
+ * cudaMalloc's implicit synchronisation is unacceptable, in a host that forbids
+ * allocator calls after start-up, or with the memory pool fully handed out):
+ * the per-CTA partials live in a fixed array inside the library's device image
+ * instead of a caller buffer, and *d_xor_out (one device word supplied by the
+ * caller) receives the XOR of every 32-bit word of the source.
+ *  - Capacity: partials for at most 4096 CTAs (16.25 KiB held on every GPU that
+ *    loads the library, until the process exits).  grid_ctas = 0 picks
+ *    4 x SM count; a larger request fails with CLPK_ERR_TOO_LARGE.
+ *  - Calls no cudaMalloc / cudaFree and no allocating library routine.  The first
+ *    call on a device resolves the array's device address
+ *    (cudaGetSymbolAddress); make that first call before any stream capture.
+ *  - All calls on one device share the array: calls that overlap on the GPU
+ *    race; serialise them. */
+CLPK_API int clpk_stream_checksum_static(const void *d_src, uint64_t n_bytes, uint32_t grid_ctas,
+                                         uint32_t *d_xor_out, void *stream);
+
 /* ---- fp32 multiply-add chains ----------------------------------------------------------
  * clpk_compute_sp: the reference chain x = fma(x,x,c), c = threadIdx.x,
  * 128 x 16 FMAs (compute_sp, src/cuda/cuda_kernels/compute_sp.cu:12-24).

@@ -256,6 +256,14 @@ int clpk_stream_triad(int, float *a, const float *b, const float *c, float s, ui
     return CLPK_OK;
 }
 int clpk_stream_status(uint32_t *st, void *) { *st = 0; return CLPK_OK; }
+int clpk_stream_checksum_static(const void *src, uint64_t n_bytes, uint32_t grid, uint32_t *out, void *)
+{
+    if (grid > 4096) return fail(CLPK_ERR_TOO_LARGE, "too many CTAs");
+    uint32_t x = 0;
+    for (uint64_t i = 0; i < n_bytes / 4; ++i) x ^= static_cast<const uint32_t *>(src)[i];
+    *out = x;
+    return CLPK_OK;
+}
 
 int clpk_compute_sp(float *out, float a, uint32_t grid, void *)
 {
