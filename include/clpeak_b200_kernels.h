@@ -229,8 +229,8 @@ CLPK_API int clpk_launch_latency(uint32_t iters, uint32_t warmup, double *mean_u
  *   I8     32   int8               s32
  *   MXF4   64   e2m1 x2 per byte   f32   + ue8m0 scale per 32 (d_sfa [128][2], d_sfb [256][2])
  *   NVF4   64   e2m1 x2 per byte   f32   + ue4m3 scale per 16 (d_sfa [128][4], d_sfb [256][4])
- *   *_SP   2:4 sparse A: d_a holds the compressed tile [128][K/2] and d_meta
- *          one byte per 4 logical-K positions... see DESIGN notes in mma_peak.cu
+ *   *_SP   2:4 sparse A (d_a = compressed tile [128][K/2], d_meta = 2-bit positions);
+ *          declared for the registry, not yet implemented: CLPK_ERR_UNSUPPORTED
  * d_out receives the first `n_out_tiles` CTAs' accumulator tiles, row-major
  * [128][256] 32-bit words; d_checksum[grid] the XOR of every CTA's accumulator
  * bits; *d_status is set non-zero if a device-side wait timed out. */
