@@ -324,6 +324,18 @@ __device__ __forceinline__ void tmem_cp_128x128b(uint32_t taddr, uint64_t smem_d
                      : "memory");
 }
 
+// 128 rows x 256 bits (lane i <- row i, eight columns).
+template <int CtaGroup>
+__device__ __forceinline__ void tmem_cp_128x256b(uint32_t taddr, uint64_t smem_desc)
+{
+    if constexpr (CtaGroup == 1)
+        asm volatile("tcgen05.cp.cta_group::1.128x256b [%0], %1;" ::"r"(taddr), "l"(smem_desc)
+                     : "memory");
+    else
+        asm volatile("tcgen05.cp.cta_group::2.128x256b [%0], %1;" ::"r"(taddr), "l"(smem_desc)
+                     : "memory");
+}
+
 // ---- tcgen05.commit ------------------------------------------------------------------
 
 // All prior tcgen05 async ops of this thread arrive (count 1) on `bar` when done.

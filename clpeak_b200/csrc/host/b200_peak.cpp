@@ -338,6 +338,126 @@ struct B200Harness {
         out.readings.push_back(ok(row.metric, t, note + "  " + pct(t, row.spec, row.specName), work, s));
     }
 
+    // 2:4 structured-sparse kinds (tcgen05.mma.sp): a dense float tile is generated on the device, pruned on the
+    // host (the selection is data dependent and tiny), and the compressed tile goes back for quantisation.
+    static const std::vector<KindRow> &sparseRows(bool integer)
+    {
+        static const std::vector<KindRow> fp = {
+            {CLPK_MMA_E4M3_SP, "wmma_fp8_e4m3_sparse", "tcgen05 FP8(E4M3) 2:4 sparse 128x256x64", "fp8_e4m3_sparse", "tflops", 2 * kSpecFp8Tflops, "sparse fp8 TFLOPS",
+             "8-bit tensor cores with structured sparsity: of every four values along a row of one input two are zero and "
+             "are skipped, which doubles the nominal rate.  Work is counted as if the zeros were multiplied."},
+            {CLPK_MMA_MXF4_SP, "wmma_mxf4_sparse", "tcgen05 MXFP4 2:4 sparse 128x256x128", "mxf4_sparse", "tflops", 2 * kSpecFp4Tflops, "sparse fp4 TFLOPS",
+             "The 4-bit MX format combined with structured sparsity (two of every four pairs kept)."},
+            {CLPK_MMA_NVF4_SP, "wmma_nvf4_sparse", "tcgen05 NVFP4 2:4 sparse 128x256x128", "nvf4_sparse", "tflops", 2 * kSpecFp4Tflops, "sparse fp4 TFLOPS",
+             "NVIDIA's 4-bit block format combined with structured sparsity -- the highest nominal rate of the chip."},
+        };
+        static const std::vector<KindRow> in = {
+            {CLPK_MMA_I8_SP, "wmma_int8_sparse", "tcgen05 int8 2:4 sparse 128x256x64", "int8_sparse", "tops", 2 * kSpecInt8Tops, "sparse int8 TOPS",
+             "8-bit whole-number tensor cores with structured sparsity: two of every four values of one input are zero and skipped."},
+        };
+        return integer ? in : fp;
+    }
+
+    static void tensorSparse(B200Worker &w, B200TestResult &out, const KindRow &row)
+    {
+        out.spec = {row.tag, row.display, row.unit, Category::Unknown, row.desc};
+        const int kind = row.kind;
+        const int K = b200check::sparseK(kind);
+        const bool fp4 = K == 128;
+        const int nsf = kind == CLPK_MMA_NVF4_SP ? 4 : 2;
+        const uint32_t grid = 4u * (uint32_t)w.info.numSMs, nMma = 1u << 14;
+        const std::string note = "2^14 instructions per CTA on " + std::to_string(grid) +
+                                 " CTAs, work counted at the logical K=" + std::to_string(K) +
+                                 "; seeded A pruned 2:4 by magnitude, final accumulator tile checked against the host.";
+        auto fail = [&](const std::string &why) { out.readings.push_back(bad(row.metric, ResultStatus::Error, why, note)); };
+
+        const size_t aBytes = 128 * 32, bBytes = 256 * 64, metaBytes = 128 * 8;   // K/2 x 8-bit = K/2 x 2 x 4-bit
+        DeviceBuffer f32, dA, dB, dSfa, dSfb, dMeta, dOut, dChk, dStatus;
+        if (!f32.alloc(256 * 128 * sizeof(float)) || !dA.alloc(aBytes) || !dB.alloc(bBytes) || !dSfa.alloc(128 * 4) ||
+            !dSfb.alloc(256 * 4) || !dMeta.alloc(metaBytes) || !dOut.alloc(128 * 256 * 4) || !dChk.alloc(grid * 4) || !dStatus.alloc(4))
+            return fail("Failed to allocate buffers");
+
+        // A: dense on the device -> host prune -> compressed floats back -> device quantise
+        std::vector<float> dense(128 * (size_t)K), comp;
+        std::vector<uint8_t> meta;
+        int rc = CLPK_OK;
+        if (kind == CLPK_MMA_I8_SP) {
+            std::vector<int8_t> raw(dense.size());
+            rc |= clpk_fill_i8(f32.as<int8_t>(), raw.size(), 2, w.stream);
+            rc |= clpk_memcpy_d2h(raw.data(), f32.p, raw.size(), w.stream);
+            rc |= clpk_stream_sync(w.stream);
+            for (size_t i = 0; i < raw.size(); ++i)
+                dense[i] = (float)raw[i];
+        } else {
+            rc |= clpk_fill_f32(f32.as<float>(), dense.size(), fp4 ? 3 : 2, fp4 ? CLPK_DIST_NORMAL : CLPK_DIST_UNIFORM_PM1, 0, 1, w.stream);
+            rc |= clpk_memcpy_d2h(dense.data(), f32.p, dense.size() * 4, w.stream);
+            rc |= clpk_stream_sync(w.stream);
+        }
+        if (rc != CLPK_OK)
+            return fail(shimError("operand generation"));
+        b200check::pruneTile(dense, 128, K, fp4, comp, meta);
+        rc |= clpk_memcpy_h2d(f32.p, comp.data(), comp.size() * 4, w.stream);
+        rc |= clpk_memcpy_h2d(dMeta.p, meta.data(), meta.size(), w.stream);
+        if (fp4)
+            rc |= clpk_quantize_fp4(dA.as<uint8_t>(), dSfa.as<uint8_t>(), f32.as<float>(), 128, K / 2,
+                                    kind == CLPK_MMA_MXF4_SP ? CLPK_DT_MXF4 : CLPK_DT_NVF4,
+                                    kind == CLPK_MMA_MXF4_SP ? 1.0f : 0.001953125f, w.stream);
+        else
+            rc |= clpk_convert_f32(dA.p, f32.as<float>(), comp.size(), kind == CLPK_MMA_I8_SP ? CLPK_DT_I8 : CLPK_DT_E4M3, w.stream);
+        // B: dense
+        if (kind == CLPK_MMA_I8_SP)
+            rc |= clpk_fill_i8(dB.as<int8_t>(), 256 * (uint64_t)K, 3, w.stream);
+        else if (!fp4) {
+            rc |= clpk_fill_f32(f32.as<float>(), 256 * (uint64_t)K, 3, CLPK_DIST_UNIFORM_PM1, 0, 1, w.stream);
+            rc |= clpk_convert_f32(dB.p, f32.as<float>(), 256 * (uint64_t)K, CLPK_DT_E4M3, w.stream);
+        } else {
+            rc |= clpk_fill_f32(f32.as<float>(), 256 * (uint64_t)K, 4, CLPK_DIST_NORMAL, 0, 1, w.stream);
+            rc |= clpk_quantize_fp4(dB.as<uint8_t>(), dSfb.as<uint8_t>(), f32.as<float>(), 256, K,
+                                    kind == CLPK_MMA_MXF4_SP ? CLPK_DT_MXF4_B64 : CLPK_DT_NVF4_B32,
+                                    kind == CLPK_MMA_MXF4_SP ? 1.0f : 0.001953125f, w.stream);
+        }
+        if (rc != CLPK_OK)
+            return fail(shimError("operand generation"));
+
+        clpk_mma_peak_args_t a{};
+        a.kind = kind;
+        a.d_a = dA.p; a.d_b = dB.p; a.d_sfa = dSfa.p; a.d_sfb = dSfb.p; a.d_meta = dMeta.p;
+        a.n_mma = nMma; a.grid = grid; a.n_out_tiles = 1;
+        a.d_out = dOut.p; a.d_checksum = dChk.as<uint32_t>(); a.d_status = dStatus.as<uint32_t>();
+
+        std::string err;
+        const double s = w.timeLaunches([&] { return clpk_mma_peak(&a, w.stream); }, err);
+        if (s < 0)
+            return fail(err);
+
+        std::vector<uint8_t> hA(aBytes), hB(bBytes), hSfa(128 * (size_t)nsf), hSfb(256 * (size_t)nsf);
+        std::vector<uint32_t> tile(128 * 256), chk(grid);
+        uint32_t status = 0;
+        clpk_memcpy_d2h(hA.data(), dA.p, aBytes, w.stream);
+        clpk_memcpy_d2h(hB.data(), dB.p, bBytes, w.stream);
+        clpk_memcpy_d2h(hSfa.data(), dSfa.p, hSfa.size(), w.stream);
+        clpk_memcpy_d2h(hSfb.data(), dSfb.p, hSfb.size(), w.stream);
+        clpk_memcpy_d2h(tile.data(), dOut.p, tile.size() * 4, w.stream);
+        clpk_memcpy_d2h(chk.data(), dChk.p, chk.size() * 4, w.stream);
+        clpk_memcpy_d2h(&status, dStatus.p, 4, w.stream);
+        if (clpk_stream_sync(w.stream) != CLPK_OK)
+            return fail(shimError("read back"));
+        if (status != 0)
+            return fail("a device-side wait timed out (status " + std::to_string(status) + ")");
+        for (uint32_t c : chk)
+            if (c != chk[0])
+                return fail("CTAs disagree on the accumulator checksum");
+        double worst = 0;
+        const std::string verdict = b200check::checkSparseTile(kind, hA.data(), meta.data(), hB.data(), hSfa.data(), hSfb.data(),
+                                                               nMma, tile.data(), &worst);
+        if (!verdict.empty())
+            return fail("accumulator check failed: " + verdict);
+
+        const double work = clpk_mma_flops_per_instr(kind) * nMma * grid;
+        const double t = work / s / 1e12;
+        out.readings.push_back(ok(row.metric, t, note + "  " + pct(t, row.spec, row.specName), work, s));
+    }
+
     static void tensorNotBuilt(B200TestResult &out, const char *tag, const char *display, const char *metric,
                                const char *unit, const char *why)
     {
@@ -368,26 +488,43 @@ struct B200Harness {
         struct Row { const char *metric; int dtype; double spec; const char *specName; };
         const Row built[] = {{"fp16", CLPK_DT_F16, kSpecBf16Tflops, "dense fp16 TFLOPS"},
                              {"bf16", CLPK_DT_BF16, kSpecBf16Tflops, "dense bf16 TFLOPS"},
-                             {"fp8_e4m3", CLPK_DT_E4M3, kSpecFp8Tflops, "dense fp8 TFLOPS"}};
+                             {"fp8_e4m3", CLPK_DT_E4M3, kSpecFp8Tflops, "dense fp8 TFLOPS"},
+                             {"nvf4_e2m1", CLPK_DT_NVF4, kSpecFp4Tflops, "dense fp4 TFLOPS"}};
         for (const char *m : {"fp32", "fp64", "tf32"})
             out.readings.push_back(bad(m, ResultStatus::Unsupported, "no tcgen05 GEMM for this type in the B200 backend"));
         for (const Row &r : built) {
-            const std::string note = "M=N=K=" + std::to_string(d) + ", A row-major, B column-major, N(0,0.02) operands, "
+            const bool nv = r.dtype == CLPK_DT_NVF4;
+            const std::string note = "M=N=K=" + std::to_string(d) + ", A row-major, B column-major, N(0,0.02) operands, " +
+                                     (nv ? "e2m1 with ue4m3 block scales and fp32 tensor scales (repacked inside the timed call), " : "") +
                                      "fp32 accumulate, bf16 out; sampled elements checked against a host dot product.";
-            const size_t es = (r.dtype == CLPK_DT_E4M3) ? 1 : 2;
             const uint64_t n = (uint64_t)d * d;
-            DeviceBuffer tmp, A, B, C, st;
-            if (!tmp.alloc(n * 4) || !A.alloc(n * es) || !B.alloc(n * es) || !C.alloc(n * 2) || !st.alloc(4)) {
+            const uint64_t rowBytes = nv ? d / 2 : (r.dtype == CLPK_DT_E4M3 ? d : 2ull * d);
+            // N(0, 0.02): |x| < 0.12, so a tensor scale of 2^-15 keeps x / scale / 6 within ue4m3's range (448).
+            const float tensorScale = nv ? std::ldexp(1.0f, -15) : 1.0f;
+            size_t wsBytes = 0;
+            if (nv && clpk_gemm_workspace_bytes(r.dtype, d, d, d, &wsBytes) != CLPK_OK) {
+                out.readings.push_back(bad(r.metric, ResultStatus::Error, shimError("workspace size"), note));
+                continue;
+            }
+            DeviceBuffer tmp, A, B, C, st, sfa, sfb, ws;
+            if (!tmp.alloc(n * 4) || !A.alloc(d * rowBytes) || !B.alloc(d * rowBytes) || !C.alloc(n * 2) || !st.alloc(4) ||
+                (nv && (!sfa.alloc(n / 16) || !sfb.alloc(n / 16) || !ws.alloc(wsBytes)))) {
                 out.readings.push_back(bad(r.metric, ResultStatus::Error, "Failed to allocate matrices", note));
                 continue;
             }
+            auto quantise = [&](DeviceBuffer &dst, DeviceBuffer &sf) {
+                return nv ? clpk_quantize_fp4(dst.as<uint8_t>(), sf.as<uint8_t>(), tmp.as<float>(), d, d, CLPK_DT_NVF4, tensorScale, w.stream)
+                          : clpk_convert_f32(dst.p, tmp.as<float>(), n, r.dtype, w.stream);
+            };
             int rc = clpk_fill_f32(tmp.as<float>(), n, 40, CLPK_DIST_NORMAL, 0.0f, 0.02f, w.stream);
-            rc |= clpk_convert_f32(A.p, tmp.as<float>(), n, r.dtype, w.stream);
+            rc |= quantise(A, sfa);
             rc |= clpk_fill_f32(tmp.as<float>(), n, 41, CLPK_DIST_NORMAL, 0.0f, 0.02f, w.stream);
-            rc |= clpk_convert_f32(B.p, tmp.as<float>(), n, r.dtype, w.stream);
+            rc |= quantise(B, sfb);
             clpk_gemm_args_t g{};
             g.dtype = r.dtype; g.m = g.n = g.k = d;
-            g.d_a = A.p; g.d_b = B.p; g.d_c = C.p; g.alpha = 1.0f; g.d_status = st.as<uint32_t>();
+            g.d_a = A.p; g.d_b = B.p; g.d_c = C.p; g.d_status = st.as<uint32_t>();
+            g.alpha = nv ? tensorScale * tensorScale : 1.0f;
+            g.d_sfa = sfa.p; g.d_sfb = sfb.p; g.d_workspace = ws.p; g.workspace_bytes = wsBytes;
             std::string err;
             const double s = rc == CLPK_OK ? w.timeLaunches([&] { return clpk_gemm(&g, w.stream); }, err) : -1.0;
             if (s < 0) {
@@ -398,16 +535,22 @@ struct B200Harness {
             std::string verdict;
             uint32_t status = 0;
             clpk_memcpy_d2h(&status, st.p, 4, w.stream);
-            std::vector<uint8_t> rowA(d * es), rowB(d * es);
+            std::vector<uint8_t> rowA(rowBytes), rowB(rowBytes), rowSfa(d / 16), rowSfb(d / 16);
             for (int sidx = 0; sidx < 16 && verdict.empty(); ++sidx) {
                 const uint64_t i = clpk_rand64(77, 2 * sidx) % d, j = clpk_rand64(77, 2 * sidx + 1) % d;
                 uint16_t c16 = 0;
-                clpk_memcpy_d2h(rowA.data(), A.as<uint8_t>() + i * d * es, d * es, w.stream);
-                clpk_memcpy_d2h(rowB.data(), B.as<uint8_t>() + j * d * es, d * es, w.stream);
+                clpk_memcpy_d2h(rowA.data(), A.as<uint8_t>() + i * rowBytes, rowBytes, w.stream);
+                clpk_memcpy_d2h(rowB.data(), B.as<uint8_t>() + j * rowBytes, rowBytes, w.stream);
+                if (nv) {
+                    clpk_memcpy_d2h(rowSfa.data(), sfa.as<uint8_t>() + i * (d / 16), d / 16, w.stream);
+                    clpk_memcpy_d2h(rowSfb.data(), sfb.as<uint8_t>() + j * (d / 16), d / 16, w.stream);
+                }
                 clpk_memcpy_d2h(&c16, C.as<uint16_t>() + i * d + j, 2, w.stream);
                 clpk_stream_sync(w.stream);
                 double sAbs = 0;
-                const double want = b200check::gemmElement(r.dtype, rowA.data(), rowB.data(), d, 0, 0, &sAbs);
+                const double want = (double)g.alpha * b200check::gemmElement(r.dtype, rowA.data(), rowB.data(), d, 0, 0, &sAbs,
+                                                                             rowSfa.data(), rowSfb.data());
+                sAbs *= g.alpha;
                 const double got = clpk_bf16_decode(c16);
                 const double tol = d * std::ldexp(1.0, -23) * sAbs + std::ldexp(1.0, -8) * std::fabs(want) + 1e-30;
                 if (!(std::fabs(got - want) <= tol))
@@ -424,7 +567,7 @@ struct B200Harness {
             const double t = work / s / 1e12;
             out.readings.push_back(ok(r.metric, t, note + "  " + pct(t, r.spec, r.specName), work, s));
         }
-        for (const char *m : {"fp8_e5m2", "mxf4_e2m1", "nvf4_e2m1"})
+        for (const char *m : {"fp8_e5m2", "mxf4_e2m1"})
             out.readings.push_back(bad(m, ResultStatus::Unsupported, "not built in the B200 backend yet"));
     }
 
@@ -812,11 +955,11 @@ int CudaPeak::runAll()
             {"wmma_tf32", "tcgen05 tf32", "wmma_tf32", "kind::tf32 path is not built yet"},
             {"wmma_fp64", "fp64 tensor path", "wmma_fp64", "tcgen05 has no fp64 kind"},
             {"wmma_fp4_e2m1", "tcgen05 FP4(E2M1) unscaled", "fp4_e2m1", "unscaled fp4 (kind::f8f6f4) path is not built yet"},
-            {"wmma_mxf4_sparse", "tcgen05 MXFP4 2:4 sparse", "mxf4_sparse", "tcgen05.mma.sp paths are not built yet"},
-            {"wmma_nvf4_sparse", "tcgen05 NVFP4 2:4 sparse", "nvf4_sparse", "tcgen05.mma.sp paths are not built yet"},
         };
         for (const NB &nb : notBuilt)
             plan.push_back([nb](B200Worker &, B200TestResult &o) { H::tensorNotBuilt(o, nb.tag, nb.display, nb.metric, "tflops", nb.why); });
+        for (const auto &row : H::sparseRows(false))
+            plan.push_back([row](B200Worker &w, B200TestResult &o) { H::tensorSparse(w, o, row); });
     }
     if (isAllowedAs(Benchmark::Cublas, Category::FpCompute))
         plan.push_back(H::gemmFp);
@@ -825,7 +968,8 @@ int CudaPeak::runAll()
         for (const auto &row : H::kindRows())
             if (row.kind == CLPK_MMA_I8)
                 plan.push_back([row](B200Worker &w, B200TestResult &o) { H::tensorPeak(w, o, row); });
-        plan.push_back([](B200Worker &, B200TestResult &o) { H::tensorNotBuilt(o, "wmma_int8_sparse", "tcgen05 int8 2:4 sparse", "int8_sparse", "tops", "tcgen05.mma.sp paths are not built yet"); });
+        for (const auto &row : H::sparseRows(true))
+            plan.push_back([row](B200Worker &w, B200TestResult &o) { H::tensorSparse(w, o, row); });
         plan.push_back([](B200Worker &, B200TestResult &o) { H::tensorNotBuilt(o, "wmma_int4", "int4 tensor path", "int4", "tops", "no int4 tensor-core path on sm_100"); });
     }
     if (isAllowedAs(Benchmark::Cublas, Category::IntCompute))

@@ -102,22 +102,15 @@ inline double decodeOperand(int kind, const uint8_t *t, const uint8_t *sf, int r
     }
 }
 
-// Compares one accumulator tile (128x256 32-bit words) after n instructions.
-// int8: exact.  Floating kinds: |got - n*P| <= (n + K) * 2^-22 * n * S with
+// Compares one accumulator tile (128x256 32-bit words) after n instructions with
+// the exact product of the decoded operands da[128][K], db[256][K].
+// Integer kinds: exact.  Floating kinds: |got - n*P| <= (n + K) * 2^-22 * n * S with
 // P the exact product and S = sum|a||b| (truncating fp32 accumulation, at most
 // two units in the last place lost per addition).  Returns an empty string when
 // the tile passes, otherwise a description of the first failure.
-inline std::string checkTile(int kind, const uint8_t *a, const uint8_t *b, const uint8_t *sfa, const uint8_t *sfb,
-                             uint32_t n, const uint32_t *tile, double *worstRatio = nullptr)
+inline std::string checkDecodedTile(const std::vector<double> &da, const std::vector<double> &db, int K, bool integer,
+                                    uint32_t n, const uint32_t *tile, double *worstRatio = nullptr)
 {
-    const int K = kindK(kind);
-    std::vector<double> da(128 * (size_t)K), db(256 * (size_t)K);
-    for (int r = 0; r < 128; ++r)
-        for (int k = 0; k < K; ++k)
-            da[r * K + k] = decodeOperand(kind, a, sfa, r, k);
-    for (int r = 0; r < 256; ++r)
-        for (int k = 0; k < K; ++k)
-            db[r * K + k] = decodeOperand(kind, b, sfb, r, k);
     const double rel = ((double)n + K) * std::ldexp(1.0, -22);
     double worst = 0.0;
     for (int i = 0; i < 128; ++i)
@@ -129,7 +122,7 @@ inline std::string checkTile(int kind, const uint8_t *a, const uint8_t *b, const
                 s += std::fabs(t);
             }
             const uint32_t word = tile[i * 256 + j];
-            if (kind == CLPK_MMA_I8) {
+            if (integer) {
                 const int32_t want = (int32_t)((uint32_t)(int32_t)p * n);
                 if ((int32_t)word != want)
                     return "int32 accumulator differs at (" + std::to_string(i) + "," + std::to_string(j) + ")";
@@ -148,13 +141,116 @@ inline std::string checkTile(int kind, const uint8_t *a, const uint8_t *b, const
     return {};
 }
 
-// One element of C = A B^T from quantised 16-bit / 8-bit operands, in double.
-inline double gemmElement(int dtype, const void *a, const void *b, uint64_t k, uint64_t i, uint64_t j, double *absSum)
+inline std::string checkTile(int kind, const uint8_t *a, const uint8_t *b, const uint8_t *sfa, const uint8_t *sfb,
+                             uint32_t n, const uint32_t *tile, double *worstRatio = nullptr)
+{
+    const int K = kindK(kind);
+    std::vector<double> da(128 * (size_t)K), db(256 * (size_t)K);
+    for (int r = 0; r < 128; ++r)
+        for (int k = 0; k < K; ++k)
+            da[r * K + k] = decodeOperand(kind, a, sfa, r, k);
+    for (int r = 0; r < 256; ++r)
+        for (int k = 0; k < K; ++k)
+            db[r * K + k] = decodeOperand(kind, b, sfb, r, k);
+    return checkDecodedTile(da, db, K, kind == CLPK_MMA_I8, n, tile, worstRatio);
+}
+
+// ---- 2:4 sparse kinds ---------------------------------------------------------------------
+
+// Keep the two largest magnitudes of every four along K (4-bit kinds: the two
+// largest |x0|+|x1| of every four pairs); ties go to the lower index.  compressed
+// is [rows][k/2] in K order, meta one nibble per group (first | second << 2), low
+// nibble first.
+inline void pruneTile(const std::vector<float> &dense, int rows, int k, bool pairs, std::vector<float> &compressed,
+                      std::vector<uint8_t> &meta)
+{
+    const int unit = pairs ? 2 : 1, group = 4 * unit;
+    compressed.assign((size_t)rows * k / 2, 0.0f);
+    meta.assign((size_t)rows * k / (2 * group), 0);
+    for (int r = 0; r < rows; ++r)
+        for (int g = 0; g < k / group; ++g) {
+            const float *x = &dense[(size_t)r * k + g * group];
+            float mag[4];
+            for (int u = 0; u < 4; ++u)
+                mag[u] = pairs ? std::fabs(x[2 * u]) + std::fabs(x[2 * u + 1]) : std::fabs(x[u]);
+            int first = 0;
+            for (int u = 1; u < 4; ++u)
+                if (mag[u] > mag[first]) first = u;
+            int second = -1;
+            for (int u = 0; u < 4; ++u)
+                if (u != first && (second < 0 || mag[u] > mag[second])) second = u;
+            const int s0 = std::min(first, second), s1 = std::max(first, second);
+            float *c = &compressed[(size_t)r * k / 2 + g * 2 * unit];
+            for (int e = 0; e < unit; ++e) {
+                c[e] = x[s0 * unit + e];
+                c[unit + e] = x[s1 * unit + e];
+            }
+            const uint8_t nib = (uint8_t)(s0 | (s1 << 2));
+            uint8_t &mb = meta[(size_t)r * (k / (2 * group)) + g / 2];
+            mb = (g & 1) ? (uint8_t)((mb & 0x0F) | (nib << 4)) : (uint8_t)((mb & 0xF0) | nib);
+        }
+}
+
+inline int sparseK(int kind) { return (kind == CLPK_MMA_MXF4_SP || kind == CLPK_MMA_NVF4_SP) ? 128 : 64; }
+
+inline std::string checkSparseTile(int kind, const uint8_t *aComp, const uint8_t *meta, const uint8_t *b,
+                                   const uint8_t *sfa, const uint8_t *sfb, uint32_t n, const uint32_t *tile,
+                                   double *worstRatio = nullptr)
+{
+    const int K = sparseK(kind);
+    const bool fp4 = K == 128;
+    const int nsf = kind == CLPK_MMA_NVF4_SP ? 4 : 2;
+    auto scale = [&](const uint8_t *sf, int row, int kpos) -> double {
+        const uint8_t sb = sf[row * nsf + kpos / (K / nsf)];
+        return kind == CLPK_MMA_MXF4_SP ? clpk_ue8m0_decode(sb) : clpk_e4m3_decode(sb);
+    };
+    std::vector<double> da(128 * (size_t)K, 0.0), db(256 * (size_t)K);
+    for (int r = 0; r < 128; ++r)
+        for (int g = 0; g < 16; ++g) {
+            const uint8_t byte = meta[r * 8 + g / 2];
+            const int nib = (g & 1) ? (byte >> 4) : (byte & 0xF);
+            const int sel[2] = {nib & 3, nib >> 2};
+            if (!fp4) {
+                for (int e = 0; e < 2; ++e) {
+                    const int ci = r * 32 + 2 * g + e;
+                    da[r * K + 4 * g + sel[e]] = kind == CLPK_MMA_I8_SP ? (double)reinterpret_cast<const int8_t *>(aComp)[ci]
+                                                                       : (double)clpk_e4m3_decode(aComp[ci]);
+                }
+            } else {
+                for (int e = 0; e < 4; ++e) {
+                    const int ci = 4 * g + e;
+                    const uint8_t cb = aComp[r * 32 + ci / 2];
+                    const int kpos = 8 * g + 2 * sel[e / 2] + (e & 1);
+                    da[r * K + kpos] = (double)clpk_e2m1_decode((ci & 1) ? (cb >> 4) : (cb & 0xF)) * scale(sfa, r, kpos);
+                }
+            }
+        }
+    for (int r = 0; r < 256; ++r)
+        for (int k = 0; k < K; ++k) {
+            if (!fp4)
+                db[r * K + k] = kind == CLPK_MMA_I8_SP ? (double)reinterpret_cast<const int8_t *>(b)[r * K + k]
+                                                      : (double)clpk_e4m3_decode(b[r * K + k]);
+            else {
+                const uint8_t bb = b[(r * K + k) / 2];
+                db[r * K + k] = (double)clpk_e2m1_decode((k & 1) ? (bb >> 4) : (bb & 0xF)) * scale(sfb, r, k);
+            }
+        }
+    return checkDecodedTile(da, db, K, kind == CLPK_MMA_I8_SP, n, tile, worstRatio);
+}
+
+// One element of C = A B^T from the quantised operands, in double.  NVFP4: packed
+// e2m1 with row-major ue4m3 scales per 16 elements (sfa / sfb), tensor scales excluded.
+inline double gemmElement(int dtype, const void *a, const void *b, uint64_t k, uint64_t i, uint64_t j, double *absSum,
+                          const uint8_t *sfa = nullptr, const uint8_t *sfb = nullptr)
 {
     double acc = 0.0, s = 0.0;
     for (uint64_t x = 0; x < k; ++x) {
         double va, vb;
-        if (dtype == CLPK_DT_BF16) {
+        if (dtype == CLPK_DT_NVF4) {
+            const uint8_t ab = static_cast<const uint8_t *>(a)[(i * k + x) / 2], bb = static_cast<const uint8_t *>(b)[(j * k + x) / 2];
+            va = (double)clpk_e2m1_decode((x & 1) ? (ab >> 4) : (ab & 0xF)) * clpk_e4m3_decode(sfa[i * (k / 16) + x / 16]);
+            vb = (double)clpk_e2m1_decode((x & 1) ? (bb >> 4) : (bb & 0xF)) * clpk_e4m3_decode(sfb[j * (k / 16) + x / 16]);
+        } else if (dtype == CLPK_DT_BF16) {
             va = clpk_bf16_decode(static_cast<const uint16_t *>(a)[i * k + x]);
             vb = clpk_bf16_decode(static_cast<const uint16_t *>(b)[j * k + x]);
         } else if (dtype == CLPK_DT_F16) {

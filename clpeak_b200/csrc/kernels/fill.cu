@@ -77,8 +77,9 @@ __global__ void absmax_kernel(float *out, const float *src, uint64_t n)
         atomicMax(reinterpret_cast<unsigned int *>(out), __float_as_uint(m));
 }
 
-// One thread per scale block.  BLOCK = 32 (MXF4, ue8m0) or 16 (NVF4, ue4m3).
-template <int BLOCK>
+// One thread per scale block of BLOCK elements; UE8M0 selects the scale format
+// (power-of-two MX scale) against ue4m3 (NVFP4 scale, after the tensor scale).
+template <int BLOCK, bool UE8M0>
 __global__ void quantize_fp4_kernel(uint8_t *packed, uint8_t *scales, const float *src,
                                     uint64_t n_blocks, float tensor_scale)
 {
@@ -89,12 +90,12 @@ __global__ void quantize_fp4_kernel(uint8_t *packed, uint8_t *scales, const floa
         float amax = 0.0f;
 #pragma unroll
         for (int i = 0; i < BLOCK; i++) {
-            v[i] = (BLOCK == 16) ? __fdiv_rn(x[i], tensor_scale) : x[i];
+            v[i] = UE8M0 ? x[i] : __fdiv_rn(x[i], tensor_scale);
             amax = fmaxf(amax, fabsf(v[i]));
         }
         uint8_t sbyte;
         float sdec;
-        if (BLOCK == 32) {
+        if (UE8M0) {
             sbyte = clpk_ue8m0_for_absmax(amax);
             sdec = clpk_ue8m0_decode(sbyte);
         } else {
@@ -185,18 +186,21 @@ int clpk_quantize_fp4(uint8_t *d_packed, uint8_t *d_scales, const float *d_src, 
                       uint64_t cols, int dtype, float tensor_scale, void *stream)
 {
     CLPK_REQUIRE(d_packed && d_scales && d_src, "NULL buffer");
-    CLPK_REQUIRE(dtype == CLPK_DT_MXF4 || dtype == CLPK_DT_NVF4, "dtype must be MXF4 or NVF4");
+    const bool mx = (dtype == CLPK_DT_MXF4 || dtype == CLPK_DT_MXF4_B64);
+    CLPK_REQUIRE(mx || dtype == CLPK_DT_NVF4 || dtype == CLPK_DT_NVF4_B32, "dtype must be an MXF4 or NVF4 variant");
     CLPK_REQUIRE(cols % 64 == 0, "cols (%llu) must be a multiple of 64", (unsigned long long)cols);
-    CLPK_REQUIRE(dtype == CLPK_DT_MXF4 || tensor_scale > 0.0f, "tensor_scale must be positive");
+    CLPK_REQUIRE(mx || tensor_scale > 0.0f, "tensor_scale must be positive");
     const uint64_t n = rows * cols;
     if (n == 0)
         return CLPK_OK;
-    if (dtype == CLPK_DT_MXF4)
-        quantize_fp4_kernel<32><<<fill_grid(), 128, 0, as_stream(stream)>>>(d_packed, d_scales, d_src,
-                                                                          n / 32, 1.0f);
-    else
-        quantize_fp4_kernel<16><<<fill_grid(), 128, 0, as_stream(stream)>>>(d_packed, d_scales, d_src,
-                                                                          n / 16, tensor_scale);
+    const int g = fill_grid();
+    cudaStream_t s = as_stream(stream);
+    switch (dtype) {
+    case CLPK_DT_MXF4:     quantize_fp4_kernel<32, true><<<g, 128, 0, s>>>(d_packed, d_scales, d_src, n / 32, 1.0f); break;
+    case CLPK_DT_MXF4_B64: quantize_fp4_kernel<64, true><<<g, 128, 0, s>>>(d_packed, d_scales, d_src, n / 64, 1.0f); break;
+    case CLPK_DT_NVF4:     quantize_fp4_kernel<16, false><<<g, 128, 0, s>>>(d_packed, d_scales, d_src, n / 16, tensor_scale); break;
+    default:               quantize_fp4_kernel<32, false><<<g, 128, 0, s>>>(d_packed, d_scales, d_src, n / 32, tensor_scale); break;
+    }
     CLPK_LAUNCH_CHECK("quantize_fp4");
     return CLPK_OK;
 }

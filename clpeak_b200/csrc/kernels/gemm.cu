@@ -236,6 +236,249 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
         tmem_dealloc<2>(tmem, 512);
 }
 
+
+// ---------------------------------------------------------------------------------
+// NVFP4 GEMM: e2m1 operands, one ue4m3 scale per 16 elements along K
+// ---------------------------------------------------------------------------------
+//
+// Same skeleton as gemm_kernel (2-CTA clusters, 256x256 tiles, TMA ring, one MMA
+// thread, four epilogue warps) with these differences:
+//  * K per stage is 256 elements (128 bytes of packed fp4) = four
+//    tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X (K = 64).
+//  * Every stage also carries scale factors: 2 KiB for this CTA's 128 rows of A
+//    and 4 KiB for all 256 columns of B (each CTA of the pair needs B's scales for
+//    the whole tile), pre-arranged in global memory in the order tensor memory
+//    wants them: per instruction a 512-byte block of 32 rows x 16 bytes, byte
+//    (r % 32) * 16 + (r / 32) * 4 + j for row r's j-th factor.  One
+//    tcgen05.cp.cta_group::2.32x128b.warpx4 per block copies it from shared to
+//    tensor memory in both CTAs (4 columns, replicated in the four lane quarters).
+//  * Twelve such copies are needed per stage.  Issued by the MMA thread they sit
+//    in front of the stage's MMAs and cost ~50 ns each (measured: 3.1 PFLOPS
+//    against 5.4 with the copies removed); a copy is mostly issue latency of the
+//    issuing thread, so four dedicated threads (warps 6-9 of the leader CTA) issue
+//    three each, run ahead of the MMA thread by up to the pipeline depth and hand
+//    over through an mbarrier (tcgen05.commit): 4.65 PFLOPS.  Writing the factors
+//    through registers (tcgen05.st from both CTAs) was tried and is slower: the
+//    per-stage cross-CTA mbarrier arrive costs about a microsecond.
+//  * Tensor memory: accumulator in columns [0,256), then one 48-column scale area
+//    per pipeline stage (16 columns A, 32 columns B).  No room is left for a second
+//    accumulator, so a tile's epilogue is not overlapped with the next main loop.
+
+constexpr int kNvStages = 5;
+constexpr int kNvCopyThreads = 4;
+constexpr int kNvGemmThreads = 32 * (6 + kNvCopyThreads);    // producer, MMA, 4 epilogue, 4 scale-copy warps
+constexpr uint32_t kSfaStageBytes = 2048;
+constexpr uint32_t kSfbStageBytes = 4096;
+constexpr uint32_t kNvStageBytes = kStageBytes + kSfaStageBytes + kSfbStageBytes;     // 38 KiB
+constexpr uint32_t kNvSfCol = 256, kNvSfColsPerStage = 48;
+
+struct NvGemmSmem {
+    uint64_t full[kNvStages];        // tiles and scale factors of both CTAs landed (leader's barrier)
+    uint64_t empty[kNvStages];       // the stage's MMAs retired (both CTAs)
+    uint64_t sf_ready[kNvStages];    // the stage's scale factors are in tensor memory (leader)
+    uint64_t tmem_full;
+    uint64_t tmem_empty;
+    uint32_t tmem_base;
+};
+
+// scales [rows][k/16] (row-major bytes) -> per-instruction 512-byte blocks.
+// is_b = 0: blocks ordered [rows/128][k/256][4];  is_b = 1: [rows/256][k/256][4][2].
+__global__ void pack_scales_kernel(uint8_t *__restrict__ out, const uint8_t *__restrict__ in, uint32_t rows, uint32_t k,
+                                   int is_b)
+{
+    const uint32_t sf_per_row = k / 16, kblocks = k / 256;
+    const uint64_t total = (uint64_t)rows * sf_per_row;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t row = (uint32_t)(i / sf_per_row), sf = (uint32_t)(i % sf_per_row);
+        const uint32_t kb = sf / 16, kk = (sf % 16) / 4, j = sf % 4;
+        const uint32_t r = row % 128;
+        uint64_t block;
+        if (!is_b)
+            block = ((uint64_t)(row / 128) * kblocks + kb) * 4 + kk;
+        else
+            block = (((uint64_t)(row / 256) * kblocks + kb) * 4 + kk) * 2 + (row % 256) / 128;
+        out[block * 512 + (r % 32) * 16 + (r / 32) * 4 + j] = in[i];
+    }
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
+    gemm_nvf4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                     const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
+                     GemmParams p)
+{
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    NvGemmSmem *sh = reinterpret_cast<NvGemmSmem *>(smem + (size_t)kNvStages * kNvStageBytes);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const uint32_t cluster_id = blockIdx.x >> 1;
+    const uint32_t n_clusters = gridDim.x >> 1;
+    const uint32_t tiles_m = p.m / kTileMN, tiles_n = p.n / kTileMN;
+    const uint32_t n_tiles = tiles_m * tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kNvStages; s++) {
+            mbar_init(&sh->full[s], 1);
+            mbar_init(&sh->empty[s], 1);
+            mbar_init(&sh->sf_ready[s], kNvCopyThreads);
+        }
+        mbar_init(&sh->tmem_full, 1);
+        mbar_init(&sh->tmem_empty, 8);
+        mbar_fence_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+        tma_prefetch_desc(&tmap_sfa);
+        tma_prefetch_desc(&tmap_sfb);
+    }
+    if (warp == 1)
+        tmem_alloc<2>(&sh->tmem_base, 512);
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync();
+    tc_fence_after_sync();
+    const uint32_t tmem = sh->tmem_base;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters) {
+                uint32_t mb, nb;
+                tile_coords(tile, tiles_m, tiles_n, mb, nb);
+                const int32_t row_a = (int32_t)(mb * kTileMN + rank * 128);
+                const int32_t row_b = (int32_t)(nb * kTileMN + rank * 128);
+                for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
+                    const uint32_t s = it % kNvStages, round = it / kNvStages;
+                    if (round > 0 && !mbar_wait(&sh->empty[s], (round - 1) & 1)) {
+                        atomicCAS(p.status, 0u, 0x211u);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t *st = smem + (size_t)s * kNvStageBytes;
+                    if (rank == 0)
+                        mbar_expect_tx(&sh->full[s], 2 * kNvStageBytes);
+                    // scale factors first: they still have to be copied on to tensor memory
+                    tma_load_pair(st + kStageBytes, &tmap_sfa, 0, (int32_t)((((mb * 2 + rank) * p.k_blocks) + kb) * 4),
+                                  &sh->full[s]);
+                    tma_load_pair(st + kStageBytes + kSfaStageBytes, &tmap_sfb, 0, (int32_t)(((nb * p.k_blocks) + kb) * 8),
+                                  &sh->full[s]);
+                    const int32_t x = (int32_t)(kb * kRowBytesK);
+                    tma_load_pair(st, &tmap_a, x, row_a, &sh->full[s]);
+                    tma_load_pair(st + kHalfTileBytes, &tmap_b, x, row_b, &sh->full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader CTA) ----------------
+        if (rank == 0 && lane == 0) {
+            const uint32_t idesc = make_idesc_block_scaled(256, 256, kFmtE2M1, kFmtE2M1, /*ue4m3*/ 0, 0, 0);
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters, tcount++) {
+                if (tcount > 0 && !mbar_wait(&sh->tmem_empty, (tcount - 1) & 1)) {
+                    atomicCAS(p.status, 0u, 0x212u);
+                    break;
+                }
+                tc_fence_after_sync();
+                for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
+                    const uint32_t s = it % kNvStages, round = it / kNvStages;
+                    // sf_ready implies full: the copy threads waited for the stage before copying
+                    if (!mbar_wait(&sh->sf_ready[s], round & 1)) {
+                        atomicCAS(p.status, 0u, 0x213u);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t base = smem_u32(smem + (size_t)s * kNvStageBytes);
+                    const uint32_t sfa_t = tmem + kNvSfCol + s * kNvSfColsPerStage, sfb_t = sfa_t + 16;
+                    const uint64_t ad = make_smem_desc(base, 16, 1024, kSwizzle128B);
+                    const uint64_t bd = make_smem_desc(base + kHalfTileBytes, 16, 1024, kSwizzle128B);
+#pragma unroll
+                    for (uint32_t kk = 0; kk < 4; kk++)
+                        mma2_nvf4_bs(tmem, ad + 2 * kk, bd + 2 * kk, idesc, sfa_t + 4 * kk, sfb_t + 8 * kk,
+                                     (kb | kk) ? 1u : 0u);
+                    tc_commit_pair(&sh->empty[s], 3);
+                }
+                if (ok)
+                    tc_commit_pair(&sh->tmem_full, 3);
+            }
+        }
+    } else if (warp >= 6) {
+        // ---------------- scale-factor copy threads (leader CTA) ----------------
+        const uint32_t me = (uint32_t)(warp - 6);
+        if (rank == 0 && lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters) {
+                for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
+                    const uint32_t s = it % kNvStages, round = it / kNvStages;
+                    if (!mbar_wait(&sh->full[s], round & 1)) {
+                        atomicCAS(p.status, 0u, 0x215u);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t sf_s = smem_u32(smem + (size_t)s * kNvStageBytes) + kStageBytes;
+                    const uint32_t sf_t = tmem + kNvSfCol + s * kNvSfColsPerStage;
+                    // twelve 512-byte blocks per stage: 4 of A scales (4 columns each), then 8 of B scales
+                    for (uint32_t blk = me; blk < 12; blk += kNvCopyThreads)
+                        tmem_cp_32x128b_warpx4<2>(sf_t + 4 * blk, make_smem_desc(sf_s + blk * 512, 16, 128, kSwizzleNone));
+                    // arrives on sf_ready[s] (this CTA) when the copies above have completed in both CTAs
+                    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                                     smem_u32(&sh->sf_ready[s]))
+                                 : "memory");
+                }
+            }
+        }
+    } else {
+        // ---------------- epilogue warps ----------------
+        const uint32_t q = (uint32_t)(warp & 3);
+        uint32_t tcount = 0;
+        for (uint32_t tile = cluster_id; tile < n_tiles; tile += n_clusters, tcount++) {
+            uint32_t mb, nb;
+            tile_coords(tile, tiles_m, tiles_n, mb, nb);
+            if (!__all_sync(0xffffffffu, mbar_wait(&sh->tmem_full, tcount & 1) ? 1 : 0)) {
+                if (lane == 0)
+                    atomicCAS(p.status, 0u, 0x214u);
+                break;
+            }
+            tc_fence_after_sync();
+            const size_t row = (size_t)mb * kTileMN + rank * 128 + q * 32 + lane;
+            __nv_bfloat16 *crow = p.c + row * p.n + (size_t)nb * kTileMN;
+            const uint32_t taddr = tmem + ((q * 32) << 16);
+#pragma unroll 2
+            for (uint32_t c = 0; c < kTileMN / 32; c++) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(taddr + c * 32, r);
+                tmem_ld_wait();
+                uint32_t w[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * i]) * p.alpha,
+                                                             __uint_as_float(r[2 * i + 1]) * p.alpha);
+                    w[i] = *reinterpret_cast<uint32_t *>(&v);
+                }
+                uint4 *dst = reinterpret_cast<uint4 *>(crow + c * 32);
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                    dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive_cluster(&sh->tmem_empty, 0);
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync();
+    if (warp == 1)
+        tmem_dealloc<2>(tmem, 512);
+}
+
 // ---- host side -----------------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -281,6 +524,30 @@ static int make_operand_map(CUtensorMap *map, const void *base, uint64_t rows, u
     return CLPK_OK;
 }
 
+
+// Packed scale factors: rows of 512 bytes (128 x u32); a box is `rows_per_box` consecutive rows.
+static int make_scale_map(CUtensorMap *map, const void *base, uint64_t n_rows, uint32_t rows_per_box)
+{
+    EncodeTiledFn enc;
+    int rc = get_encode_fn(&enc);
+    if (rc != CLPK_OK)
+        return rc;
+    const cuuint64_t dims[2] = {128, n_rows};
+    const cuuint64_t strides[1] = {512};
+    const cuuint32_t box[2] = {128, rows_per_box};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled (scales) failed with CUresult %d", (int)r);
+        return CLPK_ERR_CUDA;
+    }
+    return CLPK_OK;
+}
+
+constexpr size_t kNvGemmSmemBytes = (size_t)kNvStages * kNvStageBytes + sizeof(NvGemmSmem) + 1024;
+
 constexpr size_t kGemmSmemBytes = (size_t)kGemmStages * kStageBytes + sizeof(GemmSmem) + 1024;
 
 template <int DT>
@@ -319,6 +586,7 @@ int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
     CLPK_REQUIRE(a->m % 256 == 0 && a->n % 256 == 0 && a->m > 0 && a->n > 0,
                  "M and N must be positive multiples of 256 (got %u, %u)", a->m, a->n);
     CLPK_REQUIRE(a->k % 128 == 0 && a->k > 0, "K must be a positive multiple of 128 (got %u)", a->k);
+    CLPK_REQUIRE(a->dtype != CLPK_DT_NVF4 || a->k % 256 == 0, "NVFP4 needs K to be a multiple of 256 (got %u)", a->k);
     CLPK_REQUIRE(((uintptr_t)a->d_a % 16) == 0 && ((uintptr_t)a->d_b % 16) == 0 && ((uintptr_t)a->d_c % 16) == 0,
                  "operands must be 16-byte aligned");
     uint32_t elem_bits;
@@ -326,6 +594,7 @@ int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
     case CLPK_DT_BF16:
     case CLPK_DT_F16:  elem_bits = 16; break;
     case CLPK_DT_E4M3: elem_bits = 8; break;
+    case CLPK_DT_NVF4: elem_bits = 4; break;
     default:
         set_error("clpk_gemm: dtype %d is not available in this build", a->dtype);
         return CLPK_ERR_UNSUPPORTED;
@@ -351,6 +620,30 @@ int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
     p.c = static_cast<__nv_bfloat16 *>(a->d_c);
     p.alpha = a->alpha;
     p.status = a->d_status;
+
+
+    if (a->dtype == CLPK_DT_NVF4) {
+        const size_t sfa_bytes = (size_t)a->m * (a->k / 16), sfb_bytes = (size_t)a->n * (a->k / 16);
+        CLPK_REQUIRE(a->d_sfa && a->d_sfb, "NVFP4 needs d_sfa and d_sfb");
+        CLPK_REQUIRE(a->d_workspace && a->workspace_bytes >= sfa_bytes + sfb_bytes && ((uintptr_t)a->d_workspace % 16) == 0,
+                     "NVFP4 needs a 16-byte aligned workspace of clpk_gemm_workspace_bytes() bytes");
+        uint8_t *wsa = static_cast<uint8_t *>(a->d_workspace), *wsb = wsa + sfa_bytes;
+        const int pgrid = num_sms() * 8;
+        pack_scales_kernel<<<pgrid, 256, 0, s>>>(wsa, static_cast<const uint8_t *>(a->d_sfa), a->m, a->k, 0);
+        pack_scales_kernel<<<pgrid, 256, 0, s>>>(wsb, static_cast<const uint8_t *>(a->d_sfb), a->n, a->k, 1);
+        CLPK_LAUNCH_CHECK("pack_scales");
+        CUtensorMap tsa, tsb;
+        rc = make_scale_map(&tsa, wsa, sfa_bytes / 512, 4);
+        if (rc != CLPK_OK)
+            return rc;
+        rc = make_scale_map(&tsb, wsb, sfb_bytes / 512, 8);
+        if (rc != CLPK_OK)
+            return rc;
+        CLPK_CUDA(cudaFuncSetAttribute(gemm_nvf4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kNvGemmSmemBytes));
+        gemm_nvf4_kernel<<<(num_sms() / 2) * 2, kNvGemmThreads, kNvGemmSmemBytes, s>>>(ta, tb, tsa, tsb, p);
+        CLPK_LAUNCH_CHECK("gemm_nvf4");
+        return CLPK_OK;
+    }
     switch (a->dtype) {
     case CLPK_DT_BF16: return launch_gemm<CLPK_DT_BF16>(ta, tb, p, s);
     case CLPK_DT_F16:  return launch_gemm<CLPK_DT_F16>(ta, tb, p, s);

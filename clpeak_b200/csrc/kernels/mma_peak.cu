@@ -202,6 +202,165 @@ __global__ void __launch_bounds__(128) mma_peak_kernel(PeakParams p)
         tmem_dealloc<1>(tmem, kCols);
 }
 
+
+// ---------------------------------------------------------------------------------
+// 2:4 structured-sparse kinds (tcgen05.mma.sp)
+// ---------------------------------------------------------------------------------
+//
+// A arrives compressed: [128][K/2] elements = 32 bytes per row, staged exactly like
+// a dense A tile.  B is dense over the logical K = 64 (8-bit kinds): 64 bytes per
+// row, staged in the 128-byte-swizzle K-major layout (row pitch 128 B, 8-row atoms
+// of 1024 B, 16-byte chunk c of row r stored at chunk c ^ (r % 8)); the instruction
+// reads the first 64 bytes of each row.  The metadata -- one 4-bit selector per
+// group of four logical K positions, low 2 bits = position of the first kept
+// element, high 2 bits = position of the second -- lives in tensor memory:
+// row r in lane r, its K/8 selector bytes in K order in consecutive columns.
+
+constexpr int kSpBRowBytes = 64;
+constexpr int kSpBPitch = 128;
+constexpr int kSpBTileBytes = kTileN * kSpBPitch;   // 32 KiB
+
+__device__ __forceinline__ void stage_tile_sw128(uint8_t *smem_tile, const uint8_t *g, int rows, int row_bytes)
+{
+    const int chunks_per_row = row_bytes / 16;
+    for (int i = threadIdx.x; i < rows * chunks_per_row; i += blockDim.x) {
+        const int r = i / chunks_per_row, c = i % chunks_per_row;
+        const uint4 v = *reinterpret_cast<const uint4 *>(g + (size_t)r * row_bytes + c * 16);
+        *reinterpret_cast<uint4 *>(smem_tile + r * kSpBPitch + ((c ^ (r & 7)) * 16)) = v;
+    }
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(128) mma_peak_sparse_kernel(PeakParams p, uint32_t meta_cols)
+{
+    constexpr uint32_t kCols = 512;
+    constexpr uint32_t kMetaCol = 256, kSpSfaCol = 260, kSpSfbCol = 264;
+    constexpr bool kScaled = (KIND == CLPK_MMA_MXF4_SP || KIND == CLPK_MMA_NVF4_SP);
+    constexpr int kSfPerRow = (KIND == CLPK_MMA_NVF4_SP) ? 4 : 2;
+
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t *sA = smem;                                 // 4 KiB, core-matrix layout
+    uint8_t *sB = smem + 4096;                          // 32 KiB, 1024-aligned
+    uint64_t *bar = reinterpret_cast<uint64_t *>(smem + 4096 + kSpBTileBytes);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    stage_tile(sA, p.a, kTileM);
+    stage_tile_sw128(sB, p.b, kTileN, kSpBRowBytes);
+    if (threadIdx.x == 0) {
+        mbar_init(bar, 1);
+        mbar_fence_init();
+    }
+    fence_proxy_async_smem();
+    if (warp == 0) {
+        __syncwarp();
+        tmem_alloc<1>(tmem_slot, kCols);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    // metadata image: word (row, c) -> lane row, column kMetaCol + c
+    {
+        const uint32_t *meta = reinterpret_cast<const uint32_t *>(p.meta);
+        const int row = warp * 32 + lane;
+        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+        for (uint32_t c = 0; c < meta_cols; c++)
+            tmem_st_32x32b_x1(lane_base + kMetaCol + c, meta[row * meta_cols + c]);
+        if constexpr (kScaled) {
+            // scale factors as in the dense block-scaled kinds: row r -> lane r % 32, column r / 32
+            for (int c = 0; c < 4; c++) {
+                uint32_t w = 0;
+                for (int k = 0; k < kSfPerRow; k++)
+                    w |= (uint32_t)p.sfa[(c * 32 + lane) * kSfPerRow + k] << (8 * k);
+                tmem_st_32x32b_x1(lane_base + kSpSfaCol + c, w);
+            }
+            for (int c = 0; c < 8; c++) {
+                uint32_t w = 0;
+                for (int k = 0; k < kSfPerRow; k++)
+                    w |= (uint32_t)p.sfb[(c * 32 + lane) * kSfPerRow + k] << (8 * k);
+                tmem_st_32x32b_x1(lane_base + kSpSfbCol + c, w);
+            }
+        }
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncthreads();
+        tc_fence_after_sync();
+    }
+
+    if (threadIdx.x == 0) {
+        const uint64_t ad = make_smem_desc(smem_u32(sA), 128, 256, kSwizzleNone);
+        const uint64_t bd = make_smem_desc(smem_u32(sB), 16, 1024, kSwizzle128B);
+        uint32_t idesc;
+        if constexpr (KIND == CLPK_MMA_I8_SP)
+            idesc = make_idesc(kTileM, kTileN, kFmtS8, kFmtS8, kAccS32, true);
+        else if constexpr (KIND == CLPK_MMA_E4M3_SP)
+            idesc = make_idesc(kTileM, kTileN, kFmtE4M3, kFmtE4M3, kAccF32, true);
+        else
+            idesc = make_idesc_block_scaled(kTileM, kTileN, kFmtE2M1, kFmtE2M1, KIND == CLPK_MMA_MXF4_SP ? 1u : 0u, 0, 0, true);
+        for (uint32_t i = 0; i < p.n_mma; i++) {
+            if constexpr (KIND == CLPK_MMA_I8_SP)
+                mma_i8_sp(tmem, ad, bd, idesc, tmem + kMetaCol, i ? 1u : 0u);
+            else if constexpr (KIND == CLPK_MMA_E4M3_SP)
+                mma_f8f6f4_sp(tmem, ad, bd, idesc, tmem + kMetaCol, i ? 1u : 0u);
+            else if constexpr (KIND == CLPK_MMA_MXF4_SP)
+                mma_mxf4_sp_bs(tmem, ad, bd, idesc, tmem + kMetaCol, tmem + kSpSfaCol, tmem + kSpSfbCol, i ? 1u : 0u);
+            else
+                mma_nvf4_sp_bs(tmem, ad, bd, idesc, tmem + kMetaCol, tmem + kSpSfaCol, tmem + kSpSfbCol, i ? 1u : 0u);
+        }
+        tc_commit(bar);
+    }
+    __syncwarp();
+
+    const int done = __syncthreads_and(mbar_wait(bar, 0) ? 1 : 0);
+    tc_fence_after_sync();
+    if (!done && threadIdx.x == 0)
+        atomicCAS(p.status, 0u, 0x100u + (uint32_t)KIND);
+
+    uint32_t x = 0;
+    if (done) {
+        const int row = warp * 32 + lane;
+        uint32_t *out_row = (blockIdx.x < p.n_out_tiles) ? p.out + ((size_t)blockIdx.x * kTileM + row) * kTileN : nullptr;
+        for (int c = 0; c < kTileN / 32; c++) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(tmem + ((uint32_t)(warp * 32) << 16) + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; i++)
+                x ^= r[i];
+            if (out_row) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 4)
+                    *reinterpret_cast<uint4 *>(out_row + c * 32 + i) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
+            }
+        }
+    }
+    __shared__ uint32_t wx[4];
+    for (int o = 16; o > 0; o >>= 1)
+        x ^= __shfl_xor_sync(0xffffffffu, x, o);
+    if (lane == 0)
+        wx[warp] = x;
+    __syncthreads();
+    if (done && p.checksum && threadIdx.x == 0)
+        p.checksum[blockIdx.x] = wx[0] ^ wx[1] ^ wx[2] ^ wx[3];
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0)
+        tmem_dealloc<1>(tmem, kCols);
+}
+
+template <int KIND>
+static int launch_peak_sparse(const PeakParams &p, uint32_t grid, uint32_t meta_cols, cudaStream_t s)
+{
+    const size_t smem = (size_t)(smem_optin_bytes() * 3 / 5);      // one CTA per SM (512 TMEM columns)
+    CLPK_CUDA(cudaFuncSetAttribute(mma_peak_sparse_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    mma_peak_sparse_kernel<KIND><<<grid, 128, smem, s>>>(p, meta_cols);
+    CLPK_LAUNCH_CHECK("mma_peak_sparse");
+    return CLPK_OK;
+}
+
 struct KindInfo {
     int k;              // logical K per instruction
     bool scaled;
@@ -275,8 +434,7 @@ int clpk_mma_peak(const clpk_mma_peak_args_t *a, void *stream)
     if (ki.scaled)
         CLPK_REQUIRE(a->d_sfa && a->d_sfb, "block-scaled kinds need d_sfa and d_sfb");
     if (ki.sparse) {
-        set_error("sparse kind %d is not available in this build", a->kind);
-        return CLPK_ERR_UNSUPPORTED;
+        CLPK_REQUIRE(a->d_meta && ((uintptr_t)a->d_meta % 4) == 0, "sparse kinds need d_meta (4-byte aligned)");
     }
     cudaStream_t s = as_stream(stream);
     CLPK_CUDA(cudaMemsetAsync(a->d_status, 0, sizeof(uint32_t), s));
@@ -292,6 +450,10 @@ int clpk_mma_peak(const clpk_mma_peak_args_t *a, void *stream)
     p.checksum = a->d_checksum;
     p.status = a->d_status;
     switch (a->kind) {
+    case CLPK_MMA_E4M3_SP: return launch_peak_sparse<CLPK_MMA_E4M3_SP>(p, a->grid, (uint32_t)ki.k / 32, s);
+    case CLPK_MMA_I8_SP:   return launch_peak_sparse<CLPK_MMA_I8_SP>(p, a->grid, (uint32_t)ki.k / 32, s);
+    case CLPK_MMA_MXF4_SP: return launch_peak_sparse<CLPK_MMA_MXF4_SP>(p, a->grid, 2, s);
+    case CLPK_MMA_NVF4_SP: return launch_peak_sparse<CLPK_MMA_NVF4_SP>(p, a->grid, 2, s);
     case CLPK_MMA_F16:  return launch_peak<CLPK_MMA_F16>(p, a->grid, s);
     case CLPK_MMA_BF16: return launch_peak<CLPK_MMA_BF16>(p, a->grid, s);
     case CLPK_MMA_E4M3: return launch_peak<CLPK_MMA_E4M3>(p, a->grid, s);

@@ -114,6 +114,8 @@ CLPK_API int clpk_fill_i8(int8_t *d_dst, uint64_t n, uint64_t seed, void *stream
 #define CLPK_DT_I8    5
 #define CLPK_DT_MXF4  6   /* e2m1 pairs + one ue8m0 scale per 32 elements            */
 #define CLPK_DT_NVF4  7   /* e2m1 pairs + one ue4m3 scale per 16 elements + fp32 scale */
+#define CLPK_DT_MXF4_B64 8   /* as MXF4 with one ue8m0 scale per 64: the dense B operand of MXF4_SP */
+#define CLPK_DT_NVF4_B32 9   /* as NVF4 with one ue4m3 scale per 32: the dense B operand of NVF4_SP */
 
 /* Round-to-nearest-even conversion of n floats to a plain (unscaled) format:
  * F16, BF16, E4M3 / E5M2 (saturating to the largest finite value), I8
@@ -127,8 +129,9 @@ CLPK_API int clpk_absmax_f32(float *d_absmax, const float *d_src, uint64_t n, vo
  * (cols a multiple of 64; blocks run along a row).
  *   d_packed : rows*cols/2 bytes, element 2j in the low nibble of byte j
  *   d_scales : one byte per block, row-major [rows][cols/block]
- *              (block = 32, ue8m0 for MXF4; block = 16, ue4m3 for NVF4)
- *   tensor_scale : NVF4 only; values are divided by it before the block scale
+ *              (block = 32, ue8m0 for MXF4; block = 16, ue4m3 for NVF4; the _B64 / _B32
+ *              variants use the doubled block of the sparse kinds' dense operand)
+ *   tensor_scale : NVF4 kinds only; values are divided by it before the block scale
  *              is chosen.  Pass absmax/(6*448) for the usual recipe, 1.0f for MXF4. */
 CLPK_API int clpk_quantize_fp4(uint8_t *d_packed, uint8_t *d_scales, const float *d_src,
                                uint64_t rows, uint64_t cols, int dtype, float tensor_scale,
@@ -229,8 +232,20 @@ CLPK_API int clpk_launch_latency(uint32_t iters, uint32_t warmup, double *mean_u
  *   I8     32   int8               s32
  *   MXF4   64   e2m1 x2 per byte   f32   + ue8m0 scale per 32 (d_sfa [128][2], d_sfb [256][2])
  *   NVF4   64   e2m1 x2 per byte   f32   + ue4m3 scale per 16 (d_sfa [128][4], d_sfb [256][4])
- *   *_SP   2:4 sparse A (d_a = compressed tile [128][K/2], d_meta = 2-bit positions);
- *          declared for the registry, not yet implemented: CLPK_ERR_UNSUPPORTED
+ *   E4M3_SP / I8_SP   K = 64 logical, 2:4 sparse A: d_a is the compressed tile
+ *          [128][32] (the two kept elements of every group of four, in K order),
+ *          d_b the dense tile [256][64], d_meta [128][8] bytes: one byte per eight
+ *          logical K positions, low nibble = first group, each nibble =
+ *          position of 1st kept element | position of 2nd kept element << 2.
+ *   MXF4_SP / NVF4_SP K = 128 logical.  4-bit operands are pruned in pairs: of every
+ *          four pairs (eight positions) along K two are kept.  d_a is the compressed
+ *          tile [128][64 e2m1] = 32 bytes per row, d_b the dense tile [256][128 e2m1],
+ *          d_meta [128][8] bytes: one nibble per eight logical positions (low nibble
+ *          first) = index of 1st kept pair | index of 2nd kept pair << 2.  Scale
+ *          factors: d_sfa [128][n], d_sfb [256][n] with n = 2 (MXF4_SP, ue8m0) or 4
+ *          (NVF4_SP, ue4m3); factor j covers logical K positions [j*128/n, (j+1)*128/n),
+ *          i.e. 32 / 16 compressed elements of A (CLPK_DT_MXF4 / NVF4 on the compressed
+ *          tile) and 64 / 32 elements of B (CLPK_DT_MXF4_B64 / NVF4_B32).
  * d_out receives the first `n_out_tiles` CTAs' accumulator tiles, row-major
  * [128][256] 32-bit words; d_checksum[grid] the XOR of every CTA's accumulator
  * bits; *d_status is set non-zero if a device-side wait timed out. */

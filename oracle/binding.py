@@ -55,6 +55,8 @@ _API = {
     "orc_chase": ([_vp, _u32, _u64, C.POINTER(_u32), C.POINTER(_u32)], None),
     "orc_mma_tile": ([_i, _vp, _vp, _vp, _vp, _vp, _vp], None),
     "orc_mma_tile_i8": ([_vp, _vp, _u32, _vp], None),
+    "orc_prune_pairs_2to4": ([_vp, _vp, _vp, _vp, _u64, _u64], None),
+    "orc_mma_tile_sp": ([_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp], None),
     "orc_gemm_element": ([_i, _vp, _vp, _vp, _vp, _u64, _u64, _u64, C.POINTER(_d)], _d),
     "orc_pick_iters": ([_d, C.c_uint, C.c_uint, C.c_uint], C.c_uint),
 }
@@ -110,7 +112,7 @@ def convert_f32(src: np.ndarray, dtype: int) -> np.ndarray:
 def quantize_fp4(src: np.ndarray, dtype: int, tensor_scale: float = 1.0):
     src = np.ascontiguousarray(src, dtype=np.float32)
     rows, cols = src.shape
-    blk = 32 if dtype == 6 else 16
+    blk = {6: 32, 7: 16, 8: 64, 9: 32}[dtype]
     packed = np.empty((rows, cols // 2), dtype=np.uint8)
     scales = np.empty((rows, cols // blk), dtype=np.uint8)
     lib().orc_quantize_fp4(ptr(packed), ptr(scales), ptr(src), rows, cols, dtype, tensor_scale)
@@ -176,3 +178,23 @@ def gemm_element(dtype: int, a: np.ndarray, b: np.ndarray, k: int, i: int, j: in
     v = lib().orc_gemm_element(dtype, ptr(a), ptr(b), ptr(sfa) if sfa is not None else None,
                                ptr(sfb) if sfb is not None else None, k, i, j, C.byref(s))
     return float(v), float(s.value)
+
+
+def prune_2to4(dense: np.ndarray, pairs: bool = False):
+    """(compressed, meta bytes, pruned dense) of a [rows][k] float tile; pairs=True for 4-bit operands."""
+    dense = np.ascontiguousarray(dense, dtype=np.float32)
+    rows, k = dense.shape
+    comp = np.zeros((rows, k // 2), dtype=np.float32)
+    meta = np.zeros((rows, k // (16 if pairs else 8)), dtype=np.uint8)
+    pruned = np.zeros_like(dense)
+    fn = lib().orc_prune_pairs_2to4 if pairs else lib().orc_prune_2to4
+    fn(ptr(comp), ptr(meta), ptr(pruned), ptr(dense), rows, k)
+    return comp, meta, pruned
+
+
+def mma_tile_sp(kind: int, a_comp: np.ndarray, meta: np.ndarray, b: np.ndarray, sfa=None, sfb=None):
+    p = np.empty((128, 256), dtype=np.float64)
+    s = np.empty((128, 256), dtype=np.float64)
+    lib().orc_mma_tile_sp(kind, ptr(a_comp), ptr(meta), ptr(b), ptr(sfa) if sfa is not None else None,
+                          ptr(sfb) if sfb is not None else None, ptr(p), ptr(s))
+    return p, s

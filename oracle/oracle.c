@@ -17,8 +17,13 @@
 #pragma STDC FP_CONTRACT OFF
 
 /* dtype / kind numbering mirrors include/clpeak_b200_kernels.h */
-enum { DT_F32 = 0, DT_F16 = 1, DT_BF16 = 2, DT_E4M3 = 3, DT_E5M2 = 4, DT_I8 = 5, DT_MXF4 = 6, DT_NVF4 = 7 };
-enum { MMA_F16 = 0, MMA_BF16 = 1, MMA_E4M3 = 2, MMA_E5M2 = 3, MMA_I8 = 4, MMA_MXF4 = 5, MMA_NVF4 = 6 };
+enum { DT_F32 = 0, DT_F16 = 1, DT_BF16 = 2, DT_E4M3 = 3, DT_E5M2 = 4, DT_I8 = 5, DT_MXF4 = 6, DT_NVF4 = 7,
+       DT_MXF4_B64 = 8, DT_NVF4_B32 = 9 };
+
+static int fp4_block(int dtype) { return dtype == DT_MXF4 ? 32 : dtype == DT_NVF4 ? 16 : dtype == DT_MXF4_B64 ? 64 : 32; }
+static int fp4_is_mx(int dtype) { return dtype == DT_MXF4 || dtype == DT_MXF4_B64; }
+enum { MMA_F16 = 0, MMA_BF16 = 1, MMA_E4M3 = 2, MMA_E5M2 = 3, MMA_I8 = 4, MMA_MXF4 = 5, MMA_NVF4 = 6,
+       MMA_E4M3_SP = 7, MMA_MXF4_SP = 8, MMA_NVF4_SP = 9, MMA_I8_SP = 10 };
 
 static uint32_t f2u(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
 static float u2f(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
@@ -296,20 +301,20 @@ float orc_absmax_f32(const float *src, uint64_t n)
 void orc_quantize_fp4(uint8_t *packed, uint8_t *scales, const float *src, uint64_t rows, uint64_t cols,
                       int dtype, float tensor_scale)
 {
-    const int blk = (dtype == DT_MXF4) ? 32 : 16;
+    const int blk = fp4_block(dtype);
     const uint64_t nblk = rows * cols / (uint64_t)blk;
     for (uint64_t b = 0; b < nblk; b++) {
-        float v[32];
+        float v[64];
         float amax = 0.0f;
         for (int i = 0; i < blk; i++) {
             float x = src[b * blk + i];
-            v[i] = (dtype == DT_NVF4) ? x / tensor_scale : x;
+            v[i] = fp4_is_mx(dtype) ? x : x / tensor_scale;
             float a = fabsf(v[i]);
             if (a > amax) amax = a;
         }
         uint8_t sb;
         float sd;
-        if (dtype == DT_MXF4) { sb = orc_ue8m0_for_absmax(amax); sd = orc_ue8m0_to_f32(sb); }
+        if (fp4_is_mx(dtype)) { sb = orc_ue8m0_for_absmax(amax); sd = orc_ue8m0_to_f32(sb); }
         else { sb = orc_f32_to_e4m3(amax / 6.0f); sd = orc_e4m3_to_f32(sb); }
         scales[b] = sb;
         for (int i = 0; i < blk; i += 2) {
@@ -322,9 +327,9 @@ void orc_quantize_fp4(uint8_t *packed, uint8_t *scales, const float *src, uint64
 
 static double fp4_scale(const uint8_t *scales, uint64_t cols, int dtype, uint64_t row, uint64_t col)
 {
-    const int blk = (dtype == DT_MXF4) ? 32 : 16;
+    const int blk = fp4_block(dtype);
     uint8_t sb = scales[row * (cols / blk) + col / blk];
-    return dtype == DT_MXF4 ? (double)orc_ue8m0_to_f32(sb) : (double)orc_e4m3_to_f32(sb);
+    return fp4_is_mx(dtype) ? (double)orc_ue8m0_to_f32(sb) : (double)orc_e4m3_to_f32(sb);
 }
 
 double orc_fp4_element(const uint8_t *packed, const uint8_t *scales, uint64_t cols, int dtype,
@@ -566,6 +571,106 @@ void orc_mma_tile_i8(const int8_t *a, const int8_t *b, uint32_t n_mma, int32_t *
             for (int k = 0; k < 32; k++) p += (int32_t)a[i * 32 + k] * (int32_t)b[j * 32 + k];
             out[i * 256 + j] = (int32_t)((uint32_t)p * n_mma);       /* two's-complement wrap */
         }
+}
+
+
+/* ------------------------------------------------------------------------- */
+/* 2:4 sparse tiles                                                            */
+
+/* 4-bit operands are pruned in pairs (one byte): of every four pairs along K the
+ * two with the largest |x0|+|x1| are kept (ties: lower index).  compressed is
+ * [rows][k/2] in K order, meta one nibble per group of eight logical positions
+ * (pair index of the first kept pair | second << 2), two nibbles per byte. */
+void orc_prune_pairs_2to4(float *compressed, uint8_t *meta, float *pruned, const float *dense, uint64_t rows, uint64_t k)
+{
+    for (uint64_t r = 0; r < rows; r++) {
+        for (uint64_t g = 0; g < k / 8; g++) {
+            const float *x = dense + r * k + g * 8;
+            float mag[4];
+            for (int p = 0; p < 4; p++) mag[p] = fabsf(x[2 * p]) + fabsf(x[2 * p + 1]);
+            int first = 0;
+            for (int p = 1; p < 4; p++) if (mag[p] > mag[first]) first = p;
+            int second = -1;
+            for (int p = 0; p < 4; p++) {
+                if (p == first) continue;
+                if (second < 0 || mag[p] > mag[second]) second = p;
+            }
+            int p0 = first < second ? first : second, p1 = first < second ? second : first;
+            float *c = compressed + r * (k / 2) + g * 4;
+            c[0] = x[2 * p0]; c[1] = x[2 * p0 + 1]; c[2] = x[2 * p1]; c[3] = x[2 * p1 + 1];
+            uint8_t nib = (uint8_t)(p0 | (p1 << 2));
+            uint8_t *mb = meta + r * (k / 16) + g / 2;
+            if (g & 1) *mb = (uint8_t)((*mb & 0x0F) | (nib << 4));
+            else *mb = (uint8_t)((*mb & 0xF0) | nib);
+            if (pruned)
+                for (int i = 0; i < 8; i++)
+                    pruned[r * k + g * 8 + i] = (i / 2 == p0 || i / 2 == p1) ? x[i] : 0.0f;
+        }
+    }
+}
+
+static int sp_logical_k(int kind) { return (kind == MMA_MXF4_SP || kind == MMA_NVF4_SP) ? 128 : 64; }
+
+/* Exact product tile of one sparse instruction: A is given compressed ([128][K/2]
+ * elements in the kernel's encoding) with its selector nibbles; B is dense
+ * [256][K].  Block-scaled kinds: sfa/sfb hold 2 (MXF4) or 4 (NVF4) factors per
+ * row, factor j covering logical K positions [j*K/n, (j+1)*K/n). */
+void orc_mma_tile_sp(int kind, const void *a_comp, const uint8_t *meta, const void *b, const uint8_t *sfa,
+                     const uint8_t *sfb, double *p_out, double *s_out)
+{
+    const int K = sp_logical_k(kind);
+    const int fp4 = (K == 128);
+    const int nsf = kind == MMA_NVF4_SP ? 4 : 2;
+    double *da = (double *)calloc((size_t)128 * K, sizeof(double));
+    double *db = (double *)malloc(sizeof(double) * 256 * (size_t)K);
+    for (int r = 0; r < 128; r++) {
+        for (int g = 0; g < 16; g++) {
+            const uint8_t byte = meta[r * 8 + g / 2];
+            const int nib = (g & 1) ? (byte >> 4) : (byte & 0xF);
+            const int s0 = nib & 3, s1 = nib >> 2;
+            if (!fp4) {
+                double v[2];
+                for (int e = 0; e < 2; e++) {
+                    const int ci = r * 32 + 2 * g + e;
+                    v[e] = kind == MMA_I8_SP ? (double)((const int8_t *)a_comp)[ci]
+                                             : (double)orc_e4m3_to_f32(((const uint8_t *)a_comp)[ci]);
+                }
+                da[r * K + 4 * g + s0] = v[0];
+                da[r * K + 4 * g + s1] = v[1];
+            } else {
+                for (int e = 0; e < 4; e++) {
+                    const int ci = 4 * g + e;                               /* compressed element index in the row */
+                    const uint8_t cb = ((const uint8_t *)a_comp)[r * 32 + ci / 2];
+                    const double val = orc_e2m1_to_f32((ci & 1) ? (cb >> 4) : (cb & 0xF));
+                    const int pair = e < 2 ? s0 : s1;
+                    const int kpos = 8 * g + 2 * pair + (e & 1);
+                    const uint8_t sb = sfa[r * nsf + kpos / (K / nsf)];
+                    const double sc = kind == MMA_MXF4_SP ? (double)orc_ue8m0_to_f32(sb) : (double)orc_e4m3_to_f32(sb);
+                    da[r * K + kpos] = val * sc;
+                }
+            }
+        }
+    }
+    for (int r = 0; r < 256; r++)
+        for (int k = 0; k < K; k++) {
+            if (!fp4) {
+                db[r * K + k] = kind == MMA_I8_SP ? (double)((const int8_t *)b)[r * K + k]
+                                                  : (double)orc_e4m3_to_f32(((const uint8_t *)b)[r * K + k]);
+            } else {
+                const uint8_t bb = ((const uint8_t *)b)[(r * K + k) / 2];
+                const uint8_t sb = sfb[r * nsf + k / (K / nsf)];
+                const double sc = kind == MMA_MXF4_SP ? (double)orc_ue8m0_to_f32(sb) : (double)orc_e4m3_to_f32(sb);
+                db[r * K + k] = (double)orc_e2m1_to_f32((k & 1) ? (bb >> 4) : (bb & 0xF)) * sc;
+            }
+        }
+    for (int i = 0; i < 128; i++)
+        for (int j = 0; j < 256; j++) {
+            double p = 0.0, s = 0.0;
+            for (int k = 0; k < K; k++) { double t = da[i * K + k] * db[j * K + k]; p += t; s += fabs(t); }
+            p_out[i * 256 + j] = p;
+            if (s_out) s_out[i * 256 + j] = s;
+        }
+    free(da); free(db);
 }
 
 double orc_gemm_element(int dtype, const void *a, const void *b, const uint8_t *sfa, const uint8_t *sfb,

@@ -98,6 +98,14 @@ void     orc_mma_tile(int kind, const void *a, const void *b, const uint8_t *sfa
 /* int8: n_mma accumulations, wrapped to int32 exactly like the hardware adder. */
 void     orc_mma_tile_i8(const int8_t *a, const int8_t *b, uint32_t n_mma, int32_t *out);
 
+/* Pair-granular 2:4 pruning for 4-bit operands and the exact product tile of one
+ * sparse instruction (kinds CLPK_MMA_E4M3_SP / I8_SP: logical K = 64;
+ * MXF4_SP / NVF4_SP: logical K = 128, 2 / 4 scale factors per row). */
+void     orc_prune_pairs_2to4(float *compressed, uint8_t *meta, float *pruned, const float *dense,
+                              uint64_t rows, uint64_t k);
+void     orc_mma_tile_sp(int kind, const void *a_comp, const uint8_t *meta, const void *b, const uint8_t *sfa,
+                         const uint8_t *sfb, double *p_out, double *s_out);
+
 /* One element of C = A * B^T in double from the quantised operands.
  * dtype = CLPK_DT_BF16 / F16 / E4M3 / NVF4 (sfa/sfb used for NVF4). */
 double   orc_gemm_element(int dtype, const void *a, const void *b, const uint8_t *sfa, const uint8_t *sfb,

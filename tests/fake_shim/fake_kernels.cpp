@@ -201,15 +201,16 @@ int clpk_absmax_f32(float *out, const float *src, uint64_t n, void *)
 int clpk_quantize_fp4(uint8_t *packed, uint8_t *scales, const float *src, uint64_t rows, uint64_t cols, int dtype,
                       float ts, void *)
 {
-    const int blk = dtype == CLPK_DT_MXF4 ? 32 : 16;
+    const bool mx = dtype == CLPK_DT_MXF4 || dtype == CLPK_DT_MXF4_B64;
+    const int blk = dtype == CLPK_DT_MXF4 ? 32 : dtype == CLPK_DT_NVF4 ? 16 : dtype == CLPK_DT_MXF4_B64 ? 64 : 32;
     for (uint64_t b = 0; b < rows * cols / blk; ++b) {
-        float v[32], amax = 0;
+        float v[64], amax = 0;
         for (int i = 0; i < blk; ++i) {
-            v[i] = dtype == CLPK_DT_NVF4 ? src[b * blk + i] / ts : src[b * blk + i];
+            v[i] = mx ? src[b * blk + i] : src[b * blk + i] / ts;
             amax = std::max(amax, std::fabs(v[i]));
         }
-        const uint8_t sb = dtype == CLPK_DT_MXF4 ? clpk_ue8m0_for_absmax(amax) : toE4M3(amax / 6.0f);
-        const float sd = dtype == CLPK_DT_MXF4 ? clpk_ue8m0_decode(sb) : clpk_e4m3_decode(sb);
+        const uint8_t sb = mx ? clpk_ue8m0_for_absmax(amax) : toE4M3(amax / 6.0f);
+        const float sd = mx ? clpk_ue8m0_decode(sb) : clpk_e4m3_decode(sb);
         scales[b] = sb;
         for (int i = 0; i < blk; i += 2) {
             const uint8_t lo = sd > 0 ? clpk_e2m1_encode(v[i] / sd) : 0, hi = sd > 0 ? clpk_e2m1_encode(v[i + 1] / sd) : 0;
@@ -319,16 +320,71 @@ int clpk_mma_kind_k(int kind)
     switch (kind) {
     case CLPK_MMA_F16: case CLPK_MMA_BF16: return 16;
     case CLPK_MMA_E4M3: case CLPK_MMA_E5M2: case CLPK_MMA_I8: return 32;
-    case CLPK_MMA_MXF4: case CLPK_MMA_NVF4: return 64;
+    case CLPK_MMA_MXF4: case CLPK_MMA_NVF4: case CLPK_MMA_E4M3_SP: case CLPK_MMA_I8_SP: return 64;
+    case CLPK_MMA_MXF4_SP: case CLPK_MMA_NVF4_SP: return 128;
     default: return 0;
     }
 }
 double clpk_mma_flops_per_instr(int kind) { return 2.0 * 128 * 256 * clpk_mma_kind_k(kind); }
 
+// Sparse kinds on the CPU: expand the compressed A tile through the selector
+// nibbles into a dense [128][K] array of doubles, decode B, multiply.
+static int fake_sparse_peak(const clpk_mma_peak_args_t *a)
+{
+    if (!a->d_meta) return fail(CLPK_ERR_BAD_ARG, "sparse kinds need d_meta");
+    const int K = clpk_mma_kind_k(a->kind);
+    const bool four = K == 128, mx = a->kind == CLPK_MMA_MXF4_SP, integer = a->kind == CLPK_MMA_I8_SP;
+    const int nsf = a->kind == CLPK_MMA_NVF4_SP ? 4 : 2, span = K / nsf;
+    const uint8_t *A = static_cast<const uint8_t *>(a->d_a), *B = static_cast<const uint8_t *>(a->d_b);
+    const uint8_t *M = static_cast<const uint8_t *>(a->d_meta);
+    const uint8_t *sfa = static_cast<const uint8_t *>(a->d_sfa), *sfb = static_cast<const uint8_t *>(a->d_sfb);
+    auto sf = [&](const uint8_t *t, int row, int k) { return (double)(mx ? clpk_ue8m0_decode(t[row * nsf + k / span]) : clpk_e4m3_decode(t[row * nsf + k / span])); };
+    auto nib4 = [](const uint8_t *t, size_t idx) { const uint8_t b = t[idx / 2]; return (uint8_t)((idx & 1) ? b >> 4 : b & 0xF); };
+    std::vector<double> da(128 * (size_t)K, 0.0), db(256 * (size_t)K);
+    const int unit = four ? 2 : 1;                       // elements per selectable slot
+    for (int r = 0; r < 128; ++r)
+        for (int grp = 0; grp < K / (4 * unit); ++grp) {
+            const uint8_t sel = nib4(M + r * 8, grp);
+            const int slot[2] = {sel & 3, sel >> 2};
+            for (int which = 0; which < 2; ++which)
+                for (int e = 0; e < unit; ++e) {
+                    const size_t ci = (size_t)r * (K / 2) + grp * 2 * unit + which * unit + e;
+                    const int k = grp * 4 * unit + slot[which] * unit + e;
+                    double v;
+                    if (four) v = (double)clpk_e2m1_decode(nib4(A, ci)) * sf(sfa, r, k);
+                    else if (integer) v = (double)(int8_t)A[ci];
+                    else v = (double)clpk_e4m3_decode(A[ci]);
+                    da[(size_t)r * K + k] = v;
+                }
+        }
+    for (int r = 0; r < 256; ++r)
+        for (int k = 0; k < K; ++k) {
+            const size_t i = (size_t)r * K + k;
+            db[i] = four ? (double)clpk_e2m1_decode(nib4(B, i)) * sf(sfb, r, k) : integer ? (double)(int8_t)B[i] : (double)clpk_e4m3_decode(B[i]);
+        }
+    std::vector<uint32_t> tile(128 * 256);
+    uint32_t x = 0;
+    for (int i = 0; i < 128; ++i)
+        for (int j = 0; j < 256; ++j) {
+            double p = 0;
+            for (int k = 0; k < K; ++k) p += da[(size_t)i * K + k] * db[(size_t)j * K + k];
+            const uint32_t w = integer ? (uint32_t)(int32_t)p * a->n_mma : clpk_f32_bits((float)(p * a->n_mma));
+            tile[i * 256 + j] = w;
+            x ^= w;
+        }
+    for (uint32_t t = 0; t < a->n_out_tiles; ++t)
+        std::memcpy(static_cast<uint32_t *>(a->d_out) + (size_t)t * 128 * 256, tile.data(), tile.size() * 4);
+    if (a->d_checksum)
+        for (uint32_t c = 0; c < a->grid; ++c) a->d_checksum[c] = x;
+    *a->d_status = 0;
+    return CLPK_OK;
+}
+
 int clpk_mma_peak(const clpk_mma_peak_args_t *a, void *)
 {
     const int K = clpk_mma_kind_k(a->kind);
     if (!K) return fail(CLPK_ERR_BAD_ARG, "kind");
+    if (a->kind >= CLPK_MMA_E4M3_SP) return fake_sparse_peak(a);
     const uint8_t *A = static_cast<const uint8_t *>(a->d_a), *B = static_cast<const uint8_t *>(a->d_b);
     std::vector<uint32_t> tile(128 * 256);
     uint32_t x = 0;

@@ -9,11 +9,44 @@ from clpeak_b200 import native as N
 
 DENSE_DT = {N.MMA_F16: N.DT_F16, N.MMA_BF16: N.DT_BF16, N.MMA_E4M3: N.DT_E4M3, N.MMA_E5M2: N.DT_E5M2}
 KIND_K = {N.MMA_F16: 16, N.MMA_BF16: 16, N.MMA_E4M3: 32, N.MMA_E5M2: 32, N.MMA_I8: 32, N.MMA_MXF4: 64,
-          N.MMA_NVF4: 64}
+          N.MMA_NVF4: 64, N.MMA_E4M3_SP: 64, N.MMA_I8_SP: 64, N.MMA_MXF4_SP: 128, N.MMA_NVF4_SP: 128}
+SPARSE = (N.MMA_E4M3_SP, N.MMA_I8_SP, N.MMA_MXF4_SP, N.MMA_NVF4_SP)
+
+
+def make_sparse_operands(orc, kind):
+    """2:4 sparse kinds: a dense A tile is pruned (top-2 |x| of every 4; 4-bit kinds in pairs:
+    top-2 of every 4 pairs), compressed to K/2 and quantised; B stays dense over the logical K."""
+    k = KIND_K[kind]
+    if kind == N.MMA_I8_SP:
+        dense = orc.fill_i8(128 * k, 2).astype(np.float32).reshape(128, k)
+        comp, meta, pruned = orc.prune_2to4(dense)
+        b = orc.fill_i8(256 * k, 2, first=128 * k).reshape(256, k)
+        return dict(a=comp.astype(np.int8), b=b, meta=meta, sfa=None, sfb=None, pruned=pruned, tensor_scale=(1.0, 1.0))
+    if kind == N.MMA_E4M3_SP:
+        dense = orc.fill_f32(128 * k, 2, 1).reshape(128, k)
+        comp, meta, pruned = orc.prune_2to4(dense)
+        b = orc.convert_f32(orc.fill_f32(256 * k, 2, 1, first=128 * k), N.DT_E4M3).reshape(256, k)
+        return dict(a=orc.convert_f32(comp.ravel(), N.DT_E4M3).reshape(128, k // 2), b=b, meta=meta, sfa=None, sfb=None,
+                    pruned=pruned, tensor_scale=(1.0, 1.0))
+    dense = orc.fill_f32(128 * k, 3, 2).reshape(128, k)
+    comp, meta, pruned = orc.prune_2to4(dense, pairs=True)
+    fb = orc.fill_f32(256 * k, 3, 2, first=128 * k).reshape(256, k)
+    if kind == N.MMA_NVF4_SP:
+        tsa = np.float32(np.abs(comp).max()) / np.float32(6.0 * 448.0)
+        tsb = np.float32(np.abs(fb).max()) / np.float32(6.0 * 448.0)
+        a, sfa = orc.quantize_fp4(comp, N.DT_NVF4, float(tsa))          # 16 compressed = 32 logical per scale
+        b, sfb = orc.quantize_fp4(fb, N.DT_NVF4_B32, float(tsb))
+    else:
+        tsa = tsb = np.float32(1.0)
+        a, sfa = orc.quantize_fp4(comp, N.DT_MXF4)                       # 32 compressed = 64 logical per scale
+        b, sfb = orc.quantize_fp4(fb, N.DT_MXF4_B64)
+    return dict(a=a, b=b, meta=meta, sfa=sfa, sfb=sfb, pruned=pruned, tensor_scale=(float(tsa), float(tsb)))
 
 
 def make_operands(orc, kind):
     """Returns dict(a, b, sfa, sfb, tensor_scale) of numpy arrays in the kernel's input encoding."""
+    if kind in SPARSE:
+        return make_sparse_operands(orc, kind)
     k = KIND_K[kind]
     if kind == N.MMA_I8:
         a = orc.fill_i8(128 * k, 2).reshape(128, k)
@@ -42,7 +75,12 @@ def expected_tile(orc, kind, ops, n_mma):
     """(expected tile, tolerance tile).  int8: exact int32, tolerance None."""
     if kind == N.MMA_I8:
         return orc.mma_tile_i8(ops["a"], ops["b"], n_mma), None
-    p, s = orc.mma_tile(kind, ops["a"], ops["b"], ops["sfa"], ops["sfb"])
+    if kind in SPARSE:
+        p, s = orc.mma_tile_sp(kind, ops["a"], ops["meta"], ops["b"], ops["sfa"], ops["sfb"])
+        if kind == N.MMA_I8_SP:
+            return (p.astype(np.int64) * n_mma).astype(np.int32), None
+    else:
+        p, s = orc.mma_tile(kind, ops["a"], ops["b"], ops["sfa"], ops["sfb"])
     k = KIND_K[kind]
     # fp32 accumulation in the tensor core is not IEEE round-to-nearest: the
     # addend is aligned to the running sum and truncated.  Model: each of the n
@@ -62,13 +100,15 @@ def run_peak(K, cuda, kind, ops, n_mma, grid, n_out_tiles):
     d_b = dev_from(ops["b"].view(np.uint8))
     d_sfa = dev_from(ops["sfa"]) if ops["sfa"] is not None else None
     d_sfb = dev_from(ops["sfb"]) if ops["sfb"] is not None else None
+    d_meta = dev_from(ops["meta"]) if ops.get("meta") is not None else None
     d_out = dev_empty(max(n_out_tiles, 1) * 128 * 256, cuda.int32)
     d_chk = dev_empty(grid, cuda.int32)
     d_status = dev_empty(1, cuda.int32)
     args = N.MmaPeakArgs(kind=kind, d_a=d_a.data_ptr(), d_b=d_b.data_ptr(),
                          d_sfa=d_sfa.data_ptr() if d_sfa is not None else None,
                          d_sfb=d_sfb.data_ptr() if d_sfb is not None else None,
-                         d_meta=None, n_mma=n_mma, grid=grid, n_out_tiles=n_out_tiles,
+                         d_meta=d_meta.data_ptr() if d_meta is not None else None, n_mma=n_mma, grid=grid,
+                         n_out_tiles=n_out_tiles,
                          d_out=d_out.data_ptr(), d_checksum=d_chk.data_ptr(), d_status=d_status.data_ptr())
     K.clpk_mma_peak(C.byref(args), stream_ptr())
     sync()
@@ -78,7 +118,7 @@ def run_peak(K, cuda, kind, ops, n_mma, grid, n_out_tiles):
 
 
 def check_tile(kind, got_i32, want, tol):
-    if kind == N.MMA_I8:
+    if kind in (N.MMA_I8, N.MMA_I8_SP):
         assert np.array_equal(got_i32, want), f"int8 tile differs in {(got_i32 != want).sum()} elements"
         return 0.0
     got = got_i32.view(np.float32).astype(np.float64)

@@ -61,6 +61,13 @@ def test_launch_streams_events_and_writes_xml(ffi, one_device, tmp_path):
     assert by[("wmma_bf16", "wmma_bf16")]["unit"] == "tflops" and by[("wmma_bf16", "wmma_bf16")]["category"] == "fp_compute"
     assert by[("wmma_int8_k32", "int8_k32")]["unit"] == "tops" and by[("wmma_int8_k32", "int8_k32")]["category"] == "int_compute"
     assert by[("wmma_int4", "int4")]["status"] == "unsupported" and by[("wmma_int4", "int4")]["value"] == 0
+    # the 2:4 sparse rows prune on the host, run, and pass the host's own tile check (exact for int8)
+    for key, unit, cat in ((("wmma_int8_sparse", "int8_sparse"), "tops", "int_compute"),
+                           (("wmma_mxf4_sparse", "mxf4_sparse"), "tflops", "fp_compute"),
+                           (("wmma_nvf4_sparse", "nvf4_sparse"), "tflops", "fp_compute"),
+                           (("wmma_fp8_e4m3_sparse", "fp8_e4m3_sparse"), "tflops", "fp_compute")):
+        assert by[key]["status"] == "ok", by[key]
+        assert by[key]["unit"] == unit and by[key]["category"] == cat and by[key]["value"] > 0
     assert by[("kernel_launch_latency", "dispatch")]["status"] == "unsupported"
     assert by[("kernel_launch_latency", "roundtrip")]["category"] == "latency"
     # fp rows come before int rows, which come before latency (the reference's phase order)

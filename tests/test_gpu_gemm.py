@@ -91,3 +91,81 @@ def test_gemm_rejects_ragged(K, cuda):
     with pytest.raises(N.ClpkError) as e:
         K.clpk_gemm(C.byref(args), None)
     assert e.value.code == N.ERR_BAD_ARG
+
+
+# ---- NVFP4 ---------------------------------------------------------------------------------
+
+def make_nvfp4_operand(K, cuda, rows, k, seed):
+    """N(0, 0.02) values quantised on the device: packed e2m1, ue4m3 scale per 16, fp32 tensor scale."""
+    f = dev_empty(rows * k, cuda.float32)
+    K.clpk_fill_f32(f.data_ptr(), rows * k, seed, N.DIST_NORMAL, 0.0, 0.02, stream_ptr())
+    am = dev_empty(1, cuda.float32)
+    K.clpk_absmax_f32(am.data_ptr(), f.data_ptr(), rows * k, stream_ptr())
+    sync()
+    ts = float(np.float32(to_np(am)[0]) / np.float32(6.0 * 448.0))
+    q = dev_empty(rows * k // 2, cuda.uint8)
+    sf = dev_empty(rows * k // 16, cuda.uint8)
+    K.clpk_quantize_fp4(q.data_ptr(), sf.data_ptr(), f.data_ptr(), rows, k, N.DT_NVF4, ts, stream_ptr())
+    sync()
+    return q, sf, ts, f
+
+
+def run_nvfp4(K, cuda, m, n, k):
+    a, sfa, tsa, fa = make_nvfp4_operand(K, cuda, m, k, 40)
+    b, sfb, tsb, fb = make_nvfp4_operand(K, cuda, n, k, 41)
+    c = cuda.full((m * n,), 0x7FC0, dtype=cuda.int16, device="cuda")
+    need = C.c_size_t(0)
+    K.clpk_gemm_workspace_bytes(N.DT_NVF4, m, n, k, C.byref(need))
+    assert need.value == (m + n) * (k // 16)
+    ws = dev_empty(need.value, cuda.uint8)
+    st = dev_empty(1, cuda.int32)
+    alpha = float(np.float32(tsa) * np.float32(tsb))
+    args = N.GemmArgs(dtype=N.DT_NVF4, m=m, n=n, k=k, d_a=a.data_ptr(), d_b=b.data_ptr(), d_c=c.data_ptr(),
+                      d_sfa=sfa.data_ptr(), d_sfb=sfb.data_ptr(), alpha=alpha, d_workspace=ws.data_ptr(),
+                      workspace_bytes=need.value, d_status=st.data_ptr())
+    K.clpk_gemm(C.byref(args), stream_ptr())
+    sync()
+    assert int(to_np(st)[0]) == 0
+    return dict(a=to_np(a), b=to_np(b), sfa=to_np(sfa), sfb=to_np(sfb), c=to_np(c).view(np.uint16), alpha=alpha,
+                fa=fa, fb=fb)
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 256, 256), (256, 512, 1024), (768, 256, 512), (2048, 2048, 2048)])
+def test_gemm_nvfp4(K, orc, cuda, m, n, k):
+    r = run_nvfp4(K, cuda, m, n, k)
+    assert not np.any(r["c"] == 0x7FC0)
+    rng = np.random.default_rng(5)
+    samples = list(zip(rng.integers(0, m, 120), rng.integers(0, n, 120))) + [(0, 0), (m - 1, n - 1), (127, 128), (128, 127)]
+    worst = 0.0
+    for (i, j) in samples:
+        want, s = orc.gemm_element(N.DT_NVF4, r["a"], r["b"], k, int(i), int(j), r["sfa"], r["sfb"])
+        want *= r["alpha"]
+        s *= r["alpha"]
+        got = float(bf16_to_f64(r["c"][i * n + j: i * n + j + 1])[0])
+        tol = k * 2.0 ** -23 * s + 2.0 ** -8 * abs(want) + 1e-30
+        worst = max(worst, abs(got - want) / tol)
+    assert worst <= 1.0, f"worst sampled error is {worst:.3g}x the stated tolerance"
+
+
+def test_gemm_nvfp4_tracks_the_unquantised_product(K, orc, cuda):
+    """End-to-end sanity of the whole recipe (quantiser + scales + tensor scale): C correlates with fp32 A.B^T."""
+    m = n = 256
+    k = 2048
+    r = run_nvfp4(K, cuda, m, n, k)
+    ref = (r["fa"].view(m, k) @ r["fb"].view(n, k).T).cpu().numpy().astype(np.float64)
+    got = bf16_to_f64(r["c"]).reshape(m, n)
+    assert np.corrcoef(ref.ravel(), got.ravel())[0, 1] > 0.98
+
+
+def test_gemm_nvfp4_argument_checks(K, cuda):
+    d = dev_empty(64, cuda.uint8)
+    args = N.GemmArgs(dtype=N.DT_NVF4, m=256, n=256, k=128, d_a=d.data_ptr(), d_b=d.data_ptr(), d_c=d.data_ptr(),
+                      d_sfa=d.data_ptr(), d_sfb=d.data_ptr(), alpha=1.0, d_workspace=d.data_ptr(), workspace_bytes=64,
+                      d_status=d.data_ptr())
+    with pytest.raises(N.ClpkError) as e:
+        K.clpk_gemm(C.byref(args), None)                 # K must be a multiple of 256
+    assert e.value.code == N.ERR_BAD_ARG
+    args.k = 256
+    with pytest.raises(N.ClpkError) as e:
+        K.clpk_gemm(C.byref(args), None)                 # workspace too small
+    assert e.value.code == N.ERR_BAD_ARG
