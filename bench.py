@@ -420,20 +420,38 @@ def measure_rows(K, N, torch, stream, time_once):
     rows = {}
     spec_of = {N.MMA_F16: "fp16_tflops", N.MMA_BF16: "bf16_tflops", N.MMA_E4M3: "fp8_tflops",
                N.MMA_E5M2: "fp8_tflops", N.MMA_I8: "int8_tops", N.MMA_MXF4: "fp4_tflops", N.MMA_NVF4: "fp4_tflops"}
+    # 2:4 sparse kinds: rate counted at the logical K, against twice the dense figure
+    sparse_spec = {N.MMA_E4M3_SP: "fp8_tflops", N.MMA_I8_SP: "int8_tops", N.MMA_MXF4_SP: "fp4_tflops",
+                   N.MMA_NVF4_SP: "fp4_tflops"}
     grid, n_mma = 4 * sms, 1 << 14
     ta = torch.zeros(128 * 32, dtype=torch.uint8, device="cuda")
-    tb = torch.zeros(256 * 32, dtype=torch.uint8, device="cuda")
+    tb = torch.zeros(256 * 64, dtype=torch.uint8, device="cuda")
+    # selector bytes: groups alternate "keep slots 0,1" (nibble 0x4) and "keep slots 2,3" (nibble 0xE)
+    meta = torch.full((128 * 8,), 0xE4, dtype=torch.uint8, device="cuda")
     # operands: seeded values converted on the device (bit patterns do not change the rate check here;
     # the parity tests own the numerics)
-    f = torch.empty(256 * 64, dtype=torch.float32, device="cuda")
+    f = torch.empty(256 * 128, dtype=torch.float32, device="cuda")
     sf = torch.full((256 * 4,), 0x38, dtype=torch.uint8, device="cuda")
     chk = torch.empty(grid, dtype=torch.int32, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     for kind, name in N.MMA_KIND_NAMES.items():
-        if kind not in spec_of:
+        if kind not in spec_of and kind not in sparse_spec:
             continue
         K.clpk_fill_f32(f.data_ptr(), f.numel(), 2, N.DIST_UNIFORM_PM1, 0.0, 1.0, stream)
-        if kind in (N.MMA_F16, N.MMA_BF16, N.MMA_E4M3, N.MMA_E5M2):
+        if kind in (N.MMA_E4M3_SP, N.MMA_I8_SP):
+            if kind == N.MMA_I8_SP:
+                K.clpk_fill_i8(ta.data_ptr(), 128 * 32, 2, stream)
+                K.clpk_fill_i8(tb.data_ptr(), 256 * 64, 3, stream)
+            else:
+                K.clpk_convert_f32(ta.data_ptr(), f.data_ptr(), 128 * 32, N.DT_E4M3, stream)
+                K.clpk_convert_f32(tb.data_ptr(), f.data_ptr(), 256 * 64, N.DT_E4M3, stream)
+        elif kind in (N.MMA_MXF4_SP, N.MMA_NVF4_SP):
+            mx = kind == N.MMA_MXF4_SP
+            K.clpk_quantize_fp4(ta.data_ptr(), sf.data_ptr(), f.data_ptr(), 128, 64,
+                                N.DT_MXF4 if mx else N.DT_NVF4, 1.0, stream)
+            K.clpk_quantize_fp4(tb.data_ptr(), sf.data_ptr(), f.data_ptr(), 256, 128,
+                                N.DT_MXF4_B64 if mx else N.DT_NVF4_B32, 1.0, stream)
+        elif kind in (N.MMA_F16, N.MMA_BF16, N.MMA_E4M3, N.MMA_E5M2):
             dt = {N.MMA_F16: N.DT_F16, N.MMA_BF16: N.DT_BF16, N.MMA_E4M3: N.DT_E4M3, N.MMA_E5M2: N.DT_E5M2}[kind]
             K.clpk_convert_f32(ta.data_ptr(), f.data_ptr(), 128 * K.raw("clpk_mma_kind_k")(kind), dt, stream)
             K.clpk_convert_f32(tb.data_ptr(), f.data_ptr(), 256 * K.raw("clpk_mma_kind_k")(kind), dt, stream)
@@ -445,7 +463,7 @@ def measure_rows(K, N, torch, stream, time_once):
             K.clpk_quantize_fp4(ta.data_ptr(), sf.data_ptr(), f.data_ptr(), 128, 64, dt, 1.0, stream)
             K.clpk_quantize_fp4(tb.data_ptr(), sf.data_ptr(), f.data_ptr(), 256, 64, dt, 1.0, stream)
         args = N.MmaPeakArgs(kind=kind, d_a=ta.data_ptr(), d_b=tb.data_ptr(), d_sfa=sf.data_ptr(),
-                             d_sfb=sf.data_ptr(), d_meta=None, n_mma=n_mma, grid=grid, n_out_tiles=0, d_out=None,
+                             d_sfb=sf.data_ptr(), d_meta=meta.data_ptr() if kind in sparse_spec else None, n_mma=n_mma, grid=grid, n_out_tiles=0, d_out=None,
                              d_checksum=chk.data_ptr(), d_status=status.data_ptr())
         ms = time_once(lambda: K.clpk_mma_peak(C.byref(args), stream), reps=5)
         if int(status.item()) != 0:
@@ -453,29 +471,43 @@ def measure_rows(K, N, torch, stream, time_once):
             continue
         same = bool((chk == chk[0]).all().item())
         tf = K.raw("clpk_mma_flops_per_instr")(kind) * n_mma * grid / ms / 1e9
-        rows[f"mma_{name}"] = {"T(FL)OPS": tf, "ms": ms, "frac_of_spec": tf / SPEC[spec_of[kind]],
-                               "all_ctas_same_checksum": same}
+        spec = 2 * SPEC[sparse_spec[kind]] if kind in sparse_spec else SPEC[spec_of[kind]]
+        rows[f"mma_{name}"] = {"T(FL)OPS": tf, "ms": ms, "frac_of_spec": tf / spec, "all_ctas_same_checksum": same}
     # GEMM, 16384^3 (config 5), bf16 and fp8
-    for dt, name, spec in ((N.DT_BF16, "bf16", "bf16_tflops"), (N.DT_E4M3, "fp8_e4m3", "fp8_tflops")):
+    for dt, name, spec in ((N.DT_BF16, "bf16", "bf16_tflops"), (N.DT_E4M3, "fp8_e4m3", "fp8_tflops"),
+                           (N.DT_NVF4, "nvf4_e2m1", "fp4_tflops")):
         for m in (4096, 8192, 16384):
-            es = 2 if dt == N.DT_BF16 else 1
-            A = torch.empty(m * m * es, dtype=torch.uint8, device="cuda")
-            B = torch.empty(m * m * es, dtype=torch.uint8, device="cuda")
+            nv = dt == N.DT_NVF4
+            row_bytes = m // 2 if nv else (2 * m if dt == N.DT_BF16 else m)
+            A = torch.empty(m * row_bytes, dtype=torch.uint8, device="cuda")
+            B = torch.empty(m * row_bytes, dtype=torch.uint8, device="cuda")
             Cc = torch.empty(m * m, dtype=torch.int16, device="cuda")
             tmp = torch.empty(m * m, dtype=torch.float32, device="cuda")
-            for buf, seed in ((A, 40), (B, 41)):
+            sfs = [torch.empty(m * m // 16, dtype=torch.uint8, device="cuda") for _ in range(2)] if nv else [None, None]
+            tscale = 2.0 ** -15      # N(0, 0.02) operands: keeps x / scale / 6 inside ue4m3's range
+            for buf, sfbuf, seed in ((A, sfs[0], 40), (B, sfs[1], 41)):
                 K.clpk_fill_f32(tmp.data_ptr(), m * m, seed, N.DIST_NORMAL, 0.0, 0.02, stream)
-                K.clpk_convert_f32(buf.data_ptr(), tmp.data_ptr(), m * m, dt, stream)
+                if nv:
+                    K.clpk_quantize_fp4(buf.data_ptr(), sfbuf.data_ptr(), tmp.data_ptr(), m, m, dt, tscale, stream)
+                else:
+                    K.clpk_convert_f32(buf.data_ptr(), tmp.data_ptr(), m * m, dt, stream)
             del tmp
+            ws = None
+            ws_bytes = C.c_size_t(0)
+            if nv:
+                K.clpk_gemm_workspace_bytes(dt, m, m, m, C.byref(ws_bytes))
+                ws = torch.empty(max(ws_bytes.value, 16), dtype=torch.uint8, device="cuda")
             ga = N.GemmArgs(dtype=dt, m=m, n=m, k=m, d_a=A.data_ptr(), d_b=B.data_ptr(), d_c=Cc.data_ptr(),
-                            alpha=1.0, d_status=status.data_ptr())
+                            d_sfa=sfs[0].data_ptr() if nv else None, d_sfb=sfs[1].data_ptr() if nv else None,
+                            alpha=tscale * tscale if nv else 1.0, d_workspace=ws.data_ptr() if nv else None,
+                            workspace_bytes=ws_bytes.value, d_status=status.data_ptr())
             ms = time_once(lambda: K.clpk_gemm(C.byref(ga), stream), reps=5)
             tf = 2.0 * m * m * m / ms / 1e9
             row = {"TFLOPS": tf, "ms": ms, "frac_of_spec": tf / SPEC[spec], "status": int(status.item())}
             if dt == N.DT_BF16:
                 row["frac_of_measured_cublas_burst"] = tf / peaks["bf16_tflops"]
             rows[f"gemm_{name}_{m}"] = row
-            del A, B, Cc
+            del A, B, Cc, sfs, ws
             torch.cuda.empty_cache()
     return rows
 
