@@ -227,17 +227,14 @@ def main():
     import torch
     from clpeak_b200 import native as N
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
+    from clpeak_b200.replicas import Replicas
+
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the kernels have no CPU fallback")
     torch.cuda.set_device(local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist_mod
-        dist = dist_mod
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    reps = Replicas("nccl", torch.device("cuda", local))
+    rank, world = reps.rank, reps.world
     K = N.kernels()                      # raises if the CUDA library is missing
     K.clpk_set_device(local)
     stream = torch.cuda.current_stream().cuda_stream
@@ -299,27 +296,22 @@ def main():
     if rank == 0:
         sampler.start()
     per_step_events = [[ev() for _ in range(4)] for _ in range(args.steps)]
-    if dist:
-        dist.barrier()
+    reps.barrier()
     torch.cuda.synchronize()
     for k in range(args.steps):
         step(per_step_events[k])
     torch.cuda.synchronize()
-    if dist:
-        dist.barrier()
+    reps.barrier()
     total_ms = per_step_events[0][0].elapsed_time(per_step_events[-1][3])
     clocks = sampler.stop() if rank == 0 else None
     K.clpk_stream_status(C.byref(st), stream)      # raises on a device-side timeout
 
     kern_ms = {name: sum(e[i].elapsed_time(e[i + 1]) for e in per_step_events) / args.steps
                for i, name in enumerate(("read", "copy", "triad"))}
-    if dist:
-        t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms = float(t.item())
-    ms_per_step = total_ms / args.steps
     bytes_per_step = sum(alg_bytes.values())
-    value = world * bytes_per_step / (ms_per_step * 1e6)
+    value, total_ms = reps.whole_job_rate(bytes_per_step * args.steps, total_ms)
+    value /= 1e9
+    ms_per_step = total_ms / args.steps
 
     # checksum of the step's result vs a second, independent pass (copy then read-back XOR)
     read_xor = int(np.bitwise_xor.reduce(parts[:grids[variant["read"]]].cpu().numpy().view(np.uint32)))
@@ -331,7 +323,7 @@ def main():
         for ln in open("/proc/meminfo"):
             if ln.startswith("MemAvailable"):
                 avail_kb = int(ln.split()[1])
-        local_world = int(os.environ.get("LOCAL_WORLD_SIZE", str(world)))
+        local_world = reps.local_world
         budget = avail_kb * 1024 // (6 * max(local_world, 1))     # per pinned array, per rank
         chunk = min(n_bytes, max(256 << 20, budget // (1 << 20) * (1 << 20)))
         hb = torch.empty(chunk // 4, dtype=torch.float32).pin_memory()
@@ -352,41 +344,48 @@ def main():
 
         e2e_steps = max(3, min(args.steps, 10))
         e2e_step()
-        if dist:
-            dist.barrier()
+        reps.barrier()
         e0, e1 = ev(), ev()
         e0.record()
         for _ in range(e2e_steps):
             e2e_step()
         e1.record(); torch.cuda.synchronize()
-        e2e_ms = e0.elapsed_time(e1)
-        if dist:
-            t = torch.tensor([e2e_ms], dtype=torch.float64, device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e2e_ms = float(t.item())
-        e2e = {"value": world * bytes_per_step / (e2e_ms / e2e_steps * 1e6), "unit": UNIT,
+        e2e_rate, e2e_ms = reps.whole_job_rate(bytes_per_step * e2e_steps, e0.elapsed_time(e1))
+        e2e = {"value": e2e_rate / 1e9, "unit": UNIT,
                "h2d_bytes_per_step": 2 * n_bytes, "d2h_bytes_per_step": parts.numel() * 4,
                "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
                "host_buffer": "pinned, full size" if chunk == n_bytes else f"pinned {chunk >> 20} MiB chunk reused"}
         del hb, hc
 
     # ---- the other rows of the metric (per-dtype tensor peaks, GEMM) -----------------------------
+    # Every replica runs them at the same moment (barrier before each timing, slowest replica's time), so at
+    # N > 1 a row is the per-GPU rate with all GPUs of the box busy, and "box" = N x that.
     rows = None
-    if not args.no_rows and rank == 0:
+    if not args.no_rows:
         del a, c
         torch.cuda.empty_cache()
-        rows = measure_rows(K, N, torch, stream, time_once)
+
+        def time_together(fn, reps_=3):
+            fn(); torch.cuda.synchronize()
+            reps.barrier()
+            e0, e1 = ev(), ev()
+            e0.record()
+            for _ in range(reps_):
+                fn()
+            e1.record(); torch.cuda.synchronize()
+            return reps.max_over_ranks(e0.elapsed_time(e1) / reps_)
+
+        rows = measure_rows(K, N, torch, stream, lambda fn, reps=3: time_together(fn, reps), world)
 
     if rank != 0:
-        if dist:
-            dist.barrier(); dist.destroy_process_group()
+        reps.close()
         return 0
 
     peaks = measured_peaks()
     dom = max(kern_ms, key=kern_ms.get)
     kernel_symbol = f"stream_{dom}_{vname[variant[dom]]}"
     achieved = alg_bytes[dom] / (kern_ms[dom] * 1e6)
-    cpu = run_reference_cpu(2000) or run_port_cpu(12.0)
+    cpu = (run_reference_cpu(2000) or run_port_cpu(12.0)) if world == 1 else None
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
@@ -401,18 +400,17 @@ def main():
         "roofline": {"bound": "hbm", "kernel": kernel_symbol, "achieved": achieved, "peak": peaks["hbm_gbs"],
                      "peak_source": f"of {peaks['source']}", "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                      "frac_of_spec": achieved / SPEC["hbm_gbs"], "traffic": ncu_traffic(kernel_symbol)},
-        "cpu_baseline": {"value": cpu["value"], "unit": UNIT, "cores": cpu["cores"], "kind": cpu["kind"],
-                         "sample": cpu["sample"], "rows": cpu["rows"]},
+        "cpu_baseline": ({"value": cpu["value"], "unit": UNIT, "cores": cpu["cores"], "kind": cpu["kind"],
+                          "sample": cpu["sample"], "rows": cpu["rows"]} if cpu else None),
         "e2e": e2e, "gpu_launches": 3 * args.steps, "clocks": clocks, "read_checksum": read_xor,
         "rows": rows, "spec_peaks_per_gpu": SPEC,
     }
     print(json.dumps(line), flush=True)
-    if dist:
-        dist.barrier(); dist.destroy_process_group()
+    reps.close()
     return 0
 
 
-def measure_rows(K, N, torch, stream, time_once):
+def measure_rows(K, N, torch, stream, time_once, world=1):
     """Tensor-core peak per dtype (config 3/4) and GEMM (config 5) on this GPU, after the timed region."""
     import numpy as np
     peaks = measured_peaks()
@@ -472,7 +470,8 @@ def measure_rows(K, N, torch, stream, time_once):
         same = bool((chk == chk[0]).all().item())
         tf = K.raw("clpk_mma_flops_per_instr")(kind) * n_mma * grid / ms / 1e9
         spec = 2 * SPEC[sparse_spec[kind]] if kind in sparse_spec else SPEC[spec_of[kind]]
-        rows[f"mma_{name}"] = {"T(FL)OPS": tf, "ms": ms, "frac_of_spec": tf / spec, "all_ctas_same_checksum": same}
+        rows[f"mma_{name}"] = {"T(FL)OPS": tf, "ms": ms, "frac_of_spec": tf / spec, "all_ctas_same_checksum": same,
+                               "box_T(FL)OPS": world * tf}
     # GEMM, 16384^3 (config 5), bf16 and fp8
     for dt, name, spec in ((N.DT_BF16, "bf16", "bf16_tflops"), (N.DT_E4M3, "fp8_e4m3", "fp8_tflops"),
                            (N.DT_NVF4, "nvf4_e2m1", "fp4_tflops")):
@@ -503,7 +502,8 @@ def measure_rows(K, N, torch, stream, time_once):
                             workspace_bytes=ws_bytes.value, d_status=status.data_ptr())
             ms = time_once(lambda: K.clpk_gemm(C.byref(ga), stream), reps=5)
             tf = 2.0 * m * m * m / ms / 1e9
-            row = {"TFLOPS": tf, "ms": ms, "frac_of_spec": tf / SPEC[spec], "status": int(status.item())}
+            row = {"TFLOPS": tf, "ms": ms, "frac_of_spec": tf / SPEC[spec], "status": int(status.item()),
+                   "box_TFLOPS": world * tf}
             if dt == N.DT_BF16:
                 row["frac_of_measured_cublas_burst"] = tf / peaks["bf16_tflops"]
             rows[f"gemm_{name}_{m}"] = row
