@@ -110,4 +110,38 @@ CLPK_HD float clpk_f16_decode(uint16_t h)
     return clpk_bits_f32(s | ((e + 112u) << 23) | (m << 13));
 }
 
+// ---- bf16 / fp16 encode, round to nearest even (integer arithmetic only) ------------------
+
+CLPK_HD uint16_t clpk_bf16_encode(float x)
+{
+    const uint32_t b = clpk_f32_bits(x);
+    if ((b & 0x7FFFFFFFu) > 0x7F800000u)
+        return (uint16_t)((b >> 16) | 0x40u);                          // quiet NaN
+    return (uint16_t)((b + 0x7FFFu + ((b >> 16) & 1u)) >> 16);
+}
+
+CLPK_HD uint16_t clpk_f16_encode(float x)
+{
+    const uint32_t b = clpk_f32_bits(x), sign = (b >> 16) & 0x8000u, mag = b & 0x7FFFFFFFu;
+    if (mag > 0x7F800000u)
+        return (uint16_t)(sign | 0x7E00u);
+    if (mag >= 0x477FF000u)                                            // rounds to >= 65520: infinity
+        return (uint16_t)(sign | 0x7C00u);
+    if (mag < 0x33000001u)                                             // <= 2^-25: rounds to zero
+        return (uint16_t)sign;
+    const int exp = (int)(mag >> 23) - 127;
+    uint32_t man = (mag & 0x7FFFFFu) | 0x800000u;                      // 24-bit significand
+    int shift = 13;                                                    // normal: keep 11 bits
+    int he = exp + 15;
+    if (he <= 0) {                                                     // subnormal half
+        shift += 1 - he;
+        he = 0;
+    }
+    const uint32_t kept = man >> shift, rem = man & ((1u << shift) - 1u), half = 1u << (shift - 1);
+    uint32_t r = kept + ((rem > half || (rem == half && (kept & 1u))) ? 1u : 0u);
+    // r carries the implicit bit for normals (bit 10); adding the exponent field handles the carry
+    const uint32_t out = he > 0 ? (((uint32_t)(he - 1) << 10) + r) : r;
+    return (uint16_t)(sign | out);
+}
+
 #endif // CLPK_FORMATS_H

@@ -231,6 +231,91 @@ struct B200Harness {
             out.readings.push_back(ok("float4_seeded", work / s / 1e9, seedNote, work, s));
     }
 
+    // ---- chains of the other element types -------------------------------------------------
+
+    struct ChainVariant { int chain; const char *metric; const char *note; };
+    struct ChainTest {
+        const char *tag, *title, *unit, *desc;
+        double start;                        // the scalar the reference's host code passes
+        std::vector<ChainVariant> variants;
+    };
+
+    static const std::vector<ChainTest> &chainTests()
+    {
+        static const char *w1 = "One value per thread at a time -- the plain, unvectorised case.";
+        static const char *w2 = "Two values per thread at a time, packed into one instruction.";
+        static const std::vector<ChainTest> tests = {
+            {"half_precision_compute", "Half-precision compute", "gflops",
+             "Peak arithmetic speed on 16-bit fractional numbers -- half the size of a normal float, and what graphics "
+             "and on-device AI mostly run on.  NVIDIA shader cores reach full speed only on the packed form that does "
+             "two at a time.",
+             1.3, {{CLPK_CHAIN_HALF, "half", w1}, {CLPK_CHAIN_HALF2, "half2", w2}}},
+            {"double_precision_compute", "Double-precision compute", "gflops",
+             "Peak arithmetic speed on 64-bit fractional numbers, the high-accuracy type scientific computing relies "
+             "on.  Consumer GeForce cards run these dozens of times slower than 32-bit; the datacenter parts do not.",
+             1.3, {{CLPK_CHAIN_DOUBLE, "double", ""}}},
+            {"mixed_precision_compute", "Mixed-precision compute fp16xfp16+fp32", "gflops",
+             "Peak speed when the GPU multiplies 16-bit numbers but keeps the running total in 32 bits -- the "
+             "accuracy-preserving pattern AI code uses.  This is the shader cores, not the tensor cores.",
+             1.3, {{CLPK_CHAIN_MIXED, "mp", ""}}},
+            {"bfloat16_compute", "BF16 compute bf16xbf16+fp32", "gflops",
+             "Peak speed on bfloat16 -- 16 bits arranged for AI work, trading digits of accuracy for the number range "
+             "of a full float.  Again the shader cores, with the tensor-core figure in the tcgen05 rows.",
+             1.3, {{CLPK_CHAIN_BF16, "bf16", ""}}},
+            {"integer_compute", "Integer compute (32-bit IMAD)", "gops",
+             "Peak speed on 32-bit whole numbers -- the arithmetic behind indexing, addressing and bit manipulation, "
+             "which shaders do alongside their fractional maths.",
+             3, {{CLPK_CHAIN_INT32, "int", ""}}},
+            {"integer_compute_int8_dp", "INT8 dot-product compute (__dp4a)", "gops",
+             "Peak speed of the 8-bit dot-product instruction, which multiplies four pairs of small whole numbers and "
+             "sums them in one step -- the shader-core path for quantized (compressed) neural networks.",
+             4, {{CLPK_CHAIN_INT8_DOT1, "int8_dp", "One chain of dot products, each waiting on the one before it."},
+                 {CLPK_CHAIN_INT8_DOT2, "int8_dp2", "Two independent chains, so the GPU has a second dot product to get on with while the first is still finishing."},
+                 {CLPK_CHAIN_INT8_DOT4, "int8_dp4", "Four independent chains."},
+                 {CLPK_CHAIN_INT8_DOT8, "int8_dp8", "Eight independent chains.  Where this stops improving on four, the hardware itself is the limit, not the waiting."}}},
+        };
+        return tests;
+    }
+
+    static void typedChain(B200Worker &w, B200TestResult &out, const ChainTest &t)
+    {
+        out.spec = {t.tag, t.title, t.unit, Category::Unknown, t.desc};
+        for (const ChainVariant &v : t.variants) {
+            const std::string note = std::string(v.note) + (v.note[0] ? "  " : "") +
+                                     "Outputs of the first two blocks compared with the same chain on the host.";
+            uint32_t ops = 0, elem = 4;
+            clpk_compute_chain_info(v.chain, &ops, &elem);
+            // reference geometry: numSMs*2048*256 threads, capped by a quarter of VRAM (compute_kernel.cpp:49-57)
+            uint64_t blocks = targetGlobalThreads((uint32_t)w.info.numSMs) / 256;
+            blocks = std::min<uint64_t>(blocks, w.info.totalGlobalMem / 4 / (256ull * elem));
+            DeviceBuffer buf;
+            if (!buf.alloc(blocks * 256 * elem)) {
+                out.readings.push_back(bad(v.metric, ResultStatus::Error, "Failed to allocate output buffer", note));
+                continue;
+            }
+            std::string err;
+            const double s = w.timeLaunches([&] { return clpk_compute_chain(v.chain, buf.p, t.start, (uint32_t)blocks, w.stream); }, err);
+            if (s < 0) {
+                out.readings.push_back(bad(v.metric, ResultStatus::Error, err, note));
+                continue;
+            }
+            std::vector<uint8_t> head(512 * (size_t)elem);
+            clpk_memcpy_d2h(head.data(), buf.p, head.size(), w.stream);
+            clpk_stream_sync(w.stream);
+            bool same = true;
+            for (unsigned i = 0; i < 512 && same; ++i) {
+                uint64_t got = 0;
+                std::memcpy(&got, head.data() + (size_t)i * elem, elem);
+                same = got == b200check::typedChainBits(v.chain, t.start, i % 256);
+            }
+            const double work = (double)blocks * 256.0 * ops;
+            if (!same)
+                out.readings.push_back(bad(v.metric, ResultStatus::Error, "output differs from the host chain", note));
+            else
+                out.readings.push_back(ok(v.metric, work / s / 1e9, note, work, s));
+        }
+    }
+
     // ---- tensor-core peak ----------------------------------------------------------------
 
     struct KindRow { int kind; const char *tag, *display, *metric, *unit; double spec; const char *specName; const char *desc; };
@@ -728,6 +813,93 @@ struct B200Harness {
              ("Scaling one array, adding a second and storing to a third: two reads and a write per element.  " + sz).c_str());
     }
 
+    static void localBandwidth(B200Worker &w, B200TestResult &out)
+    {
+        out.spec = {"local_memory_bandwidth", "Local memory bandwidth", "gbps", Category::Unknown,
+                    "How many bytes per second the GPU moves through shared memory -- the small on-chip scratchpad a "
+                    "block of threads passes data through, which never goes out to the card's main memory."};
+        const char *widthNote[3] = {"One value per thread at a time -- the plain, unvectorised case.",
+                                    "Two values per thread at a time, packed into one instruction.",
+                                    "Four values per thread at a time, as one 4-wide vector."};
+        const char *labels[3] = {"float", "float2", "float4"};
+        const uint64_t threads = targetGlobalThreads((uint32_t)w.info.numSMs);
+        const uint32_t blocks = (uint32_t)(threads / 256);
+        DeviceBuffer buf;
+        if (!buf.alloc(threads * sizeof(float))) {
+            for (int vi = 0; vi < 3; ++vi)
+                out.readings.push_back(bad(labels[vi], ResultStatus::Error, "Buffer alloc failed", widthNote[vi]));
+            return;
+        }
+        for (int vi = 0; vi < 3; ++vi) {
+            const int width = 1 << vi;
+            std::string err;
+            const double s = w.timeLaunches([&] { return clpk_local_bandwidth(width, buf.as<float>(), blocks, w.stream); }, err);
+            if (s < 0) {
+                out.readings.push_back(bad(labels[vi], ResultStatus::Error, err, widthNote[vi]));
+                continue;
+            }
+            // first two blocks and the last one against the closed form
+            std::vector<float> head(512), tail(256);
+            clpk_memcpy_d2h(head.data(), buf.p, head.size() * 4, w.stream);
+            clpk_memcpy_d2h(tail.data(), buf.as<float>() + (threads - 256), tail.size() * 4, w.stream);
+            clpk_stream_sync(w.stream);
+            bool same = true;
+            for (uint64_t i = 0; i < 512 && same; ++i)
+                same = b200check::sameFloat(head[i], b200check::localBandwidthReference(width, i));
+            for (uint64_t i = 0; i < 256 && same; ++i)
+                same = b200check::sameFloat(tail[i], b200check::localBandwidthReference(width, threads - 256 + i));
+            const double bytes = (double)LMEM_REPS * 2.0 * width * sizeof(float) * (double)threads;
+            if (!same)
+                out.readings.push_back(bad(labels[vi], ResultStatus::Error, "outputs differ from the closed form", widthNote[vi]));
+            else
+                out.readings.push_back(ok(labels[vi], bytes / s / 1e9, widthNote[vi], bytes, s));
+        }
+    }
+
+    static void imageBandwidth(B200Worker &w, B200TestResult &out)
+    {
+        out.spec = {"image_memory_bandwidth", "Image memory bandwidth", "gbps", Category::Unknown,
+                    "How many bytes per second the GPU reads through its texture units, which take a different path "
+                    "to memory than plain buffer reads.  Each pixel of the image is read exactly once, so caching "
+                    "cannot flatter the number."};
+        const char *note = "Each fetch returns one whole pixel -- four 32-bit colour values, 16 bytes.";
+        const uint32_t imgW = 4096, imgH = 4096;
+        const uint64_t texels = (uint64_t)imgW * imgH, threads = texels / IMAGE_FETCH_PER_WI;
+        const uint32_t blocks = (uint32_t)(threads / 256);
+        const uint64_t seed = 5;
+        void *image = nullptr;
+        if (clpk_image_create(&image, imgW, imgH, seed, w.stream) != CLPK_OK) {
+            out.readings.push_back(bad("float4", ResultStatus::Error, shimError("image create"), note));
+            return;
+        }
+        DeviceBuffer buf;
+        if (!buf.alloc(threads * sizeof(float))) {
+            clpk_image_destroy(image);
+            out.readings.push_back(bad("float4", ResultStatus::Error, "Buffer alloc failed", note));
+            return;
+        }
+        std::string err;
+        const double s = w.timeLaunches([&] { return clpk_image_bandwidth(image, buf.as<float>(), blocks, w.stream); }, err);
+        if (s < 0) {
+            out.readings.push_back(bad("float4", ResultStatus::Error, err, note));
+        } else {
+            std::vector<float> head(256), tail(256);
+            clpk_memcpy_d2h(head.data(), buf.p, head.size() * 4, w.stream);
+            clpk_memcpy_d2h(tail.data(), buf.as<float>() + (threads - 256), tail.size() * 4, w.stream);
+            clpk_stream_sync(w.stream);
+            bool same = true;
+            for (uint64_t i = 0; i < 256 && same; ++i)
+                same = b200check::sameFloat(head[i], b200check::imageBandwidthReference(i, threads, texels, seed)) &&
+                       b200check::sameFloat(tail[i], b200check::imageBandwidthReference(threads - 256 + i, threads, texels, seed));
+            const double bytes = (double)IMAGE_FETCH_PER_WI * 4.0 * sizeof(float) * (double)threads;
+            if (!same)
+                out.readings.push_back(bad("float4", ResultStatus::Error, "sums differ from the host replay", note));
+            else
+                out.readings.push_back(ok("float4", bytes / s / 1e9, note, bytes, s));
+        }
+        clpk_image_destroy(image);
+    }
+
     static void transferBandwidth(B200Worker &w, B200TestResult &out)
     {
         out.spec = {"transfer_bandwidth", "Transfer bandwidth", "gbps", Category::Unknown,
@@ -945,6 +1117,15 @@ int CudaPeak::runAll()
     const bool fp = isAllowedAs(Benchmark::Wmma, Category::FpCompute);
     if (isAllowed(Benchmark::ComputeSP))
         plan.push_back(H::computeSP);
+    {
+        // same order as the reference's floating phase (src/cuda/cuda_peak.cpp:165-174)
+        const Benchmark fpChains[] = {Benchmark::ComputeHP, Benchmark::ComputeDP, Benchmark::ComputeMP, Benchmark::ComputeBF16};
+        for (size_t i = 0; i < 4; ++i)
+            if (isAllowed(fpChains[i])) {
+                const H::ChainTest &t = H::chainTests()[i];
+                plan.push_back([&t](B200Worker &w, B200TestResult &o) { H::typedChain(w, o, t); });
+            }
+    }
     if (fp) {
         for (const auto &row : H::kindRows())
             if (row.kind != CLPK_MMA_I8)
@@ -963,6 +1144,14 @@ int CudaPeak::runAll()
     }
     if (isAllowedAs(Benchmark::Cublas, Category::FpCompute))
         plan.push_back(H::gemmFp);
+    if (isAllowed(Benchmark::ComputeInt)) {
+        const H::ChainTest &t = H::chainTests()[4];
+        plan.push_back([&t](B200Worker &w, B200TestResult &o) { H::typedChain(w, o, t); });
+    }
+    if (isAllowed(Benchmark::ComputeInt8DP)) {
+        const H::ChainTest &t = H::chainTests()[5];
+        plan.push_back([&t](B200Worker &w, B200TestResult &o) { H::typedChain(w, o, t); });
+    }
     if (isAllowedAs(Benchmark::Wmma, Category::IntCompute)) {
         plan.push_back([](B200Worker &, B200TestResult &o) { H::tensorNotBuilt(o, "wmma_int8", "wmma int8 16x16x16", "wmma_int8", "tops", "superseded by the tcgen05 int8_k32 row on sm_100"); });
         for (const auto &row : H::kindRows())
@@ -976,6 +1165,10 @@ int CudaPeak::runAll()
         plan.push_back(H::gemmInt);
     if (isAllowed(Benchmark::GlobalBW))
         plan.push_back(H::globalBandwidth);
+    if (isAllowed(Benchmark::LocalBW))
+        plan.push_back(H::localBandwidth);
+    if (isAllowed(Benchmark::ImageBW))
+        plan.push_back(H::imageBandwidth);
     if (isAllowed(Benchmark::TransferBW))
         plan.push_back(H::transferBandwidth);
     if (isAllowed(Benchmark::MemoryLatency))

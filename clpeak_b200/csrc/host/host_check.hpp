@@ -10,6 +10,7 @@
 
 #include <cmath>
 #include <cstdint>
+#include <cstring>
 #include <string>
 #include <vector>
 
@@ -26,6 +27,120 @@ inline float chainReference(float a, unsigned lane)
     for (int i = 0; i < 128 * 16; ++i)
         x = std::fmaf(x, x, c);
     return x;
+}
+
+// ---- chains of the other element types (clpk_compute_chain) --------------------------------
+// Bit pattern of what thread `tid` of any block stores: float bits for the half,
+// half2, mixed and bf16 chains, double bits for the double chain, the int32 for the
+// integer chains.
+
+inline float throughHalf(float x) { return clpk_f16_decode(clpk_f16_encode(x)); }
+inline float throughBf16(float x) { return clpk_bf16_decode(clpk_bf16_encode(x)); }
+// One-rounding fp16 FMA: half x half is exact in double, so std::fma in double rounds the
+// exact sum once, and 53 >= 2*11 + 2 bits keep the later rounding to half harmless.
+inline float halfFma(float x, float c) { return throughHalf((float)std::fma((double)x, (double)x, (double)c)); }
+
+inline int32_t dot4Bytes(uint32_t x, uint32_t y, int32_t acc)
+{
+    int64_t s = acc;
+    for (int b = 0; b < 4; ++b)
+        s += (int64_t)(int8_t)(x >> (8 * b)) * (int64_t)(int8_t)(y >> (8 * b));
+    return (int32_t)(uint32_t)(uint64_t)s;
+}
+
+inline uint64_t typedChainBits(int chain, double a, unsigned tid)
+{
+    auto fbits = [](float v) { return (uint64_t)clpk_f32_bits(v); };
+    switch (chain) {
+    case CLPK_CHAIN_HALF: {
+        float x0 = throughHalf((float)a), x1 = throughHalf((float)a + 1.0f);
+        const float c = throughHalf((float)tid);
+        for (int i = 0; i < 1024; ++i) {
+            x0 = halfFma(x0, c);
+            x1 = halfFma(x1, c);
+        }
+        return fbits(throughHalf(x0 + x1));
+    }
+    case CLPK_CHAIN_HALF2: {
+        float x = throughHalf((float)a);
+        const float c = throughHalf((float)tid);
+        for (int i = 0; i < 1024; ++i)
+            x = halfFma(x, c);
+        return fbits(x + x);
+    }
+    case CLPK_CHAIN_DOUBLE: {
+        double x = a;
+        const double c = (double)tid;
+        for (int i = 0; i < 2048; ++i)
+            x = std::fma(x, x, c);
+        uint64_t bits;
+        std::memcpy(&bits, &x, sizeof bits);
+        return bits;
+    }
+    case CLPK_CHAIN_MIXED:
+    case CLPK_CHAIN_BF16: {
+        const bool half = chain == CLPK_CHAIN_MIXED;
+        auto through = [&](float v) { return half ? throughHalf(v) : throughBf16(v); };
+        float x = through((float)a);
+        const float c = through((float)tid);
+        const int inner = half ? 16 : 128;
+        for (int o = 0; o < 2048 / inner; ++o) {
+            for (int i = 0; i < inner; ++i)
+                x = std::fmaf(x, x, c);
+            x = through(x);
+        }
+        return fbits(x);
+    }
+    case CLPK_CHAIN_INT32: {
+        uint32_t x = (uint32_t)(int32_t)a;
+        for (int i = 0; i < 2048; ++i)
+            x = x * x + tid;
+        return x;
+    }
+    default: {
+        static const int offsets[4][8] = {{0}, {0, 7}, {0, 7, 13, 19}, {0, 11, 17, 23, 29, 31, 37, 41}};
+        const int row = chain - CLPK_CHAIN_INT8_DOT1, chains = 1 << row, ai = (int)a;
+        const uint32_t x = (uint32_t)(ai & 0xff) | ((uint32_t)((ai + 1) & 0xff) << 8) |
+                           ((uint32_t)((ai + 2) & 0xff) << 16) | ((uint32_t)((ai + 3) & 0xff) << 24);
+        uint32_t y[8], sum = 0;
+        int32_t acc[8];
+        for (int j = 0; j < chains; ++j) {
+            y[j] = tid + (uint32_t)j;
+            acc[j] = (int32_t)tid + offsets[row][j];
+        }
+        for (int o = 0; o < 64 / chains; ++o)
+            for (int j = 0; j < chains; ++j)
+                for (int i = 0; i < 16; ++i) {
+                    acc[j] = dot4Bytes(x, y[j], acc[j]);
+                    y[j] ^= (uint32_t)acc[j];
+                }
+        for (int j = 0; j < chains; ++j)
+            sum += (uint32_t)acc[j];
+        return sum;
+    }
+    }
+}
+
+// What thread gid of the shared-memory rotation ends with (64 rotations by one slot).
+inline float localBandwidthReference(int width, uint64_t gid)
+{
+    const uint32_t g = (uint32_t)(gid / 256 * 256 + (gid % 256 + 64) % 256);
+    float s = (float)g;
+    for (int l = 1; l < width; ++l)
+        s = s + (float)(g + (uint32_t)l);
+    return s;
+}
+
+// What thread gid of the texture read stores: 16 texels at (gid + i*threads) % texels.
+inline float imageBandwidthReference(uint64_t gid, uint64_t threads, uint64_t texels, uint64_t seed)
+{
+    float s[4] = {0, 0, 0, 0};
+    for (int i = 0; i < 16; ++i) {
+        const uint64_t px = (gid + (uint64_t)i * threads) % texels;
+        for (int ch = 0; ch < 4; ++ch)
+            s[ch] = s[ch] + clpk_uniform01(seed, 4 * px + (uint64_t)ch);
+    }
+    return ((s[0] + s[1]) + s[2]) + s[3];
 }
 
 inline float seededChain(uint64_t seed, uint64_t item, float y, unsigned iters)

@@ -21,6 +21,12 @@ STREAM_LDG, STREAM_TMA = 0, 1
 (MMA_F16, MMA_BF16, MMA_E4M3, MMA_E5M2, MMA_I8, MMA_MXF4, MMA_NVF4,
  MMA_E4M3_SP, MMA_MXF4_SP, MMA_NVF4_SP, MMA_I8_SP) = range(11)
 
+(CHAIN_HALF, CHAIN_HALF2, CHAIN_DOUBLE, CHAIN_MIXED, CHAIN_BF16, CHAIN_INT32, CHAIN_INT8_DOT1, CHAIN_INT8_DOT2,
+ CHAIN_INT8_DOT4, CHAIN_INT8_DOT8) = range(10)
+CHAIN_NAMES = {CHAIN_HALF: "half", CHAIN_HALF2: "half2", CHAIN_DOUBLE: "double", CHAIN_MIXED: "mp", CHAIN_BF16: "bf16",
+               CHAIN_INT32: "int", CHAIN_INT8_DOT1: "int8_dp", CHAIN_INT8_DOT2: "int8_dp2", CHAIN_INT8_DOT4: "int8_dp4",
+               CHAIN_INT8_DOT8: "int8_dp8"}
+
 MMA_KIND_NAMES = {
     MMA_F16: "fp16", MMA_BF16: "bf16", MMA_E4M3: "fp8_e4m3", MMA_E5M2: "fp8_e5m2", MMA_I8: "int8",
     MMA_MXF4: "mxf4_e2m1", MMA_NVF4: "nvf4_e2m1", MMA_E4M3_SP: "fp8_e4m3_sparse",
@@ -109,6 +115,12 @@ KERNEL_API = {
     "clpk_stream_checksum_static": [_vp, _u64, _u32, _vp, _vp],
     "clpk_compute_sp": [_vp, _f, _u32, _vp],
     "clpk_mad_chain": [_vp, _u64, _u64, _f, _u32, _vp],
+    "clpk_compute_chain": [_i, _vp, C.c_double, _u32, _vp],
+    "clpk_compute_chain_info": [_i, C.POINTER(_u32), C.POINTER(_u32)],
+    "clpk_local_bandwidth": [_i, _vp, _u32, _vp],
+    "clpk_image_create": [C.POINTER(_vp), _u32, _u32, _u64, _vp],
+    "clpk_image_bandwidth": [_vp, _vp, _u32, _vp],
+    "clpk_image_destroy": [_vp],
     "clpk_pointer_chase": [_vp, _u32, _u64, _vp, _vp],
     "clpk_build_chase_cycle": [_vp, _u64, _u64],
     "clpk_launch_noop": [_vp],

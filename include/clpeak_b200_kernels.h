@@ -200,6 +200,51 @@ CLPK_API int clpk_compute_sp(float *d_out, float a, uint32_t grid, void *stream)
 CLPK_API int clpk_mad_chain(float *d_out, uint64_t n_items, uint64_t seed, float y,
                             uint32_t iters, void *stream);
 
+/* clpk_compute_chain: the shader-core chains of the other element types, with the
+ * arithmetic of the reference kernels compute_hp / compute_hp2 / compute_dp /
+ * compute_mp / compute_bf16 / compute_int32 / compute_int8_dp{,2,4,8}
+ * (src/cuda/cuda_kernels/compute_*.cu): recurrence x = x*x + c with c = threadIdx.x,
+ * started from `a` (1.3 for the floating chains, 3 for int32, 4 for the dot
+ * products in the reference's host code, src/cuda/compute_float.cpp:30-125,
+ * src/cuda/compute_int.cpp:10-64).  grid blocks of 256 threads; d_out holds
+ * grid*256 elements of clpk_compute_chain_info()'s size (float for the floating
+ * chains except DOUBLE, int32 for the integer ones). */
+#define CLPK_CHAIN_HALF       0   /* two scalar fp16 chains of 1024 FMAs, out = float(x0 + x1)       */
+#define CLPK_CHAIN_HALF2      1   /* 1024 packed half2 FMAs, out = float(lo) + float(hi)            */
+#define CLPK_CHAIN_DOUBLE     2   /* 2048 fp64 FMAs                                                 */
+#define CLPK_CHAIN_MIXED      3   /* 2048 fp32 FMAs, value rounded through fp16 every 16            */
+#define CLPK_CHAIN_BF16       4   /* 2048 fp32 FMAs, value rounded through bf16 every 128           */
+#define CLPK_CHAIN_INT32      5   /* 2048 wrapping 32-bit multiply-adds                             */
+#define CLPK_CHAIN_INT8_DOT1  6   /* 1024 dp4a steps (a = dp4a(x, y, a); y ^= a) in 1 chain         */
+#define CLPK_CHAIN_INT8_DOT2  7   /* ... split over 2 independent chains                            */
+#define CLPK_CHAIN_INT8_DOT4  8   /* ... 4 chains                                                   */
+#define CLPK_CHAIN_INT8_DOT8  9   /* ... 8 chains                                                   */
+#define CLPK_CHAIN_COUNT      10
+CLPK_API int clpk_compute_chain(int chain, void *d_out, double a, uint32_t grid, void *stream);
+/* Operations counted per thread (4096; 8192 for the dot products: COMPUTE_FP_WORK_PER_WI,
+ * COMPUTE_INT8_DP_WORK_PER_WI, include/common/common.h:100,114) and bytes per output element. */
+CLPK_API int clpk_compute_chain_info(int chain, uint32_t *ops_per_thread, uint32_t *out_elem_bytes);
+
+/* ---- shared-memory and texture bandwidth ---------------------------------------------------
+ * clpk_local_bandwidth: 64 rounds of "store my value to shared memory, barrier, load
+ * my neighbour's, barrier" on `width` (1, 2, 4) floats per thread
+ * (local_bandwidth_v1/v2/v4, src/cuda/cuda_kernels/local_bandwidth.cu).  grid blocks
+ * of 256 threads; d_out[gid] = sum of the lanes the thread ends with, which are
+ * (float)(g + l), l < width, for g = block*256 + (thread + 64) % 256.
+ * Bytes per launch: 64 * 2 * width * 4 * grid * 256 (src/cuda/local_bandwidth.cpp). */
+CLPK_API int clpk_local_bandwidth(int width, float *d_out, uint32_t grid, void *stream);
+/* A width x height image of float4 texels in a CUDA array behind a point-sampled texture
+ * object (src/cuda/image_bandwidth.cpp builds the same from populate()); texel (x, y)
+ * channel ch = clpk uniform[0,1) number 4*(y*width + x) + ch of `seed`.  Allocates; the
+ * call synchronises the stream. */
+CLPK_API int clpk_image_create(void **image, uint32_t width, uint32_t height, uint64_t seed, void *stream);
+/* 16 float4 fetches per thread, fetch i at texel (gid + i*grid*256) mod (width*height),
+ * channel-wise running sums then x+y+z+w (image_bandwidth,
+ * src/cuda/cuda_kernels/image_bandwidth.cu).  d_out holds grid*256 floats.  Bytes per
+ * launch: 16 * 16 * grid * 256. */
+CLPK_API int clpk_image_bandwidth(void *image, float *d_out, uint32_t grid, void *stream);
+CLPK_API int clpk_image_destroy(void *image);
+
 /* ---- latency -------------------------------------------------------------------------------
  * clpk_pointer_chase: one thread follows next[] for `hops` dependent loads
  * starting at `start` (the CUDA backend has no such test; the model is

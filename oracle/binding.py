@@ -50,6 +50,9 @@ _API = {
     "orc_stream_pass_mt": ([_i, _vp, _vp, _vp, _u64, _i, _i, C.POINTER(_u32)], _d),
     "orc_compute_sp": ([_vp, _f, _u64], None),
     "orc_mad_chain": ([_vp, _u64, _u64, _u64, _f, _u32], None),
+    "orc_compute_chain": ([_i, _vp, _d, _u64], None),
+    "orc_local_bandwidth": ([_i, _vp, _u64], None),
+    "orc_image_bandwidth": ([_vp, _u64, _u64, _u64, _u64, _u64], None),
     "orc_chase_cycle": ([_vp, _u64, _u64], None),
     "orc_is_single_cycle": ([_vp, _u64], _i),
     "orc_chase": ([_vp, _u32, _u64, C.POINTER(_u32), C.POINTER(_u32)], None),
@@ -138,6 +141,27 @@ def triad(b: np.ndarray, c: np.ndarray, s: float) -> np.ndarray:
 def compute_sp(a: float, n_threads: int) -> np.ndarray:
     out = np.empty(n_threads, dtype=np.float32)
     lib().orc_compute_sp(ptr(out), a, n_threads)
+    return out
+
+
+def compute_chain(chain: int, a: float, n_threads: int) -> np.ndarray:
+    """chain = CLPK_CHAIN_*; float32 output for 0, 1, 3, 4, float64 for 2, int32 for 5..9."""
+    dtype = np.float64 if chain == 2 else (np.int32 if chain >= 5 else np.float32)
+    out = np.empty(n_threads, dtype=dtype)
+    lib().orc_compute_chain(chain, ptr(out), a, n_threads)
+    return out
+
+
+def local_bandwidth(width: int, n_threads: int) -> np.ndarray:
+    out = np.empty(n_threads, dtype=np.float32)
+    lib().orc_local_bandwidth(width, ptr(out), n_threads)
+    return out
+
+
+def image_bandwidth(n_threads: int, texels: int, seed: int, first: int = 0, count: int | None = None) -> np.ndarray:
+    count = n_threads - first if count is None else count
+    out = np.empty(count, dtype=np.float32)
+    lib().orc_image_bandwidth(ptr(out), first, count, n_threads, texels, seed)
     return out
 
 

@@ -473,6 +473,121 @@ void orc_compute_sp(float *out, float a, uint64_t n_threads)
     }
 }
 
+/* The other shader-core chains, src/cuda/cuda_kernels/compute_hp.cu (scalar: two chains
+ * x0 = A, x1 = A + 1; packed: both lanes A), compute_dp.cu, compute_mp.cu (value
+ * through fp16 after every 16 FMAs), compute_bf16.cu (through bf16 after every 128),
+ * compute_int32.cu (wrapping x*x + c) and compute_int8_dp.cu (a = dot4(x, y) + a;
+ * y ^= a, chains taking turns in runs of 16).  chain = CLPK_CHAIN_*.  out: float
+ * for chains 0, 1, 3, 4; double for 2; int32 for 5..9.  Thread t uses c = t % 256. */
+static float half_round(float x) { return orc_f16_to_f32(orc_f32_to_f16(x)); }
+static float bf16_round(float x) { return orc_bf16_to_f32(orc_f32_to_bf16(x)); }
+/* fp16 FMA with one rounding: the product of two halves is exact in double, so the
+ * double fma below is a correctly rounded sum of two doubles, and 53 >= 2*11 + 2 bits
+ * make the second rounding (to half, through float: 24 >= 2*11 + 2) innocuous. */
+static float half_fma(float x, float c) { return half_round((float)fma((double)x, (double)x, (double)c)); }
+
+static int32_t dot4(uint32_t x, uint32_t y, int32_t a)
+{
+    int64_t s = a;
+    for (int b = 0; b < 4; b++)
+        s += (int64_t)(int8_t)(x >> (8 * b)) * (int64_t)(int8_t)(y >> (8 * b));
+    return (int32_t)(uint32_t)(uint64_t)s;
+}
+
+void orc_compute_chain(int chain, void *out, double a, uint64_t n_threads)
+{
+    static const int dot_offsets[4][8] = {{0}, {0, 7}, {0, 7, 13, 19}, {0, 11, 17, 23, 29, 31, 37, 41}};
+    for (uint64_t t = 0; t < n_threads; t++) {
+        const uint32_t tid = (uint32_t)(t % 256);
+        switch (chain) {
+        case 0: {
+            float x0 = half_round((float)a), x1 = half_round((float)a + 1.0f), c = half_round((float)tid);
+            for (int i = 0; i < 1024; i++) { x0 = half_fma(x0, c); x1 = half_fma(x1, c); }
+            ((float *)out)[t] = half_round(x0 + x1);      /* sum of two halves: exact in float, one rounding */
+            break;
+        }
+        case 1: {
+            float x = half_round((float)a), c = half_round((float)tid);
+            for (int i = 0; i < 1024; i++) x = half_fma(x, c);
+            ((float *)out)[t] = x + x;                    /* both lanes carry the same value */
+            break;
+        }
+        case 2: {
+            double x = a, c = (double)tid;
+            for (int i = 0; i < 2048; i++) x = fma(x, x, c);
+            ((double *)out)[t] = x;
+            break;
+        }
+        case 3: {
+            float x = half_round((float)a), c = half_round((float)tid);
+            for (int o = 0; o < 128; o++) {
+                for (int i = 0; i < 16; i++) x = fmaf(x, x, c);
+                x = half_round(x);
+            }
+            ((float *)out)[t] = x;
+            break;
+        }
+        case 4: {
+            float x = bf16_round((float)a), c = bf16_round((float)tid);
+            for (int o = 0; o < 16; o++) {
+                for (int i = 0; i < 128; i++) x = fmaf(x, x, c);
+                x = bf16_round(x);
+            }
+            ((float *)out)[t] = x;
+            break;
+        }
+        case 5: {
+            uint32_t x = (uint32_t)(int32_t)a;
+            for (int i = 0; i < 2048; i++) x = x * x + tid;
+            ((int32_t *)out)[t] = (int32_t)x;
+            break;
+        }
+        default: {
+            const int row = chain - 6, chains = 1 << row, ai = (int)a;
+            const uint32_t x = (uint32_t)(ai & 0xff) | ((uint32_t)((ai + 1) & 0xff) << 8) |
+                               ((uint32_t)((ai + 2) & 0xff) << 16) | ((uint32_t)((ai + 3) & 0xff) << 24);
+            uint32_t y[8];
+            int32_t acc[8];
+            for (int j = 0; j < chains; j++) { y[j] = tid + (uint32_t)j; acc[j] = (int32_t)tid + dot_offsets[row][j]; }
+            for (int o = 0; o < 64 / chains; o++)
+                for (int j = 0; j < chains; j++)
+                    for (int i = 0; i < 16; i++) { acc[j] = dot4(x, y[j], acc[j]); y[j] ^= (uint32_t)acc[j]; }
+            uint32_t sum = 0;
+            for (int j = 0; j < chains; j++) sum += (uint32_t)acc[j];
+            ((int32_t *)out)[t] = (int32_t)sum;
+            break;
+        }
+        }
+    }
+}
+
+/* local_bandwidth_v1/v2/v4, src/cuda/cuda_kernels/local_bandwidth.cu: after 64 rotations
+ * by one slot thread t holds the start value of thread (t + 64) % 256 of its block. */
+void orc_local_bandwidth(int width, float *out, uint64_t n_threads)
+{
+    for (uint64_t t = 0; t < n_threads; t++) {
+        const uint32_t g = (uint32_t)(t / 256 * 256 + (t % 256 + 64) % 256);
+        float s = (float)g;
+        for (int l = 1; l < width; l++) s = s + (float)(g + (uint32_t)l);
+        out[t] = s;
+    }
+}
+
+/* image_bandwidth, src/cuda/cuda_kernels/image_bandwidth.cu: 16 texel fetches per thread at
+ * (gid + i * n_threads) % texels, channel-wise sums, then x + y + z + w.  Texel values are
+ * the seeded uniform[0,1) stream, four per texel. */
+void orc_image_bandwidth(float *out, uint64_t first, uint64_t count, uint64_t n_threads, uint64_t texels, uint64_t seed)
+{
+    for (uint64_t t = first; t < first + count; t++) {
+        float s[4] = {0, 0, 0, 0};
+        for (int i = 0; i < 16; i++) {
+            const uint64_t px = (t + (uint64_t)i * n_threads) % texels;
+            for (int ch = 0; ch < 4; ch++) s[ch] = s[ch] + orc_uniform01(seed, 4 * px + (uint64_t)ch);
+        }
+        out[t - first] = ((s[0] + s[1]) + s[2]) + s[3];
+    }
+}
+
 void orc_mad_chain(float *out, uint64_t first, uint64_t n_items, uint64_t seed, float y, uint32_t iters)
 {
     for (uint64_t n = 0; n < n_items; n++) {

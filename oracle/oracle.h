@@ -81,6 +81,13 @@ double   orc_stream_pass_mt(int kind, float *a, const float *b, const float *c, 
 /* ---- chains -------------------------------------------------------------------------- */
 /* src/cuda/cuda_kernels/compute_sp.cu:12-24: x = fma(x,x,c), c = thread index in block. */
 void     orc_compute_sp(float *out, float a, uint64_t n_threads);
+/* chain = CLPK_CHAIN_* (half, half2, double, mixed, bf16, int32, int8 dot x1/2/4/8):
+ * src/cuda/cuda_kernels/compute_{hp,dp,mp,bf16,int32,int8_dp}.cu. */
+void     orc_compute_chain(int chain, void *out, double a, uint64_t n_threads);
+/* src/cuda/cuda_kernels/local_bandwidth.cu, image_bandwidth.cu. */
+void     orc_local_bandwidth(int width, float *out, uint64_t n_threads);
+/* threads [first, first + count) of a launch of n_threads */
+void     orc_image_bandwidth(float *out, uint64_t first, uint64_t count, uint64_t n_threads, uint64_t texels, uint64_t seed);
 void     orc_mad_chain(float *out, uint64_t first, uint64_t n_items, uint64_t seed, float y, uint32_t iters);
 
 /* ---- pointer chase ---------------------------------------------------------------------- */

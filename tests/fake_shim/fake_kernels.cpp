@@ -18,6 +18,9 @@
 #include "../../include/clpeak_b200_kernels.h"
 #include "../../clpeak_b200/csrc/clpk_formats.h"
 #include "../../clpeak_b200/csrc/clpk_rng.h"
+// the new chain / shared-memory / texture rows reuse the backend's own host references: this double
+// exercises the host plumbing, the numerics are pinned on the GPU against the oracle
+#include "../../clpeak_b200/csrc/host/host_check.hpp"
 
 namespace {
 thread_local char g_err[256] = "";
@@ -276,6 +279,58 @@ int clpk_compute_sp(float *out, float a, uint32_t grid, void *)
         lane[l] = x;
     }
     for (uint64_t i = 0; i < (uint64_t)grid * 256; ++i) out[i] = lane[i % 256];
+    return CLPK_OK;
+}
+
+int clpk_compute_chain_info(int chain, uint32_t *ops, uint32_t *bytes)
+{
+    if (chain < 0 || chain >= CLPK_CHAIN_COUNT) return fail(CLPK_ERR_BAD_ARG, "chain");
+    if (ops) *ops = chain >= CLPK_CHAIN_INT8_DOT1 ? 8192u : 4096u;
+    if (bytes) *bytes = chain == CLPK_CHAIN_DOUBLE ? 8u : 4u;
+    return CLPK_OK;
+}
+
+int clpk_compute_chain(int chain, void *out, double a, uint32_t grid, void *)
+{
+    if (chain < 0 || chain >= CLPK_CHAIN_COUNT) return fail(CLPK_ERR_BAD_ARG, "chain");
+    uint64_t lane[256];
+    for (unsigned l = 0; l < 256; ++l) lane[l] = b200check::typedChainBits(chain, a, l);
+    const uint64_t n = (uint64_t)grid * 256;
+    if (chain == CLPK_CHAIN_DOUBLE)
+        for (uint64_t i = 0; i < n; ++i) static_cast<uint64_t *>(out)[i] = lane[i % 256];
+    else
+        for (uint64_t i = 0; i < n; ++i) static_cast<uint32_t *>(out)[i] = (uint32_t)lane[i % 256];
+    return CLPK_OK;
+}
+
+int clpk_local_bandwidth(int width, float *out, uint32_t grid, void *)
+{
+    if (width != 1 && width != 2 && width != 4) return fail(CLPK_ERR_BAD_ARG, "width");
+    for (uint64_t i = 0; i < (uint64_t)grid * 256; ++i) out[i] = b200check::localBandwidthReference(width, i);
+    return CLPK_OK;
+}
+
+struct FakeImage { uint32_t w, h; uint64_t seed; };
+
+int clpk_image_create(void **image, uint32_t w, uint32_t h, uint64_t seed, void *)
+{
+    *image = new FakeImage{w, h, seed};
+    return CLPK_OK;
+}
+
+int clpk_image_bandwidth(void *image, float *out, uint32_t grid, void *)
+{
+    const FakeImage *im = static_cast<const FakeImage *>(image);
+    const uint64_t n = (uint64_t)grid * 256, texels = (uint64_t)im->w * im->h;
+    // exact for the threads the host samples (the first and the last 256), zero elsewhere
+    for (uint64_t i = 0; i < n; ++i)
+        out[i] = (i < 256 || i + 256 >= n) ? b200check::imageBandwidthReference(i, n, texels, im->seed) : 0.0f;
+    return CLPK_OK;
+}
+
+int clpk_image_destroy(void *image)
+{
+    delete static_cast<FakeImage *>(image);
     return CLPK_OK;
 }
 

@@ -116,7 +116,21 @@ def test_selection_grammar(ffi, one_device):
     assert tests_run(["--latency", "--no-memory-latency"]) == ["kernel_launch_latency"]
     assert tests_run(["--no-cuda"]) == []
     assert tests_run(["--cpu"]) == []                         # positive backend flag: only the named backends
-    assert tests_run(["--cuda", "--int-compute", "--no-cublas"]) == ["wmma_int4", "wmma_int8", "wmma_int8_k32", "wmma_int8_sparse"]
+    assert tests_run(["--cuda", "--int-compute", "--no-cublas"]) == [
+        "integer_compute", "integer_compute_int8_dp", "wmma_int4", "wmma_int8", "wmma_int8_k32", "wmma_int8_sparse"]
+    assert tests_run(["--half-precision-compute", "--double-precision-compute", "--mixed-precision-compute",
+                      "--bfloat16-compute"]) == ["bfloat16_compute", "double_precision_compute",
+                                                 "half_precision_compute", "mixed_precision_compute"]
+    assert tests_run(["--bandwidth", "--no-global-memory-bandwidth", "--no-transfer-bandwidth"]) == [
+        "image_memory_bandwidth", "local_memory_bandwidth"]
+    rc, ev = ffi.launch(["--integer-compute", "--int8-dot-product-compute", "--local-memory-bandwidth",
+                         "--image-memory-bandwidth", "--half-precision-compute", *FAST])
+    rows = {(e["test"], e["metric"]): e for e in ev if e["t"] == "metric"}
+    for key in (("integer_compute", "int"), ("integer_compute_int8_dp", "int8_dp"), ("integer_compute_int8_dp", "int8_dp8"),
+                ("half_precision_compute", "half2"), ("local_memory_bandwidth", "float4"),
+                ("image_memory_bandwidth", "float4")):
+        assert rows[key]["status"] == "ok" and rows[key]["value"] > 0, rows[key]
+    assert rows[("integer_compute", "int")]["unit"] == "gops" and rows[("local_memory_bandwidth", "float")]["unit"] == "gbps"
     both = tests_run(["--wmma", "--no-fp-compute"])
     assert "wmma_int8_k32" in both and "wmma_bf16" not in both
 

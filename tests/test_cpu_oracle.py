@@ -214,3 +214,81 @@ def test_mma_tile_oracle_against_numpy(orc):
     i8 = M.make_operands(orc, N.MMA_I8)
     want = (i8["a"].astype(np.int64) @ i8["b"].astype(np.int64).T) * 5
     assert np.array_equal(orc.mma_tile_i8(i8["a"], i8["b"], 5), want.astype(np.int32))
+
+
+# ---- typed chains, shared-memory rotation, texture read -------------------------------------
+
+def test_int32_chain_against_python_integers(orc):
+    got = orc.compute_chain(5, 3, 256)
+    for tid in (0, 1, 2, 97, 255):
+        x = 3
+        for _ in range(2048):
+            x = (x * x + tid) & 0xFFFFFFFF
+        assert int(got[tid]) & 0xFFFFFFFF == x
+
+
+def _dp4a(x, y, a):
+    s = a
+    for b in range(4):
+        xb = (x >> (8 * b)) & 0xFF
+        yb = (y >> (8 * b)) & 0xFF
+        s += (xb - 256 if xb > 127 else xb) * (yb - 256 if yb > 127 else yb)
+    s &= 0xFFFFFFFF
+    return s - (1 << 32) if s >= (1 << 31) else s
+
+
+@pytest.mark.parametrize("row", [0, 1, 2, 3])
+def test_int8_dot_chains_against_python_integers(orc, row):
+    offsets = [[0], [0, 7], [0, 7, 13, 19], [0, 11, 17, 23, 29, 31, 37, 41]][row]
+    chains = 1 << row
+    got = orc.compute_chain(6 + row, 4, 256)
+    x = 4 | (5 << 8) | (6 << 16) | (7 << 24)          # the reference packs A, A+1, A+2, A+3 with A = 4
+    for tid in (0, 3, 200, 255):
+        y = [(tid + j) & 0xFFFFFFFF for j in range(chains)]
+        acc = [tid + offsets[j] for j in range(chains)]
+        for _ in range(64 // chains):
+            for j in range(chains):
+                for _ in range(16):
+                    acc[j] = _dp4a(x, y[j], acc[j])
+                    y[j] ^= acc[j] & 0xFFFFFFFF
+        total = sum(a & 0xFFFFFFFF for a in acc) & 0xFFFFFFFF
+        assert int(got[tid]) & 0xFFFFFFFF == total
+
+
+def test_floating_chains_run_away_like_the_reference(orc):
+    # x = x*x + c from 1.3 overflows every format within a few steps: the stored value is +inf
+    for chain in (0, 1, 2, 3, 4):
+        out = orc.compute_chain(chain, 1.3, 256)
+        assert np.all(np.isinf(out)) and np.all(out > 0)
+
+
+def test_half_chain_small_start_against_numpy_float16(orc):
+    # thread 0 (c = 0) from 0.5: repeated squaring in half, underflows to zero; thread 1 runs away
+    got = orc.compute_chain(1, 0.5, 2)
+    x = np.float16(0.5)
+    for _ in range(1024):
+        x = np.float16(np.float64(x) * np.float64(x))
+    assert got[0] == np.float32(x) + np.float32(x) == 0.0
+    assert np.isinf(got[1])
+    # mixed chain, thread 0, a few exact steps: 0.5 -> 2^-2 -> ... stays a power of two until it underflows
+    assert orc.compute_chain(3, 0.5, 1)[0] == 0.0
+
+
+def test_local_bandwidth_closed_form(orc):
+    out = orc.local_bandwidth(4, 512)
+    assert out[0] == 64 + 65 + 66 + 67 and out[200] == sum(range(8, 12)) and out[256] == sum(range(320, 324))
+    assert orc.local_bandwidth(1, 256)[255] == 63.0
+
+
+def test_image_bandwidth_reads_every_texel_once(orc):
+    threads, texels, seed = 64, 1024, 9
+    out = orc.image_bandwidth(threads, texels, seed)
+    vals = orc.fill_f32(4 * texels, seed, 0)
+    assert abs(float(out.astype(np.float64).sum()) - float(vals.astype(np.float64).sum())) < 1e-2
+    # thread 5: texels 5, 69, 133, ...; channel-wise sums in order
+    s = np.zeros(4, dtype=np.float32)
+    for i in range(16):
+        px = (5 + i * threads) % texels
+        s = (s + vals[4 * px:4 * px + 4]).astype(np.float32)
+    assert out[5] == np.float32(np.float32(np.float32(s[0] + s[1]) + s[2]) + s[3])
+    assert np.array_equal(orc.image_bandwidth(threads, texels, seed, first=10, count=7), out[10:17])
