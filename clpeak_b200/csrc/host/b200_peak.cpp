@@ -326,12 +326,18 @@ struct B200Harness {
             {CLPK_MMA_F16, "wmma_fp16", "tcgen05 fp16xfp16+fp32 128x256x16", "wmma_fp16", "tflops", kSpecBf16Tflops, "dense fp16 TFLOPS",
              "Peak speed of the tensor cores on 16-bit inputs with a 32-bit running total, issued as Blackwell tcgen05.mma "
              "instructions that accumulate in tensor memory.  This is the everyday precision of AI work."},
+            {CLPK_MMA_F16_F16, "wmma_fp16_f16", "tcgen05 fp16xfp16+fp16 128x256x16", "fp16_f16acc", "tflops", kSpecBf16Tflops, "dense fp16 TFLOPS",
+             "The same 16-bit tensor-core path keeping its running total in 16 bits as well -- cheaper to store, easier to overflow."},
             {CLPK_MMA_BF16, "wmma_bf16", "tcgen05 bf16xbf16+fp32 128x256x16", "wmma_bf16", "tflops", kSpecBf16Tflops, "dense bf16 TFLOPS",
              "Tensor cores on bfloat16 -- 16 bits arranged for AI work, trading digits of accuracy for the number range of a full float."},
+            {CLPK_MMA_TF32, "wmma_tf32", "tcgen05 tf32xtf32+fp32 128x256x8", "wmma_tf32", "tflops", kSpecBf16Tflops / 2, "dense tf32 TFLOPS",
+             "Tensor cores on TF32: 32-bit storage of which the multiplier reads 19 bits, NVIDIA's drop-in speed-up for float code."},
             {CLPK_MMA_E4M3, "wmma_fp8_e4m3", "tcgen05 FP8(E4M3)+fp32 128x256x32", "fp8_e4m3", "tflops", kSpecFp8Tflops, "dense fp8 TFLOPS",
              "Tensor cores on 8-bit numbers, in the variant that spends its bits on accuracy rather than range."},
             {CLPK_MMA_E5M2, "wmma_fp8_e5m2", "tcgen05 FP8(E5M2)+fp32 128x256x32", "fp8_e5m2", "tflops", kSpecFp8Tflops, "dense fp8 TFLOPS",
              "The same 8-bit tensor-core path in the variant that spends its bits on range rather than accuracy."},
+            {CLPK_MMA_E2M1, "wmma_fp4_e2m1", "tcgen05 FP4(E2M1) unscaled 128x256x32", "fp4_e2m1", "tflops", kSpecFp8Tflops, "dense fp8 TFLOPS (this path runs at the 8-bit rate)",
+             "4-bit numbers fed through the 8-bit tensor-core path without block scale factors: storage halves, speed does not."},
             {CLPK_MMA_MXF4, "wmma_mxf4_e2m1", "tcgen05 MXFP4(E2M1) block-scaled 128x256x64", "mxf4_e2m1", "tflops", kSpecFp4Tflops, "dense fp4 TFLOPS",
              "4-bit numbers with a shared scale factor per block of 32, the open MX format."},
             {CLPK_MMA_NVF4, "wmma_nvf4_e2m1", "tcgen05 NVFP4(E2M1) block-scaled 128x256x64", "nvf4_e2m1", "tflops", kSpecFp4Tflops, "dense fp4 TFLOPS",
@@ -368,8 +374,11 @@ struct B200Harness {
             }
             if (!scaled) {
                 rc |= clpk_fill_f32(f32.as<float>(), (uint64_t)rows * K, 2 + first, CLPK_DIST_UNIFORM_PM1, 0, 1, w.stream);
-                const int dt = kind == CLPK_MMA_F16 ? CLPK_DT_F16 : kind == CLPK_MMA_BF16 ? CLPK_DT_BF16
-                             : kind == CLPK_MMA_E4M3 ? CLPK_DT_E4M3 : CLPK_DT_E5M2;
+                const int dt = (kind == CLPK_MMA_F16 || kind == CLPK_MMA_F16_F16) ? CLPK_DT_F16 : kind == CLPK_MMA_BF16 ? CLPK_DT_BF16
+                             : kind == CLPK_MMA_E4M3 ? CLPK_DT_E4M3 : kind == CLPK_MMA_TF32 ? CLPK_DT_TF32
+                             : kind == CLPK_MMA_E2M1 ? CLPK_DT_E2M1 : CLPK_DT_E5M2;
+                if (kind == CLPK_MMA_E2M1)      // spread over e2m1's +-6 range
+                    rc |= clpk_fill_f32(f32.as<float>(), (uint64_t)rows * K, 2 + first, CLPK_DIST_NORMAL, 0, 2, w.stream);
                 rc |= clpk_convert_f32(dst, f32.as<float>(), (uint64_t)rows * K, dt, w.stream);
                 return;
             }
@@ -414,7 +423,20 @@ struct B200Harness {
             if (c != chk[0])
                 return fail("CTAs disagree on the accumulator checksum");
         double worst = 0;
-        const std::string verdict = b200check::checkTile(kind, hA.data(), hB.data(), hSfa.data(), hSfb.data(), nMma, tile.data(), &worst);
+        std::string verdict;
+        if (kind == CLPK_MMA_F16_F16) {
+            // 2^14 additions saturate a 16-bit running total; the arithmetic is checked on one instruction
+            a.n_mma = 1;
+            a.grid = 1;
+            if (clpk_mma_peak(&a, w.stream) != CLPK_OK)
+                return fail(shimError("single-instruction launch"));
+            clpk_memcpy_d2h(tile.data(), dOut.p, tile.size() * 4, w.stream);
+            if (clpk_stream_sync(w.stream) != CLPK_OK)
+                return fail(shimError("read back"));
+            verdict = b200check::checkHalfAccumTile(hA.data(), hB.data(), tile.data(), &worst);
+        } else {
+            verdict = b200check::checkTile(kind, hA.data(), hB.data(), hSfa.data(), hSfb.data(), nMma, tile.data(), &worst);
+        }
         if (!verdict.empty())
             return fail("accumulator check failed: " + verdict);
 
@@ -1127,18 +1149,14 @@ int CudaPeak::runAll()
             }
     }
     if (fp) {
-        for (const auto &row : H::kindRows())
-            if (row.kind != CLPK_MMA_I8)
-                plan.push_back([row](B200Worker &w, B200TestResult &o) { H::tensorPeak(w, o, row); });
-        struct NB { const char *tag, *display, *metric, *why; };
-        static const NB notBuilt[] = {
-            {"wmma_fp16_f16", "tcgen05 fp16 with fp16 accumulate", "fp16_f16acc", "fp16-accumulate tcgen05 path is not built yet"},
-            {"wmma_tf32", "tcgen05 tf32", "wmma_tf32", "kind::tf32 path is not built yet"},
-            {"wmma_fp64", "fp64 tensor path", "wmma_fp64", "tcgen05 has no fp64 kind"},
-            {"wmma_fp4_e2m1", "tcgen05 FP4(E2M1) unscaled", "fp4_e2m1", "unscaled fp4 (kind::f8f6f4) path is not built yet"},
-        };
-        for (const NB &nb : notBuilt)
-            plan.push_back([nb](B200Worker &, B200TestResult &o) { H::tensorNotBuilt(o, nb.tag, nb.display, nb.metric, "tflops", nb.why); });
+        // the reference's row order (src/cuda/wmma.cpp): fp16, fp16 acc, bf16, tf32, fp64, fp8 x2, fp4, mxf4, nvf4, sparse
+        for (const auto &row : H::kindRows()) {
+            if (row.kind == CLPK_MMA_I8)
+                continue;
+            plan.push_back([row](B200Worker &w, B200TestResult &o) { H::tensorPeak(w, o, row); });
+            if (row.kind == CLPK_MMA_TF32)
+                plan.push_back([](B200Worker &, B200TestResult &o) { H::tensorNotBuilt(o, "wmma_fp64", "fp64 tensor path", "wmma_fp64", "tflops", "tcgen05 has no fp64 kind"); });
+        }
         for (const auto &row : H::sparseRows(false))
             plan.push_back([row](B200Worker &w, B200TestResult &o) { H::tensorSparse(w, o, row); });
     }

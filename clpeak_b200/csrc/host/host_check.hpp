@@ -191,8 +191,9 @@ inline float readSumReference(const float *in, int width, uint64_t outIndex)
 inline int kindK(int kind)
 {
     switch (kind) {
-    case CLPK_MMA_F16: case CLPK_MMA_BF16: return 16;
-    case CLPK_MMA_E4M3: case CLPK_MMA_E5M2: case CLPK_MMA_I8: return 32;
+    case CLPK_MMA_TF32: return 8;
+    case CLPK_MMA_F16: case CLPK_MMA_BF16: case CLPK_MMA_F16_F16: return 16;
+    case CLPK_MMA_E4M3: case CLPK_MMA_E5M2: case CLPK_MMA_I8: case CLPK_MMA_E2M1: return 32;
     default: return 64;
     }
 }
@@ -201,7 +202,13 @@ inline double decodeOperand(int kind, const uint8_t *t, const uint8_t *sf, int r
 {
     const int K = kindK(kind);
     switch (kind) {
-    case CLPK_MMA_F16: return clpk_f16_decode(reinterpret_cast<const uint16_t *>(t)[row * K + k]);
+    case CLPK_MMA_F16: case CLPK_MMA_F16_F16:
+        return clpk_f16_decode(reinterpret_cast<const uint16_t *>(t)[row * K + k]);
+    case CLPK_MMA_TF32: return reinterpret_cast<const float *>(t)[row * K + k];
+    case CLPK_MMA_E2M1: {
+        const uint8_t byte = t[(row * K + k) / 2];
+        return clpk_e2m1_decode((k & 1) ? (byte >> 4) : (byte & 0xF));
+    }
     case CLPK_MMA_BF16: return clpk_bf16_decode(reinterpret_cast<const uint16_t *>(t)[row * K + k]);
     case CLPK_MMA_E4M3: return clpk_e4m3_decode(t[row * K + k]);
     case CLPK_MMA_E5M2: return clpk_e5m2_decode(t[row * K + k]);
@@ -268,6 +275,32 @@ inline std::string checkTile(int kind, const uint8_t *a, const uint8_t *b, const
         for (int k = 0; k < K; ++k)
             db[r * K + k] = decodeOperand(kind, b, sfb, r, k);
     return checkDecodedTile(da, db, K, kind == CLPK_MMA_I8, n, tile, worstRatio);
+}
+
+// fp16-accumulate tile after ONE instruction: each output word holds a half in its low 16
+// bits; it must lie within 2^-10 of the exact product relative to sum|a||b| (one rounding
+// to half, plus whatever the data path loses before it).
+inline std::string checkHalfAccumTile(const uint8_t *a, const uint8_t *b, const uint32_t *tile, double *worstRatio = nullptr)
+{
+    double worst = 0.0;
+    for (int i = 0; i < 128; ++i)
+        for (int j = 0; j < 256; ++j) {
+            double p = 0.0, s = 0.0;
+            for (int k = 0; k < 16; ++k) {
+                const double t = (double)decodeOperand(CLPK_MMA_F16, a, nullptr, i, k) * (double)decodeOperand(CLPK_MMA_F16, b, nullptr, j, k);
+                p += t;
+                s += std::fabs(t);
+            }
+            const double got = clpk_f16_decode((uint16_t)(tile[i * 256 + j] & 0xFFFFu));
+            const double ratio = std::fabs(got - p) / (std::ldexp(1.0, -10) * s + 1e-30);
+            worst = std::max(worst, ratio);
+            if (!(ratio <= 1.0))
+                return "fp16 accumulator off by " + std::to_string(ratio) + "x the bound at (" + std::to_string(i) + "," +
+                       std::to_string(j) + ")";
+        }
+    if (worstRatio)
+        *worstRatio = worst;
+    return {};
 }
 
 // ---- 2:4 sparse kinds ---------------------------------------------------------------------

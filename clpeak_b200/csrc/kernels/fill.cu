@@ -52,6 +52,14 @@ __global__ void convert_kernel(void *dst, const float *src, uint64_t n, int dtyp
         case CLPK_DT_E5M2:
             reinterpret_cast<uint8_t *>(dst)[i] = __nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E5M2);
             break;
+        case CLPK_DT_TF32: {
+            // nearest even at bit 13 in integer arithmetic (infinities and NaNs keep their class)
+            uint32_t b = __float_as_uint(x);
+            if ((b & 0x7F800000u) != 0x7F800000u)
+                b += 0xFFFu + ((b >> 13) & 1u);
+            reinterpret_cast<uint32_t *>(dst)[i] = b & 0xFFFFE000u;
+            break;
+        }
         case CLPK_DT_I8: {
             int v = __float2int_rn(x);
             v = v < -128 ? -128 : (v > 127 ? 127 : v);
@@ -62,6 +70,13 @@ __global__ void convert_kernel(void *dst, const float *src, uint64_t n, int dtyp
             break;
         }
     }
+}
+
+__global__ void convert_e2m1_kernel(uint8_t *dst, const float *src, uint64_t n_pairs)
+{
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_pairs; i += stride)
+        dst[i] = (uint8_t)(clpk_e2m1_encode(src[2 * i]) | (clpk_e2m1_encode(src[2 * i + 1]) << 4));
 }
 
 __global__ void absmax_kernel(float *out, const float *src, uint64_t n)
@@ -161,10 +176,16 @@ int clpk_convert_f32(void *d_dst, const float *d_src, uint64_t n, int dtype, voi
 {
     CLPK_REQUIRE((d_dst && d_src) || n == 0, "NULL buffer");
     CLPK_REQUIRE(dtype == CLPK_DT_F16 || dtype == CLPK_DT_BF16 || dtype == CLPK_DT_E4M3 ||
-                     dtype == CLPK_DT_E5M2 || dtype == CLPK_DT_I8,
+                     dtype == CLPK_DT_E5M2 || dtype == CLPK_DT_I8 || dtype == CLPK_DT_TF32 || dtype == CLPK_DT_E2M1,
                  "clpk_convert_f32: dtype %d has no plain conversion", dtype);
     if (n == 0)
         return CLPK_OK;
+    if (dtype == CLPK_DT_E2M1) {
+        CLPK_REQUIRE(n % 2 == 0, "E2M1 packs two elements per byte: n (%llu) must be even", (unsigned long long)n);
+        convert_e2m1_kernel<<<fill_grid(), 256, 0, as_stream(stream)>>>(static_cast<uint8_t *>(d_dst), d_src, n / 2);
+        CLPK_LAUNCH_CHECK("convert_e2m1");
+        return CLPK_OK;
+    }
     convert_kernel<<<fill_grid(), 256, 0, as_stream(stream)>>>(d_dst, d_src, n, dtype);
     CLPK_LAUNCH_CHECK("convert");
     return CLPK_OK;

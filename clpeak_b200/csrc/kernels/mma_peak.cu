@@ -20,6 +20,10 @@
 // r / 32 of the scale area, replicated in all four 32-lane quarters; B's 256
 // rows take 8 columns the same way.  The probes write them with tcgen05.st.
 //
+// kind::tf32 reads 32-bit words (K = 8 per instruction) and ignores the low 13 mantissa
+// bits; the fp16-accumulate variant of kind::f16 keeps a 16-bit accumulator in the low
+// half of each 32-bit tensor-memory cell.
+//
 // Residency: dense kinds take 256 TMEM columns, so two CTAs fit one SM; the
 // launch asks for enough dynamic shared memory that a third never becomes
 // resident (tcgen05.alloc would otherwise block on it).  Kinds with scale
@@ -59,8 +63,24 @@ __device__ __forceinline__ void stage_tile(uint8_t *smem_tile, const uint8_t *g,
     }
 }
 
+// Unscaled 4-bit operands of kind::f8f6f4: the input tile is [rows][32] e2m1 packed two per
+// byte (16 bytes per row); in shared memory every 16 elements (8 bytes) sit at the start of
+// a 16-byte slot whose other half is padding, so a row again takes two 16-byte chunks.
+__device__ __forceinline__ void stage_tile_fp4_padded(uint8_t *smem_tile, const uint8_t *g, int rows)
+{
+    const int chunks = rows * 2;
+    for (int i = threadIdx.x; i < chunks; i += blockDim.x) {
+        const int r = i >> 1, kc = i & 1;
+        const uint2 v = *reinterpret_cast<const uint2 *>(g + (size_t)r * 16 + kc * 8);
+        *reinterpret_cast<uint4 *>(smem_tile + (r >> 3) * 256 + kc * 128 + (r & 7) * 16) = make_uint4(v.x, v.y, 0u, 0u);
+    }
+}
+
 template <int KIND>
 struct KindTraits;
+template <> struct KindTraits<CLPK_MMA_TF32>    { static constexpr bool scaled = false; static constexpr int sf_per_row = 0; };
+template <> struct KindTraits<CLPK_MMA_F16_F16> { static constexpr bool scaled = false; static constexpr int sf_per_row = 0; };
+template <> struct KindTraits<CLPK_MMA_E2M1>    { static constexpr bool scaled = false; static constexpr int sf_per_row = 0; };
 template <> struct KindTraits<CLPK_MMA_F16>  { static constexpr bool scaled = false; static constexpr int sf_per_row = 0; };
 template <> struct KindTraits<CLPK_MMA_BF16> { static constexpr bool scaled = false; static constexpr int sf_per_row = 0; };
 template <> struct KindTraits<CLPK_MMA_E4M3> { static constexpr bool scaled = false; static constexpr int sf_per_row = 0; };
@@ -83,6 +103,12 @@ __device__ __forceinline__ void issue_mma(uint32_t d, uint64_t ad, uint64_t bd, 
         mma_f8f6f4_ss(d, ad, bd, make_idesc(kTileM, kTileN, kFmtE5M2, kFmtE5M2, kAccF32), acc);
     } else if constexpr (KIND == CLPK_MMA_I8) {
         mma_i8_ss(d, ad, bd, make_idesc(kTileM, kTileN, kFmtS8, kFmtS8, kAccS32), acc);
+    } else if constexpr (KIND == CLPK_MMA_TF32) {
+        mma_tf32_ss(d, ad, bd, make_idesc(kTileM, kTileN, kFmtTF32, kFmtTF32, kAccF32), acc);
+    } else if constexpr (KIND == CLPK_MMA_F16_F16) {
+        mma_f16_ss(d, ad, bd, make_idesc(kTileM, kTileN, kFmtF16, kFmtF16, kAccF16), acc);
+    } else if constexpr (KIND == CLPK_MMA_E2M1) {
+        mma_f8f6f4_ss(d, ad, bd, make_idesc(kTileM, kTileN, kFmtE2M1x8, kFmtE2M1x8, kAccF32), acc);
     } else if constexpr (KIND == CLPK_MMA_MXF4) {
         mma_mxf4_bs(d, ad, bd,
                     make_idesc_block_scaled(kTileM, kTileN, kFmtE2M1, kFmtE2M1, /*ue8m0*/ 1, 0, 0),
@@ -109,8 +135,13 @@ __global__ void __launch_bounds__(128) mma_peak_kernel(PeakParams p)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    stage_tile(sA, p.a, kTileM);
-    stage_tile(sB, p.b, kTileN);
+    if constexpr (KIND == CLPK_MMA_E2M1) {
+        stage_tile_fp4_padded(sA, p.a, kTileM);
+        stage_tile_fp4_padded(sB, p.b, kTileN);
+    } else {
+        stage_tile(sA, p.a, kTileM);
+        stage_tile(sB, p.b, kTileN);
+    }
     if (threadIdx.x == 0) {
         mbar_init(bar, 1);
         mbar_fence_init();
@@ -375,6 +406,9 @@ static bool kind_info(int kind, KindInfo *ki)
     case CLPK_MMA_E4M3:    *ki = {32, false, false}; return true;
     case CLPK_MMA_E5M2:    *ki = {32, false, false}; return true;
     case CLPK_MMA_I8:      *ki = {32, false, false}; return true;
+    case CLPK_MMA_TF32:    *ki = {8, false, false};  return true;
+    case CLPK_MMA_F16_F16: *ki = {16, false, false}; return true;
+    case CLPK_MMA_E2M1:    *ki = {32, false, false}; return true;
     case CLPK_MMA_MXF4:    *ki = {64, true, false};  return true;
     case CLPK_MMA_NVF4:    *ki = {64, true, false};  return true;
     case CLPK_MMA_E4M3_SP: *ki = {64, false, true};  return true;
@@ -459,6 +493,9 @@ int clpk_mma_peak(const clpk_mma_peak_args_t *a, void *stream)
     case CLPK_MMA_E4M3: return launch_peak<CLPK_MMA_E4M3>(p, a->grid, s);
     case CLPK_MMA_E5M2: return launch_peak<CLPK_MMA_E5M2>(p, a->grid, s);
     case CLPK_MMA_I8:   return launch_peak<CLPK_MMA_I8>(p, a->grid, s);
+    case CLPK_MMA_TF32: return launch_peak<CLPK_MMA_TF32>(p, a->grid, s);
+    case CLPK_MMA_F16_F16: return launch_peak<CLPK_MMA_F16_F16>(p, a->grid, s);
+    case CLPK_MMA_E2M1: return launch_peak<CLPK_MMA_E2M1>(p, a->grid, s);
     case CLPK_MMA_MXF4: return launch_peak<CLPK_MMA_MXF4>(p, a->grid, s);
     case CLPK_MMA_NVF4: return launch_peak<CLPK_MMA_NVF4>(p, a->grid, s);
     default: break;

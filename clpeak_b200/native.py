@@ -16,10 +16,11 @@ LIB_DIR = Path(__file__).resolve().parent / "_lib"
 OK, ERR_CUDA, ERR_BAD_ARG, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_NO_DEVICE, ERR_TOO_LARGE = range(7)
 
 DIST_UNIFORM01, DIST_UNIFORM_PM1, DIST_NORMAL = 0, 1, 2
-DT_F32, DT_F16, DT_BF16, DT_E4M3, DT_E5M2, DT_I8, DT_MXF4, DT_NVF4, DT_MXF4_B64, DT_NVF4_B32 = range(10)
+(DT_F32, DT_F16, DT_BF16, DT_E4M3, DT_E5M2, DT_I8, DT_MXF4, DT_NVF4, DT_MXF4_B64, DT_NVF4_B32, DT_TF32,
+ DT_E2M1) = range(12)
 STREAM_LDG, STREAM_TMA = 0, 1
 (MMA_F16, MMA_BF16, MMA_E4M3, MMA_E5M2, MMA_I8, MMA_MXF4, MMA_NVF4,
- MMA_E4M3_SP, MMA_MXF4_SP, MMA_NVF4_SP, MMA_I8_SP) = range(11)
+ MMA_E4M3_SP, MMA_MXF4_SP, MMA_NVF4_SP, MMA_I8_SP, MMA_TF32, MMA_F16_F16, MMA_E2M1) = range(14)
 
 (CHAIN_HALF, CHAIN_HALF2, CHAIN_DOUBLE, CHAIN_MIXED, CHAIN_BF16, CHAIN_INT32, CHAIN_INT8_DOT1, CHAIN_INT8_DOT2,
  CHAIN_INT8_DOT4, CHAIN_INT8_DOT8) = range(10)
@@ -31,6 +32,7 @@ MMA_KIND_NAMES = {
     MMA_F16: "fp16", MMA_BF16: "bf16", MMA_E4M3: "fp8_e4m3", MMA_E5M2: "fp8_e5m2", MMA_I8: "int8",
     MMA_MXF4: "mxf4_e2m1", MMA_NVF4: "nvf4_e2m1", MMA_E4M3_SP: "fp8_e4m3_sparse",
     MMA_MXF4_SP: "mxf4_sparse", MMA_NVF4_SP: "nvf4_sparse", MMA_I8_SP: "int8_sparse",
+    MMA_TF32: "tf32", MMA_F16_F16: "fp16_f16acc", MMA_E2M1: "fp4_e2m1",
 }
 
 

@@ -116,10 +116,13 @@ CLPK_API int clpk_fill_i8(int8_t *d_dst, uint64_t n, uint64_t seed, void *stream
 #define CLPK_DT_NVF4  7   /* e2m1 pairs + one ue4m3 scale per 16 elements + fp32 scale */
 #define CLPK_DT_MXF4_B64 8   /* as MXF4 with one ue8m0 scale per 64: the dense B operand of MXF4_SP */
 #define CLPK_DT_NVF4_B32 9   /* as NVF4 with one ue4m3 scale per 32: the dense B operand of NVF4_SP */
+#define CLPK_DT_TF32  10  /* fp32 word rounded (nearest even) to 10 mantissa bits, low 13 bits clear       */
+#define CLPK_DT_E2M1  11  /* plain e2m1, two per byte (element 2i in the low nibble), saturating at +-6   */
 
 /* Round-to-nearest-even conversion of n floats to a plain (unscaled) format:
  * F16, BF16, E4M3 / E5M2 (saturating to the largest finite value), I8
- * (round-to-nearest-even, saturating). */
+ * (round-to-nearest-even, saturating), TF32 (a 4-byte word per element) and E2M1
+ * (two per byte; n must be even). */
 CLPK_API int clpk_convert_f32(void *d_dst, const float *d_src, uint64_t n, int dtype, void *stream);
 
 /* max |x| over n floats -> *d_absmax (a float the call overwrites). */
@@ -275,6 +278,9 @@ CLPK_API int clpk_launch_latency(uint32_t iters, uint32_t warmup, double *mean_u
  *   F16    16   fp16               f32      BF16  16  bf16  f32
  *   E4M3   32   fp8 e4m3           f32      E5M2  32  e5m2  f32
  *   I8     32   int8               s32
+ *   TF32    8   fp32 word, 10-bit mantissa   f32
+ *   F16_F16 16  fp16               f16 (one half per 32-bit output word, bits 0..15)
+ *   E2M1   32   e2m1 x2 per byte   f32   unscaled 4-bit operands of kind::f8f6f4; 16 bytes per row
  *   MXF4   64   e2m1 x2 per byte   f32   + ue8m0 scale per 32 (d_sfa [128][2], d_sfb [256][2])
  *   NVF4   64   e2m1 x2 per byte   f32   + ue4m3 scale per 16 (d_sfa [128][4], d_sfb [256][4])
  *   E4M3_SP / I8_SP   K = 64 logical, 2:4 sparse A: d_a is the compressed tile
@@ -305,7 +311,10 @@ CLPK_API int clpk_launch_latency(uint32_t iters, uint32_t warmup, double *mean_u
 #define CLPK_MMA_MXF4_SP  8
 #define CLPK_MMA_NVF4_SP  9
 #define CLPK_MMA_I8_SP    10
-#define CLPK_MMA_KIND_COUNT 11
+#define CLPK_MMA_TF32     11  /* K = 8: fp32 words with the low 13 mantissa bits clear (CLPK_DT_TF32), f32 accumulate  */
+#define CLPK_MMA_F16_F16  12  /* K = 16: fp16 operands, fp16 accumulate; output words hold the half in bits 0..15   */
+#define CLPK_MMA_E2M1     13  /* K = 32: unscaled e2m1 through kind::f8f6f4; tiles [rows][16 bytes], two per byte    */
+#define CLPK_MMA_KIND_COUNT 14
 
 typedef struct clpk_mma_peak_args {
     int         kind;

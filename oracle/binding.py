@@ -102,11 +102,17 @@ def fill_i8(n: int, seed: int, first: int = 0) -> np.ndarray:
     return out
 
 
-_DT_NP = {1: np.uint16, 2: np.uint16, 3: np.uint8, 4: np.uint8, 5: np.int8}
+_DT_NP = {1: np.uint16, 2: np.uint16, 3: np.uint8, 4: np.uint8, 5: np.int8, 10: np.uint32}
 
 
 def convert_f32(src: np.ndarray, dtype: int) -> np.ndarray:
+    """Plain conversions; dtype 10 (TF32) returns the fp32 words, 11 (E2M1) a flat array of n/2 packed bytes."""
     src = np.ascontiguousarray(src, dtype=np.float32)
+    if dtype == 11:
+        assert src.size % 2 == 0
+        out = np.zeros(src.size // 2, dtype=np.uint8)
+        lib().orc_convert_f32(ptr(out), ptr(src), src.size, dtype)
+        return out
     out = np.empty(src.shape, dtype=_DT_NP[dtype])
     lib().orc_convert_f32(ptr(out), ptr(src), src.size, dtype)
     return out

@@ -18,12 +18,13 @@
 
 /* dtype / kind numbering mirrors include/clpeak_b200_kernels.h */
 enum { DT_F32 = 0, DT_F16 = 1, DT_BF16 = 2, DT_E4M3 = 3, DT_E5M2 = 4, DT_I8 = 5, DT_MXF4 = 6, DT_NVF4 = 7,
-       DT_MXF4_B64 = 8, DT_NVF4_B32 = 9 };
+       DT_MXF4_B64 = 8, DT_NVF4_B32 = 9, DT_TF32 = 10, DT_E2M1 = 11 };
 
 static int fp4_block(int dtype) { return dtype == DT_MXF4 ? 32 : dtype == DT_NVF4 ? 16 : dtype == DT_MXF4_B64 ? 64 : 32; }
 static int fp4_is_mx(int dtype) { return dtype == DT_MXF4 || dtype == DT_MXF4_B64; }
 enum { MMA_F16 = 0, MMA_BF16 = 1, MMA_E4M3 = 2, MMA_E5M2 = 3, MMA_I8 = 4, MMA_MXF4 = 5, MMA_NVF4 = 6,
-       MMA_E4M3_SP = 7, MMA_MXF4_SP = 8, MMA_NVF4_SP = 9, MMA_I8_SP = 10 };
+       MMA_E4M3_SP = 7, MMA_MXF4_SP = 8, MMA_NVF4_SP = 9, MMA_I8_SP = 10, MMA_TF32 = 11, MMA_F16_F16 = 12,
+       MMA_E2M1 = 13 };
 
 static uint32_t f2u(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
 static float u2f(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
@@ -286,6 +287,18 @@ void orc_convert_f32(void *dst, const float *src, uint64_t n, int dtype)
         case DT_E4M3: ((uint8_t *)dst)[i] = orc_f32_to_e4m3(src[i]); break;
         case DT_E5M2: ((uint8_t *)dst)[i] = orc_f32_to_e5m2(src[i]); break;
         case DT_I8:   ((int8_t *)dst)[i] = orc_f32_to_i8(src[i]); break;
+        case DT_TF32: {     /* nearest even at bit 13; infinities and NaNs keep their class */
+            uint32_t b; memcpy(&b, &src[i], 4);
+            if ((b & 0x7F800000u) != 0x7F800000u) b += 0xFFFu + ((b >> 13) & 1u);
+            ((uint32_t *)dst)[i] = b & 0xFFFFE000u;
+            break;
+        }
+        case DT_E2M1: {     /* two per byte, even element in the low nibble (n even) */
+            uint8_t nib = orc_f32_to_e2m1(src[i]);
+            uint8_t *byte = &((uint8_t *)dst)[i / 2];
+            *byte = (i & 1) ? (uint8_t)((*byte & 0x0F) | (nib << 4)) : nib;
+            break;
+        }
         default: break;
         }
     }
@@ -641,8 +654,9 @@ void orc_chase(const uint32_t *next, uint32_t start, uint64_t hops, uint32_t *fi
 static int kind_k(int kind)
 {
     switch (kind) {
-    case MMA_F16: case MMA_BF16: return 16;
-    case MMA_E4M3: case MMA_E5M2: case MMA_I8: return 32;
+    case MMA_TF32: return 8;
+    case MMA_F16: case MMA_BF16: case MMA_F16_F16: return 16;
+    case MMA_E4M3: case MMA_E5M2: case MMA_I8: case MMA_E2M1: return 32;
     default: return 64;
     }
 }
@@ -650,7 +664,13 @@ static int kind_k(int kind)
 static double decode_elem(int kind, const void *t, const uint8_t *sf, int row, int k, int K)
 {
     switch (kind) {
-    case MMA_F16:  return (double)orc_f16_to_f32(((const uint16_t *)t)[row * K + k]);
+    case MMA_F16: case MMA_F16_F16:
+                   return (double)orc_f16_to_f32(((const uint16_t *)t)[row * K + k]);
+    case MMA_TF32: return (double)((const float *)t)[row * K + k];
+    case MMA_E2M1: {
+        const uint8_t byte = ((const uint8_t *)t)[(row * K + k) / 2];
+        return (double)orc_e2m1_to_f32((k & 1) ? (uint8_t)(byte >> 4) : (uint8_t)(byte & 0xF));
+    }
     case MMA_BF16: return (double)orc_bf16_to_f32(((const uint16_t *)t)[row * K + k]);
     case MMA_E4M3: return (double)orc_e4m3_to_f32(((const uint8_t *)t)[row * K + k]);
     case MMA_E5M2: return (double)orc_e5m2_to_f32(((const uint8_t *)t)[row * K + k]);

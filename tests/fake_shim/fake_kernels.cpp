@@ -97,7 +97,12 @@ uint16_t toBF16(float x)
 double decode(int kind, const uint8_t *t, const uint8_t *sf, int row, int k, int K)
 {
     switch (kind) {
-    case CLPK_MMA_F16: return clpk_f16_decode(reinterpret_cast<const uint16_t *>(t)[row * K + k]);
+    case CLPK_MMA_F16: case CLPK_MMA_F16_F16: return clpk_f16_decode(reinterpret_cast<const uint16_t *>(t)[row * K + k]);
+    case CLPK_MMA_TF32: return reinterpret_cast<const float *>(t)[row * K + k];
+    case CLPK_MMA_E2M1: {
+        const uint8_t byte = t[(row * K + k) / 2];
+        return clpk_e2m1_decode((k & 1) ? (byte >> 4) : (byte & 0xF));
+    }
     case CLPK_MMA_BF16: return clpk_bf16_decode(reinterpret_cast<const uint16_t *>(t)[row * K + k]);
     case CLPK_MMA_E4M3: return clpk_e4m3_decode(t[row * K + k]);
     case CLPK_MMA_E5M2: return clpk_e5m2_decode(t[row * K + k]);
@@ -187,6 +192,18 @@ int clpk_convert_f32(void *dst, const float *src, uint64_t n, int dtype, void *)
         case CLPK_DT_E4M3: static_cast<uint8_t *>(dst)[i] = toE4M3(src[i]); break;
         case CLPK_DT_E5M2: static_cast<uint8_t *>(dst)[i] = toE5M2(src[i]); break;
         case CLPK_DT_I8: static_cast<int8_t *>(dst)[i] = (int8_t)std::max(-128.0, std::min(127.0, std::nearbyint((double)src[i]))); break;
+        case CLPK_DT_TF32: {
+            uint32_t b = clpk_f32_bits(src[i]);
+            if ((b & 0x7F800000u) != 0x7F800000u) b += 0xFFFu + ((b >> 13) & 1u);
+            static_cast<uint32_t *>(dst)[i] = b & 0xFFFFE000u;
+            break;
+        }
+        case CLPK_DT_E2M1: {
+            uint8_t &byte = static_cast<uint8_t *>(dst)[i / 2];
+            const uint8_t nib = clpk_e2m1_encode(src[i]);
+            byte = (i & 1) ? (uint8_t)((byte & 0x0F) | (nib << 4)) : nib;
+            break;
+        }
         default: return fail(CLPK_ERR_BAD_ARG, "dtype");
         }
     }
@@ -373,8 +390,9 @@ int clpk_launch_latency(uint32_t, uint32_t, double *mean_us, void *) { *mean_us 
 int clpk_mma_kind_k(int kind)
 {
     switch (kind) {
-    case CLPK_MMA_F16: case CLPK_MMA_BF16: return 16;
-    case CLPK_MMA_E4M3: case CLPK_MMA_E5M2: case CLPK_MMA_I8: return 32;
+    case CLPK_MMA_TF32: return 8;
+    case CLPK_MMA_F16: case CLPK_MMA_BF16: case CLPK_MMA_F16_F16: return 16;
+    case CLPK_MMA_E4M3: case CLPK_MMA_E5M2: case CLPK_MMA_I8: case CLPK_MMA_E2M1: return 32;
     case CLPK_MMA_MXF4: case CLPK_MMA_NVF4: case CLPK_MMA_E4M3_SP: case CLPK_MMA_I8_SP: return 64;
     case CLPK_MMA_MXF4_SP: case CLPK_MMA_NVF4_SP: return 128;
     default: return 0;
@@ -439,7 +457,7 @@ int clpk_mma_peak(const clpk_mma_peak_args_t *a, void *)
 {
     const int K = clpk_mma_kind_k(a->kind);
     if (!K) return fail(CLPK_ERR_BAD_ARG, "kind");
-    if (a->kind >= CLPK_MMA_E4M3_SP) return fake_sparse_peak(a);
+    if (a->kind >= CLPK_MMA_E4M3_SP && a->kind <= CLPK_MMA_I8_SP) return fake_sparse_peak(a);
     const uint8_t *A = static_cast<const uint8_t *>(a->d_a), *B = static_cast<const uint8_t *>(a->d_b);
     std::vector<uint32_t> tile(128 * 256);
     uint32_t x = 0;
@@ -451,6 +469,7 @@ int clpk_mma_peak(const clpk_mma_peak_args_t *a, void *)
                      decode(a->kind, B, static_cast<const uint8_t *>(a->d_sfb), j, k, K);
             uint32_t w;
             if (a->kind == CLPK_MMA_I8) w = (uint32_t)(int32_t)p * a->n_mma;
+            else if (a->kind == CLPK_MMA_F16_F16) w = clpk_f16_encode((float)(p * a->n_mma));
             else w = clpk_f32_bits((float)(p * a->n_mma));
             tile[i * 256 + j] = w;
             x ^= w;

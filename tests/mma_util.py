@@ -7,8 +7,9 @@ import numpy as np
 
 from clpeak_b200 import native as N
 
-DENSE_DT = {N.MMA_F16: N.DT_F16, N.MMA_BF16: N.DT_BF16, N.MMA_E4M3: N.DT_E4M3, N.MMA_E5M2: N.DT_E5M2}
-KIND_K = {N.MMA_F16: 16, N.MMA_BF16: 16, N.MMA_E4M3: 32, N.MMA_E5M2: 32, N.MMA_I8: 32, N.MMA_MXF4: 64,
+DENSE_DT = {N.MMA_F16: N.DT_F16, N.MMA_BF16: N.DT_BF16, N.MMA_E4M3: N.DT_E4M3, N.MMA_E5M2: N.DT_E5M2,
+            N.MMA_TF32: N.DT_TF32, N.MMA_F16_F16: N.DT_F16}
+KIND_K = {N.MMA_TF32: 8, N.MMA_F16_F16: 16, N.MMA_E2M1: 32, N.MMA_F16: 16, N.MMA_BF16: 16, N.MMA_E4M3: 32, N.MMA_E5M2: 32, N.MMA_I8: 32, N.MMA_MXF4: 64,
           N.MMA_NVF4: 64, N.MMA_E4M3_SP: 64, N.MMA_I8_SP: 64, N.MMA_MXF4_SP: 128, N.MMA_NVF4_SP: 128}
 SPARSE = (N.MMA_E4M3_SP, N.MMA_I8_SP, N.MMA_MXF4_SP, N.MMA_NVF4_SP)
 
@@ -52,6 +53,12 @@ def make_operands(orc, kind):
         a = orc.fill_i8(128 * k, 2).reshape(128, k)
         b = orc.fill_i8(256 * k, 2, first=128 * k).reshape(256, k)
         return dict(a=a, b=b, sfa=None, sfb=None, tensor_scale=(1.0, 1.0))
+    if kind == N.MMA_E2M1:
+        # unscaled 4-bit operands: uniform[-1,1) stretched over e2m1's range (+-6)
+        fa = orc.fill_f32(128 * k, 2, 1) * np.float32(6.0)
+        fb = orc.fill_f32(256 * k, 2, 1, first=128 * k) * np.float32(6.0)
+        return dict(a=orc.convert_f32(fa, N.DT_E2M1).reshape(128, k // 2),
+                    b=orc.convert_f32(fb, N.DT_E2M1).reshape(256, k // 2), sfa=None, sfb=None, tensor_scale=(1.0, 1.0))
     if kind in DENSE_DT:
         fa = orc.fill_f32(128 * k, 2, 1)
         fb = orc.fill_f32(256 * k, 2, 1, first=128 * k)
@@ -82,6 +89,10 @@ def expected_tile(orc, kind, ops, n_mma):
     else:
         p, s = orc.mma_tile(kind, ops["a"], ops["b"], ops["sfa"], ops["sfb"])
     k = KIND_K[kind]
+    if kind == N.MMA_F16_F16:
+        # 16-bit accumulator: one rounding to half per instruction at least; the bound is relative to the
+        # running magnitude n*S and only meant for a handful of instructions
+        return p * n_mma, (n_mma + 1) * 2.0 ** -11 * n_mma * s + 1e-30
     # fp32 accumulation in the tensor core is not IEEE round-to-nearest: the
     # addend is aligned to the running sum and truncated.  Model: each of the n
     # additions into the running sum, and each of the K product additions
@@ -121,7 +132,11 @@ def check_tile(kind, got_i32, want, tol):
     if kind in (N.MMA_I8, N.MMA_I8_SP):
         assert np.array_equal(got_i32, want), f"int8 tile differs in {(got_i32 != want).sum()} elements"
         return 0.0
-    got = got_i32.view(np.float32).astype(np.float64)
+    if kind == N.MMA_F16_F16:
+        assert not (got_i32.view(np.uint32) >> 16).any(), "fp16 accumulator words carry data in their high halves"
+        got = (got_i32.view(np.uint32) & 0xFFFF).astype(np.uint16).view(np.float16).astype(np.float64)
+    else:
+        got = got_i32.view(np.float32).astype(np.float64)
     err = np.abs(got - want)
     worst = float((err / tol).max())
     assert worst <= 1.0, f"kind {kind}: error is {worst:.3g}x the stated tolerance"

@@ -45,7 +45,7 @@ def test_fill_i8(K, orc, cuda):
 
 
 @pytest.mark.parametrize("dtype,scale", [(N.DT_F16, 1.0), (N.DT_BF16, 1.0), (N.DT_E4M3, 200.0),
-                                         (N.DT_E5M2, 3.0e4), (N.DT_I8, 60.0)])
+                                         (N.DT_E5M2, 3.0e4), (N.DT_I8, 60.0), (N.DT_TF32, 1.0), (N.DT_E2M1, 3.0)])
 def test_convert_matches_oracle(K, orc, cuda, dtype, scale):
     n = 1 << 18
     src = orc.fill_f32(n, 5, 2, 0.0, scale)
@@ -53,10 +53,11 @@ def test_convert_matches_oracle(K, orc, cuda, dtype, scale):
     edges = np.array([0.0, -0.0, 0.5, 1.5, 2.5, 448.0, 449.0, 464.0, 1e9, -1e9, 2 ** -9, 2 ** -10, 3 * 2 ** -11,
                       57344.0, 61440.0, 65504.0, 65520.0, 127.5, -128.5, 1e-30], dtype=np.float32)
     src[: edges.size] = edges
+    src[edges.size: edges.size + 10] = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0, 7.0, -0.25], dtype=np.float32)
     tdt = {N.DT_F16: cuda.int16, N.DT_BF16: cuda.int16, N.DT_E4M3: cuda.uint8, N.DT_E5M2: cuda.uint8,
-           N.DT_I8: cuda.int8}[dtype]
+           N.DT_I8: cuda.int8, N.DT_TF32: cuda.int32, N.DT_E2M1: cuda.uint8}[dtype]
     d_src = dev_from(src)
-    d_dst = dev_empty(n, tdt)
+    d_dst = dev_empty(n // 2 if dtype == N.DT_E2M1 else n, tdt)
     K.clpk_convert_f32(d_dst.data_ptr(), d_src.data_ptr(), n, dtype, stream_ptr())
     sync()
     assert_bits_equal(to_np(d_dst), orc.convert_f32(src, dtype), f"convert dtype={dtype}")

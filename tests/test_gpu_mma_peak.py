@@ -9,7 +9,7 @@ from tests import mma_util as M
 
 pytestmark = pytest.mark.gpu
 
-DENSE = [N.MMA_F16, N.MMA_BF16, N.MMA_E4M3, N.MMA_E5M2, N.MMA_I8]
+DENSE = [N.MMA_F16, N.MMA_BF16, N.MMA_E4M3, N.MMA_E5M2, N.MMA_I8, N.MMA_TF32, N.MMA_E2M1]
 SCALED = [N.MMA_MXF4, N.MMA_NVF4]
 
 
@@ -39,6 +39,37 @@ def test_full_config_all_ctas_agree(K, orc, cuda, kind):
     # every CTA computed the same tile: one checksum value across the grid
     assert np.all(chk == chk[0])
     assert int(chk[0]) == int(np.bitwise_xor.reduce(tiles[0].view(np.uint32).ravel()))
+
+
+@pytest.mark.parametrize("n_mma", [1, 2, 3])
+def test_fp16_accumulate_tile(K, orc, cuda, n_mma):
+    """kind::f16 with a 16-bit accumulator: one half per 32-bit tensor-memory cell, low 16 bits."""
+    ops = M.make_operands(orc, N.MMA_F16_F16)
+    status, tiles, chk = M.run_peak(K, cuda, N.MMA_F16_F16, ops, n_mma, grid=2, n_out_tiles=2)
+    assert status == 0
+    want, tol = M.expected_tile(orc, N.MMA_F16_F16, ops, n_mma)
+    for t in tiles:
+        M.check_tile(N.MMA_F16_F16, t, want, tol)
+    assert chk[0] == chk[1]
+
+
+def test_fp16_accumulate_full_config_runs_and_ctas_agree(K, orc, cuda):
+    # 2^14 accumulations saturate a 16-bit accumulator, so only agreement between CTAs is checked here
+    sms = cuda.cuda.get_device_properties(0).multi_processor_count
+    ops = M.make_operands(orc, N.MMA_F16_F16)
+    status, _, chk = M.run_peak(K, cuda, N.MMA_F16_F16, ops, 1 << 14, grid=4 * sms, n_out_tiles=1)
+    assert status == 0 and np.all(chk == chk[0])
+
+
+def test_tf32_ignores_the_low_mantissa_bits(K, orc, cuda):
+    # the same tile with noise in the 13 bits below the tf32 mantissa gives the same accumulator
+    ops = M.make_operands(orc, N.MMA_TF32)
+    _, clean, _ = M.run_peak(K, cuda, N.MMA_TF32, ops, 3, 1, 1)
+    noisy = dict(ops)
+    noisy["a"] = (ops["a"].view(np.uint32) | np.uint32(0x1555)).view(ops["a"].dtype)
+    noisy["b"] = (ops["b"].view(np.uint32) | np.uint32(0x0AAA)).view(ops["b"].dtype)
+    _, dirty, _ = M.run_peak(K, cuda, N.MMA_TF32, noisy, 3, 1, 1)
+    assert np.array_equal(clean[0], dirty[0])
 
 
 def test_linearity_in_instruction_count(K, orc, cuda):
