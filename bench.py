@@ -509,6 +509,17 @@ def measure_rows(K, N, torch, stream, time_once, world=1):
             rows[f"gemm_{name}_{m}"] = row
             del A, B, Cc, sfs, ws
             torch.cuda.empty_cache()
+    # vendor library on the same GPU in the same thermal state, for comparison only (never on the product path)
+    for m in (4096, 8192, 16384):
+        x = torch.randn(m, m, dtype=torch.bfloat16, device="cuda") * 0.02
+        y = torch.randn(m, m, dtype=torch.bfloat16, device="cuda") * 0.02
+        ms = time_once(lambda: torch.matmul(x, y.t()), reps=5)
+        tf = 2.0 * m * m * m / ms / 1e9
+        rows[f"library_cublas_bf16_{m}"] = {"TFLOPS": tf, "ms": ms, "note": "torch.matmul (cuBLAS), bf16 in / bf16 out, TN"}
+        if f"gemm_bf16_{m}" in rows:
+            rows[f"gemm_bf16_{m}"]["vs_cublas_same_run"] = rows[f"gemm_bf16_{m}"]["TFLOPS"] / tf
+        del x, y
+        torch.cuda.empty_cache()
     return rows
 
 

@@ -464,6 +464,8 @@ CLPK_DEFINE_MMA_SS(mma_i8_ss, "kind::i8")
 
 CLPK_DEFINE_MMA2_SS(mma2_f16_ss, "kind::f16")
 CLPK_DEFINE_MMA2_SS(mma2_f8f6f4_ss, "kind::f8f6f4")
+CLPK_DEFINE_MMA2_SS(mma2_tf32_ss, "kind::tf32")
+CLPK_DEFINE_MMA2_SS(mma2_i8_ss, "kind::i8")
 
 // Block-scaled: scale factors for A and B live in TMEM.
 #define CLPK_DEFINE_MMA_BS(NAME, CTAGROUP, KINDSTR)                                              \
@@ -484,6 +486,7 @@ CLPK_DEFINE_MMA2_SS(mma2_f8f6f4_ss, "kind::f8f6f4")
 CLPK_DEFINE_MMA_BS(mma_mxf4_bs, "1", "kind::mxf4.block_scale.scale_vec::2X")
 CLPK_DEFINE_MMA_BS(mma_nvf4_bs, "1", "kind::mxf4nvf4.block_scale.scale_vec::4X")
 CLPK_DEFINE_MMA_BS(mma2_nvf4_bs, "2", "kind::mxf4nvf4.block_scale.scale_vec::4X")
+CLPK_DEFINE_MMA_BS(mma2_mxf4_bs, "2", "kind::mxf4.block_scale.scale_vec::2X")
 
 // 2:4 sparse A: metadata lives in TMEM.
 #define CLPK_DEFINE_MMA_SP(NAME, KINDSTR)                                                        \

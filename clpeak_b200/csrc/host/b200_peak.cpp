@@ -585,103 +585,131 @@ struct B200Harness {
         return (uint32_t)(d / 256 * 256);
     }
 
+    struct GemmRow { const char *metric; int dtype; double spec; const char *specName; const char *desc; };
+
+    // One square GEMM row: operands generated and quantised on the device, timed, 16 sampled
+    // elements of C compared with a host dot product of the same quantised operands.
+    static void gemmRow(B200Worker &w, B200TestResult &out, const GemmRow &r)
+    {
+        const uint32_t d = gemmDim(w);
+        const int dt = r.dtype;
+        const bool nv = dt == CLPK_DT_NVF4, mx = dt == CLPK_DT_MXF4, scaled = nv || mx;
+        const bool wideOut = dt == CLPK_DT_TF32 || dt == CLPK_DT_I8;
+        const uint32_t sfBlock = nv ? 16 : 32;
+        const char *outName = dt == CLPK_DT_TF32 ? "fp32 out" : dt == CLPK_DT_I8 ? "int32 accumulate and out" : "fp32 accumulate, bf16 out";
+        const std::string note = "M=N=K=" + std::to_string(d) + ", A row-major, B column-major, " +
+                                 (dt == CLPK_DT_I8 ? "uniform[-8,7] operands, " : "N(0,0.02) operands, ") +
+                                 (nv ? "e2m1 with ue4m3 block scales and fp32 tensor scales (repacked inside the timed call), " : "") +
+                                 (mx ? "e2m1 with ue8m0 block scales (repacked inside the timed call), " : "") +
+                                 (dt == CLPK_DT_E5M2 ? "e5m2 A times e4m3 B, " : "") + outName +
+                                 "; sampled elements checked against a host dot product.";
+        auto fail = [&](const std::string &why) { out.readings.push_back(bad(r.metric, ResultStatus::Error, why, note)); };
+        const uint64_t n = (uint64_t)d * d;
+        const uint64_t rowBytes = scaled ? d / 2 : dt == CLPK_DT_TF32 ? 4ull * d
+                                : (dt == CLPK_DT_F16 || dt == CLPK_DT_BF16) ? 2ull * d : d;
+        // N(0, 0.02): |x| < 0.12, so a tensor scale of 2^-15 keeps x / scale / 6 within ue4m3's range (448).
+        const float tensorScale = nv ? std::ldexp(1.0f, -15) : 1.0f;
+        size_t wsBytes = 0;
+        if (scaled && clpk_gemm_workspace_bytes(dt, d, d, d, &wsBytes) != CLPK_OK)
+            return fail(shimError("workspace size"));
+        DeviceBuffer tmp, A, B, C, st, sfa, sfb, ws;
+        if (!tmp.alloc(n * 4) || !A.alloc(d * rowBytes) || !B.alloc(d * rowBytes) || !C.alloc(n * (wideOut ? 4 : 2)) || !st.alloc(4) ||
+            (scaled && (!sfa.alloc(n / sfBlock) || !sfb.alloc(n / sfBlock) || !ws.alloc(wsBytes))))
+            return fail("Failed to allocate matrices");
+        auto operand = [&](DeviceBuffer &dst, DeviceBuffer &sf, uint64_t seed, bool isB) {
+            if (dt == CLPK_DT_I8)
+                return clpk_fill_i8(dst.as<int8_t>(), n, seed, w.stream);
+            int rc = clpk_fill_f32(tmp.as<float>(), n, seed, CLPK_DIST_NORMAL, 0.0f, 0.02f, w.stream);
+            if (scaled)
+                return rc | clpk_quantize_fp4(dst.as<uint8_t>(), sf.as<uint8_t>(), tmp.as<float>(), d, d, dt, tensorScale, w.stream);
+            return rc | clpk_convert_f32(dst.p, tmp.as<float>(), n, (dt == CLPK_DT_E5M2 && isB) ? CLPK_DT_E4M3 : dt, w.stream);
+        };
+        int rc = operand(A, sfa, 40, false);
+        rc |= operand(B, sfb, 41, true);
+        clpk_gemm_args_t g{};
+        g.dtype = dt; g.m = g.n = g.k = d;
+        g.d_a = A.p; g.d_b = B.p; g.d_c = C.p; g.d_status = st.as<uint32_t>();
+        g.alpha = nv ? tensorScale * tensorScale : 1.0f;
+        g.d_sfa = sfa.p; g.d_sfb = sfb.p; g.d_workspace = ws.p; g.workspace_bytes = wsBytes;
+        std::string err;
+        const double s = rc == CLPK_OK ? w.timeLaunches([&] { return clpk_gemm(&g, w.stream); }, err) : -1.0;
+        if (s < 0)
+            return fail(err.empty() ? shimError("operand generation") : err);
+        std::string verdict;
+        uint32_t status = 0;
+        clpk_memcpy_d2h(&status, st.p, 4, w.stream);
+        const uint64_t sfRow = d / sfBlock;
+        std::vector<uint8_t> rowA(rowBytes), rowB(rowBytes), rowSfa(sfRow), rowSfb(sfRow);
+        for (int sidx = 0; sidx < 16 && verdict.empty(); ++sidx) {
+            const uint64_t i = clpk_rand64(77, 2 * sidx) % d, j = clpk_rand64(77, 2 * sidx + 1) % d;
+            uint32_t cWord = 0;
+            clpk_memcpy_d2h(rowA.data(), A.as<uint8_t>() + i * rowBytes, rowBytes, w.stream);
+            clpk_memcpy_d2h(rowB.data(), B.as<uint8_t>() + j * rowBytes, rowBytes, w.stream);
+            if (scaled) {
+                clpk_memcpy_d2h(rowSfa.data(), sfa.as<uint8_t>() + i * sfRow, sfRow, w.stream);
+                clpk_memcpy_d2h(rowSfb.data(), sfb.as<uint8_t>() + j * sfRow, sfRow, w.stream);
+            }
+            if (wideOut)
+                clpk_memcpy_d2h(&cWord, C.as<uint32_t>() + i * d + j, 4, w.stream);
+            else
+                clpk_memcpy_d2h(&cWord, C.as<uint16_t>() + i * d + j, 2, w.stream);
+            clpk_stream_sync(w.stream);
+            double sAbs = 0;
+            const double want = (double)g.alpha * b200check::gemmElement(dt, rowA.data(), rowB.data(), d, 0, 0, &sAbs,
+                                                                         rowSfa.data(), rowSfb.data());
+            sAbs *= g.alpha;
+            double got, tol;
+            if (dt == CLPK_DT_I8) {
+                got = (double)(int32_t)cWord;
+                tol = 0.0;
+            } else if (dt == CLPK_DT_TF32) {
+                got = clpk_bits_f32(cWord);
+                tol = d * std::ldexp(1.0, -23) * sAbs + 1e-30;
+            } else {
+                got = clpk_bf16_decode((uint16_t)cWord);
+                tol = d * std::ldexp(1.0, -23) * sAbs + std::ldexp(1.0, -8) * std::fabs(want) + 1e-30;
+            }
+            if (!(std::fabs(got - want) <= tol))
+                verdict = "C(" + std::to_string(i) + "," + std::to_string(j) + ") = " + std::to_string(got) +
+                          ", host " + std::to_string(want);
+        }
+        if (status != 0)
+            verdict = "a device-side wait timed out (status " + std::to_string(status) + ")";
+        if (!verdict.empty())
+            return fail("result check failed: " + verdict);
+        const double work = 2.0 * d * d * d;
+        const double t = work / s / 1e12;
+        out.readings.push_back(ok(r.metric, t, note + "  " + pct(t, r.spec, r.specName), work, s));
+    }
+
     static void gemmFp(B200Worker &w, B200TestResult &out)
     {
         out.spec = {"cublas-fp", "GEMM peak (in-house tcgen05 GEMM)", "tflops", Category::Unknown,
                     "A whole matrix multiplication C = A*B on the tensor cores, operands streamed from memory by TMA: "
                     "what a well-tuned library routine reaches, as opposed to the bare instruction rate of the rows above.  "
                     "The reference calls cuBLASLt here; this backend runs its own warp-specialised 2-CTA tcgen05 kernel."};
-        const uint32_t d = gemmDim(w);
-        struct Row { const char *metric; int dtype; double spec; const char *specName; };
-        const Row built[] = {{"fp16", CLPK_DT_F16, kSpecBf16Tflops, "dense fp16 TFLOPS"},
-                             {"bf16", CLPK_DT_BF16, kSpecBf16Tflops, "dense bf16 TFLOPS"},
-                             {"fp8_e4m3", CLPK_DT_E4M3, kSpecFp8Tflops, "dense fp8 TFLOPS"},
-                             {"nvf4_e2m1", CLPK_DT_NVF4, kSpecFp4Tflops, "dense fp4 TFLOPS"}};
-        for (const char *m : {"fp32", "fp64", "tf32"})
-            out.readings.push_back(bad(m, ResultStatus::Unsupported, "no tcgen05 GEMM for this type in the B200 backend"));
-        for (const Row &r : built) {
-            const bool nv = r.dtype == CLPK_DT_NVF4;
-            const std::string note = "M=N=K=" + std::to_string(d) + ", A row-major, B column-major, N(0,0.02) operands, " +
-                                     (nv ? "e2m1 with ue4m3 block scales and fp32 tensor scales (repacked inside the timed call), " : "") +
-                                     "fp32 accumulate, bf16 out; sampled elements checked against a host dot product.";
-            const uint64_t n = (uint64_t)d * d;
-            const uint64_t rowBytes = nv ? d / 2 : (r.dtype == CLPK_DT_E4M3 ? d : 2ull * d);
-            // N(0, 0.02): |x| < 0.12, so a tensor scale of 2^-15 keeps x / scale / 6 within ue4m3's range (448).
-            const float tensorScale = nv ? std::ldexp(1.0f, -15) : 1.0f;
-            size_t wsBytes = 0;
-            if (nv && clpk_gemm_workspace_bytes(r.dtype, d, d, d, &wsBytes) != CLPK_OK) {
-                out.readings.push_back(bad(r.metric, ResultStatus::Error, shimError("workspace size"), note));
-                continue;
-            }
-            DeviceBuffer tmp, A, B, C, st, sfa, sfb, ws;
-            if (!tmp.alloc(n * 4) || !A.alloc(d * rowBytes) || !B.alloc(d * rowBytes) || !C.alloc(n * 2) || !st.alloc(4) ||
-                (nv && (!sfa.alloc(n / 16) || !sfb.alloc(n / 16) || !ws.alloc(wsBytes)))) {
-                out.readings.push_back(bad(r.metric, ResultStatus::Error, "Failed to allocate matrices", note));
-                continue;
-            }
-            auto quantise = [&](DeviceBuffer &dst, DeviceBuffer &sf) {
-                return nv ? clpk_quantize_fp4(dst.as<uint8_t>(), sf.as<uint8_t>(), tmp.as<float>(), d, d, CLPK_DT_NVF4, tensorScale, w.stream)
-                          : clpk_convert_f32(dst.p, tmp.as<float>(), n, r.dtype, w.stream);
-            };
-            int rc = clpk_fill_f32(tmp.as<float>(), n, 40, CLPK_DIST_NORMAL, 0.0f, 0.02f, w.stream);
-            rc |= quantise(A, sfa);
-            rc |= clpk_fill_f32(tmp.as<float>(), n, 41, CLPK_DIST_NORMAL, 0.0f, 0.02f, w.stream);
-            rc |= quantise(B, sfb);
-            clpk_gemm_args_t g{};
-            g.dtype = r.dtype; g.m = g.n = g.k = d;
-            g.d_a = A.p; g.d_b = B.p; g.d_c = C.p; g.d_status = st.as<uint32_t>();
-            g.alpha = nv ? tensorScale * tensorScale : 1.0f;
-            g.d_sfa = sfa.p; g.d_sfb = sfb.p; g.d_workspace = ws.p; g.workspace_bytes = wsBytes;
-            std::string err;
-            const double s = rc == CLPK_OK ? w.timeLaunches([&] { return clpk_gemm(&g, w.stream); }, err) : -1.0;
-            if (s < 0) {
-                out.readings.push_back(bad(r.metric, ResultStatus::Error, err.empty() ? shimError("operand generation") : err, note));
-                continue;
-            }
-            // sampled check: 16 (row, column) pairs, full K
-            std::string verdict;
-            uint32_t status = 0;
-            clpk_memcpy_d2h(&status, st.p, 4, w.stream);
-            std::vector<uint8_t> rowA(rowBytes), rowB(rowBytes), rowSfa(d / 16), rowSfb(d / 16);
-            for (int sidx = 0; sidx < 16 && verdict.empty(); ++sidx) {
-                const uint64_t i = clpk_rand64(77, 2 * sidx) % d, j = clpk_rand64(77, 2 * sidx + 1) % d;
-                uint16_t c16 = 0;
-                clpk_memcpy_d2h(rowA.data(), A.as<uint8_t>() + i * rowBytes, rowBytes, w.stream);
-                clpk_memcpy_d2h(rowB.data(), B.as<uint8_t>() + j * rowBytes, rowBytes, w.stream);
-                if (nv) {
-                    clpk_memcpy_d2h(rowSfa.data(), sfa.as<uint8_t>() + i * (d / 16), d / 16, w.stream);
-                    clpk_memcpy_d2h(rowSfb.data(), sfb.as<uint8_t>() + j * (d / 16), d / 16, w.stream);
-                }
-                clpk_memcpy_d2h(&c16, C.as<uint16_t>() + i * d + j, 2, w.stream);
-                clpk_stream_sync(w.stream);
-                double sAbs = 0;
-                const double want = (double)g.alpha * b200check::gemmElement(r.dtype, rowA.data(), rowB.data(), d, 0, 0, &sAbs,
-                                                                             rowSfa.data(), rowSfb.data());
-                sAbs *= g.alpha;
-                const double got = clpk_bf16_decode(c16);
-                const double tol = d * std::ldexp(1.0, -23) * sAbs + std::ldexp(1.0, -8) * std::fabs(want) + 1e-30;
-                if (!(std::fabs(got - want) <= tol))
-                    verdict = "C(" + std::to_string(i) + "," + std::to_string(j) + ") = " + std::to_string(got) +
-                              ", host " + std::to_string(want);
-            }
-            if (status != 0)
-                verdict = "a device-side wait timed out (status " + std::to_string(status) + ")";
-            if (!verdict.empty()) {
-                out.readings.push_back(bad(r.metric, ResultStatus::Error, "result check failed: " + verdict, note));
-                continue;
-            }
-            const double work = 2.0 * d * d * d;
-            const double t = work / s / 1e12;
-            out.readings.push_back(ok(r.metric, t, note + "  " + pct(t, r.spec, r.specName), work, s));
-        }
-        for (const char *m : {"fp8_e5m2", "mxf4_e2m1"})
-            out.readings.push_back(bad(m, ResultStatus::Unsupported, "not built in the B200 backend yet"));
+        // the reference's row order (src/cuda/cuda_blas.cpp:567-676)
+        for (const char *m : {"fp32", "fp64"})
+            out.readings.push_back(bad(m, ResultStatus::Unsupported, "shader-core GEMM: no tcgen05 kind for this type, not built in the B200 backend"));
+        static const GemmRow rows[] = {
+            {"tf32", CLPK_DT_TF32, kSpecBf16Tflops / 2, "dense tf32 TFLOPS", ""},
+            {"fp16", CLPK_DT_F16, kSpecBf16Tflops, "dense fp16 TFLOPS", ""},
+            {"bf16", CLPK_DT_BF16, kSpecBf16Tflops, "dense bf16 TFLOPS", ""},
+            {"fp8_e4m3", CLPK_DT_E4M3, kSpecFp8Tflops, "dense fp8 TFLOPS", ""},
+            {"fp8_e5m2", CLPK_DT_E5M2, kSpecFp8Tflops, "dense fp8 TFLOPS", ""},
+            {"mxf4_e2m1", CLPK_DT_MXF4, kSpecFp4Tflops, "dense fp4 TFLOPS", ""},
+            {"nvf4_e2m1", CLPK_DT_NVF4, kSpecFp4Tflops, "dense fp4 TFLOPS", ""},
+        };
+        for (const GemmRow &r : rows)
+            gemmRow(w, out, r);
     }
 
-    static void gemmInt(B200Worker &, B200TestResult &out)
+    static void gemmInt(B200Worker &w, B200TestResult &out)
     {
-        out.spec = {"cublas-int", "GEMM peak, integer (in-house tcgen05 GEMM)", "tops", Category::Unknown, ""};
-        out.readings.push_back(bad("int8", ResultStatus::Unsupported, "int8 GEMM is not built in the B200 backend yet"));
+        out.spec = {"cublas-int", "GEMM peak, integer (in-house tcgen05 GEMM)", "tops", Category::Unknown,
+                    "The same matrix multiply on whole-number formats, which is how a quantized (compressed) model actually runs."};
+        static const GemmRow int8Row = {"int8", CLPK_DT_I8, kSpecInt8Tops, "dense int8 TOPS", ""};
+        gemmRow(w, out, int8Row);
         out.readings.push_back(bad("int4", ResultStatus::Unsupported, "no int4 tensor-core path on sm_100"));
     }
 

@@ -394,16 +394,28 @@ inline double gemmElement(int dtype, const void *a, const void *b, uint64_t k, u
     double acc = 0.0, s = 0.0;
     for (uint64_t x = 0; x < k; ++x) {
         double va, vb;
-        if (dtype == CLPK_DT_NVF4) {
+        if (dtype == CLPK_DT_NVF4 || dtype == CLPK_DT_MXF4) {
+            const bool mx = dtype == CLPK_DT_MXF4;
+            const uint64_t blk = mx ? 32 : 16;
             const uint8_t ab = static_cast<const uint8_t *>(a)[(i * k + x) / 2], bb = static_cast<const uint8_t *>(b)[(j * k + x) / 2];
-            va = (double)clpk_e2m1_decode((x & 1) ? (ab >> 4) : (ab & 0xF)) * clpk_e4m3_decode(sfa[i * (k / 16) + x / 16]);
-            vb = (double)clpk_e2m1_decode((x & 1) ? (bb >> 4) : (bb & 0xF)) * clpk_e4m3_decode(sfb[j * (k / 16) + x / 16]);
+            const uint8_t sa = sfa[i * (k / blk) + x / blk], sb = sfb[j * (k / blk) + x / blk];
+            va = (double)clpk_e2m1_decode((x & 1) ? (ab >> 4) : (ab & 0xF)) * (mx ? clpk_ue8m0_decode(sa) : clpk_e4m3_decode(sa));
+            vb = (double)clpk_e2m1_decode((x & 1) ? (bb >> 4) : (bb & 0xF)) * (mx ? clpk_ue8m0_decode(sb) : clpk_e4m3_decode(sb));
         } else if (dtype == CLPK_DT_BF16) {
             va = clpk_bf16_decode(static_cast<const uint16_t *>(a)[i * k + x]);
             vb = clpk_bf16_decode(static_cast<const uint16_t *>(b)[j * k + x]);
         } else if (dtype == CLPK_DT_F16) {
             va = clpk_f16_decode(static_cast<const uint16_t *>(a)[i * k + x]);
             vb = clpk_f16_decode(static_cast<const uint16_t *>(b)[j * k + x]);
+        } else if (dtype == CLPK_DT_I8) {
+            va = static_cast<const int8_t *>(a)[i * k + x];
+            vb = static_cast<const int8_t *>(b)[j * k + x];
+        } else if (dtype == CLPK_DT_TF32) {
+            va = clpk_bits_f32(static_cast<const uint32_t *>(a)[i * k + x] & 0xFFFFE000u);
+            vb = clpk_bits_f32(static_cast<const uint32_t *>(b)[j * k + x] & 0xFFFFE000u);
+        } else if (dtype == CLPK_DT_E5M2) {     // e5m2 A times e4m3 B
+            va = clpk_e5m2_decode(static_cast<const uint8_t *>(a)[i * k + x]);
+            vb = clpk_e4m3_decode(static_cast<const uint8_t *>(b)[j * k + x]);
         } else {
             va = clpk_e4m3_decode(static_cast<const uint8_t *>(a)[i * k + x]);
             vb = clpk_e4m3_decode(static_cast<const uint8_t *>(b)[j * k + x]);

@@ -41,7 +41,7 @@ struct GemmParams {
     uint32_t m, n, k;
     uint32_t k_blocks;          // K / (elements per 128 B)
     uint32_t k_block_elems;
-    __nv_bfloat16 *c;
+    void *c;                    // bf16, or fp32 (TF32) / int32 (I8): see out_elem_bytes()
     float alpha;
     uint32_t *status;
 };
@@ -66,6 +66,38 @@ __device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uin
     nb = first_n + within % width;
 }
 
+// Output element of a GEMM dtype: fp32 for TF32, int32 for I8, bf16 for everything else.
+template <int DT> struct OutBytes { static constexpr uint32_t value = (DT == CLPK_DT_TF32 || DT == CLPK_DT_I8) ? 4u : 2u; };
+
+// Thread-local epilogue step: 32 consecutive accumulator columns of one row -> global memory.
+template <int DT>
+__device__ __forceinline__ void store_columns(uint8_t *dst_bytes, const uint32_t (&r)[32], float alpha)
+{
+    if constexpr (DT == CLPK_DT_I8) {
+        uint4 *dst = reinterpret_cast<uint4 *>(dst_bytes);
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            dst[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+    } else if constexpr (DT == CLPK_DT_TF32) {
+        uint4 *dst = reinterpret_cast<uint4 *>(dst_bytes);
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            dst[i] = make_uint4(__float_as_uint(__uint_as_float(r[4 * i]) * alpha), __float_as_uint(__uint_as_float(r[4 * i + 1]) * alpha),
+                                __float_as_uint(__uint_as_float(r[4 * i + 2]) * alpha), __float_as_uint(__uint_as_float(r[4 * i + 3]) * alpha));
+    } else {
+        uint32_t w[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * i]) * alpha, __uint_as_float(r[2 * i + 1]) * alpha);
+            w[i] = *reinterpret_cast<uint32_t *>(&v);
+        }
+        uint4 *dst = reinterpret_cast<uint4 *>(dst_bytes);
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+    }
+}
+
 // 2-D tile load whose completion bytes go to the barrier at the same offset in
 // the pair's leader CTA (cluster rank 0).
 __device__ __forceinline__ void tma_load_pair(void *smem_dst, const CUtensorMap *tmap, int32_t x,
@@ -80,7 +112,8 @@ __device__ __forceinline__ void tma_load_pair(void *smem_dst, const CUtensorMap 
         : "memory");
 }
 
-// KIND: CLPK_DT_BF16 / CLPK_DT_F16 -> kind::f16 (K=16); CLPK_DT_E4M3 -> kind::f8f6f4 (K=32).
+// DT: BF16 / F16 -> kind::f16 (K = 16 per instruction); E4M3 / E5M2 -> kind::f8f6f4 (K = 32);
+// TF32 -> kind::tf32 (K = 8, fp32 out); I8 -> kind::i8 (K = 32, int32 out).  Always 128 bytes of K per stage.
 template <int DT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
     gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -149,8 +182,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
     } else if (warp == 1) {
         // ---------------- MMA issuer (leader CTA) ----------------
         if (rank == 0 && lane == 0) {
-            constexpr uint32_t kAFmt = (DT == CLPK_DT_BF16) ? kFmtBF16 : (DT == CLPK_DT_F16 ? kFmtF16 : kFmtE4M3);
-            const uint32_t idesc = make_idesc(256, 256, kAFmt, kAFmt, kAccF32);
+            constexpr uint32_t kAFmt = DT == CLPK_DT_BF16 ? kFmtBF16 : DT == CLPK_DT_F16 ? kFmtF16 : DT == CLPK_DT_TF32 ? kFmtTF32
+                                     : DT == CLPK_DT_I8 ? kFmtS8 : DT == CLPK_DT_E5M2 ? kFmtE5M2 : kFmtE4M3;
+            // the E5M2 variant multiplies e5m2 A by e4m3 B (the pairing the reference's fp8_e5m2 row uses)
+            constexpr uint32_t kBFmt = DT == CLPK_DT_E5M2 ? kFmtE4M3 : kAFmt;
+            const uint32_t idesc = make_idesc(256, 256, kAFmt, kBFmt, DT == CLPK_DT_I8 ? kAccS32 : kAccF32);
             uint32_t it = 0, tcount = 0;
             bool ok = true;
             for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters, tcount++) {
@@ -175,8 +211,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
 #pragma unroll
                     for (uint32_t kk = 0; kk < 4; kk++) {
                         // +32 bytes of K per instruction: +2 in the (>>4) address field
-                        if constexpr (DT == CLPK_DT_E4M3)
+                        if constexpr (DT == CLPK_DT_E4M3 || DT == CLPK_DT_E5M2)
                             mma2_f8f6f4_ss(d, ad + 2 * kk, bd + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
+                        else if constexpr (DT == CLPK_DT_TF32)
+                            mma2_tf32_ss(d, ad + 2 * kk, bd + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
+                        else if constexpr (DT == CLPK_DT_I8)
+                            mma2_i8_ss(d, ad + 2 * kk, bd + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
                         else
                             mma2_f16_ss(d, ad + 2 * kk, bd + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
                     }
@@ -202,25 +242,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
             }
             tc_fence_after_sync();
             const size_t row = (size_t)mb * kTileMN + rank * 128 + q * 32 + lane;
-            __nv_bfloat16 *crow = p.c + row * p.n + (size_t)nb * kTileMN;
+            uint8_t *crow = static_cast<uint8_t *>(p.c) + (row * p.n + (size_t)nb * kTileMN) * OutBytes<DT>::value;
             const uint32_t taddr = tmem + b * 256 + ((q * 32) << 16);
 #pragma unroll 2
             for (uint32_t c = 0; c < kTileMN / 32; c++) {
                 uint32_t r[32];
                 tmem_ld_32x32b_x32(taddr + c * 32, r);
                 tmem_ld_wait();
-                uint32_t w[16];
-#pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    const float lo = __uint_as_float(r[2 * i]) * p.alpha;
-                    const float hi = __uint_as_float(r[2 * i + 1]) * p.alpha;
-                    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-                    w[i] = *reinterpret_cast<uint32_t *>(&v);
-                }
-                uint4 *dst = reinterpret_cast<uint4 *>(crow + c * 32);
-#pragma unroll
-                for (int i = 0; i < 4; i++)
-                    dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+                store_columns<DT>(crow + (size_t)c * 32 * OutBytes<DT>::value, r, p.alpha);
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -263,6 +292,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
 //  * Tensor memory: accumulator in columns [0,256), then one 48-column scale area
 //    per pipeline stage (16 columns A, 32 columns B).  No room is left for a second
 //    accumulator, so a tile's epilogue is not overlapped with the next main loop.
+//  * MXFP4 (MX = true: kind::mxf4.block_scale.scale_vec::2X, one ue8m0 scale per 32
+//    elements) has two factors per row per instruction, so one 32-bit word serves
+//    two instructions: the instruction descriptor's scale-factor id picks bytes 0-1
+//    or 2-3.  Half the blocks (2 of A + 4 of B per stage), half the copies.
 
 constexpr int kNvStages = 5;
 constexpr int kNvCopyThreads = 4;
@@ -271,6 +304,14 @@ constexpr uint32_t kSfaStageBytes = 2048;
 constexpr uint32_t kSfbStageBytes = 4096;
 constexpr uint32_t kNvStageBytes = kStageBytes + kSfaStageBytes + kSfbStageBytes;     // 38 KiB
 constexpr uint32_t kNvSfCol = 256, kNvSfColsPerStage = 48;
+
+template <bool MX> struct BlockScaled {
+    static constexpr uint32_t a_blocks = MX ? 2 : 4;            // 512-byte scale blocks of A per stage (per CTA)
+    static constexpr uint32_t b_blocks = MX ? 4 : 8;            // ... of B (all 256 columns)
+    static constexpr uint32_t blocks = a_blocks + b_blocks;
+    static constexpr uint32_t sf_bytes = blocks * 512;
+    static constexpr uint32_t sf_per_kblock = MX ? 8 : 16;      // factors per row per 256 elements of K
+};
 
 struct NvGemmSmem {
     uint64_t full[kNvStages];        // tiles and scale factors of both CTAs landed (leader's barrier)
@@ -281,28 +322,31 @@ struct NvGemmSmem {
     uint32_t tmem_base;
 };
 
-// scales [rows][k/16] (row-major bytes) -> per-instruction 512-byte blocks.
-// is_b = 0: blocks ordered [rows/128][k/256][4];  is_b = 1: [rows/256][k/256][4][2].
+// Row-major scale bytes [rows][k / block] -> 512-byte blocks in tensor-memory order, one
+// 32-bit word (four factors) per row per block.  NVFP4: 16 factors per row per stage =
+// 4 words; MXFP4: 8 factors = 2 words.  words = words per row per stage.
+// is_b = 0: blocks ordered [rows/128][k/256][words];  is_b = 1: [rows/256][k/256][words][2].
 __global__ void pack_scales_kernel(uint8_t *__restrict__ out, const uint8_t *__restrict__ in, uint32_t rows, uint32_t k,
-                                   int is_b)
+                                   int is_b, uint32_t words)
 {
-    const uint32_t sf_per_row = k / 16, kblocks = k / 256;
+    const uint32_t per_stage = words * 4, sf_per_row = k / 256 * per_stage, kblocks = k / 256;
     const uint64_t total = (uint64_t)rows * sf_per_row;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
         const uint32_t row = (uint32_t)(i / sf_per_row), sf = (uint32_t)(i % sf_per_row);
-        const uint32_t kb = sf / 16, kk = (sf % 16) / 4, j = sf % 4;
+        const uint32_t kb = sf / per_stage, kk = (sf % per_stage) / 4, j = sf % 4;
         const uint32_t r = row % 128;
         uint64_t block;
         if (!is_b)
-            block = ((uint64_t)(row / 128) * kblocks + kb) * 4 + kk;
+            block = ((uint64_t)(row / 128) * kblocks + kb) * words + kk;
         else
-            block = (((uint64_t)(row / 256) * kblocks + kb) * 4 + kk) * 2 + (row % 256) / 128;
+            block = (((uint64_t)(row / 256) * kblocks + kb) * words + kk) * 2 + (row % 256) / 128;
         out[block * 512 + (r % 32) * 16 + (r / 32) * 4 + j] = in[i];
     }
 }
 
+template <bool MX>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
-    gemm_nvf4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+    gemm_block_scaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                      GemmParams p)
 {
@@ -357,13 +401,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
                         break;
                     }
                     uint8_t *st = smem + (size_t)s * kNvStageBytes;
+                    using BS = BlockScaled<MX>;
                     if (rank == 0)
-                        mbar_expect_tx(&sh->full[s], 2 * kNvStageBytes);
+                        mbar_expect_tx(&sh->full[s], 2 * (kStageBytes + BS::sf_bytes));
                     // scale factors first: they still have to be copied on to tensor memory
-                    tma_load_pair(st + kStageBytes, &tmap_sfa, 0, (int32_t)((((mb * 2 + rank) * p.k_blocks) + kb) * 4),
-                                  &sh->full[s]);
-                    tma_load_pair(st + kStageBytes + kSfaStageBytes, &tmap_sfb, 0, (int32_t)(((nb * p.k_blocks) + kb) * 8),
-                                  &sh->full[s]);
+                    tma_load_pair(st + kStageBytes, &tmap_sfa, 0,
+                                  (int32_t)((((mb * 2 + rank) * p.k_blocks) + kb) * BS::a_blocks), &sh->full[s]);
+                    tma_load_pair(st + kStageBytes + BS::a_blocks * 512, &tmap_sfb, 0,
+                                  (int32_t)(((nb * p.k_blocks) + kb) * BS::b_blocks), &sh->full[s]);
                     const int32_t x = (int32_t)(kb * kRowBytesK);
                     tma_load_pair(st, &tmap_a, x, row_a, &sh->full[s]);
                     tma_load_pair(st + kHalfTileBytes, &tmap_b, x, row_b, &sh->full[s]);
@@ -373,7 +418,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
     } else if (warp == 1) {
         // ---------------- MMA issuer (leader CTA) ----------------
         if (rank == 0 && lane == 0) {
-            const uint32_t idesc = make_idesc_block_scaled(256, 256, kFmtE2M1, kFmtE2M1, /*ue4m3*/ 0, 0, 0);
+            // MXFP4: instruction kk reads bytes 0-1 (id 0) or 2-3 (id 2) of word kk / 2
+            const uint32_t idesc = make_idesc_block_scaled(256, 256, kFmtE2M1, kFmtE2M1, MX ? 1u : 0u, 0, 0);
+            const uint32_t idesc_hi = make_idesc_block_scaled(256, 256, kFmtE2M1, kFmtE2M1, 1u, 2, 2);
             uint32_t it = 0, tcount = 0;
             bool ok = true;
             for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters, tcount++) {
@@ -396,9 +443,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
                     const uint64_t ad = make_smem_desc(base, 16, 1024, kSwizzle128B);
                     const uint64_t bd = make_smem_desc(base + kHalfTileBytes, 16, 1024, kSwizzle128B);
 #pragma unroll
-                    for (uint32_t kk = 0; kk < 4; kk++)
-                        mma2_nvf4_bs(tmem, ad + 2 * kk, bd + 2 * kk, idesc, sfa_t + 4 * kk, sfb_t + 8 * kk,
-                                     (kb | kk) ? 1u : 0u);
+                    for (uint32_t kk = 0; kk < 4; kk++) {
+                        if constexpr (MX)
+                            mma2_mxf4_bs(tmem, ad + 2 * kk, bd + 2 * kk, (kk & 1) ? idesc_hi : idesc, sfa_t + 4 * (kk / 2),
+                                         sfb_t + 8 * (kk / 2), (kb | kk) ? 1u : 0u);
+                        else
+                            mma2_nvf4_bs(tmem, ad + 2 * kk, bd + 2 * kk, idesc, sfa_t + 4 * kk, sfb_t + 8 * kk,
+                                         (kb | kk) ? 1u : 0u);
+                    }
                     tc_commit_pair(&sh->empty[s], 3);
                 }
                 if (ok)
@@ -422,9 +474,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
                     tc_fence_after_sync();
                     const uint32_t sf_s = smem_u32(smem + (size_t)s * kNvStageBytes) + kStageBytes;
                     const uint32_t sf_t = tmem + kNvSfCol + s * kNvSfColsPerStage;
-                    // twelve 512-byte blocks per stage: 4 of A scales (4 columns each), then 8 of B scales
-                    for (uint32_t blk = me; blk < 12; blk += kNvCopyThreads)
-                        tmem_cp_32x128b_warpx4<2>(sf_t + 4 * blk, make_smem_desc(sf_s + blk * 512, 16, 128, kSwizzleNone));
+                    // 512-byte blocks of the stage: A's (4 columns each, from column 0), then B's (from column 16)
+                    using BS = BlockScaled<MX>;
+                    for (uint32_t blk = me; blk < BS::blocks; blk += kNvCopyThreads) {
+                        const uint32_t col = blk < BS::a_blocks ? 4 * blk : 16 + 4 * (blk - BS::a_blocks);
+                        tmem_cp_32x128b_warpx4<2>(sf_t + col, make_smem_desc(sf_s + blk * 512, 16, 128, kSwizzleNone));
+                    }
                     // arrives on sf_ready[s] (this CTA) when the copies above have completed in both CTAs
                     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                                      smem_u32(&sh->sf_ready[s]))
@@ -446,24 +501,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
             }
             tc_fence_after_sync();
             const size_t row = (size_t)mb * kTileMN + rank * 128 + q * 32 + lane;
-            __nv_bfloat16 *crow = p.c + row * p.n + (size_t)nb * kTileMN;
+            uint8_t *crow = static_cast<uint8_t *>(p.c) + (row * p.n + (size_t)nb * kTileMN) * 2;
             const uint32_t taddr = tmem + ((q * 32) << 16);
 #pragma unroll 2
             for (uint32_t c = 0; c < kTileMN / 32; c++) {
                 uint32_t r[32];
                 tmem_ld_32x32b_x32(taddr + c * 32, r);
                 tmem_ld_wait();
-                uint32_t w[16];
-#pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * i]) * p.alpha,
-                                                             __uint_as_float(r[2 * i + 1]) * p.alpha);
-                    w[i] = *reinterpret_cast<uint32_t *>(&v);
-                }
-                uint4 *dst = reinterpret_cast<uint4 *>(crow + c * 32);
-#pragma unroll
-                for (int i = 0; i < 4; i++)
-                    dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+                store_columns<CLPK_DT_NVF4>(crow + (size_t)c * 64, r, p.alpha);
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -573,6 +618,8 @@ int clpk_gemm_workspace_bytes(int dtype, uint32_t m, uint32_t n, uint32_t k, siz
     *bytes = 0;
     if (dtype == CLPK_DT_NVF4)
         *bytes = ((size_t)m + n) * (k / 16);
+    if (dtype == CLPK_DT_MXF4)              // packed into 4-byte words of which each instruction uses two bytes
+        *bytes = ((size_t)m + n) * (k / 32);
     return CLPK_OK;
 }
 
@@ -585,15 +632,20 @@ int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
     CLPK_REQUIRE(a->d_a && a->d_b && a->d_c && a->d_status, "NULL buffer");
     CLPK_REQUIRE(a->m % 256 == 0 && a->n % 256 == 0 && a->m > 0 && a->n > 0,
                  "M and N must be positive multiples of 256 (got %u, %u)", a->m, a->n);
-    CLPK_REQUIRE(a->k % 128 == 0 && a->k > 0, "K must be a positive multiple of 128 (got %u)", a->k);
-    CLPK_REQUIRE(a->dtype != CLPK_DT_NVF4 || a->k % 256 == 0, "NVFP4 needs K to be a multiple of 256 (got %u)", a->k);
+    CLPK_REQUIRE(a->k > 0, "K must be positive");
+    const bool block_scaled = a->dtype == CLPK_DT_NVF4 || a->dtype == CLPK_DT_MXF4;
+    CLPK_REQUIRE(!block_scaled || a->k % 256 == 0, "block-scaled FP4 needs K to be a multiple of 256 (got %u)", a->k);
     CLPK_REQUIRE(((uintptr_t)a->d_a % 16) == 0 && ((uintptr_t)a->d_b % 16) == 0 && ((uintptr_t)a->d_c % 16) == 0,
                  "operands must be 16-byte aligned");
     uint32_t elem_bits;
     switch (a->dtype) {
     case CLPK_DT_BF16:
     case CLPK_DT_F16:  elem_bits = 16; break;
-    case CLPK_DT_E4M3: elem_bits = 8; break;
+    case CLPK_DT_TF32: elem_bits = 32; break;
+    case CLPK_DT_E4M3:
+    case CLPK_DT_E5M2:
+    case CLPK_DT_I8:   elem_bits = 8; break;
+    case CLPK_DT_MXF4:
     case CLPK_DT_NVF4: elem_bits = 4; break;
     default:
         set_error("clpk_gemm: dtype %d is not available in this build", a->dtype);
@@ -603,6 +655,8 @@ int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
     CLPK_CUDA(cudaMemsetAsync(a->d_status, 0, sizeof(uint32_t), s));
 
     const uint64_t row_bytes = (uint64_t)a->k * elem_bits / 8;
+    CLPK_REQUIRE(((uint64_t)a->k * elem_bits) % (8 * kRowBytesK) == 0,
+                 "K = %u: a row of %u-bit elements must be a multiple of 128 bytes", a->k, elem_bits);
     CUtensorMap ta, tb;
     rc = make_operand_map(&ta, a->d_a, a->m, row_bytes);
     if (rc != CLPK_OK)
@@ -617,36 +671,47 @@ int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
     p.k = a->k;
     p.k_block_elems = kRowBytesK;          // x coordinate is in bytes: the maps are typed UINT8
     p.k_blocks = (uint32_t)(row_bytes / kRowBytesK);
-    p.c = static_cast<__nv_bfloat16 *>(a->d_c);
+    p.c = a->d_c;
     p.alpha = a->alpha;
     p.status = a->d_status;
 
 
-    if (a->dtype == CLPK_DT_NVF4) {
-        const size_t sfa_bytes = (size_t)a->m * (a->k / 16), sfb_bytes = (size_t)a->n * (a->k / 16);
-        CLPK_REQUIRE(a->d_sfa && a->d_sfb, "NVFP4 needs d_sfa and d_sfb");
+    if (block_scaled) {
+        const bool mx = a->dtype == CLPK_DT_MXF4;
+        const uint32_t words = mx ? 2 : 4;                      // 32-bit scale words per row per 256 elements of K
+        const size_t sfa_bytes = (size_t)a->m * (a->k / 256) * words * 4, sfb_bytes = (size_t)a->n * (a->k / 256) * words * 4;
+        CLPK_REQUIRE(a->d_sfa && a->d_sfb, "block-scaled FP4 needs d_sfa and d_sfb");
         CLPK_REQUIRE(a->d_workspace && a->workspace_bytes >= sfa_bytes + sfb_bytes && ((uintptr_t)a->d_workspace % 16) == 0,
-                     "NVFP4 needs a 16-byte aligned workspace of clpk_gemm_workspace_bytes() bytes");
+                     "block-scaled FP4 needs a 16-byte aligned workspace of clpk_gemm_workspace_bytes() bytes");
         uint8_t *wsa = static_cast<uint8_t *>(a->d_workspace), *wsb = wsa + sfa_bytes;
         const int pgrid = num_sms() * 8;
-        pack_scales_kernel<<<pgrid, 256, 0, s>>>(wsa, static_cast<const uint8_t *>(a->d_sfa), a->m, a->k, 0);
-        pack_scales_kernel<<<pgrid, 256, 0, s>>>(wsb, static_cast<const uint8_t *>(a->d_sfb), a->n, a->k, 1);
+        pack_scales_kernel<<<pgrid, 256, 0, s>>>(wsa, static_cast<const uint8_t *>(a->d_sfa), a->m, a->k, 0, words);
+        pack_scales_kernel<<<pgrid, 256, 0, s>>>(wsb, static_cast<const uint8_t *>(a->d_sfb), a->n, a->k, 1, words);
         CLPK_LAUNCH_CHECK("pack_scales");
         CUtensorMap tsa, tsb;
-        rc = make_scale_map(&tsa, wsa, sfa_bytes / 512, 4);
+        rc = make_scale_map(&tsa, wsa, sfa_bytes / 512, words);
         if (rc != CLPK_OK)
             return rc;
-        rc = make_scale_map(&tsb, wsb, sfb_bytes / 512, 8);
+        rc = make_scale_map(&tsb, wsb, sfb_bytes / 512, 2 * words);
         if (rc != CLPK_OK)
             return rc;
-        CLPK_CUDA(cudaFuncSetAttribute(gemm_nvf4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kNvGemmSmemBytes));
-        gemm_nvf4_kernel<<<(num_sms() / 2) * 2, kNvGemmThreads, kNvGemmSmemBytes, s>>>(ta, tb, tsa, tsb, p);
-        CLPK_LAUNCH_CHECK("gemm_nvf4");
+        const int grid = (num_sms() / 2) * 2;
+        if (mx) {
+            CLPK_CUDA(cudaFuncSetAttribute(gemm_block_scaled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kNvGemmSmemBytes));
+            gemm_block_scaled_kernel<true><<<grid, kNvGemmThreads, kNvGemmSmemBytes, s>>>(ta, tb, tsa, tsb, p);
+        } else {
+            CLPK_CUDA(cudaFuncSetAttribute(gemm_block_scaled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kNvGemmSmemBytes));
+            gemm_block_scaled_kernel<false><<<grid, kNvGemmThreads, kNvGemmSmemBytes, s>>>(ta, tb, tsa, tsb, p);
+        }
+        CLPK_LAUNCH_CHECK("gemm_block_scaled");
         return CLPK_OK;
     }
     switch (a->dtype) {
     case CLPK_DT_BF16: return launch_gemm<CLPK_DT_BF16>(ta, tb, p, s);
     case CLPK_DT_F16:  return launch_gemm<CLPK_DT_F16>(ta, tb, p, s);
+    case CLPK_DT_TF32: return launch_gemm<CLPK_DT_TF32>(ta, tb, p, s);
+    case CLPK_DT_I8:   return launch_gemm<CLPK_DT_I8>(ta, tb, p, s);
+    case CLPK_DT_E5M2: return launch_gemm<CLPK_DT_E5M2>(ta, tb, p, s);
     default:           return launch_gemm<CLPK_DT_E4M3>(ta, tb, p, s);
     }
 }

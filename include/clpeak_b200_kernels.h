@@ -341,20 +341,30 @@ CLPK_API double clpk_mma_flops_per_instr(int kind);
 /* ---- GEMM (takes the place of cuBLASLt in CudaPeak::runCublas) -----------------------------------
  * C[M][N] = A[M][K] * B[N][K]^T: A row-major, B "column-major K x N" = N rows
  * of K contiguous elements -- the reference's TN layout
- * (src/cuda/cuda_blas.cpp:275-287).  fp32 accumulation in tensor memory, bf16
- * output, no epilogue beyond the NVF4 tensor scale `alpha`.
- * dtype: CLPK_DT_BF16, CLPK_DT_F16, CLPK_DT_E4M3, CLPK_DT_NVF4.
- * M and N multiples of 256, K a multiple of 128.
- * NVF4: d_a/d_b are packed e2m1 (K/2 bytes per row); d_sfa/d_sfb are ue4m3
- * scales row-major [rows][K/16] as written by clpk_quantize_fp4; the call
- * repacks them into the tensor-core tile order in d_workspace
- * (clpk_gemm_workspace_bytes) before the main kernel. */
+ * (src/cuda/cuda_blas.cpp:275-287).  Accumulation in tensor memory, no epilogue
+ * beyond the multiplication by `alpha` (the product of the NVF4 tensor scales).
+ *   dtype            A / B elements                  accumulate   C element
+ *   CLPK_DT_BF16     bf16                            fp32         bf16
+ *   CLPK_DT_F16      fp16                            fp32         bf16
+ *   CLPK_DT_TF32     fp32 words (19 bits read)       fp32         fp32
+ *   CLPK_DT_E4M3     e4m3                            fp32         bf16
+ *   CLPK_DT_E5M2     A e5m2, B e4m3 (the pairing of the reference's fp8_e5m2 row,
+ *                    src/cuda/cuda_blas.cpp:632-638)  fp32         bf16
+ *   CLPK_DT_I8       int8                            int32        int32 (alpha ignored)
+ *   CLPK_DT_MXF4     e2m1 + ue8m0 per 32             fp32         bf16
+ *   CLPK_DT_NVF4     e2m1 + ue4m3 per 16             fp32         bf16
+ * M and N multiples of 256; K such that a row holds a multiple of 128 bytes
+ * (256 elements for the FP4 kinds).
+ * FP4 kinds: d_a/d_b are packed e2m1 (K/2 bytes per row); d_sfa/d_sfb are the
+ * scale bytes row-major [rows][K/16] (NVF4) or [rows][K/32] (MXF4) as written by
+ * clpk_quantize_fp4; the call repacks them into the tensor-core tile order in
+ * d_workspace (clpk_gemm_workspace_bytes) before the main kernel. */
 typedef struct clpk_gemm_args {
     int         dtype;
     uint32_t    m, n, k;
     const void *d_a;
     const void *d_b;
-    void       *d_c;          /* bf16 [M][N] row-major */
+    void       *d_c;          /* [M][N] row-major, element type by dtype (table above) */
     const void *d_sfa;
     const void *d_sfb;
     float       alpha;        /* applied in the epilogue; pass 1.0f when unused */

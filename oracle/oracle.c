@@ -818,6 +818,15 @@ double orc_gemm_element(int dtype, const void *a, const void *b, const uint8_t *
         case DT_BF16: va = orc_bf16_to_f32(((const uint16_t *)a)[i * k + x]); vb = orc_bf16_to_f32(((const uint16_t *)b)[j * k + x]); break;
         case DT_F16:  va = orc_f16_to_f32(((const uint16_t *)a)[i * k + x]);  vb = orc_f16_to_f32(((const uint16_t *)b)[j * k + x]); break;
         case DT_E4M3: va = orc_e4m3_to_f32(((const uint8_t *)a)[i * k + x]);  vb = orc_e4m3_to_f32(((const uint8_t *)b)[j * k + x]); break;
+        /* the reference's "fp8_e5m2" GEMM row multiplies e5m2 A by e4m3 B (src/cuda/cuda_blas.cpp:632-638) */
+        case DT_E5M2: va = orc_e5m2_to_f32(((const uint8_t *)a)[i * k + x]);  vb = orc_e4m3_to_f32(((const uint8_t *)b)[j * k + x]); break;
+        case DT_I8:   va = ((const int8_t *)a)[i * k + x];                    vb = ((const int8_t *)b)[j * k + x]; break;
+        case DT_TF32: {   /* the multiplier reads sign, exponent and 10 mantissa bits of each fp32 word */
+            uint32_t wa = ((const uint32_t *)a)[i * k + x] & 0xFFFFE000u, wb = ((const uint32_t *)b)[j * k + x] & 0xFFFFE000u;
+            float fa, fb; memcpy(&fa, &wa, 4); memcpy(&fb, &wb, 4);
+            va = fa; vb = fb;
+            break;
+        }
         default:
             va = orc_fp4_element((const uint8_t *)a, sfa, k, dtype, i, x);
             vb = orc_fp4_element((const uint8_t *)b, sfb, k, dtype, j, x);

@@ -114,7 +114,8 @@ void     orc_mma_tile_sp(int kind, const void *a_comp, const uint8_t *meta, cons
                          const uint8_t *sfb, double *p_out, double *s_out);
 
 /* One element of C = A * B^T in double from the quantised operands.
- * dtype = CLPK_DT_BF16 / F16 / E4M3 / NVF4 (sfa/sfb used for NVF4). */
+ * dtype = CLPK_DT_BF16 / F16 / E4M3 / E5M2 (e5m2 A x e4m3 B) / I8 / TF32 / MXF4 / NVF4
+ * (sfa/sfb used for the block-scaled kinds). */
 double   orc_gemm_element(int dtype, const void *a, const void *b, const uint8_t *sfa, const uint8_t *sfb,
                           uint64_t k, uint64_t i, uint64_t j, double *abs_sum);
 

@@ -10,25 +10,35 @@ from tests.gpu_util import dev_empty, stream_ptr, sync, to_np
 
 pytestmark = pytest.mark.gpu
 
-NP_DT = {N.DT_BF16: np.uint16, N.DT_F16: np.uint16, N.DT_E4M3: np.uint8}
+NP_DT = {N.DT_BF16: np.uint16, N.DT_F16: np.uint16, N.DT_E4M3: np.uint8, N.DT_E5M2: np.uint8, N.DT_I8: np.int8,
+         N.DT_TF32: np.uint32}
+WIDE_OUT = (N.DT_TF32, N.DT_I8)          # fp32 / int32 output; everything else writes bf16
 
 
 def make_gemm_operands(K, cuda, dtype, m, n, k, seed=40):
-    """A, B ~ N(0, 0.02) generated and quantised on the device (config 5)."""
-    tdt = cuda.int16 if NP_DT[dtype] == np.uint16 else cuda.uint8
+    """A, B ~ N(0, 0.02) generated and quantised on the device (config 5); int8 draws uniform[-8, 7].
+    The E5M2 variant pairs an e5m2 A with an e4m3 B."""
+    tdt = {np.uint16: cuda.int16, np.uint8: cuda.uint8, np.int8: cuda.int8, np.uint32: cuda.int32}[NP_DT[dtype]]
     out = []
-    for rows, sd in ((m, seed), (n, seed + 1)):
-        f = dev_empty(rows * k, cuda.float32)
-        K.clpk_fill_f32(f.data_ptr(), rows * k, sd, N.DIST_NORMAL, 0.0, 0.02, stream_ptr())
+    for which, (rows, sd) in enumerate(((m, seed), (n, seed + 1))):
         q = dev_empty(rows * k, tdt)
-        K.clpk_convert_f32(q.data_ptr(), f.data_ptr(), rows * k, dtype, stream_ptr())
+        if dtype == N.DT_I8:
+            K.clpk_fill_i8(q.data_ptr(), rows * k, sd, stream_ptr())
+        else:
+            f = dev_empty(rows * k, cuda.float32)
+            K.clpk_fill_f32(f.data_ptr(), rows * k, sd, N.DIST_NORMAL, 0.0, 0.02, stream_ptr())
+            conv = N.DT_E4M3 if (dtype == N.DT_E5M2 and which == 1) else dtype
+            K.clpk_convert_f32(q.data_ptr(), f.data_ptr(), rows * k, conv, stream_ptr())
         out.append(q)
     sync()
     return out
 
 
 def run_gemm(K, cuda, dtype, m, n, k, d_a, d_b):
-    d_c = cuda.full((m * n,), 0x7FC0, dtype=cuda.int16, device="cuda")     # bf16 NaN canary
+    if dtype in WIDE_OUT:
+        d_c = cuda.full((m * n,), 0x7FC00000, dtype=cuda.int32, device="cuda")   # fp32 NaN / unlikely int canary
+    else:
+        d_c = cuda.full((m * n,), 0x7FC0, dtype=cuda.int16, device="cuda")     # bf16 NaN canary
     d_status = dev_empty(1, cuda.int32)
     args = N.GemmArgs(dtype=dtype, m=m, n=n, k=k, d_a=d_a.data_ptr(), d_b=d_b.data_ptr(), d_c=d_c.data_ptr(),
                       d_sfa=None, d_sfb=None, alpha=1.0, d_workspace=None, workspace_bytes=0,
@@ -47,6 +57,13 @@ def check_samples(orc, dtype, a, b, c_u16, m, n, k, samples):
     worst = 0.0
     for (i, j) in samples:
         want, s = orc.gemm_element(dtype, a, b, k, int(i), int(j))
+        if dtype == N.DT_I8:
+            assert int(c_u16.view(np.int32)[i * n + j]) == int(want), f"int8 GEMM element ({i},{j}) is not exact"
+            continue
+        if dtype == N.DT_TF32:
+            got = float(c_u16.view(np.float32)[i * n + j])
+            worst = max(worst, abs(got - want) / (k * 2.0 ** -23 * s + 1e-30))      # fp32 out: no output rounding term
+            continue
         got = float(bf16_to_f64(c_u16[i * n + j: i * n + j + 1])[0])
         # fp32 accumulation over K terms (<= K*2^-24 relative to sum|a||b|, generous
         # for a truncating adder) plus the final rounding to bf16 (2^-9 relative).
@@ -55,30 +72,39 @@ def check_samples(orc, dtype, a, b, c_u16, m, n, k, samples):
     assert worst <= 1.0, f"worst sampled error is {worst:.3g}x the stated tolerance"
 
 
-@pytest.mark.parametrize("dtype", [N.DT_BF16, N.DT_F16, N.DT_E4M3])
+def c_view(dtype, d_c):
+    c = to_np(d_c)
+    if dtype in WIDE_OUT:
+        assert not np.any(c.view(np.uint32) == 0x7FC00000), "some of C was never written"
+        return c.view(np.uint32)
+    assert not np.any(c.view(np.uint16) == 0x7FC0), "some of C was never written"
+    return c.view(np.uint16)
+
+
+@pytest.mark.parametrize("dtype", [N.DT_BF16, N.DT_F16, N.DT_E4M3, N.DT_E5M2, N.DT_TF32, N.DT_I8])
 @pytest.mark.parametrize("m,n,k", [(256, 256, 128), (256, 256, 1024), (512, 768, 256), (1024, 1024, 2048)])
 def test_gemm_small_full_check(K, orc, cuda, dtype, m, n, k):
+    if dtype == N.DT_TF32:
+        k = max(k // 4, 32)               # K counts elements; the kernel wants 128 bytes of K per stage
     d_a, d_b = make_gemm_operands(K, cuda, dtype, m, n, k)
     d_c = run_gemm(K, cuda, dtype, m, n, k, d_a, d_b)
     a = to_np(d_a).view(NP_DT[dtype])
     b = to_np(d_b).view(NP_DT[dtype])
-    c = to_np(d_c).view(np.uint16)
-    assert not np.any(c == 0x7FC0), "some of C was never written"
+    c = c_view(dtype, d_c)
     rng = np.random.default_rng(1)
     samples = list(zip(rng.integers(0, m, 200), rng.integers(0, n, 200)))
     samples += [(0, 0), (m - 1, n - 1), (127, 128), (128, 127), (255, 255), (m - 1, 0), (0, n - 1)]
     check_samples(orc, dtype, a, b, c, m, n, k, samples)
 
 
-@pytest.mark.parametrize("dtype", [N.DT_BF16, N.DT_E4M3])
+@pytest.mark.parametrize("dtype", [N.DT_BF16, N.DT_E4M3, N.DT_I8, N.DT_TF32])
 def test_gemm_4096_sampled(K, orc, cuda, dtype):
     m = n = k = 4096
     d_a, d_b = make_gemm_operands(K, cuda, dtype, m, n, k)
     d_c = run_gemm(K, cuda, dtype, m, n, k, d_a, d_b)
     a = to_np(d_a).view(NP_DT[dtype])
     b = to_np(d_b).view(NP_DT[dtype])
-    c = to_np(d_c).view(np.uint16)
-    assert not np.any(c == 0x7FC0)
+    c = c_view(dtype, d_c)
     rng = np.random.default_rng(2)
     samples = list(zip(rng.integers(0, m, 300), rng.integers(0, n, 300)))
     check_samples(orc, dtype, a, b, c, m, n, k, samples)
@@ -95,32 +121,33 @@ def test_gemm_rejects_ragged(K, cuda):
 
 # ---- NVFP4 ---------------------------------------------------------------------------------
 
-def make_nvfp4_operand(K, cuda, rows, k, seed):
-    """N(0, 0.02) values quantised on the device: packed e2m1, ue4m3 scale per 16, fp32 tensor scale."""
+def make_nvfp4_operand(K, cuda, rows, k, seed, dtype=N.DT_NVF4):
+    """N(0, 0.02) values quantised on the device: packed e2m1 with a ue4m3 scale per 16 and an fp32
+    tensor scale (NVFP4), or a ue8m0 scale per 32 and no tensor scale (MXFP4)."""
     f = dev_empty(rows * k, cuda.float32)
     K.clpk_fill_f32(f.data_ptr(), rows * k, seed, N.DIST_NORMAL, 0.0, 0.02, stream_ptr())
     am = dev_empty(1, cuda.float32)
     K.clpk_absmax_f32(am.data_ptr(), f.data_ptr(), rows * k, stream_ptr())
     sync()
-    ts = float(np.float32(to_np(am)[0]) / np.float32(6.0 * 448.0))
+    ts = float(np.float32(to_np(am)[0]) / np.float32(6.0 * 448.0)) if dtype == N.DT_NVF4 else 1.0
     q = dev_empty(rows * k // 2, cuda.uint8)
-    sf = dev_empty(rows * k // 16, cuda.uint8)
-    K.clpk_quantize_fp4(q.data_ptr(), sf.data_ptr(), f.data_ptr(), rows, k, N.DT_NVF4, ts, stream_ptr())
+    sf = dev_empty(rows * k // (16 if dtype == N.DT_NVF4 else 32), cuda.uint8)
+    K.clpk_quantize_fp4(q.data_ptr(), sf.data_ptr(), f.data_ptr(), rows, k, dtype, ts, stream_ptr())
     sync()
     return q, sf, ts, f
 
 
-def run_nvfp4(K, cuda, m, n, k):
-    a, sfa, tsa, fa = make_nvfp4_operand(K, cuda, m, k, 40)
-    b, sfb, tsb, fb = make_nvfp4_operand(K, cuda, n, k, 41)
+def run_nvfp4(K, cuda, m, n, k, dtype=N.DT_NVF4):
+    a, sfa, tsa, fa = make_nvfp4_operand(K, cuda, m, k, 40, dtype)
+    b, sfb, tsb, fb = make_nvfp4_operand(K, cuda, n, k, 41, dtype)
     c = cuda.full((m * n,), 0x7FC0, dtype=cuda.int16, device="cuda")
     need = C.c_size_t(0)
-    K.clpk_gemm_workspace_bytes(N.DT_NVF4, m, n, k, C.byref(need))
-    assert need.value == (m + n) * (k // 16)
+    K.clpk_gemm_workspace_bytes(dtype, m, n, k, C.byref(need))
+    assert need.value == (m + n) * (k // (16 if dtype == N.DT_NVF4 else 32))
     ws = dev_empty(need.value, cuda.uint8)
     st = dev_empty(1, cuda.int32)
     alpha = float(np.float32(tsa) * np.float32(tsb))
-    args = N.GemmArgs(dtype=N.DT_NVF4, m=m, n=n, k=k, d_a=a.data_ptr(), d_b=b.data_ptr(), d_c=c.data_ptr(),
+    args = N.GemmArgs(dtype=dtype, m=m, n=n, k=k, d_a=a.data_ptr(), d_b=b.data_ptr(), d_c=c.data_ptr(),
                       d_sfa=sfa.data_ptr(), d_sfb=sfb.data_ptr(), alpha=alpha, d_workspace=ws.data_ptr(),
                       workspace_bytes=need.value, d_status=st.data_ptr())
     K.clpk_gemm(C.byref(args), stream_ptr())
@@ -130,15 +157,16 @@ def run_nvfp4(K, cuda, m, n, k):
                 fa=fa, fb=fb)
 
 
+@pytest.mark.parametrize("dtype", [N.DT_NVF4, N.DT_MXF4])
 @pytest.mark.parametrize("m,n,k", [(256, 256, 256), (256, 512, 1024), (768, 256, 512), (2048, 2048, 2048)])
-def test_gemm_nvfp4(K, orc, cuda, m, n, k):
-    r = run_nvfp4(K, cuda, m, n, k)
+def test_gemm_nvfp4(K, orc, cuda, m, n, k, dtype):
+    r = run_nvfp4(K, cuda, m, n, k, dtype)
     assert not np.any(r["c"] == 0x7FC0)
     rng = np.random.default_rng(5)
     samples = list(zip(rng.integers(0, m, 120), rng.integers(0, n, 120))) + [(0, 0), (m - 1, n - 1), (127, 128), (128, 127)]
     worst = 0.0
     for (i, j) in samples:
-        want, s = orc.gemm_element(N.DT_NVF4, r["a"], r["b"], k, int(i), int(j), r["sfa"], r["sfb"])
+        want, s = orc.gemm_element(dtype, r["a"], r["b"], k, int(i), int(j), r["sfa"], r["sfb"])
         want *= r["alpha"]
         s *= r["alpha"]
         got = float(bf16_to_f64(r["c"][i * n + j: i * n + j + 1])[0])
@@ -147,11 +175,12 @@ def test_gemm_nvfp4(K, orc, cuda, m, n, k):
     assert worst <= 1.0, f"worst sampled error is {worst:.3g}x the stated tolerance"
 
 
-def test_gemm_nvfp4_tracks_the_unquantised_product(K, orc, cuda):
+@pytest.mark.parametrize("dtype", [N.DT_NVF4, N.DT_MXF4])
+def test_gemm_nvfp4_tracks_the_unquantised_product(K, orc, cuda, dtype):
     """End-to-end sanity of the whole recipe (quantiser + scales + tensor scale): C correlates with fp32 A.B^T."""
     m = n = 256
     k = 2048
-    r = run_nvfp4(K, cuda, m, n, k)
+    r = run_nvfp4(K, cuda, m, n, k, dtype)
     ref = (r["fa"].view(m, k) @ r["fb"].view(n, k).T).cpu().numpy().astype(np.float64)
     got = bf16_to_f64(r["c"]).reshape(m, n)
     assert np.corrcoef(ref.ravel(), got.ravel())[0, 1] > 0.98
