@@ -1,19 +1,18 @@
 // C[M][N] = A[M][K] * B[N][K]^T on tcgen05.mma, the in-house replacement for the
 // cuBLASLt call the reference makes for its "GEMM peak" rows.
 //
-// Shape of the kernel
+// Shape of the dense kernel (gemm_kernel; the block-scaled FP4 kernel further down
+// keeps a 256 x 256 cluster tile because its scale factors need tensor-memory columns)
 //  * Persistent: one 2-CTA cluster per SM pair, tiles handed out round-robin.
-//  * A cluster computes a 256x256 tile with 2-SM MMAs (cta_group::2, M=256,
-//    N=256): CTA r of the pair owns rows [128r, 128r+128) of the tile and holds
-//    that half of the accumulator in its own tensor memory; it loads its 128
-//    rows of A and its 128-row half of B, and the MMA reads both CTAs' shared
+//  * A cluster computes a 512 x 256 tile with 2-SM MMAs (cta_group::2, M = 256,
+//    N = 256), two row blocks sharing one B tile; each CTA holds 256 x 256 of the
+//    accumulator, i.e. all of its tensor memory.  The MMA reads both CTAs' shared
 //    memory.  No TMA multicast anywhere: each CTA fetches what it needs itself.
 //  * Warp roles (192 threads): warp 0 TMA producer, warp 1 MMA issuer (leader
-//    CTA only) and TMEM owner, warps 2-5 epilogue (TMEM -> registers -> bf16 ->
-//    global).  TMEM holds two 256-column accumulators so the epilogue of tile
-//    i overlaps the main loop of tile i+1.
+//    CTA only) and TMEM owner, warps 2-5 epilogue (TMEM -> registers -> output
+//    type -> global).
 //  * K is consumed in blocks of 128 bytes per row (64 x 16-bit, 128 x 8-bit),
-//    the width of one 128-byte-swizzled TMA box; a stage is 16 KiB of A and
+//    the width of one 128-byte-swizzled TMA box; a stage is 32 KiB of A and
 //    16 KiB of B per CTA.  Both CTAs' loads signal the leader's "full"
 //    barrier; tcgen05.commit releases a stage in both CTAs at once.
 //  * Every mbarrier wait is bounded; on expiry the status word is set and all
@@ -24,15 +23,17 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <atomic>
+#include <cstdlib>
+
 #include "../clpk_internal.h"
 #include "../clpk_ptx.cuh"
 
 namespace clpk {
 
-constexpr int kGemmStages = 6;
 constexpr uint32_t kRowBytesK = 128;                        // K bytes per row per stage
 constexpr uint32_t kHalfTileBytes = 128 * kRowBytesK;       // 16 KiB: 128 rows x 128 B
-constexpr uint32_t kStageBytes = 2 * kHalfTileBytes;        // A half + B half
+constexpr uint32_t kStageBytes = 2 * kHalfTileBytes;        // A half + B half (block-scaled kernel)
 constexpr uint32_t kTileMN = 256;
 constexpr int kGemmThreads = 192;
 constexpr int kGroupN = 8;                                  // tile columns per raster group
@@ -44,14 +45,9 @@ struct GemmParams {
     void *c;                    // bf16, or fp32 (TF32) / int32 (I8): see out_elem_bytes()
     float alpha;
     uint32_t *status;
-};
-
-struct GemmSmem {
-    uint64_t full[kGemmStages];
-    uint64_t empty[kGemmStages];
-    uint64_t tmem_full[2];
-    uint64_t tmem_empty[2];
-    uint32_t tmem_base;
+    uint32_t group;             // tile columns per raster group (dense kernel)
+    unsigned int *wave_sync;    // one counter for this launch, or NULL: see wave_align()
+    unsigned long long *trace;  // optional: start time of every tile, [cluster][64]
 };
 
 __device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uint32_t tiles_n,
@@ -114,6 +110,79 @@ __device__ __forceinline__ void tma_load_pair(void *smem_dst, const CUtensorMap 
 
 // DT: BF16 / F16 -> kind::f16 (K = 16 per instruction); E4M3 / E5M2 -> kind::f8f6f4 (K = 32);
 // TF32 -> kind::tf32 (K = 8, fp32 out); I8 -> kind::i8 (K = 32, int32 out).  Always 128 bytes of K per stage.
+//
+// Tile shape.  A cluster computes 512 x 256 of C: two M = 256 row blocks ("halves") that
+// share one B tile.  Row block h covers cluster rows [256h, 256h + 256); CTA r of the pair
+// owns the r-th 128 of them and keeps that part of the accumulator in tensor-memory
+// columns [256h, 256h + 256) -- all 512 columns of each CTA are accumulator.  Per stage a
+// CTA loads two 16 KiB A sub-tiles and its 16 KiB half of B (48 KiB; four stages), and the
+// leader issues eight 2-CTA instructions (2 halves x 4 K steps).  Against a 256 x 256
+// cluster tile this reads a third fewer operand bytes per flop from L2 and DRAM and reads
+// B from shared memory once for two row blocks; the price is that the accumulator cannot
+// be double-buffered, so the epilogue of a tile (a few microseconds per ~200) is exposed.
+// Rows of C beyond M (M a multiple of 256 but not of 512) come out of zero-filled TMA boxes
+// and are not stored.
+constexpr int kDenseStages = 4;
+constexpr uint32_t kDenseStageBytes = 3 * kHalfTileBytes;          // A half 0, A half 1, B half
+constexpr uint32_t kDenseTileM = 512;
+
+struct DenseSmem {
+    uint64_t full[kDenseStages];
+    uint64_t empty[kDenseStages];
+    uint64_t tmem_full;
+    uint64_t tmem_empty;
+    uint32_t tmem_base;
+};
+
+// Tiles are walked in groups of `group` tile columns, M fastest inside a group.
+__device__ __forceinline__ void dense_tile_coords(uint32_t tile, uint32_t tiles_m, uint32_t tiles_n, uint32_t group,
+                                                  uint32_t &mb, uint32_t &nb)
+{
+    const uint32_t per_group = group * tiles_m;
+    const uint32_t g = tile / per_group;
+    const uint32_t within = tile - g * per_group;
+    const uint32_t first_n = g * group;
+    const uint32_t width = (tiles_n - first_n) < group ? (tiles_n - first_n) : group;
+    mb = within / width;
+    nb = first_n + within % width;
+}
+
+// Keeping the clusters in step.  The schedule is static, so all clusters start wave w
+// (their w-th tile) together only if they run at exactly the same speed.  They do not:
+// measured on a B200, the start times of a wave spread by about 4 us more with every
+// wave (some SM pairs are persistently ~1.7 % slower), 70 us after 20 waves.  Clusters
+// that share an operand panel then ask for it that far apart, the L2 has long replaced
+// it, and every panel is fetched from DRAM several times per wave.  So the producers
+// meet before each wave: every CTA adds one to a counter and waits until the counter
+// shows that all CTAs of the wave have arrived.  The kernel is launched cooperatively
+// (all CTAs resident), and the wait is bounded all the same: a CTA that has waited
+// 40 us stops taking part, after which the others time out once each and the kernel
+// finishes unaligned.
+__device__ __forceinline__ void wave_align(const GemmParams &p, uint32_t wave, uint32_t n_tiles, uint32_t n_clusters,
+                                           bool &enabled)
+{
+    if (!enabled || wave == 0)
+        return;
+    // arrivals expected up to and including this wave: two CTAs per tile of waves 1..wave
+    const uint32_t tiles_through = (wave + 1) * n_clusters < n_tiles ? (wave + 1) * n_clusters : n_tiles;
+    const unsigned int target = 2u * (tiles_through - n_clusters);
+    atomicAdd(p.wave_sync, 1u);
+    unsigned long long t0, t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (;;) {
+        unsigned int seen;
+        asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.wave_sync) : "memory");
+        if (seen >= target)
+            return;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        if (t1 - t0 > 40000ull) {
+            enabled = false;
+            return;
+        }
+        __nanosleep(64);
+    }
+}
+
 template <int DT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
     gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -123,24 +192,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
     // The runtime only guarantees 16-byte alignment of dynamic shared memory;
     // the swizzled tiles need 1024.
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    GemmSmem *sh = reinterpret_cast<GemmSmem *>(smem + (size_t)kGemmStages * kStageBytes);
+    DenseSmem *sh = reinterpret_cast<DenseSmem *>(smem + (size_t)kDenseStages * kDenseStageBytes);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const uint32_t cluster_id = blockIdx.x >> 1;
     const uint32_t n_clusters = gridDim.x >> 1;
-    const uint32_t tiles_m = p.m / kTileMN, tiles_n = p.n / kTileMN;
+    const uint32_t tiles_m = (p.m + kDenseTileM - 1) / kDenseTileM, tiles_n = p.n / kTileMN;
     const uint32_t n_tiles = tiles_m * tiles_n;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kGemmStages; s++) {
+        for (int s = 0; s < kDenseStages; s++) {
             mbar_init(&sh->full[s], 1);
             mbar_init(&sh->empty[s], 1);
         }
-        for (int b = 0; b < 2; b++) {
-            mbar_init(&sh->tmem_full[b], 1);
-            mbar_init(&sh->tmem_empty[b], 8);    // 4 epilogue warps x 2 CTAs
-        }
+        mbar_init(&sh->tmem_full, 1);
+        mbar_init(&sh->tmem_empty, 8);       // 4 epilogue warps x 2 CTAs
         mbar_fence_init();
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
@@ -157,25 +224,32 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             uint32_t it = 0;
-            bool ok = true;
+            bool ok = true, aligned = p.wave_sync != nullptr;
             for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters) {
                 uint32_t mb, nb;
-                tile_coords(tile, tiles_m, tiles_n, mb, nb);
-                const int32_t row_a = (int32_t)(mb * kTileMN + rank * 128);
+                dense_tile_coords(tile, tiles_m, tiles_n, p.group, mb, nb);
+                wave_align(p, tile / n_clusters, n_tiles, n_clusters, aligned);
+                if (p.trace && rank == 0) {
+                    unsigned long long t;
+                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+                    p.trace[(size_t)cluster_id * 64 + ((tile / n_clusters) & 63)] = t;
+                }
+                const int32_t row_a0 = (int32_t)(mb * kDenseTileM + rank * 128);
                 const int32_t row_b = (int32_t)(nb * kTileMN + rank * 128);
                 for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
-                    const uint32_t s = it % kGemmStages, round = it / kGemmStages;
+                    const uint32_t s = it % kDenseStages, round = it / kDenseStages;
                     if (round > 0 && !mbar_wait(&sh->empty[s], (round - 1) & 1)) {
                         atomicCAS(p.status, 0u, 0x201u);
                         ok = false;
                         break;
                     }
-                    uint8_t *st = smem + (size_t)s * kStageBytes;
+                    uint8_t *st = smem + (size_t)s * kDenseStageBytes;
                     if (rank == 0)
-                        mbar_expect_tx(&sh->full[s], 2 * kStageBytes);
+                        mbar_expect_tx(&sh->full[s], 2 * kDenseStageBytes);
                     const int32_t x = (int32_t)(kb * p.k_block_elems);
-                    tma_load_pair(st, &tmap_a, x, row_a, &sh->full[s]);
-                    tma_load_pair(st + kHalfTileBytes, &tmap_b, x, row_b, &sh->full[s]);
+                    tma_load_pair(st, &tmap_a, x, row_a0, &sh->full[s]);
+                    tma_load_pair(st + kHalfTileBytes, &tmap_a, x, row_a0 + 256, &sh->full[s]);
+                    tma_load_pair(st + 2 * kHalfTileBytes, &tmap_b, x, row_b, &sh->full[s]);
                 }
             }
         }
@@ -190,40 +264,42 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
             uint32_t it = 0, tcount = 0;
             bool ok = true;
             for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters, tcount++) {
-                const uint32_t b = tcount & 1, use = tcount >> 1;
-                if (use > 0 && !mbar_wait(&sh->tmem_empty[b], (use - 1) & 1)) {
+                if (tcount > 0 && !mbar_wait(&sh->tmem_empty, (tcount - 1) & 1)) {
                     atomicCAS(p.status, 0u, 0x202u);
                     break;
                 }
                 tc_fence_after_sync();
-                const uint32_t d = tmem + b * 256;
                 for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
-                    const uint32_t s = it % kGemmStages, round = it / kGemmStages;
+                    const uint32_t s = it % kDenseStages, round = it / kDenseStages;
                     if (!mbar_wait(&sh->full[s], round & 1)) {
                         atomicCAS(p.status, 0u, 0x203u);
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
-                    const uint32_t a_addr = smem_u32(smem + (size_t)s * kStageBytes);
-                    const uint64_t ad = make_smem_desc(a_addr, 16, 1024, kSwizzle128B);
-                    const uint64_t bd = make_smem_desc(a_addr + kHalfTileBytes, 16, 1024, kSwizzle128B);
+                    const uint32_t base = smem_u32(smem + (size_t)s * kDenseStageBytes);
+                    const uint64_t bd = make_smem_desc(base + 2 * kHalfTileBytes, 16, 1024, kSwizzle128B);
 #pragma unroll
-                    for (uint32_t kk = 0; kk < 4; kk++) {
-                        // +32 bytes of K per instruction: +2 in the (>>4) address field
-                        if constexpr (DT == CLPK_DT_E4M3 || DT == CLPK_DT_E5M2)
-                            mma2_f8f6f4_ss(d, ad + 2 * kk, bd + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
-                        else if constexpr (DT == CLPK_DT_TF32)
-                            mma2_tf32_ss(d, ad + 2 * kk, bd + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
-                        else if constexpr (DT == CLPK_DT_I8)
-                            mma2_i8_ss(d, ad + 2 * kk, bd + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
-                        else
-                            mma2_f16_ss(d, ad + 2 * kk, bd + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
+                    for (uint32_t h = 0; h < 2; h++) {
+                        const uint64_t ad = make_smem_desc(base + h * kHalfTileBytes, 16, 1024, kSwizzle128B);
+                        const uint32_t d = tmem + h * 256;
+#pragma unroll
+                        for (uint32_t kk = 0; kk < 4; kk++) {
+                            // +32 bytes of K per instruction: +2 in the (>>4) address field
+                            if constexpr (DT == CLPK_DT_E4M3 || DT == CLPK_DT_E5M2)
+                                mma2_f8f6f4_ss(d, ad + 2 * kk, bd + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
+                            else if constexpr (DT == CLPK_DT_TF32)
+                                mma2_tf32_ss(d, ad + 2 * kk, bd + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
+                            else if constexpr (DT == CLPK_DT_I8)
+                                mma2_i8_ss(d, ad + 2 * kk, bd + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
+                            else
+                                mma2_f16_ss(d, ad + 2 * kk, bd + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
+                        }
                     }
                     tc_commit_pair(&sh->empty[s], 3);
                 }
                 if (ok)
-                    tc_commit_pair(&sh->tmem_full[b], 3);
+                    tc_commit_pair(&sh->tmem_full, 3);
             }
         }
     } else {
@@ -232,29 +308,33 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
         uint32_t tcount = 0;
         for (uint32_t tile = cluster_id; tile < n_tiles; tile += n_clusters, tcount++) {
             uint32_t mb, nb;
-            tile_coords(tile, tiles_m, tiles_n, mb, nb);
-            const uint32_t b = tcount & 1, use = tcount >> 1;
+            dense_tile_coords(tile, tiles_m, tiles_n, p.group, mb, nb);
             // warp-uniform verdict: the tcgen05.ld below is warp-aligned
-            if (!__all_sync(0xffffffffu, mbar_wait(&sh->tmem_full[b], use & 1) ? 1 : 0)) {
+            if (!__all_sync(0xffffffffu, mbar_wait(&sh->tmem_full, tcount & 1) ? 1 : 0)) {
                 if (lane == 0)
                     atomicCAS(p.status, 0u, 0x204u);
                 break;
             }
             tc_fence_after_sync();
-            const size_t row = (size_t)mb * kTileMN + rank * 128 + q * 32 + lane;
-            uint8_t *crow = static_cast<uint8_t *>(p.c) + (row * p.n + (size_t)nb * kTileMN) * OutBytes<DT>::value;
-            const uint32_t taddr = tmem + b * 256 + ((q * 32) << 16);
+#pragma unroll 1
+            for (uint32_t h = 0; h < 2; h++) {
+                const size_t row = (size_t)mb * kDenseTileM + h * 256 + rank * 128 + q * 32 + lane;
+                const bool in_range = row < p.m;
+                uint8_t *crow = static_cast<uint8_t *>(p.c) + (row * p.n + (size_t)nb * kTileMN) * OutBytes<DT>::value;
+                const uint32_t taddr = tmem + h * 256 + ((q * 32) << 16);
 #pragma unroll 2
-            for (uint32_t c = 0; c < kTileMN / 32; c++) {
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(taddr + c * 32, r);
-                tmem_ld_wait();
-                store_columns<DT>(crow + (size_t)c * 32 * OutBytes<DT>::value, r, p.alpha);
+                for (uint32_t c = 0; c < kTileMN / 32; c++) {
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(taddr + c * 32, r);
+                    tmem_ld_wait();
+                    if (in_range)
+                        store_columns<DT>(crow + (size_t)c * 32 * OutBytes<DT>::value, r, p.alpha);
+                }
             }
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0)
-                mbar_arrive_cluster(&sh->tmem_empty[b], 0);
+                mbar_arrive_cluster(&sh->tmem_empty, 0);
         }
     }
 
@@ -593,14 +673,43 @@ static int make_scale_map(CUtensorMap *map, const void *base, uint64_t n_rows, u
 
 constexpr size_t kNvGemmSmemBytes = (size_t)kNvStages * kNvStageBytes + sizeof(NvGemmSmem) + 1024;
 
-constexpr size_t kGemmSmemBytes = (size_t)kGemmStages * kStageBytes + sizeof(GemmSmem) + 1024;
+constexpr size_t kGemmSmemBytes = (size_t)kDenseStages * kDenseStageBytes + sizeof(DenseSmem) + 1024;
+
+// One wave counter per launch, from a small ring so that launches on different streams
+// do not share one; zeroed in stream order before the kernel.
+constexpr int kSyncSlots = 32;
+__device__ unsigned int g_wave_sync[kSyncSlots];
+static std::atomic<unsigned> g_next_sync_slot{0};
 
 template <int DT>
-static int launch_gemm(const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, cudaStream_t s)
+static int launch_gemm(const CUtensorMap &ta, const CUtensorMap &tb, GemmParams p, cudaStream_t s)
 {
     CLPK_CUDA(cudaFuncSetAttribute(gemm_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)kGemmSmemBytes));
     const int grid = (num_sms() / 2) * 2;
+    const char *off = getenv("CLPK_GEMM_NO_ALIGN");
+    p.wave_sync = nullptr;
+    if (!(off && off[0] == '1')) {
+        unsigned int *base = nullptr;
+        CLPK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&base), g_wave_sync));
+        p.wave_sync = base + g_next_sync_slot.fetch_add(1) % kSyncSlots;
+        CLPK_CUDA(cudaMemsetAsync(p.wave_sync, 0, sizeof(unsigned int), s));
+        // cooperative: every CTA is resident before any runs, so the wave counter can fill up
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)grid);
+        cfg.blockDim = dim3(kGemmThreads);
+        cfg.dynamicSmemBytes = kGemmSmemBytes;
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeCooperative;
+        attr[0].val.cooperative = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, gemm_kernel<DT>, ta, tb, p) == cudaSuccess)
+            return CLPK_OK;
+        (void)cudaGetLastError();       // not co-schedulable here: run without the alignment
+        p.wave_sync = nullptr;
+    }
     gemm_kernel<DT><<<grid, kGemmThreads, kGemmSmemBytes, s>>>(ta, tb, p);
     CLPK_LAUNCH_CHECK("gemm");
     return CLPK_OK;
@@ -674,6 +783,15 @@ int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
     p.c = a->d_c;
     p.alpha = a->alpha;
     p.status = a->d_status;
+    // waves of ~(SM pairs) tiles that are about square in elements: twice as many 256-wide tile columns
+    // as 512-tall tile rows (74 pairs: 12 x 6)
+    p.group = 12;
+    p.wave_sync = nullptr;
+    p.trace = nullptr;
+    if (const char *e = getenv("CLPK_GEMM_TRACE"))
+        p.trace = (unsigned long long *)strtoull(e, nullptr, 0);
+    if (const char *e = getenv("CLPK_GEMM_GROUP"))
+        p.group = (uint32_t)atoi(e) > 0 ? (uint32_t)atoi(e) : p.group;
 
 
     if (block_scaled) {
