@@ -35,7 +35,7 @@ constexpr uint32_t kRowBytesK = 128;                        // K bytes per row p
 constexpr uint32_t kHalfTileBytes = 128 * kRowBytesK;       // 16 KiB: 128 rows x 128 B
 constexpr uint32_t kStageBytes = 2 * kHalfTileBytes;        // A half + B half (block-scaled kernel)
 constexpr uint32_t kTileMN = 256;
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;                          // dense kernel: producer, MMA, 8 epilogue warps
 constexpr int kGroupN = 8;                                  // tile columns per raster group
 
 struct GemmParams {
@@ -47,7 +47,7 @@ struct GemmParams {
     uint32_t *status;
     uint32_t group;             // tile columns per raster group (dense kernel)
     unsigned int *wave_sync;    // one counter for this launch, or NULL: see wave_align()
-    unsigned long long *trace;  // optional: start time of every tile, [cluster][64]
+    uint32_t align_at;          // K block of a tile before which the producers meet
 };
 
 __device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uint32_t tiles_n,
@@ -126,6 +126,9 @@ constexpr int kDenseStages = 4;
 constexpr uint32_t kDenseStageBytes = 3 * kHalfTileBytes;          // A half 0, A half 1, B half
 constexpr uint32_t kDenseTileM = 512;
 
+constexpr int kEpilogueWarps = 8;
+constexpr uint32_t kStagingBytes = 32 * 128;                       // 32 rows x 128 bytes of C
+
 struct DenseSmem {
     uint64_t full[kDenseStages];
     uint64_t empty[kDenseStages];
@@ -186,13 +189,14 @@ __device__ __forceinline__ void wave_align(const GemmParams &p, uint32_t wave, u
 template <int DT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
     gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                GemmParams p)
+                const __grid_constant__ CUtensorMap tmap_c, GemmParams p)
 {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // The runtime only guarantees 16-byte alignment of dynamic shared memory;
     // the swizzled tiles need 1024.
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    DenseSmem *sh = reinterpret_cast<DenseSmem *>(smem + (size_t)kDenseStages * kDenseStageBytes);
+    uint8_t *staging = smem + (size_t)kDenseStages * kDenseStageBytes;           // one 4 KiB box per epilogue warp
+    DenseSmem *sh = reinterpret_cast<DenseSmem *>(staging + kEpilogueWarps * kStagingBytes);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
@@ -207,10 +211,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
             mbar_init(&sh->empty[s], 1);
         }
         mbar_init(&sh->tmem_full, 1);
-        mbar_init(&sh->tmem_empty, 8);       // 4 epilogue warps x 2 CTAs
+        mbar_init(&sh->tmem_empty, 16);      // 8 epilogue warps x 2 CTAs
         mbar_fence_init();
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
+        tma_prefetch_desc(&tmap_c);
     }
     if (warp == 1)
         tmem_alloc<2>(&sh->tmem_base, 512);
@@ -228,15 +233,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
             for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters) {
                 uint32_t mb, nb;
                 dense_tile_coords(tile, tiles_m, tiles_n, p.group, mb, nb);
-                wave_align(p, tile / n_clusters, n_tiles, n_clusters, aligned);
-                if (p.trace && rank == 0) {
-                    unsigned long long t;
-                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-                    p.trace[(size_t)cluster_id * 64 + ((tile / n_clusters) & 63)] = t;
-                }
                 const int32_t row_a0 = (int32_t)(mb * kDenseTileM + rank * 128);
                 const int32_t row_b = (int32_t)(nb * kTileMN + rank * 128);
+                // Meet the other producers after the tile's first two stages are on their way, not
+                // before: the MMA thread then has work while the slowest producer arrives.
+                const uint32_t align_at = p.k_blocks > p.align_at ? p.align_at : 0u;
                 for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
+                    if (kb == align_at)
+                        wave_align(p, tile / n_clusters, n_tiles, n_clusters, aligned);
                     const uint32_t s = it % kDenseStages, round = it / kDenseStages;
                     if (round > 0 && !mbar_wait(&sh->empty[s], (round - 1) & 1)) {
                         atomicCAS(p.status, 0u, 0x201u);
@@ -304,7 +308,23 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
         }
     } else {
         // ---------------- epilogue warps ----------------
-        const uint32_t q = (uint32_t)(warp & 3);        // TMEM lane quarter this warp may read
+        // Eight warps: warp w may read TMEM lanes 32 (w % 4) .. +31; the two warps of a lane
+        // quarter split each row block's 256 columns in halves.  A warp moves its 32 rows
+        // x 128 columns in boxes of 128 bytes per row (64 bf16 or 32 fp32/int32 columns):
+        // tcgen05.ld -> convert -> its own 4 KiB staging box in shared memory, written in the
+        // 128-byte swizzle so that the 32 lanes (one row each) spread over the banks -> one
+        // TMA store per box, which writes whole lines of C and clips rows beyond M.  A
+        // thread-per-row store straight to global memory costs 32 partial-sector
+        // transactions per instruction and held the drain at 8 us per tile.
+        // Tensor memory is handed back as soon as the tile's last tcgen05.ld has landed,
+        // before the tail of the stores.
+        constexpr uint32_t kColsPerBox = 128 / OutBytes<DT>::value;
+        constexpr uint32_t kBoxes = 128 / kColsPerBox;                  // per row block per warp
+        const uint32_t q = (uint32_t)(warp & 3);
+        const uint32_t col_half = (uint32_t)(warp - 2) >> 2;
+        uint8_t *box = staging + (size_t)(warp - 2) * kStagingBytes;
+        uint8_t *my_row = box + lane * 128;
+        const uint32_t sw = (uint32_t)(lane & 7);
         uint32_t tcount = 0;
         for (uint32_t tile = cluster_id; tile < n_tiles; tile += n_clusters, tcount++) {
             uint32_t mb, nb;
@@ -317,25 +337,57 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
             }
             tc_fence_after_sync();
 #pragma unroll 1
-            for (uint32_t h = 0; h < 2; h++) {
-                const size_t row = (size_t)mb * kDenseTileM + h * 256 + rank * 128 + q * 32 + lane;
-                const bool in_range = row < p.m;
-                uint8_t *crow = static_cast<uint8_t *>(p.c) + (row * p.n + (size_t)nb * kTileMN) * OutBytes<DT>::value;
-                const uint32_t taddr = tmem + h * 256 + ((q * 32) << 16);
-#pragma unroll 2
-                for (uint32_t c = 0; c < kTileMN / 32; c++) {
-                    uint32_t r[32];
-                    tmem_ld_32x32b_x32(taddr + c * 32, r);
+            for (uint32_t hb = 0; hb < 2 * kBoxes; hb++) {
+                const uint32_t h = hb / kBoxes, bx = hb % kBoxes;
+                const uint32_t col0 = col_half * 128 + bx * kColsPerBox;
+                const uint32_t taddr = tmem + h * 256 + col0 + ((q * 32) << 16);
+                uint32_t w[32];                                          // 128 bytes of output
+                if constexpr (OutBytes<DT>::value == 2) {
+                    uint32_t r0[32], r1[32];
+                    tmem_ld_32x32b_x32(taddr, r0);
+                    tmem_ld_32x32b_x32(taddr + 32, r1);
                     tmem_ld_wait();
-                    if (in_range)
-                        store_columns<DT>(crow + (size_t)c * 32 * OutBytes<DT>::value, r, p.alpha);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        __nv_bfloat162 v0 = __floats2bfloat162_rn(__uint_as_float(r0[2 * i]) * p.alpha, __uint_as_float(r0[2 * i + 1]) * p.alpha);
+                        __nv_bfloat162 v1 = __floats2bfloat162_rn(__uint_as_float(r1[2 * i]) * p.alpha, __uint_as_float(r1[2 * i + 1]) * p.alpha);
+                        w[i] = *reinterpret_cast<uint32_t *>(&v0);
+                        w[16 + i] = *reinterpret_cast<uint32_t *>(&v1);
+                    }
+                } else {
+                    tmem_ld_32x32b_x32(taddr, w);
+                    tmem_ld_wait();
+                    if constexpr (DT == CLPK_DT_TF32) {
+#pragma unroll
+                        for (int i = 0; i < 32; i++)
+                            w[i] = __float_as_uint(__uint_as_float(w[i]) * p.alpha);
+                    }
+                }
+                if (hb == 2 * kBoxes - 1) {
+                    // the accumulator is in registers: the next tile may overwrite tensor memory
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0)
+                        mbar_arrive_cluster(&sh->tmem_empty, 0);
+                }
+                // the previous box must have been read out of shared memory by its store
+                if (lane == 0)
+                    bulk_wait_read<0>();
+                __syncwarp();
+#pragma unroll
+                for (uint32_t j = 0; j < 8; j++)
+                    *reinterpret_cast<uint4 *>(my_row + ((j ^ sw) << 4)) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_2d(&tmap_c, box, (int32_t)(nb * kTileMN + col0),
+                                 (int32_t)(mb * kDenseTileM + h * 256 + rank * 128 + q * 32));
+                    bulk_commit();
                 }
             }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0)
-                mbar_arrive_cluster(&sh->tmem_empty, 0);
         }
+        if (lane == 0)
+            bulk_wait<0>();
     }
 
     tc_fence_before_sync();
@@ -650,6 +702,30 @@ static int make_operand_map(CUtensorMap *map, const void *base, uint64_t rows, u
 }
 
 
+// C [m][n] row-major for the epilogue's stores: box = 32 rows x 128 bytes, 128-byte swizzle.
+static int make_output_map(CUtensorMap *map, void *base, uint64_t m, uint64_t n, int dtype)
+{
+    EncodeTiledFn enc;
+    int rc = get_encode_fn(&enc);
+    if (rc != CLPK_OK)
+        return rc;
+    const bool wide = dtype == CLPK_DT_TF32 || dtype == CLPK_DT_I8;
+    const CUtensorMapDataType type = dtype == CLPK_DT_TF32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                   : dtype == CLPK_DT_I8 ? CU_TENSOR_MAP_DATA_TYPE_INT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    const uint32_t elem = wide ? 4 : 2;
+    const cuuint64_t dims[2] = {n, m};
+    const cuuint64_t strides[1] = {n * elem};
+    const cuuint32_t box[2] = {128 / elem, 32};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, type, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled (output) failed with CUresult %d", (int)r);
+        return CLPK_ERR_CUDA;
+    }
+    return CLPK_OK;
+}
+
 // Packed scale factors: rows of 512 bytes (128 x u32); a box is `rows_per_box` consecutive rows.
 static int make_scale_map(CUtensorMap *map, const void *base, uint64_t n_rows, uint32_t rows_per_box)
 {
@@ -673,7 +749,7 @@ static int make_scale_map(CUtensorMap *map, const void *base, uint64_t n_rows, u
 
 constexpr size_t kNvGemmSmemBytes = (size_t)kNvStages * kNvStageBytes + sizeof(NvGemmSmem) + 1024;
 
-constexpr size_t kGemmSmemBytes = (size_t)kDenseStages * kDenseStageBytes + sizeof(DenseSmem) + 1024;
+constexpr size_t kGemmSmemBytes = (size_t)kDenseStages * kDenseStageBytes + kEpilogueWarps * kStagingBytes + sizeof(DenseSmem) + 1024;
 
 // One wave counter per launch, from a small ring so that launches on different streams
 // do not share one; zeroed in stream order before the kernel.
@@ -682,7 +758,7 @@ __device__ unsigned int g_wave_sync[kSyncSlots];
 static std::atomic<unsigned> g_next_sync_slot{0};
 
 template <int DT>
-static int launch_gemm(const CUtensorMap &ta, const CUtensorMap &tb, GemmParams p, cudaStream_t s)
+static int launch_gemm(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, GemmParams p, cudaStream_t s)
 {
     CLPK_CUDA(cudaFuncSetAttribute(gemm_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)kGemmSmemBytes));
@@ -705,12 +781,12 @@ static int launch_gemm(const CUtensorMap &ta, const CUtensorMap &tb, GemmParams 
         attr[0].val.cooperative = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        if (cudaLaunchKernelEx(&cfg, gemm_kernel<DT>, ta, tb, p) == cudaSuccess)
+        if (cudaLaunchKernelEx(&cfg, gemm_kernel<DT>, ta, tb, tc, p) == cudaSuccess)
             return CLPK_OK;
         (void)cudaGetLastError();       // not co-schedulable here: run without the alignment
         p.wave_sync = nullptr;
     }
-    gemm_kernel<DT><<<grid, kGemmThreads, kGemmSmemBytes, s>>>(ta, tb, p);
+    gemm_kernel<DT><<<grid, kGemmThreads, kGemmSmemBytes, s>>>(ta, tb, tc, p);
     CLPK_LAUNCH_CHECK("gemm");
     return CLPK_OK;
 }
@@ -787,9 +863,9 @@ int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
     // as 512-tall tile rows (74 pairs: 12 x 6)
     p.group = 12;
     p.wave_sync = nullptr;
-    p.trace = nullptr;
-    if (const char *e = getenv("CLPK_GEMM_TRACE"))
-        p.trace = (unsigned long long *)strtoull(e, nullptr, 0);
+    p.align_at = 2;
+    if (const char *e = getenv("CLPK_GEMM_ALIGN_AT"))
+        p.align_at = (uint32_t)atoi(e);
     if (const char *e = getenv("CLPK_GEMM_GROUP"))
         p.group = (uint32_t)atoi(e) > 0 ? (uint32_t)atoi(e) : p.group;
 
@@ -824,13 +900,17 @@ int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
         CLPK_LAUNCH_CHECK("gemm_block_scaled");
         return CLPK_OK;
     }
+    CUtensorMap tc;
+    rc = make_output_map(&tc, a->d_c, a->m, a->n, a->dtype);
+    if (rc != CLPK_OK)
+        return rc;
     switch (a->dtype) {
-    case CLPK_DT_BF16: return launch_gemm<CLPK_DT_BF16>(ta, tb, p, s);
-    case CLPK_DT_F16:  return launch_gemm<CLPK_DT_F16>(ta, tb, p, s);
-    case CLPK_DT_TF32: return launch_gemm<CLPK_DT_TF32>(ta, tb, p, s);
-    case CLPK_DT_I8:   return launch_gemm<CLPK_DT_I8>(ta, tb, p, s);
-    case CLPK_DT_E5M2: return launch_gemm<CLPK_DT_E5M2>(ta, tb, p, s);
-    default:           return launch_gemm<CLPK_DT_E4M3>(ta, tb, p, s);
+    case CLPK_DT_BF16: return launch_gemm<CLPK_DT_BF16>(ta, tb, tc, p, s);
+    case CLPK_DT_F16:  return launch_gemm<CLPK_DT_F16>(ta, tb, tc, p, s);
+    case CLPK_DT_TF32: return launch_gemm<CLPK_DT_TF32>(ta, tb, tc, p, s);
+    case CLPK_DT_I8:   return launch_gemm<CLPK_DT_I8>(ta, tb, tc, p, s);
+    case CLPK_DT_E5M2: return launch_gemm<CLPK_DT_E5M2>(ta, tb, tc, p, s);
+    default:           return launch_gemm<CLPK_DT_E4M3>(ta, tb, tc, p, s);
     }
 }
 
