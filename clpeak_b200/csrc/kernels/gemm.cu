@@ -48,6 +48,7 @@ struct GemmParams {
     uint32_t group;             // tile columns per raster group (dense kernel)
     unsigned int *wave_sync;    // one counter for this launch, or NULL: see wave_align()
     uint32_t align_at;          // K block of a tile before which the producers meet
+    uint32_t align_period;      // ... in every align_period-th wave
 };
 
 __device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uint32_t tiles_n,
@@ -150,6 +151,75 @@ __device__ __forceinline__ void dense_tile_coords(uint32_t tile, uint32_t tiles_
     nb = first_n + within % width;
 }
 
+// Epilogue of one warp for one tile: the warp's 32 rows (TMEM lanes) x 128 columns of each of
+// `row_blocks` row blocks, moved in boxes of 128 bytes per row (64 bf16 or 32 fp32/int32
+// columns): tcgen05.ld -> convert -> the warp's own 4 KiB staging box in shared memory, written
+// in the 128-byte swizzle so that the 32 lanes (one row each) spread over the banks -> one TMA
+// store per box, which writes whole lines of C and clips rows beyond M.  (A thread-per-row
+// store straight to global memory costs 32 partial-sector transactions per instruction and held
+// the drain of a 256 x 256 CTA tile at 8 us.)  `empty_bar` (in the leader CTA) is arrived on
+// as soon as the tile's last tcgen05.ld has landed: the next tile may then overwrite tensor
+// memory while the tail of the stores is still in flight.
+//   taddr0   : tensor-memory address of this warp's lanes, column 0 of its 128 columns, row block 0
+//   row0/col0: C coordinates of the same element
+template <int DT>
+__device__ __forceinline__ void drain_warp_tile(uint32_t taddr0, uint32_t row_blocks, uint32_t row0, uint32_t col0,
+                                                uint8_t *box, const CUtensorMap *tmap_c, float alpha, uint64_t *empty_bar,
+                                                int lane)
+{
+    constexpr uint32_t kColsPerBox = 128 / OutBytes<DT>::value;
+    constexpr uint32_t kBoxes = 128 / kColsPerBox;                  // per row block per warp
+    uint8_t *my_row = box + lane * 128;
+    const uint32_t sw = (uint32_t)(lane & 7);
+    const uint32_t n_boxes = row_blocks * kBoxes;
+#pragma unroll 1
+    for (uint32_t hb = 0; hb < n_boxes; hb++) {
+        const uint32_t h = hb / kBoxes, c = (hb % kBoxes) * kColsPerBox;
+        const uint32_t taddr = taddr0 + h * 256 + c;
+        uint32_t w[32];                                          // 128 bytes of output
+        if constexpr (OutBytes<DT>::value == 2) {
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32b_x32(taddr, r0);
+            tmem_ld_32x32b_x32(taddr + 32, r1);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                __nv_bfloat162 v0 = __floats2bfloat162_rn(__uint_as_float(r0[2 * i]) * alpha, __uint_as_float(r0[2 * i + 1]) * alpha);
+                __nv_bfloat162 v1 = __floats2bfloat162_rn(__uint_as_float(r1[2 * i]) * alpha, __uint_as_float(r1[2 * i + 1]) * alpha);
+                w[i] = *reinterpret_cast<uint32_t *>(&v0);
+                w[16 + i] = *reinterpret_cast<uint32_t *>(&v1);
+            }
+        } else {
+            tmem_ld_32x32b_x32(taddr, w);
+            tmem_ld_wait();
+            if constexpr (DT == CLPK_DT_TF32) {
+#pragma unroll
+                for (int i = 0; i < 32; i++)
+                    w[i] = __float_as_uint(__uint_as_float(w[i]) * alpha);
+            }
+        }
+        if (hb == n_boxes - 1) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive_cluster(empty_bar, 0);
+        }
+        // the previous box must have been read out of shared memory by its store
+        if (lane == 0)
+            bulk_wait_read<0>();
+        __syncwarp();
+#pragma unroll
+        for (uint32_t j = 0; j < 8; j++)
+            *reinterpret_cast<uint4 *>(my_row + ((j ^ sw) << 4)) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            tma_store_2d(tmap_c, box, (int32_t)(col0 + c), (int32_t)(row0 + h * 256));
+            bulk_commit();
+        }
+    }
+}
+
 // Keeping the clusters in step.  The schedule is static, so all clusters start wave w
 // (their w-th tile) together only if they run at exactly the same speed.  They do not:
 // measured on a B200, the start times of a wave spread by about 4 us more with every
@@ -164,11 +234,13 @@ __device__ __forceinline__ void dense_tile_coords(uint32_t tile, uint32_t tiles_
 __device__ __forceinline__ void wave_align(const GemmParams &p, uint32_t wave, uint32_t n_tiles, uint32_t n_clusters,
                                            bool &enabled)
 {
-    if (!enabled || wave == 0)
+    // every align_period-th wave (short tiles drift less per wave and a meeting costs about a microsecond)
+    if (!enabled || wave == 0 || wave % p.align_period != 0)
         return;
-    // arrivals expected up to and including this wave: two CTAs per tile of waves 1..wave
-    const uint32_t tiles_through = (wave + 1) * n_clusters < n_tiles ? (wave + 1) * n_clusters : n_tiles;
-    const unsigned int target = 2u * (tiles_through - n_clusters);
+    // arrivals expected up to and including this meeting: two CTAs per cluster for each earlier
+    // meeting (those waves were full) plus two per tile of this wave
+    const uint32_t in_wave = n_tiles - wave * n_clusters < n_clusters ? n_tiles - wave * n_clusters : n_clusters;
+    const unsigned int target = 2u * (n_clusters * (wave / p.align_period - 1u) + in_wave);
     atomicAdd(p.wave_sync, 1u);
     unsigned long long t0, t1;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
@@ -309,22 +381,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
     } else {
         // ---------------- epilogue warps ----------------
         // Eight warps: warp w may read TMEM lanes 32 (w % 4) .. +31; the two warps of a lane
-        // quarter split each row block's 256 columns in halves.  A warp moves its 32 rows
-        // x 128 columns in boxes of 128 bytes per row (64 bf16 or 32 fp32/int32 columns):
-        // tcgen05.ld -> convert -> its own 4 KiB staging box in shared memory, written in the
-        // 128-byte swizzle so that the 32 lanes (one row each) spread over the banks -> one
-        // TMA store per box, which writes whole lines of C and clips rows beyond M.  A
-        // thread-per-row store straight to global memory costs 32 partial-sector
-        // transactions per instruction and held the drain at 8 us per tile.
-        // Tensor memory is handed back as soon as the tile's last tcgen05.ld has landed,
-        // before the tail of the stores.
-        constexpr uint32_t kColsPerBox = 128 / OutBytes<DT>::value;
-        constexpr uint32_t kBoxes = 128 / kColsPerBox;                  // per row block per warp
+        // quarter split each row block's 256 columns in halves (drain_warp_tile).
         const uint32_t q = (uint32_t)(warp & 3);
         const uint32_t col_half = (uint32_t)(warp - 2) >> 2;
         uint8_t *box = staging + (size_t)(warp - 2) * kStagingBytes;
-        uint8_t *my_row = box + lane * 128;
-        const uint32_t sw = (uint32_t)(lane & 7);
         uint32_t tcount = 0;
         for (uint32_t tile = cluster_id; tile < n_tiles; tile += n_clusters, tcount++) {
             uint32_t mb, nb;
@@ -336,55 +396,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
                 break;
             }
             tc_fence_after_sync();
-#pragma unroll 1
-            for (uint32_t hb = 0; hb < 2 * kBoxes; hb++) {
-                const uint32_t h = hb / kBoxes, bx = hb % kBoxes;
-                const uint32_t col0 = col_half * 128 + bx * kColsPerBox;
-                const uint32_t taddr = tmem + h * 256 + col0 + ((q * 32) << 16);
-                uint32_t w[32];                                          // 128 bytes of output
-                if constexpr (OutBytes<DT>::value == 2) {
-                    uint32_t r0[32], r1[32];
-                    tmem_ld_32x32b_x32(taddr, r0);
-                    tmem_ld_32x32b_x32(taddr + 32, r1);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        __nv_bfloat162 v0 = __floats2bfloat162_rn(__uint_as_float(r0[2 * i]) * p.alpha, __uint_as_float(r0[2 * i + 1]) * p.alpha);
-                        __nv_bfloat162 v1 = __floats2bfloat162_rn(__uint_as_float(r1[2 * i]) * p.alpha, __uint_as_float(r1[2 * i + 1]) * p.alpha);
-                        w[i] = *reinterpret_cast<uint32_t *>(&v0);
-                        w[16 + i] = *reinterpret_cast<uint32_t *>(&v1);
-                    }
-                } else {
-                    tmem_ld_32x32b_x32(taddr, w);
-                    tmem_ld_wait();
-                    if constexpr (DT == CLPK_DT_TF32) {
-#pragma unroll
-                        for (int i = 0; i < 32; i++)
-                            w[i] = __float_as_uint(__uint_as_float(w[i]) * p.alpha);
-                    }
-                }
-                if (hb == 2 * kBoxes - 1) {
-                    // the accumulator is in registers: the next tile may overwrite tensor memory
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0)
-                        mbar_arrive_cluster(&sh->tmem_empty, 0);
-                }
-                // the previous box must have been read out of shared memory by its store
-                if (lane == 0)
-                    bulk_wait_read<0>();
-                __syncwarp();
-#pragma unroll
-                for (uint32_t j = 0; j < 8; j++)
-                    *reinterpret_cast<uint4 *>(my_row + ((j ^ sw) << 4)) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) {
-                    tma_store_2d(&tmap_c, box, (int32_t)(nb * kTileMN + col0),
-                                 (int32_t)(mb * kDenseTileM + h * 256 + rank * 128 + q * 32));
-                    bulk_commit();
-                }
-            }
+            drain_warp_tile<DT>(tmem + col_half * 128 + ((q * 32) << 16), 2, mb * kDenseTileM + rank * 128 + q * 32,
+                                nb * kTileMN + col_half * 128, box, &tmap_c, p.alpha, &sh->tmem_empty, lane);
         }
         if (lane == 0)
             bulk_wait<0>();
@@ -431,7 +444,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
 
 constexpr int kNvStages = 5;
 constexpr int kNvCopyThreads = 4;
-constexpr int kNvGemmThreads = 32 * (6 + kNvCopyThreads);    // producer, MMA, 4 epilogue, 4 scale-copy warps
+constexpr int kNvGemmThreads = 32 * (2 + kEpilogueWarps + kNvCopyThreads);    // producer, MMA, 8 epilogue, 4 scale-copy warps
 constexpr uint32_t kSfaStageBytes = 2048;
 constexpr uint32_t kSfbStageBytes = 4096;
 constexpr uint32_t kNvStageBytes = kStageBytes + kSfaStageBytes + kSfbStageBytes;     // 38 KiB
@@ -480,11 +493,12 @@ template <bool MX>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
     gemm_block_scaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
-                     GemmParams p)
+                     const __grid_constant__ CUtensorMap tmap_c, GemmParams p)
 {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    NvGemmSmem *sh = reinterpret_cast<NvGemmSmem *>(smem + (size_t)kNvStages * kNvStageBytes);
+    uint8_t *staging = smem + (size_t)kNvStages * kNvStageBytes;                 // one 4 KiB box per epilogue warp
+    NvGemmSmem *sh = reinterpret_cast<NvGemmSmem *>(staging + kEpilogueWarps * kStagingBytes);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
@@ -500,12 +514,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
             mbar_init(&sh->sf_ready[s], kNvCopyThreads);
         }
         mbar_init(&sh->tmem_full, 1);
-        mbar_init(&sh->tmem_empty, 8);
+        mbar_init(&sh->tmem_empty, 2 * kEpilogueWarps);
         mbar_fence_init();
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
         tma_prefetch_desc(&tmap_sfa);
         tma_prefetch_desc(&tmap_sfb);
+        tma_prefetch_desc(&tmap_c);
     }
     if (warp == 1)
         tmem_alloc<2>(&sh->tmem_base, 512);
@@ -519,13 +534,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             uint32_t it = 0;
-            bool ok = true;
+            bool ok = true, aligned = p.wave_sync != nullptr;
             for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters) {
                 uint32_t mb, nb;
                 tile_coords(tile, tiles_m, tiles_n, mb, nb);
                 const int32_t row_a = (int32_t)(mb * kTileMN + rank * 128);
                 const int32_t row_b = (int32_t)(nb * kTileMN + rank * 128);
+                const uint32_t align_at = p.k_blocks > p.align_at ? p.align_at : 0u;
                 for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
+                    if (kb == align_at)
+                        wave_align(p, tile / n_clusters, n_tiles, n_clusters, aligned);
                     const uint32_t s = it % kNvStages, round = it / kNvStages;
                     if (round > 0 && !mbar_wait(&sh->empty[s], (round - 1) & 1)) {
                         atomicCAS(p.status, 0u, 0x211u);
@@ -589,9 +607,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
                     tc_commit_pair(&sh->tmem_full, 3);
             }
         }
-    } else if (warp >= 6) {
+    } else if (warp >= 2 + kEpilogueWarps) {
         // ---------------- scale-factor copy threads (leader CTA) ----------------
-        const uint32_t me = (uint32_t)(warp - 6);
+        const uint32_t me = (uint32_t)(warp - (2 + kEpilogueWarps));
         if (rank == 0 && lane == 0) {
             uint32_t it = 0;
             bool ok = true;
@@ -620,8 +638,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
             }
         }
     } else {
-        // ---------------- epilogue warps ----------------
+        // ---------------- epilogue warps (as in the dense kernel, one row block) ----------------
         const uint32_t q = (uint32_t)(warp & 3);
+        const uint32_t col_half = (uint32_t)(warp - 2) >> 2;
+        uint8_t *box = staging + (size_t)(warp - 2) * kStagingBytes;
         uint32_t tcount = 0;
         for (uint32_t tile = cluster_id; tile < n_tiles; tile += n_clusters, tcount++) {
             uint32_t mb, nb;
@@ -632,21 +652,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
                 break;
             }
             tc_fence_after_sync();
-            const size_t row = (size_t)mb * kTileMN + rank * 128 + q * 32 + lane;
-            uint8_t *crow = static_cast<uint8_t *>(p.c) + (row * p.n + (size_t)nb * kTileMN) * 2;
-            const uint32_t taddr = tmem + ((q * 32) << 16);
-#pragma unroll 2
-            for (uint32_t c = 0; c < kTileMN / 32; c++) {
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(taddr + c * 32, r);
-                tmem_ld_wait();
-                store_columns<CLPK_DT_NVF4>(crow + (size_t)c * 64, r, p.alpha);
-            }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0)
-                mbar_arrive_cluster(&sh->tmem_empty, 0);
+            drain_warp_tile<CLPK_DT_NVF4>(tmem + col_half * 128 + ((q * 32) << 16), 1, mb * kTileMN + rank * 128 + q * 32,
+                                          nb * kTileMN + col_half * 128, box, &tmap_c, p.alpha, &sh->tmem_empty, lane);
         }
+        if (lane == 0)
+            bulk_wait<0>();
     }
 
     tc_fence_before_sync();
@@ -747,7 +757,7 @@ static int make_scale_map(CUtensorMap *map, const void *base, uint64_t n_rows, u
     return CLPK_OK;
 }
 
-constexpr size_t kNvGemmSmemBytes = (size_t)kNvStages * kNvStageBytes + sizeof(NvGemmSmem) + 1024;
+constexpr size_t kNvGemmSmemBytes = (size_t)kNvStages * kNvStageBytes + kEpilogueWarps * kStagingBytes + sizeof(NvGemmSmem) + 1024;
 
 constexpr size_t kGemmSmemBytes = (size_t)kDenseStages * kDenseStageBytes + kEpilogueWarps * kStagingBytes + sizeof(DenseSmem) + 1024;
 
@@ -757,11 +767,13 @@ constexpr int kSyncSlots = 32;
 __device__ unsigned int g_wave_sync[kSyncSlots];
 static std::atomic<unsigned> g_next_sync_slot{0};
 
-template <int DT>
-static int launch_gemm(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, GemmParams p, cudaStream_t s)
+// Launches a persistent cluster kernel whose last parameter is GemmParams: cooperatively with a
+// fresh wave counter when the alignment is on, plainly (and unaligned) otherwise.
+template <typename Kernel, typename... Maps>
+static int launch_persistent(Kernel kernel, const char *what, int threads, size_t smem, cudaStream_t s, GemmParams p,
+                             const Maps &...maps)
 {
-    CLPK_CUDA(cudaFuncSetAttribute(gemm_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   (int)kGemmSmemBytes));
+    CLPK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int grid = (num_sms() / 2) * 2;
     const char *off = getenv("CLPK_GEMM_NO_ALIGN");
     p.wave_sync = nullptr;
@@ -773,22 +785,34 @@ static int launch_gemm(const CUtensorMap &ta, const CUtensorMap &tb, const CUten
         // cooperative: every CTA is resident before any runs, so the wave counter can fill up
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)grid);
-        cfg.blockDim = dim3(kGemmThreads);
-        cfg.dynamicSmemBytes = kGemmSmemBytes;
+        cfg.blockDim = dim3((unsigned)threads);
+        cfg.dynamicSmemBytes = smem;
         cfg.stream = s;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeCooperative;
         attr[0].val.cooperative = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        if (cudaLaunchKernelEx(&cfg, gemm_kernel<DT>, ta, tb, tc, p) == cudaSuccess)
+        if (cudaLaunchKernelEx(&cfg, kernel, maps..., p) == cudaSuccess)
             return CLPK_OK;
         (void)cudaGetLastError();       // not co-schedulable here: run without the alignment
         p.wave_sync = nullptr;
     }
-    gemm_kernel<DT><<<grid, kGemmThreads, kGemmSmemBytes, s>>>(ta, tb, tc, p);
-    CLPK_LAUNCH_CHECK("gemm");
+    cudaLaunchConfig_t plain = {};
+    plain.gridDim = dim3((unsigned)grid);
+    plain.blockDim = dim3((unsigned)threads);
+    plain.dynamicSmemBytes = smem;
+    plain.stream = s;
+    const cudaError_t e = cudaLaunchKernelEx(&plain, kernel, maps..., p);
+    if (e != cudaSuccess)
+        return cuda_fail(e, what);
     return CLPK_OK;
+}
+
+template <int DT>
+static int launch_gemm(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, const GemmParams &p, cudaStream_t s)
+{
+    return launch_persistent(gemm_kernel<DT>, "gemm", kGemmThreads, kGemmSmemBytes, s, p, ta, tb, tc);
 }
 
 } // namespace clpk
@@ -864,6 +888,7 @@ int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
     p.group = 12;
     p.wave_sync = nullptr;
     p.align_at = 2;
+    p.align_period = block_scaled ? 8 : 1;
     if (const char *e = getenv("CLPK_GEMM_ALIGN_AT"))
         p.align_at = (uint32_t)atoi(e);
     if (const char *e = getenv("CLPK_GEMM_GROUP"))
@@ -889,16 +914,12 @@ int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
         rc = make_scale_map(&tsb, wsb, sfb_bytes / 512, 2 * words);
         if (rc != CLPK_OK)
             return rc;
-        const int grid = (num_sms() / 2) * 2;
-        if (mx) {
-            CLPK_CUDA(cudaFuncSetAttribute(gemm_block_scaled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kNvGemmSmemBytes));
-            gemm_block_scaled_kernel<true><<<grid, kNvGemmThreads, kNvGemmSmemBytes, s>>>(ta, tb, tsa, tsb, p);
-        } else {
-            CLPK_CUDA(cudaFuncSetAttribute(gemm_block_scaled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kNvGemmSmemBytes));
-            gemm_block_scaled_kernel<false><<<grid, kNvGemmThreads, kNvGemmSmemBytes, s>>>(ta, tb, tsa, tsb, p);
-        }
-        CLPK_LAUNCH_CHECK("gemm_block_scaled");
-        return CLPK_OK;
+        CUtensorMap tc;
+        rc = make_output_map(&tc, a->d_c, a->m, a->n, a->dtype);
+        if (rc != CLPK_OK)
+            return rc;
+        return mx ? launch_persistent(gemm_block_scaled_kernel<true>, "gemm_mxf4", kNvGemmThreads, kNvGemmSmemBytes, s, p, ta, tb, tsa, tsb, tc)
+                  : launch_persistent(gemm_block_scaled_kernel<false>, "gemm_nvf4", kNvGemmThreads, kNvGemmSmemBytes, s, p, ta, tb, tsa, tsb, tc);
     }
     CUtensorMap tc;
     rc = make_output_map(&tc, a->d_c, a->m, a->n, a->dtype);
