@@ -71,16 +71,42 @@ def ncu_traffic(kernel: str):
 # ---------------------------------------------------------------------------------
 
 class ClockSampler:
+    """SM clock, power and throttle reasons sampled DURING the timed region: an NVML thread (10 ms period),
+    or `nvidia-smi -lms 100` where the NVML binding is missing.  Reading only; nothing is set."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    # nvmlClocksEventReason* bits
+    BITS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
-    def __init__(self, gpu_index: int):
+    def __init__(self, gpu_index: int, uuid: str | None = None):
         self.gpu = gpu_index
+        self.uuid = uuid
         self.proc = None
         self.lines: list[str] = []
+        self.samples: list[tuple] = []
+        self.stop_flag = threading.Event()
+        self.thread = None
+        self.nvml = None
 
     def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = None
+            if self.uuid:
+                try:
+                    h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + self.uuid).encode() if not self.uuid.startswith("GPU-") else self.uuid.encode())
+                except Exception:
+                    h = None
+            if h is None:
+                h = pynvml.nvmlDeviceGetHandleByIndex(self.gpu)
+            self.nvml = (pynvml, h)
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
@@ -89,34 +115,64 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def _poll(self):
+        nv, h = self.nvml
+        smax = None
+        while not self.stop_flag.is_set():
+            try:
+                if smax is None:
+                    smax = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+                sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                pw = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
+                try:
+                    rs = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                except Exception:
+                    rs = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                self.samples.append((float(sm), float(smax), pw, int(rs)))
+            except Exception:
+                pass
+            time.sleep(0.01)
+
     def _pump(self):
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
     def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
         sm, smax, reasons, power = [], [], set(), []
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
-            f = [x.strip() for x in ln.split(",")]
-            if len(f) < 9:
-                continue
+        if self.nvml is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            for a, b, c, r in self.samples:
+                sm.append(a); smax.append(b); power.append(c)
+                for name, bit in self.BITS.items():
+                    if r & bit:
+                        reasons.add(name)
+            source = "nvml, 10 ms period"
+        elif self.proc is not None:
+            self.proc.terminate()
             try:
-                sm.append(float(f[1])); smax.append(float(f[2])); power.append(float(f[3]))
-            except ValueError:
-                continue
-            for name, v in zip(names, f[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+            for ln in self.lines:
+                f = [x.strip() for x in ln.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1])); smax.append(float(f[2])); power.append(float(f[3]))
+                except ValueError:
+                    continue
+                for name, v in zip(names, f[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            source = "nvidia-smi -lms 100"
+        else:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no NVML binding and no nvidia-smi"]}
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons),
+                "source": source}
 
 
 # ---------------------------------------------------------------------------------
@@ -246,7 +302,7 @@ def main():
         K.clpk_fill_f32(t.data_ptr(), n_floats, 100 + i, N.DIST_UNIFORM01, 0.0, 1.0, stream)
 
     grids = {}
-    for v in (N.STREAM_LDG, N.STREAM_TMA):
+    for v in N.STREAM_VARIANTS:
         g = C.c_int(0)
         K.clpk_stream_read_grid(v, C.byref(g))
         grids[v] = g.value
@@ -274,9 +330,9 @@ def main():
     # pick the faster flavour of each kernel once, outside the timed region
     variant = {}
     for name, fn in ops.items():
-        t = {v: time_once(lambda v=v: fn(v)) for v in (N.STREAM_LDG, N.STREAM_TMA)}
+        t = {v: time_once(lambda v=v: fn(v)) for v in N.STREAM_VARIANTS}
         variant[name] = min(t, key=t.get)
-    vname = {N.STREAM_LDG: "ldg", N.STREAM_TMA: "tma"}
+    vname = {N.STREAM_LDG: "ldg", N.STREAM_TMA: "tma", N.STREAM_WIDE: "wide"}
 
     def step(events=None):
         for i, name in enumerate(("read", "copy", "triad")):
@@ -292,7 +348,11 @@ def main():
     st = C.c_uint32(0)
     K.clpk_stream_status(C.byref(st), stream)
 
-    sampler = ClockSampler(local)
+    try:
+        uuid = str(torch.cuda.get_device_properties(local).uuid)
+    except Exception:
+        uuid = None
+    sampler = ClockSampler(local, uuid)
     if rank == 0:
         sampler.start()
     per_step_events = [[ev() for _ in range(4)] for _ in range(args.steps)]

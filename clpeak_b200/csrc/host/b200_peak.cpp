@@ -730,10 +730,13 @@ struct B200Harness {
         // whole blocks of the widest variant: 256 threads x 16 fetches x 4 floats
         const uint64_t refFloats = std::min<uint64_t>((1ull << 29) / sizeof(float), nF) / 16384 * 16384;
         DeviceBuffer a, b, c, parts;
-        int grid0 = 0, grid1 = 0;
-        clpk_stream_read_grid(CLPK_STREAM_LDG, &grid0);
-        clpk_stream_read_grid(CLPK_STREAM_TMA, &grid1);
-        const int gridMax = std::max(grid0, grid1);
+        const int variants[3] = {CLPK_STREAM_LDG, CLPK_STREAM_TMA, CLPK_STREAM_WIDE};
+        const char *variantName[3] = {"128-bit loads, persistent grid", "TMA bulk copy", "256-bit loads, one 8 KiB tile per CTA"};
+        int grids[3] = {0, 0, 0};
+        for (int v : variants)
+            clpk_stream_read_grid(v, &grids[v]);
+        const int grid0 = grids[CLPK_STREAM_LDG];
+        const int gridMax = std::max(grids[0], std::max(grids[1], grids[2]));
         if (!a.alloc(streamBytes) || !b.alloc(streamBytes) || !c.alloc(streamBytes) || !parts.alloc((size_t)gridMax * 4)) {
             for (const char *m : {"float", "float2", "float4", "read", "copy", "triad"})
                 out.readings.push_back(bad(m, ResultStatus::Error, "Failed to allocate buffers"));
@@ -778,7 +781,7 @@ struct B200Harness {
             double bestS = -1;
             int bestV = 0;
             std::string err;
-            for (int v : {CLPK_STREAM_LDG, CLPK_STREAM_TMA}) {
+            for (int v : variants) {
                 const double s = w.timeLaunches([&] { return launch(v); }, err);
                 uint32_t st = 0;
                 if (clpk_stream_status(&st, w.stream) != CLPK_OK) {
@@ -801,7 +804,7 @@ struct B200Harness {
                 return;
             }
             const double g = bytes / bestS / 1e9;
-            out.readings.push_back(ok(metric, g, std::string(what) + "  Fastest flavour: " + (bestV == CLPK_STREAM_TMA ? "TMA bulk copy" : "128-bit loads") +
+            out.readings.push_back(ok(metric, g, std::string(what) + "  Fastest flavour: " + variantName[bestV] +
                                                      ".  " + pct(g, kSpecHbmGBps, "HBM3e GB/s"), bytes, bestS));
         };
 
@@ -809,17 +812,16 @@ struct B200Harness {
         best("read", (double)streamBytes,
              [&](int v) { return clpk_stream_read(v, b.p, streamBytes, parts.as<uint32_t>(), w.stream); },
              [&]() -> std::string {
-                 // both flavours must agree on the XOR of the whole array, and the head must match the host
-                 uint32_t x[2] = {0, 0};
-                 for (int v : {CLPK_STREAM_LDG, CLPK_STREAM_TMA}) {
-                     const int g = v == CLPK_STREAM_LDG ? grid0 : grid1;
-                     std::vector<uint32_t> p((size_t)g);
+                 // all flavours must agree on the XOR of the whole array, and the head must match the host
+                 uint32_t x[3] = {0, 0, 0};
+                 for (int v : variants) {
+                     std::vector<uint32_t> p((size_t)grids[v]);
                      clpk_stream_read(v, b.p, streamBytes, parts.as<uint32_t>(), w.stream);
                      clpk_memcpy_d2h(p.data(), parts.p, p.size() * 4, w.stream);
                      clpk_stream_sync(w.stream);
                      for (uint32_t q : p) x[v] ^= q;
                  }
-                 if (x[0] != x[1]) return "the two flavours disagree on the checksum";
+                 if (x[0] != x[1] || x[0] != x[2]) return "the flavours disagree on the checksum";
                  std::vector<uint32_t> p((size_t)grid0);
                  clpk_stream_read(CLPK_STREAM_LDG, b.p, headFloats * 4, parts.as<uint32_t>(), w.stream);
                  clpk_memcpy_d2h(p.data(), parts.p, p.size() * 4, w.stream);

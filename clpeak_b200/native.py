@@ -18,7 +18,8 @@ OK, ERR_CUDA, ERR_BAD_ARG, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_NO_DEVICE, ERR_TOO_
 DIST_UNIFORM01, DIST_UNIFORM_PM1, DIST_NORMAL = 0, 1, 2
 (DT_F32, DT_F16, DT_BF16, DT_E4M3, DT_E5M2, DT_I8, DT_MXF4, DT_NVF4, DT_MXF4_B64, DT_NVF4_B32, DT_TF32,
  DT_E2M1) = range(12)
-STREAM_LDG, STREAM_TMA = 0, 1
+STREAM_LDG, STREAM_TMA, STREAM_WIDE = 0, 1, 2
+STREAM_VARIANTS = (STREAM_LDG, STREAM_TMA, STREAM_WIDE)
 (MMA_F16, MMA_BF16, MMA_E4M3, MMA_E5M2, MMA_I8, MMA_MXF4, MMA_NVF4,
  MMA_E4M3_SP, MMA_MXF4_SP, MMA_NVF4_SP, MMA_I8_SP, MMA_TF32, MMA_F16_F16, MMA_E2M1) = range(14)
 

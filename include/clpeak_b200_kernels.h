@@ -154,12 +154,15 @@ CLPK_API int clpk_global_bandwidth(int width, const float *d_in, float *d_out,
  * -- its CUDA backend has read only.  `variant`:
  *   CLPK_STREAM_LDG : 128-bit loads/stores from registers
  *   CLPK_STREAM_TMA : cp.async.bulk global->shared->global staging
+ *   CLPK_STREAM_WIDE: 256-bit loads/stores, one 8 KiB tile per CTA (pointers 32-byte
+ *                     aligned); the read flavour XORs into 4096 partial words
  * n_bytes must be a multiple of 16.
  * read  : d_partials[grid] receives per-CTA XOR of all 32-bit words read
  *         (clpk_stream_read_grid() gives the grid size to allocate for).
  * copy  : dst = src.           triad : a = b + s*c (no FMA contraction). */
 #define CLPK_STREAM_LDG 0
 #define CLPK_STREAM_TMA 1
+#define CLPK_STREAM_WIDE 2
 CLPK_API int clpk_stream_read_grid(int variant, int *grid);
 CLPK_API int clpk_stream_read(int variant, const void *d_src, uint64_t n_bytes,
                               uint32_t *d_partials, void *stream);

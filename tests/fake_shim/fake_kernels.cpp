@@ -257,14 +257,15 @@ int clpk_global_bandwidth(int width, const float *in, float *out, uint64_t n_flo
     return CLPK_OK;
 }
 
-int clpk_stream_read_grid(int, int *grid) { *grid = 4; return CLPK_OK; }
-int clpk_stream_read(int, const void *src, uint64_t n_bytes, uint32_t *parts, void *)
+int clpk_stream_read_grid(int variant, int *grid) { *grid = variant == CLPK_STREAM_WIDE ? 4096 : 4; return CLPK_OK; }
+int clpk_stream_read(int variant, const void *src, uint64_t n_bytes, uint32_t *parts, void *)
 {
     uint32_t x = 0;
     const uint32_t *w = static_cast<const uint32_t *>(src);
     for (uint64_t i = 0; i < n_bytes / 4; ++i) x ^= w[i];
+    const int slots = variant == CLPK_STREAM_WIDE ? 4096 : 4;
+    for (int i = 1; i < slots; ++i) parts[i] = 0;
     parts[0] = x;
-    parts[1] = parts[2] = parts[3] = 0;
     return CLPK_OK;
 }
 int clpk_stream_copy(int, void *dst, const void *src, uint64_t n, void *) { std::memcpy(dst, src, n); return CLPK_OK; }

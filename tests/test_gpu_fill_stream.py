@@ -117,10 +117,10 @@ def _read_xor(K, cuda, variant, d_src, n_bytes):
 
 
 # sizes in bytes: empty, one vector, ragged tails around the tile sizes, larger than one wave
-SIZES = [0, 16, 4096 + 16, 32768, 32768 * 3 + 48, (1 << 24) + 1616, 1 << 27]
+SIZES = [0, 16, 4096 + 16, 8192, 8192 + 16, 32768, 32768 * 3 + 48, (1 << 24) + 1616, 1 << 27]
 
 
-@pytest.mark.parametrize("variant", [N.STREAM_LDG, N.STREAM_TMA])
+@pytest.mark.parametrize("variant", list(N.STREAM_VARIANTS))
 @pytest.mark.parametrize("n_bytes", SIZES)
 def test_stream_read_xor(K, orc, cuda, variant, n_bytes):
     n = max(n_bytes // 4, 4)
@@ -130,7 +130,7 @@ def test_stream_read_xor(K, orc, cuda, variant, n_bytes):
     assert got == orc.xor_words(src[: n_bytes // 4])
 
 
-@pytest.mark.parametrize("variant", [N.STREAM_LDG, N.STREAM_TMA])
+@pytest.mark.parametrize("variant", list(N.STREAM_VARIANTS))
 @pytest.mark.parametrize("n_bytes", SIZES)
 def test_stream_copy(K, orc, cuda, variant, n_bytes):
     n = max(n_bytes // 4, 4)
@@ -145,7 +145,7 @@ def test_stream_copy(K, orc, cuda, variant, n_bytes):
     assert np.all(got[n_bytes // 4:] == -1.0), "copy wrote past the end"
 
 
-@pytest.mark.parametrize("variant", [N.STREAM_LDG, N.STREAM_TMA])
+@pytest.mark.parametrize("variant", list(N.STREAM_VARIANTS))
 @pytest.mark.parametrize("n_floats", [0, 4, 8192 + 4, 3 * 8192 + 12, (1 << 22) + 404, 1 << 25])
 def test_stream_triad(K, orc, cuda, variant, n_floats):
     n = max(n_floats, 4)
@@ -172,6 +172,37 @@ def test_stream_triad_ldg_ragged_floats(K, orc, cuda):
     assert_bits_equal(to_np(d_a), orc.triad(b, c, 1.5), "triad ragged")
     with pytest.raises(N.ClpkError):
         K.clpk_stream_triad(N.STREAM_TMA, d_a.data_ptr(), d_a.data_ptr(), d_a.data_ptr(), 1.5, n, stream_ptr())
+    # the 256-bit flavour takes any length (its tail is element-wise) but wants 32-byte aligned pointers
+    d_a2 = dev_empty(n, cuda.float32)
+    K.clpk_stream_triad(N.STREAM_WIDE, d_a2.data_ptr(), d_b.data_ptr(), d_c.data_ptr(), 1.5, n, stream_ptr())
+    sync()
+    assert_bits_equal(to_np(d_a2), orc.triad(b, c, 1.5), "triad ragged, 256-bit flavour")
+    with pytest.raises(N.ClpkError):
+        K.clpk_stream_triad(N.STREAM_WIDE, d_a2.data_ptr() + 16, d_b.data_ptr() + 16, d_c.data_ptr() + 16, 1.5, 64, stream_ptr())
+    with pytest.raises(N.ClpkError):
+        K.clpk_stream_copy(N.STREAM_WIDE, d_a2.data_ptr() + 16, d_b.data_ptr(), 64, stream_ptr())
+
+
+def test_stream_variants_agree_on_a_large_buffer(K, orc, cuda):
+    """512 MiB: the three flavours of each kernel give identical bits (read: identical XOR)."""
+    n = (512 << 20) // 4
+    b, c = dev_empty(n, cuda.float32), dev_empty(n, cuda.float32)
+    K.clpk_fill_f32(b.data_ptr(), n, 31, 0, 0.0, 1.0, stream_ptr())
+    K.clpk_fill_f32(c.data_ptr(), n, 32, 0, 0.0, 1.0, stream_ptr())
+    xors = {v: _read_xor(K, cuda, v, b, n * 4) for v in N.STREAM_VARIANTS}
+    assert len(set(xors.values())) == 1
+    outs = []
+    for v in N.STREAM_VARIANTS:
+        a = dev_empty(n, cuda.float32)
+        K.clpk_stream_triad(v, a.data_ptr(), b.data_ptr(), c.data_ptr(), 1.5, n, stream_ptr())
+        st = C.c_uint32(0)
+        K.clpk_stream_status(C.byref(st), stream_ptr())
+        outs.append(a)
+    assert cuda.equal(outs[0].view(cuda.int32), outs[1].view(cuda.int32)) and cuda.equal(outs[0].view(cuda.int32), outs[2].view(cuda.int32))
+    d = dev_empty(n, cuda.float32)
+    K.clpk_stream_copy(N.STREAM_WIDE, d.data_ptr(), outs[0].data_ptr(), n * 4, stream_ptr())
+    sync()
+    assert cuda.equal(d.view(cuda.int32), outs[0].view(cuda.int32))
 
 
 def test_compute_sp_reference_chain(K, orc, cuda):

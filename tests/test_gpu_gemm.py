@@ -198,3 +198,37 @@ def test_gemm_nvfp4_argument_checks(K, cuda):
     with pytest.raises(N.ClpkError) as e:
         K.clpk_gemm(C.byref(args), None)                 # workspace too small
     assert e.value.code == N.ERR_BAD_ARG
+
+
+# ---- scheduling knobs do not change the numbers ---------------------------------------------
+
+@pytest.mark.parametrize("dtype", [N.DT_BF16, N.DT_I8])
+def test_gemm_is_bitwise_the_same_with_and_without_producer_alignment(K, cuda, dtype, monkeypatch):
+    """The per-wave meeting of the producers and the raster group width only move work in time and
+    across SM pairs; every element of C is still one cluster's sum over K in the same order."""
+    m, n, k = 2048, 4096, 1024
+    d_a, d_b = make_gemm_operands(K, cuda, dtype, m, n, k)
+    monkeypatch.delenv("CLPK_GEMM_NO_ALIGN", raising=False)
+    monkeypatch.delenv("CLPK_GEMM_GROUP", raising=False)
+    base = to_np(run_gemm(K, cuda, dtype, m, n, k, d_a, d_b)).copy()
+    for env in ({"CLPK_GEMM_NO_ALIGN": "1"}, {"CLPK_GEMM_GROUP": "3"}, {"CLPK_GEMM_ALIGN_AT": "0"}):
+        for key, val in env.items():
+            monkeypatch.setenv(key, val)
+        other = to_np(run_gemm(K, cuda, dtype, m, n, k, d_a, d_b))
+        assert np.array_equal(base.view(np.uint8), other.view(np.uint8)), env
+        for key in env:
+            monkeypatch.delenv(key)
+
+
+def test_gemm_many_waves_small_k(K, orc, cuda):
+    """Many short tiles: 16 x 32 = 512 tiles of 512 x 256 on 74 clusters (7 waves) with K = 128."""
+    m = n = 8192
+    k = 128
+    d_a, d_b = make_gemm_operands(K, cuda, N.DT_BF16, m, n, k)
+    d_c = run_gemm(K, cuda, N.DT_BF16, m, n, k, d_a, d_b)
+    a = to_np(d_a).view(np.uint16)
+    b = to_np(d_b).view(np.uint16)
+    c = c_view(N.DT_BF16, d_c)
+    rng = np.random.default_rng(9)
+    samples = list(zip(rng.integers(0, m, 400), rng.integers(0, n, 400))) + [(m - 1, n - 1), (0, 0), (511, 255), (512, 256)]
+    check_samples(orc, N.DT_BF16, a, b, c, m, n, k, samples)
