@@ -28,6 +28,8 @@
 // launch asks for enough dynamic shared memory that a third never becomes
 // resident (tcgen05.alloc would otherwise block on it).  Kinds with scale
 // factors or metadata take all 512 columns: one CTA per SM.
+#include <cstdlib>
+
 #include "../clpk_internal.h"
 #include "../clpk_ptx.cuh"
 
@@ -89,43 +91,47 @@ template <> struct KindTraits<CLPK_MMA_I8>   { static constexpr bool scaled = fa
 template <> struct KindTraits<CLPK_MMA_MXF4> { static constexpr bool scaled = true;  static constexpr int sf_per_row = 2; };
 template <> struct KindTraits<CLPK_MMA_NVF4> { static constexpr bool scaled = true;  static constexpr int sf_per_row = 4; };
 
-template <int KIND>
+// PAIR: the cta_group::2 form.  The two CTAs of a cluster hold the same A tile and one
+// half of B each (B rows [128r, 128r + 128) in CTA r); one instruction of shape M256 N256
+// fills both CTAs' 128 x 256 accumulators with the same A.B^T tile a lone CTA computes.
+// Per flop it reads a third less shared memory (B once per pair), which under the power
+// cap is worth a few per cent of clock.
+template <int KIND, bool PAIR>
 __device__ __forceinline__ void issue_mma(uint32_t d, uint64_t ad, uint64_t bd, uint32_t sfa,
                                           uint32_t sfb, uint32_t acc)
 {
-    if constexpr (KIND == CLPK_MMA_F16) {
-        mma_f16_ss(d, ad, bd, make_idesc(kTileM, kTileN, kFmtF16, kFmtF16, kAccF32), acc);
-    } else if constexpr (KIND == CLPK_MMA_BF16) {
-        mma_f16_ss(d, ad, bd, make_idesc(kTileM, kTileN, kFmtBF16, kFmtBF16, kAccF32), acc);
-    } else if constexpr (KIND == CLPK_MMA_E4M3) {
-        mma_f8f6f4_ss(d, ad, bd, make_idesc(kTileM, kTileN, kFmtE4M3, kFmtE4M3, kAccF32), acc);
-    } else if constexpr (KIND == CLPK_MMA_E5M2) {
-        mma_f8f6f4_ss(d, ad, bd, make_idesc(kTileM, kTileN, kFmtE5M2, kFmtE5M2, kAccF32), acc);
+    constexpr uint32_t M = PAIR ? 256 : kTileM;
+    if constexpr (KIND == CLPK_MMA_F16 || KIND == CLPK_MMA_BF16 || KIND == CLPK_MMA_F16_F16) {
+        const uint32_t fmt = KIND == CLPK_MMA_BF16 ? kFmtBF16 : kFmtF16;
+        const uint32_t idesc = make_idesc(M, kTileN, fmt, fmt, KIND == CLPK_MMA_F16_F16 ? kAccF16 : kAccF32);
+        if constexpr (PAIR) mma2_f16_ss(d, ad, bd, idesc, acc); else mma_f16_ss(d, ad, bd, idesc, acc);
+    } else if constexpr (KIND == CLPK_MMA_E4M3 || KIND == CLPK_MMA_E5M2 || KIND == CLPK_MMA_E2M1) {
+        const uint32_t fmt = KIND == CLPK_MMA_E4M3 ? kFmtE4M3 : KIND == CLPK_MMA_E5M2 ? kFmtE5M2 : kFmtE2M1x8;
+        const uint32_t idesc = make_idesc(M, kTileN, fmt, fmt, kAccF32);
+        if constexpr (PAIR) mma2_f8f6f4_ss(d, ad, bd, idesc, acc); else mma_f8f6f4_ss(d, ad, bd, idesc, acc);
     } else if constexpr (KIND == CLPK_MMA_I8) {
-        mma_i8_ss(d, ad, bd, make_idesc(kTileM, kTileN, kFmtS8, kFmtS8, kAccS32), acc);
+        const uint32_t idesc = make_idesc(M, kTileN, kFmtS8, kFmtS8, kAccS32);
+        if constexpr (PAIR) mma2_i8_ss(d, ad, bd, idesc, acc); else mma_i8_ss(d, ad, bd, idesc, acc);
     } else if constexpr (KIND == CLPK_MMA_TF32) {
-        mma_tf32_ss(d, ad, bd, make_idesc(kTileM, kTileN, kFmtTF32, kFmtTF32, kAccF32), acc);
-    } else if constexpr (KIND == CLPK_MMA_F16_F16) {
-        mma_f16_ss(d, ad, bd, make_idesc(kTileM, kTileN, kFmtF16, kFmtF16, kAccF16), acc);
-    } else if constexpr (KIND == CLPK_MMA_E2M1) {
-        mma_f8f6f4_ss(d, ad, bd, make_idesc(kTileM, kTileN, kFmtE2M1x8, kFmtE2M1x8, kAccF32), acc);
+        const uint32_t idesc = make_idesc(M, kTileN, kFmtTF32, kFmtTF32, kAccF32);
+        if constexpr (PAIR) mma2_tf32_ss(d, ad, bd, idesc, acc); else mma_tf32_ss(d, ad, bd, idesc, acc);
     } else if constexpr (KIND == CLPK_MMA_MXF4) {
-        mma_mxf4_bs(d, ad, bd,
-                    make_idesc_block_scaled(kTileM, kTileN, kFmtE2M1, kFmtE2M1, /*ue8m0*/ 1, 0, 0),
-                    sfa, sfb, acc);
+        const uint32_t idesc = make_idesc_block_scaled(M, kTileN, kFmtE2M1, kFmtE2M1, /*ue8m0*/ 1, 0, 0);
+        if constexpr (PAIR) mma2_mxf4_bs(d, ad, bd, idesc, sfa, sfb, acc); else mma_mxf4_bs(d, ad, bd, idesc, sfa, sfb, acc);
     } else if constexpr (KIND == CLPK_MMA_NVF4) {
-        mma_nvf4_bs(d, ad, bd,
-                    make_idesc_block_scaled(kTileM, kTileN, kFmtE2M1, kFmtE2M1, /*ue4m3*/ 0, 0, 0),
-                    sfa, sfb, acc);
+        const uint32_t idesc = make_idesc_block_scaled(M, kTileN, kFmtE2M1, kFmtE2M1, /*ue4m3*/ 0, 0, 0);
+        if constexpr (PAIR) mma2_nvf4_bs(d, ad, bd, idesc, sfa, sfb, acc); else mma_nvf4_bs(d, ad, bd, idesc, sfa, sfb, acc);
     }
 }
 
-template <int KIND>
+template <int KIND, bool PAIR>
 __global__ void __launch_bounds__(128) mma_peak_kernel(PeakParams p)
 {
     using T = KindTraits<KIND>;
     constexpr uint32_t kCols = T::scaled ? 512u : 256u;
     constexpr uint32_t kSfaCol = 256, kSfbCol = 260;
+    constexpr int kGroup = PAIR ? 2 : 1;
+    constexpr int kBRows = PAIR ? kTileN / 2 : kTileN;          // rows of B this CTA stages
 
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t *sA = smem;
@@ -134,13 +140,15 @@ __global__ void __launch_bounds__(128) mma_peak_kernel(PeakParams p)
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+    const uint8_t *b_rows = p.b + (size_t)rank * kBRows * (KIND == CLPK_MMA_E2M1 ? 16 : kRowBytes);
 
     if constexpr (KIND == CLPK_MMA_E2M1) {
         stage_tile_fp4_padded(sA, p.a, kTileM);
-        stage_tile_fp4_padded(sB, p.b, kTileN);
+        stage_tile_fp4_padded(sB, b_rows, kBRows);
     } else {
         stage_tile(sA, p.a, kTileM);
-        stage_tile(sB, p.b, kTileN);
+        stage_tile(sB, b_rows, kBRows);
     }
     if (threadIdx.x == 0) {
         mbar_init(bar, 1);
@@ -149,10 +157,12 @@ __global__ void __launch_bounds__(128) mma_peak_kernel(PeakParams p)
     fence_proxy_async_smem();
     if (warp == 0) {
         __syncwarp();
-        tmem_alloc<1>(tmem_slot, kCols);
+        tmem_alloc<kGroup>(tmem_slot, kCols);
     }
     tc_fence_before_sync();
     __syncthreads();
+    if constexpr (PAIR)
+        cluster_sync();                 // both CTAs' tiles, barriers and tensor memory are in place
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
@@ -176,17 +186,22 @@ __global__ void __launch_bounds__(128) mma_peak_kernel(PeakParams p)
         tmem_st_wait();
         tc_fence_before_sync();
         __syncthreads();
+        if constexpr (PAIR)
+            cluster_sync();
         tc_fence_after_sync();
     }
 
-    if (threadIdx.x == 0) {
+    if (threadIdx.x == 0 && rank == 0) {
         const uint64_t ad = make_smem_desc(smem_u32(sA), 128, 256, kSwizzleNone);
         const uint64_t bd = make_smem_desc(smem_u32(sB), 128, 256, kSwizzleNone);
         const uint32_t sfa = tmem + kSfaCol, sfb = tmem + kSfbCol;
-        issue_mma<KIND>(tmem, ad, bd, sfa, sfb, 0u);
+        issue_mma<KIND, PAIR>(tmem, ad, bd, sfa, sfb, 0u);
         for (uint32_t i = 1; i < p.n_mma; i++)
-            issue_mma<KIND>(tmem, ad, bd, sfa, sfb, 1u);
-        tc_commit(bar);
+            issue_mma<KIND, PAIR>(tmem, ad, bd, sfa, sfb, 1u);
+        if constexpr (PAIR)
+            tc_commit_pair(bar, 3);
+        else
+            tc_commit(bar);
     }
     __syncwarp();
 
@@ -229,8 +244,10 @@ __global__ void __launch_bounds__(128) mma_peak_kernel(PeakParams p)
 
     tc_fence_before_sync();
     __syncthreads();
+    if constexpr (PAIR)
+        cluster_sync();                 // the peer's shared memory and barrier stay valid until both are done
     if (warp == 0)
-        tmem_dealloc<1>(tmem, kCols);
+        tmem_dealloc<kGroup>(tmem, kCols);
 }
 
 
@@ -425,9 +442,33 @@ static int launch_peak(const PeakParams &p, uint32_t grid, cudaStream_t s)
     // Dense: ~100 KiB so that exactly two CTAs fit one SM; scaled: one CTA.
     const int optin = smem_optin_bytes();
     const size_t smem = KindTraits<KIND>::scaled ? (size_t)(optin * 3 / 5) : (size_t)(optin * 2 / 5);
-    CLPK_CUDA(cudaFuncSetAttribute(mma_peak_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    // CTA pairs (cta_group::2) where they measured faster on B200 -- int8 +1.5..4 %, MXFP4 / NVFP4 +2..4 %;
+    // fp16 / bf16 / fp8 lose 4..7 % as pairs and stay solo.  CLPK_MMA_PAIR=0 / 1 overrides for every kind.
+    bool pair = KIND == CLPK_MMA_I8 || KIND == CLPK_MMA_MXF4 || KIND == CLPK_MMA_NVF4;
+    if (const char *e = getenv("CLPK_MMA_PAIR"))
+        pair = e[0] == '1';
+    if (grid % 2 == 0 && pair) {
+        CLPK_CUDA(cudaFuncSetAttribute(mma_peak_kernel<KIND, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(128);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, mma_peak_kernel<KIND, true>, p);
+        if (e != cudaSuccess)
+            return cuda_fail(e, "launch mma_peak (pairs)");
+        return CLPK_OK;
+    }
+    CLPK_CUDA(cudaFuncSetAttribute(mma_peak_kernel<KIND, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)smem));
-    mma_peak_kernel<KIND><<<grid, 128, smem, s>>>(p);
+    mma_peak_kernel<KIND, false><<<grid, 128, smem, s>>>(p);
     CLPK_LAUNCH_CHECK("mma_peak");
     return CLPK_OK;
 }

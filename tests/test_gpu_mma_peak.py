@@ -72,6 +72,22 @@ def test_tf32_ignores_the_low_mantissa_bits(K, orc, cuda):
     assert np.array_equal(clean[0], dirty[0])
 
 
+@pytest.mark.parametrize("kind", DENSE + SCALED)
+def test_cta_pairs_and_lone_ctas_compute_the_same_tile(K, orc, cuda, kind, monkeypatch):
+    """cta_group::2 (two CTAs share B) against cta_group::1: same accumulator bits, tile by tile."""
+    ops = M.make_operands(orc, kind)
+    out = {}
+    for pair in ("0", "1"):
+        monkeypatch.setenv("CLPK_MMA_PAIR", pair)
+        status, tiles, chk = M.run_peak(K, cuda, kind, ops, 5, grid=4, n_out_tiles=4)
+        assert status == 0
+        out[pair] = (tiles.copy(), chk.copy())
+    assert np.array_equal(out["0"][0], out["1"][0]) and np.array_equal(out["0"][1], out["1"][1])
+    want, tol = M.expected_tile(orc, kind, ops, 5)
+    for t in out["1"][0]:
+        M.check_tile(kind, t, want, tol)
+
+
 def test_linearity_in_instruction_count(K, orc, cuda):
     # int8 is exact, so n instructions give exactly n times one instruction.
     ops = M.make_operands(orc, N.MMA_I8)
