@@ -212,6 +212,25 @@ def run_reference_cpu(max_time_ms: int):
                       f"(<=512 MiB per array), all logical cores, --max-time-cpu {max_time_ms} ms, gcc build"}
 
 
+def run_reference_cpu_pairs(max_time_ms: int):
+    """The reference CPU backend's rows that pair with configs 1a / 2b: fp32 compute and memory latency."""
+    exe = ROOT / "oracle" / "_ref" / "clpeak_ref"
+    if not exe.exists():
+        return None
+    with tempfile.TemporaryDirectory() as td:
+        xml = Path(td) / "ref.xml"
+        r = subprocess.run([str(exe), "--cpu", "--single-precision-compute", "--memory-latency", "--max-time-cpu",
+                            str(max_time_ms), "--xml-file", str(xml)], capture_output=True, text=True, timeout=600)
+        if r.returncode != 0 or not xml.exists():
+            return None
+        txt = xml.read_text()
+    out = {}
+    for test, metrics in re.findall(r'<test name="([^"]+)"[^>]*>(.*?)</test>', txt, flags=re.S):
+        for name, val in re.findall(r'<metric name="([^"]+)"[^>]*>([0-9.]+)</metric>', metrics):
+            out[f"{test}/{name}"] = float(val)
+    return out
+
+
 def run_port_cpu(seconds: float):
     """Fallback: the oracle's C port of the three passes on 256 MiB arrays."""
     import numpy as np
@@ -436,6 +455,8 @@ def main():
             return reps.max_over_ranks(e0.elapsed_time(e1) / reps_)
 
         rows = measure_rows(K, N, torch, stream, lambda fn, reps=3: time_together(fn, reps), world)
+        if world == 1:
+            rows.update(measure_small_rows(K, N, torch, stream, time_once))
 
     if rank != 0:
         reps.close()
@@ -461,13 +482,51 @@ def main():
                      "peak_source": f"of {peaks['source']}", "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                      "frac_of_spec": achieved / SPEC["hbm_gbs"], "traffic": ncu_traffic(kernel_symbol)},
         "cpu_baseline": ({"value": cpu["value"], "unit": UNIT, "cores": cpu["cores"], "kind": cpu["kind"],
-                          "sample": cpu["sample"], "rows": cpu["rows"]} if cpu else None),
+                          "sample": cpu["sample"], "rows": cpu["rows"],
+                          "other_reference_cpu_rows": (run_reference_cpu_pairs(500) if not args.no_rows else None)}
+                         if cpu else None),
         "e2e": e2e, "gpu_launches": 3 * args.steps, "clocks": clocks, "read_checksum": read_xor,
         "rows": rows, "spec_peaks_per_gpu": SPEC,
     }
     print(json.dumps(line), flush=True)
     reps.close()
     return 0
+
+
+def measure_small_rows(K, N, torch, stream, time_once):
+    """Configs 1a, 1b, 2b, 2c on this GPU (rank 0, one GPU): chain, read-and-sum, pointer chase, launch roundtrip."""
+    import numpy as np
+    rows = {}
+    items = 1 << 20
+    out = torch.empty(items, dtype=torch.float32, device="cuda")
+    ms = time_once(lambda: K.clpk_mad_chain(out.data_ptr(), items, 0, 0.999, 4096, stream), reps=20)
+    rows["mad_chain_2^20x4096"] = {"GFLOPS": items * 4 * 4096 * 2 / ms / 1e6, "ms": ms}
+    n = (256 << 20) // 4
+    src = torch.empty(n, dtype=torch.float32, device="cuda")
+    K.clpk_fill_f32(src.data_ptr(), n, 1, N.DIST_UNIFORM01, 0.0, 1.0, stream)
+    dst = torch.empty(n // 64, dtype=torch.float32, device="cuda")
+    ms = time_once(lambda: K.clpk_global_bandwidth(4, src.data_ptr(), dst.data_ptr(), n, stream), reps=16)
+    rows["read_sum_float4_256MiB"] = {"GBps": n * 4 / ms / 1e6, "ms": ms,
+                                      "note": "256 MiB is about twice the L2: partly L2-resident between repeats"}
+    del src, dst
+    # pointer chase: 2^28 x uint32 (1 GiB) single cycle, 2^24 dependent hops
+    n_idx, hops = 1 << 28, 1 << 24
+    host_next = np.empty(n_idx, dtype=np.uint32)
+    K.clpk_build_chase_cycle(host_next.ctypes.data, n_idx, 0xC0FFEE)
+    nxt = torch.from_numpy(host_next.view(np.int32)).cuda()
+    res = torch.zeros(4, dtype=torch.int32, device="cuda")
+    K.clpk_pointer_chase(nxt.data_ptr(), 0, 1 << 16, res.data_ptr(), stream)        # warm the TLBs a little
+    K.clpk_pointer_chase(nxt.data_ptr(), 0, hops, res.data_ptr(), stream)
+    torch.cuda.synchronize()
+    r = res.cpu().numpy().view(np.uint32)
+    ns = (int(r[2]) | (int(r[3]) << 32)) / hops
+    rows["pointer_chase_1GiB"] = {"ns_per_hop": ns, "hops": hops, "final_index": int(r[0])}
+    del nxt
+    mean_us = C.c_double(0.0)
+    K.clpk_launch_latency(20000, 200, C.byref(mean_us), stream)
+    rows["launch_roundtrip"] = {"us": mean_us.value, "launches": 20000}
+    torch.cuda.empty_cache()
+    return rows
 
 
 def measure_rows(K, N, torch, stream, time_once, world=1):
