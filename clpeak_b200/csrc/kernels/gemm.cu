@@ -771,13 +771,15 @@ static std::atomic<unsigned> g_next_sync_slot{0};
 // fresh wave counter when the alignment is on, plainly (and unaligned) otherwise.
 template <typename Kernel, typename... Maps>
 static int launch_persistent(Kernel kernel, const char *what, int threads, size_t smem, cudaStream_t s, GemmParams p,
-                             const Maps &...maps)
+                             uint32_t n_tiles, const Maps &...maps)
 {
     CLPK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int grid = (num_sms() / 2) * 2;
     const char *off = getenv("CLPK_GEMM_NO_ALIGN");
     p.wave_sync = nullptr;
-    if (!(off && off[0] == '1')) {
+    // nothing to keep in step in the first two waves: small problems skip the counter and its memset
+    const bool worth_aligning = n_tiles > 2u * (uint32_t)(grid / 2) * p.align_period;
+    if (worth_aligning && !(off && off[0] == '1')) {
         unsigned int *base = nullptr;
         CLPK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&base), g_wave_sync));
         p.wave_sync = base + g_next_sync_slot.fetch_add(1) % kSyncSlots;
@@ -812,7 +814,8 @@ static int launch_persistent(Kernel kernel, const char *what, int threads, size_
 template <int DT>
 static int launch_gemm(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, const GemmParams &p, cudaStream_t s)
 {
-    return launch_persistent(gemm_kernel<DT>, "gemm", kGemmThreads, kGemmSmemBytes, s, p, ta, tb, tc);
+    const uint32_t n_tiles = ((p.m + kDenseTileM - 1) / kDenseTileM) * (p.n / kTileMN);
+    return launch_persistent(gemm_kernel<DT>, "gemm", kGemmThreads, kGemmSmemBytes, s, p, n_tiles, ta, tb, tc);
 }
 
 } // namespace clpk
@@ -918,8 +921,9 @@ int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
         rc = make_output_map(&tc, a->d_c, a->m, a->n, a->dtype);
         if (rc != CLPK_OK)
             return rc;
-        return mx ? launch_persistent(gemm_block_scaled_kernel<true>, "gemm_mxf4", kNvGemmThreads, kNvGemmSmemBytes, s, p, ta, tb, tsa, tsb, tc)
-                  : launch_persistent(gemm_block_scaled_kernel<false>, "gemm_nvf4", kNvGemmThreads, kNvGemmSmemBytes, s, p, ta, tb, tsa, tsb, tc);
+        const uint32_t n_tiles = (a->m / kTileMN) * (a->n / kTileMN);
+        return mx ? launch_persistent(gemm_block_scaled_kernel<true>, "gemm_mxf4", kNvGemmThreads, kNvGemmSmemBytes, s, p, n_tiles, ta, tb, tsa, tsb, tc)
+                  : launch_persistent(gemm_block_scaled_kernel<false>, "gemm_nvf4", kNvGemmThreads, kNvGemmSmemBytes, s, p, n_tiles, ta, tb, tsa, tsb, tc);
     }
     CUtensorMap tc;
     rc = make_output_map(&tc, a->d_c, a->m, a->n, a->dtype);

@@ -1,0 +1,165 @@
+// TEST PROGRAM: the backend's own host references (clpeak_b200/csrc/host/host_check.hpp, product
+// code) against the CPU oracle (oracle/oracle.h, test infrastructure) on the same seeded inputs.
+// Prints one line per check; exit code = number of failed checks.
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+#include "host_check.hpp"
+#include "../../oracle/oracle.h"
+
+static int g_failed = 0;
+static void report(const char *what, bool ok)
+{
+    std::printf("%-58s %s\n", what, ok ? "ok" : "FAILED");
+    if (!ok)
+        ++g_failed;
+}
+
+int main()
+{
+    // ---- typed chains: all 256 lanes, several start values --------------------------------------
+    for (int chain = 0; chain < CLPK_CHAIN_COUNT; ++chain) {
+        const double starts[] = {chain >= CLPK_CHAIN_INT32 ? 3.0 : 1.3, 0.25, 4.0, -0.75};
+        bool ok = true;
+        for (double a : starts) {
+            std::vector<uint64_t> buf(256);
+            orc_compute_chain(chain, buf.data(), a, 256);
+            for (unsigned t = 0; t < 256 && ok; ++t) {
+                uint64_t want = 0;
+                const size_t elem = chain == CLPK_CHAIN_DOUBLE ? 8 : 4;
+                std::memcpy(&want, reinterpret_cast<const uint8_t *>(buf.data()) + t * elem, elem);
+                const uint64_t got = b200check::typedChainBits(chain, a, t);
+                // NaNs may differ in payload between two correct implementations; compare classes then
+                bool same = got == want;
+                if (!same && elem == 4) {
+                    float g = clpk_bits_f32((uint32_t)got), w = clpk_bits_f32((uint32_t)want);
+                    same = std::isnan(g) && std::isnan(w);
+                }
+                ok = same;
+            }
+        }
+        char name[64];
+        std::snprintf(name, sizeof name, "typed chain %d equals the oracle", chain);
+        report(name, ok);
+    }
+
+    // ---- shared-memory rotation and texture read ----------------------------------------------------
+    {
+        bool ok = true;
+        for (int w : {1, 2, 4}) {
+            std::vector<float> o(1024);
+            orc_local_bandwidth(w, o.data(), o.size());
+            for (size_t i = 0; i < o.size(); ++i)
+                ok = ok && b200check::sameFloat(o[i], b200check::localBandwidthReference(w, i));
+        }
+        report("local bandwidth closed form equals the oracle", ok);
+        std::vector<float> o(512);
+        orc_image_bandwidth(o.data(), 100, 512, 4096, 1 << 16, 5);
+        ok = true;
+        for (size_t i = 0; i < o.size(); ++i)
+            ok = ok && b200check::sameFloat(o[i], b200check::imageBandwidthReference(100 + i, 4096, 1 << 16, 5));
+        report("image bandwidth replay equals the oracle", ok);
+    }
+
+    // ---- 2:4 pruning ------------------------------------------------------------------------------------
+    for (int pairs = 0; pairs < 2; ++pairs) {
+        const int k = pairs ? 128 : 64;
+        std::vector<float> dense(128 * (size_t)k), oc(128 * (size_t)k / 2), op(dense.size()), hc;
+        orc_fill_f32(dense.data(), 0, dense.size(), 3, 2, 0.0f, 1.0f);
+        // ties on purpose: every 16th group gets equal magnitudes
+        for (size_t g = 0; g < dense.size() / 4; g += 16)
+            dense[4 * g] = dense[4 * g + 1] = -dense[4 * g + 2];
+        std::vector<uint8_t> om(128 * (size_t)k / (pairs ? 16 : 8)), hm;
+        if (pairs)
+            orc_prune_pairs_2to4(oc.data(), om.data(), op.data(), dense.data(), 128, k);
+        else
+            orc_prune_2to4(oc.data(), om.data(), op.data(), dense.data(), 128, k);
+        b200check::pruneTile(dense, 128, k, pairs != 0, hc, hm);
+        report(pairs ? "pair-wise 2:4 pruning equals the oracle" : "element-wise 2:4 pruning equals the oracle",
+               hc.size() == oc.size() && hm.size() == om.size() && std::memcmp(hc.data(), oc.data(), oc.size() * 4) == 0 &&
+                   std::memcmp(hm.data(), om.data(), om.size()) == 0);
+    }
+
+    // ---- sparse tile check accepts the oracle's tile and rejects a corrupted one ------------------------
+    {
+        const int kinds[] = {CLPK_MMA_E4M3_SP, CLPK_MMA_I8_SP, CLPK_MMA_MXF4_SP, CLPK_MMA_NVF4_SP};
+        for (int kind : kinds) {
+            const bool fp4 = kind == CLPK_MMA_MXF4_SP || kind == CLPK_MMA_NVF4_SP;
+            const int K = fp4 ? 128 : 64, nsf = kind == CLPK_MMA_NVF4_SP ? 4 : 2;
+            std::vector<float> dense(128 * (size_t)K), comp, fb(256 * (size_t)K);
+            std::vector<uint8_t> meta;
+            if (kind == CLPK_MMA_I8_SP) {
+                std::vector<int8_t> raw(dense.size());
+                orc_fill_i8(raw.data(), 0, raw.size(), 2);
+                for (size_t i = 0; i < raw.size(); ++i) dense[i] = raw[i];
+            } else {
+                orc_fill_f32(dense.data(), 0, dense.size(), 2, fp4 ? 2 : 1, 0.0f, 1.0f);
+            }
+            b200check::pruneTile(dense, 128, K, fp4, comp, meta);
+            std::vector<uint8_t> a(128 * 32), b(256 * 64), sfa(128 * 4), sfb(256 * 4);
+            if (kind == CLPK_MMA_I8_SP) {
+                orc_convert_f32(a.data(), comp.data(), comp.size(), 5);
+                orc_fill_i8(reinterpret_cast<int8_t *>(b.data()), 0, b.size(), 3);
+            } else if (!fp4) {
+                orc_convert_f32(a.data(), comp.data(), comp.size(), 3);
+                orc_fill_f32(fb.data(), 0, fb.size(), 3, 1, 0.0f, 1.0f);
+                orc_convert_f32(b.data(), fb.data(), fb.size(), 3);
+            } else {
+                const bool mx = kind == CLPK_MMA_MXF4_SP;
+                orc_quantize_fp4(a.data(), sfa.data(), comp.data(), 128, K / 2, mx ? 6 : 7, mx ? 1.0f : 0.001953125f);
+                orc_fill_f32(fb.data(), 0, fb.size(), 4, 2, 0.0f, 1.0f);
+                orc_quantize_fp4(b.data(), sfb.data(), fb.data(), 256, K, mx ? 8 : 9, mx ? 1.0f : 0.001953125f);
+            }
+            std::vector<double> p(128 * 256), s(128 * 256);
+            orc_mma_tile_sp(kind, a.data(), meta.data(), b.data(), sfa.data(), sfb.data(), p.data(), s.data());
+            const uint32_t n = 7;
+            std::vector<uint32_t> tile(128 * 256);
+            for (size_t i = 0; i < tile.size(); ++i)
+                tile[i] = kind == CLPK_MMA_I8_SP ? (uint32_t)((int32_t)p[i] * (int32_t)n) : clpk_f32_bits((float)(p[i] * n));
+            const bool accepts = b200check::checkSparseTile(kind, a.data(), meta.data(), b.data(), sfa.data(), sfb.data(), n, tile.data()).empty();
+            tile[777] = kind == CLPK_MMA_I8_SP ? tile[777] + 1 : clpk_f32_bits(clpk_bits_f32(tile[777]) * 1.01f + 0.5f);
+            const bool rejects = !b200check::checkSparseTile(kind, a.data(), meta.data(), b.data(), sfa.data(), sfb.data(), n, tile.data()).empty();
+            (void)nsf;
+            char name[80];
+            std::snprintf(name, sizeof name, "sparse tile check, kind %d: accepts oracle tile, rejects corrupt", kind);
+            report(name, accepts && rejects);
+        }
+    }
+
+    // ---- GEMM element ------------------------------------------------------------------------------------
+    {
+        const uint64_t k = 512;
+        const int dts[] = {CLPK_DT_F16, CLPK_DT_BF16, CLPK_DT_E4M3, CLPK_DT_E5M2, CLPK_DT_I8, CLPK_DT_TF32, CLPK_DT_MXF4, CLPK_DT_NVF4};
+        for (int dt : dts) {
+            std::vector<float> fa(4 * k), fb(4 * k);
+            orc_fill_f32(fa.data(), 0, fa.size(), 40, 2, 0.0f, 0.02f);
+            orc_fill_f32(fb.data(), 0, fb.size(), 41, 2, 0.0f, 0.02f);
+            std::vector<uint8_t> a(4 * k * 4), b(4 * k * 4), sfa(4 * k / 16), sfb(4 * k / 16);
+            if (dt == CLPK_DT_MXF4 || dt == CLPK_DT_NVF4) {
+                const float ts = dt == CLPK_DT_NVF4 ? 3.0517578125e-05f : 1.0f;
+                orc_quantize_fp4(a.data(), sfa.data(), fa.data(), 4, k, dt, ts);
+                orc_quantize_fp4(b.data(), sfb.data(), fb.data(), 4, k, dt, ts);
+            } else if (dt == CLPK_DT_I8) {
+                orc_fill_i8(reinterpret_cast<int8_t *>(a.data()), 0, 4 * k, 40);
+                orc_fill_i8(reinterpret_cast<int8_t *>(b.data()), 0, 4 * k, 41);
+            } else {
+                orc_convert_f32(a.data(), fa.data(), fa.size(), dt);
+                orc_convert_f32(b.data(), fb.data(), fb.size(), dt == CLPK_DT_E5M2 ? CLPK_DT_E4M3 : dt);
+            }
+            bool ok = true;
+            for (uint64_t i = 0; i < 4; ++i)
+                for (uint64_t j = 0; j < 4; ++j) {
+                    double so = 0, sh = 0;
+                    const double o = orc_gemm_element(dt, a.data(), b.data(), sfa.data(), sfb.data(), k, i, j, &so);
+                    const double h = b200check::gemmElement(dt, a.data(), b.data(), k, i, j, &sh, sfa.data(), sfb.data());
+                    ok = ok && o == h && so == sh;
+                }
+            char name[64];
+            std::snprintf(name, sizeof name, "GEMM element, dtype %d, equals the oracle", dt);
+            report(name, ok);
+        }
+    }
+    return g_failed;
+}

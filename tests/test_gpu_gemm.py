@@ -206,7 +206,7 @@ def test_gemm_nvfp4_argument_checks(K, cuda):
 def test_gemm_is_bitwise_the_same_with_and_without_producer_alignment(K, cuda, dtype, monkeypatch):
     """The per-wave meeting of the producers and the raster group width only move work in time and
     across SM pairs; every element of C is still one cluster's sum over K in the same order."""
-    m, n, k = 2048, 4096, 1024
+    m, n, k = 8192, 8192, 256                # 512 tiles on 74 clusters: seven waves, so the producers do meet
     d_a, d_b = make_gemm_operands(K, cuda, dtype, m, n, k)
     monkeypatch.delenv("CLPK_GEMM_NO_ALIGN", raising=False)
     monkeypatch.delenv("CLPK_GEMM_GROUP", raising=False)
