@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Headline benchmark: HBM streaming bandwidth (BASELINE config 2a) on N B200s.
+"""Headline benchmark: HBM streaming bandwidth (8 GiB read / copy / triad) on N B200s.
 
 A *step* is one pass of the three STREAM kernels over 8 GiB fp32 buffers:
 read (8 GiB), copy (16 GiB), triad a = b + 1.5*c (24 GiB) -> 48 GiB of
@@ -471,7 +471,7 @@ def main():
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"hbm_stream_read_copy_triad_{args.size_gib:g}GiB_fp32 (BASELINE configs[1]a)",
+        "config": {"workload": f"hbm_stream_read_copy_triad_{args.size_gib:g}GiB_fp32 (configs[1](a) of the benchmark definition)",
                    "bytes_per_array": n_bytes, "algorithmic_bytes_per_step": bytes_per_step,
                    "variants": {k: vname[v] for k, v in variant.items()},
                    "l2": "inputs (3 x %.0f GiB) far exceed the 126 MB L2; no flush needed" % args.size_gib,

@@ -1,6 +1,6 @@
 """Operand construction and checking for the tensor-core tests.
 
-Config (BASELINE): dense kinds draw uniform[-1,1) (ints uniform[-8,7]) from
+Benchmark configuration: dense kinds draw uniform[-1,1) (ints uniform[-8,7]) from
 seed 2; block-scaled kinds draw N(0,1) from seed 3 and quantise per block.
 """
 import numpy as np

@@ -14,7 +14,7 @@ import pytest
 from tests.host_fake import FakeFfi
 
 ROOT = Path(__file__).resolve().parent.parent
-REF_RESULTS = Path("/root/reference/results")
+REF_RESULTS = Path(os.environ.get("CLPEAK_REFERENCE_DIR", "/root/reference")) / "results"
 FAST = ["-i", "1", "-w", "0"]
 
 

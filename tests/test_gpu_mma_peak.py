@@ -26,7 +26,7 @@ def test_single_cta_tile(K, orc, cuda, kind, n_mma):
 
 @pytest.mark.parametrize("kind", DENSE + SCALED)
 def test_full_config_all_ctas_agree(K, orc, cuda, kind):
-    # BASELINE config: 2^14 instructions per CTA, grid = 4 x SM count.
+    # full configuration: 2^14 instructions per CTA, grid = 4 x SM count.
     sms = cuda.cuda.get_device_properties(0).multi_processor_count
     grid = 4 * sms
     n_mma = 1 << 14
