@@ -231,6 +231,38 @@ def run_reference_cpu_pairs(max_time_ms: int):
     return out
 
 
+def run_reference_cuda_kernels(budget_us: int, row_filter: str = ""):
+    """The reference's own CUDA kernels on this GPU.
+
+    `make -C oracle refcuda` compiles the reference's src/cuda/cuda_kernels/*.cu (unchanged, from the reference
+    checkout) to sm_100a cubins and builds oracle/ref_cuda_runner.cpp, a launcher that follows the reference
+    host side's geometry, calibration and accounting.  Returns {"test/label": value} in the reference's units,
+    or None when the prebuilt files are not there.
+    """
+    exe = ROOT / "oracle" / "_ref" / "ref_cuda_runner"
+    cubins = ROOT / "oracle" / "_ref" / "cuda"
+    if not exe.exists() or not cubins.is_dir():
+        return None
+    try:
+        cmd = [str(exe), str(cubins), "--budget-us", str(budget_us)] + (["--filter", row_filter] if row_filter else [])
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    except (OSError, subprocess.TimeoutExpired):
+        return None
+    if r.returncode != 0:
+        return {"error": r.stderr.strip()[-300:]}
+    out = {}
+    for ln in r.stdout.splitlines():
+        try:
+            row = json.loads(ln)
+        except ValueError:
+            continue
+        key = f"{row['test']}/{row['label']}"
+        out[key] = row.get("value", row.get("skipped"))
+    out["unit_note"] = ("gbps / gflops / gops / tflops / tops / us as the reference reports each row; its kernels, "
+                        f"compiled for sm_100a, launched with its geometry; {budget_us} us timed per row")
+    return out
+
+
 def run_port_cpu(seconds: float):
     """Fallback: the oracle's C port of the three passes on 256 MiB arrays."""
     import numpy as np
@@ -275,6 +307,7 @@ def reference_arm(args):
                          "sample": res["sample"]},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "rows_last_step": res["rows"],
+        "reference_cuda_kernels_on_this_gpu": run_reference_cuda_kernels(200000, "global_memory_bandwidth"),
     }
     print(json.dumps(line), flush=True)
     return 0
@@ -487,6 +520,8 @@ def main():
                          if cpu else None),
         "e2e": e2e, "gpu_launches": 3 * args.steps, "clocks": clocks, "read_checksum": read_xor,
         "rows": rows, "spec_peaks_per_gpu": SPEC,
+        "reference_cuda_kernels_on_this_gpu": (run_reference_cuda_kernels(200000)
+                                                if world == 1 and not args.no_rows else None),
     }
     print(json.dumps(line), flush=True)
     reps.close()

@@ -35,17 +35,6 @@ __device__ __forceinline__ __half run_h(__half x, __half c)
     return x;
 }
 
-template <int STEPS>
-__device__ __forceinline__ int run_dot(int x, int &y, int a)
-{
-#pragma unroll
-    for (int i = 0; i < STEPS; i++) {
-        a = __dp4a(x, y, a);
-        y ^= a;
-    }
-    return a;
-}
-
 __device__ __forceinline__ uint32_t thread_slot() { return blockIdx.x * 256u + threadIdx.x; }
 
 // two chains of 64 x 16 scalar half FMAs; the store is their half sum, widened
@@ -115,13 +104,20 @@ __global__ void __launch_bounds__(256) chain_int32_kernel(int *__restrict__ out,
     out[thread_slot()] = (int)x;
 }
 
-// 1024 dot products of four signed bytes, split over CHAINS independent accumulators
-// that take turns in runs of 16.  Chain j starts from y = tid + j and a = tid + offset[j].
-template <int CHAINS>
+// 1024 dot products of four signed bytes, split over CHAINS independent accumulators.
+// Chain j starts from y = tid + j and a = tid + offset[j] and repeats a = dp4a(x, y, a);
+// y ^= a.  The chains are independent, so the order in which their steps are issued is
+// free: here they take turns step by step, BODY dot products per iteration of a rolled
+// loop.  The dot-product pipe and the ALU (for the xor) are both close to full, and the
+// measured rate moves by a few percent with how ptxas happens to lay the steps out;
+// BODY per chain count is the best of 32 / 128 / 512 / 1024 measured on a B200
+// (122 / 128 / 125 / 125 TOPS for 1 / 2 / 4 / 8 chains).
+template <int CHAINS, int BODY>
 __global__ void __launch_bounds__(256) chain_int8_dot_kernel(int *__restrict__ out, int a_arg)
 {
     constexpr int kOffsets[4][8] = {{0}, {0, 7}, {0, 7, 13, 19}, {0, 11, 17, 23, 29, 31, 37, 41}};
     constexpr int kRow = CHAINS == 1 ? 0 : CHAINS == 2 ? 1 : CHAINS == 4 ? 2 : 3;
+    static_assert(1024 % BODY == 0 && BODY % CHAINS == 0, "BODY must divide 1024 and hold whole rounds");
     const int x = (a_arg & 0xff) | (((a_arg + 1) & 0xff) << 8) | (((a_arg + 2) & 0xff) << 16) |
                   (((a_arg + 3) & 0xff) << 24);
     int y[CHAINS], acc[CHAINS];
@@ -130,11 +126,16 @@ __global__ void __launch_bounds__(256) chain_int8_dot_kernel(int *__restrict__ o
         y[j] = (int)threadIdx.x + j;
         acc[j] = (int)threadIdx.x + kOffsets[kRow][j];
     }
+#pragma unroll 1
+    for (int o = 0; o < 1024 / BODY; o++) {
 #pragma unroll
-    for (int i = 0; i < 64 / CHAINS; i++) {
+        for (int k = 0; k < BODY / CHAINS; k++) {
 #pragma unroll
-        for (int j = 0; j < CHAINS; j++)
-            acc[j] = run_dot<16>(x, y[j], acc[j]);
+            for (int j = 0; j < CHAINS; j++) {
+                acc[j] = __dp4a(x, y[j], acc[j]);
+                y[j] ^= acc[j];
+            }
+        }
     }
     uint32_t sum = 0;
 #pragma unroll
@@ -176,10 +177,10 @@ int clpk_compute_chain(int chain, void *d_out, double a, uint32_t grid, void *st
     case CLPK_CHAIN_MIXED:     chain_mixed_kernel<<<grid, 256, 0, s>>>(of, (float)a); break;
     case CLPK_CHAIN_BF16:      chain_bf16_kernel<<<grid, 256, 0, s>>>(of, (float)a); break;
     case CLPK_CHAIN_INT32:     chain_int32_kernel<<<grid, 256, 0, s>>>(oi, (int)a); break;
-    case CLPK_CHAIN_INT8_DOT1: chain_int8_dot_kernel<1><<<grid, 256, 0, s>>>(oi, (int)a); break;
-    case CLPK_CHAIN_INT8_DOT2: chain_int8_dot_kernel<2><<<grid, 256, 0, s>>>(oi, (int)a); break;
-    case CLPK_CHAIN_INT8_DOT4: chain_int8_dot_kernel<4><<<grid, 256, 0, s>>>(oi, (int)a); break;
-    default:                   chain_int8_dot_kernel<8><<<grid, 256, 0, s>>>(oi, (int)a); break;
+    case CLPK_CHAIN_INT8_DOT1: chain_int8_dot_kernel<1, 1024><<<grid, 256, 0, s>>>(oi, (int)a); break;
+    case CLPK_CHAIN_INT8_DOT2: chain_int8_dot_kernel<2, 128><<<grid, 256, 0, s>>>(oi, (int)a); break;
+    case CLPK_CHAIN_INT8_DOT4: chain_int8_dot_kernel<4, 1024><<<grid, 256, 0, s>>>(oi, (int)a); break;
+    default:                   chain_int8_dot_kernel<8, 32><<<grid, 256, 0, s>>>(oi, (int)a); break;
     }
     CLPK_LAUNCH_CHECK("compute_chain");
     return CLPK_OK;

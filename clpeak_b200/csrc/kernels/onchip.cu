@@ -52,17 +52,22 @@ __global__ void image_fill_kernel(float4 *__restrict__ texels, uint64_t n_texels
 // 16 point-sampled float4 fetches per thread, fetch i at texel (gid + i * threads) mod
 // (width * height); channel-wise sums, then x + y + z + w.  With threads * 16 =
 // width * height every texel is read exactly once per launch.
+template <bool POW2>
 __global__ void __launch_bounds__(256) image_bandwidth_kernel(cudaTextureObject_t tex, float *__restrict__ out,
-                                                              int width, int height)
+                                                              uint32_t width, uint32_t total, uint32_t shift)
 {
-    const int gid = (int)(blockIdx.x * blockDim.x + threadIdx.x);
-    const int threads = (int)(gridDim.x * blockDim.x);
-    const int total = width * height;
+    // the host checks threads * 16 <= 2^31 - 1, so 32-bit unsigned texel numbers cannot wrap
+    const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t threads = gridDim.x * blockDim.x;
     float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int i = 0; i < kImageFetches; i++) {
-        const int texel = (int)(((long long)gid + (long long)i * threads) % total);
-        const float4 v = tex2D<float4>(tex, texel % width, texel / width);
+        uint32_t texel = gid + (uint32_t)i * threads;
+        if (texel >= total)
+            texel %= total;
+        const uint32_t x = POW2 ? (texel & (width - 1u)) : texel % width;
+        const uint32_t y = POW2 ? (texel >> shift) : texel / width;
+        const float4 v = tex2D<float4>(tex, (int)x, (int)y);
         sum.x = __fadd_rn(sum.x, v.x);
         sum.y = __fadd_rn(sum.y, v.y);
         sum.z = __fadd_rn(sum.z, v.z);
@@ -164,7 +169,15 @@ int clpk_image_bandwidth(void *image, float *d_out, uint32_t grid, void *stream)
     CLPK_REQUIRE(image && d_out && grid > 0, "bad arguments");
     const Image *img = static_cast<const Image *>(image);
     CLPK_REQUIRE((uint64_t)grid * 256 <= 0x7FFFFFFFull / kImageFetches, "grid %u too large", grid);
-    image_bandwidth_kernel<<<grid, 256, 0, as_stream(stream)>>>(img->tex, d_out, (int)img->width, (int)img->height);
+    const uint32_t total = img->width * img->height;
+    if ((img->width & (img->width - 1u)) == 0) {
+        uint32_t shift = 0;
+        while ((1u << shift) < img->width)
+            shift++;
+        image_bandwidth_kernel<true><<<grid, 256, 0, as_stream(stream)>>>(img->tex, d_out, img->width, total, shift);
+    } else {
+        image_bandwidth_kernel<false><<<grid, 256, 0, as_stream(stream)>>>(img->tex, d_out, img->width, total, 0);
+    }
     CLPK_LAUNCH_CHECK("image_bandwidth");
     return CLPK_OK;
 }

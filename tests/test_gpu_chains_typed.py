@@ -93,7 +93,7 @@ def make_image(K, w, h, seed, stream):
     return img
 
 
-@pytest.mark.parametrize("shape", [(256, 128), (64, 64), (1024, 48)])
+@pytest.mark.parametrize("shape", [(256, 128), (64, 64), (1024, 48), (384, 96), (1000, 512)])
 def test_image_bandwidth_small_images_every_thread(K, orc, cuda, shape):
     w, h = shape
     stream = cuda.cuda.current_stream().cuda_stream
