@@ -109,6 +109,24 @@ __device__ __forceinline__ void tma_load_pair(void *smem_dst, const CUtensorMap 
         : "memory");
 }
 
+// The same with the leader's barrier address already mapped (mapa hoisted out of the loop).
+__device__ __forceinline__ void tma_load_pair_at(void *smem_dst, const CUtensorMap *tmap, int32_t x, int32_t y,
+                                                 uint32_t leader_bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(smem_dst)),
+        "l"(tmap), "r"(leader_bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ uint32_t leader_addr(const void *p)
+{
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(a) : "r"(smem_u32(p)));
+    return a;
+}
+
 // DT: BF16 / F16 -> kind::f16 (K = 16 per instruction); E4M3 / E5M2 -> kind::f8f6f4 (K = 32);
 // TF32 -> kind::tf32 (K = 8, fp32 out); I8 -> kind::i8 (K = 32, int32 out).  Always 128 bytes of K per stage.
 //
@@ -215,6 +233,57 @@ __device__ __forceinline__ void drain_warp_tile(uint32_t taddr0, uint32_t row_bl
         __syncwarp();
         if (lane == 0) {
             tma_store_2d(tmap_c, box, (int32_t)(col0 + c), (int32_t)(row0 + h * 256));
+            bulk_commit();
+        }
+    }
+}
+
+// The same for a kernel with a single accumulator (bf16 output, one row block), where the
+// next tile's main loop cannot start before tensor memory is free: all 128 columns are read
+// and tensor memory is released before anything is written out.  Two rounds of two
+// tcgen05.ld (64 fp32 registers in flight, 32 packed ones kept) rather than one of four,
+// which would not fit the register file.
+__device__ __forceinline__ void drain_warp_tile_early(uint32_t taddr0, uint32_t row0, uint32_t col0, uint8_t *box,
+                                                      const CUtensorMap *tmap_c, float alpha, uint64_t *empty_bar,
+                                                      int lane)
+{
+    uint8_t *my_row = box + lane * 128;
+    const uint32_t sw = (uint32_t)(lane & 7);
+    uint32_t w[2][32];
+#pragma unroll
+    for (uint32_t b = 0; b < 2; b++) {
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32b_x32(taddr0 + b * 64, r0);
+        tmem_ld_32x32b_x32(taddr0 + b * 64 + 32, r1);
+        tmem_ld_wait();
+        if (b == 1) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive_cluster(empty_bar, 0);
+        }
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            __nv_bfloat162 v0 = __floats2bfloat162_rn(__uint_as_float(r0[2 * i]) * alpha, __uint_as_float(r0[2 * i + 1]) * alpha);
+            __nv_bfloat162 v1 = __floats2bfloat162_rn(__uint_as_float(r1[2 * i]) * alpha, __uint_as_float(r1[2 * i + 1]) * alpha);
+            w[b][i] = *reinterpret_cast<uint32_t *>(&v0);
+            w[b][16 + i] = *reinterpret_cast<uint32_t *>(&v1);
+        }
+    }
+#pragma unroll
+    for (uint32_t b = 0; b < 2; b++) {
+        // the previous box must have been read out of shared memory by its store
+        if (lane == 0)
+            bulk_wait_read<0>();
+        __syncwarp();
+#pragma unroll
+        for (uint32_t j = 0; j < 8; j++)
+            *reinterpret_cast<uint4 *>(my_row + ((j ^ sw) << 4)) =
+                make_uint4(w[b][4 * j], w[b][4 * j + 1], w[b][4 * j + 2], w[b][4 * j + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            tma_store_2d(tmap_c, box, (int32_t)(col0 + b * 64), (int32_t)row0);
             bulk_commit();
         }
     }
@@ -415,10 +484,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
 // NVFP4 GEMM: e2m1 operands, one ue4m3 scale per 16 elements along K
 // ---------------------------------------------------------------------------------
 //
-// Same skeleton as gemm_kernel (2-CTA clusters, 256x256 tiles, TMA ring, one MMA
-// thread, four epilogue warps) with these differences:
-//  * K per stage is 256 elements (128 bytes of packed fp4) = four
-//    tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X (K = 64).
+// Same skeleton as gemm_kernel (2-CTA clusters, TMA ring, one MMA thread, eight epilogue
+// warps) with these differences:
+//  * 256 x 256 tile per cluster, one accumulator.  K per stage is 256 elements (128 bytes
+//    of packed fp4) = four tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X
+//    (K = 64), 512 tensor-core cycles.
 //  * Every stage also carries scale factors: 2 KiB for this CTA's 128 rows of A
 //    and 4 KiB for all 256 columns of B (each CTA of the pair needs B's scales for
 //    the whole tile), pre-arranged in global memory in the order tensor memory
@@ -429,22 +499,42 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
 //  * Twelve such copies are needed per stage.  Issued by the MMA thread they sit
 //    in front of the stage's MMAs and cost ~50 ns each (measured: 3.1 PFLOPS
 //    against 5.4 with the copies removed); a copy is mostly issue latency of the
-//    issuing thread, so four dedicated threads (warps 6-9 of the leader CTA) issue
+//    issuing thread, so four dedicated threads (warps 10-13 of the leader CTA) issue
 //    three each, run ahead of the MMA thread by up to the pipeline depth and hand
-//    over through an mbarrier (tcgen05.commit): 4.65 PFLOPS.  Writing the factors
-//    through registers (tcgen05.st from both CTAs) was tried and is slower: the
-//    per-stage cross-CTA mbarrier arrive costs about a microsecond.
+//    over through an mbarrier (tcgen05.commit).  Writing the factors through
+//    registers (tcgen05.st from both CTAs) was tried and is slower: the per-stage
+//    cross-CTA mbarrier arrive costs about a microsecond.
+//  * Two producer threads per CTA, each with its own barriers: one loads the A and B
+//    tiles (full / empty), one the scale factors (sf_full; their shared-memory area is
+//    free again at sf_ready of the previous round, before that round's MMAs have even
+//    run).  A thread issues a TMA load about every 130 cycles, so four loads per
+//    512-cycle stage from one thread paced the whole kernel; and the copies to tensor
+//    memory now start when the 6 KiB of factors have landed instead of after the 64 KiB
+//    of tiles.
 //  * Tensor memory: accumulator in columns [0,256), then one 48-column scale area
 //    per pipeline stage (16 columns A, 32 columns B).  No room is left for a second
-//    accumulator, so a tile's epilogue is not overlapped with the next main loop.
+//    accumulator, so a tile's epilogue is not overlapped with the next main loop; the
+//    epilogue therefore reads all of its columns and releases tensor memory before it
+//    writes anything out (drain_warp_tile_early).
 //  * MXFP4 (MX = true: kind::mxf4.block_scale.scale_vec::2X, one ue8m0 scale per 32
 //    elements) has two factors per row per instruction, so one 32-bit word serves
 //    two instructions: the instruction descriptor's scale-factor id picks bytes 0-1
 //    or 2-3.  Half the blocks (2 of A + 4 of B per stage), half the copies.
+//  * What bounds it.  The ring holds five stages = 2560 tensor-core cycles of work, and a
+//    stage's round trip (MMAs retire -> empty -> producer -> TMA through L2, ~1700
+//    cycles under load -> full -> MMA thread) is about that long, so the tensor pipe
+//    runs dry for part of every stage: 64-72 % of cycles busy.  Shared memory (227 KiB)
+//    and tensor memory (512 columns) are both full, so the ring cannot be deepened, and a
+//    512 x 256 tile (which is what gives the dense kernel 1024 cycles per stage) would
+//    need all 512 columns for accumulators.  Tried and measured without effect:
+//    halving the operand bytes per stage (as sharing B between two clusters by
+//    multicast would; 4-6 %), an L2 prefetch cursor ahead of the loads (slower), parked
+//    mbarrier waits, one polling lane per epilogue warp, and letting the copies queue
+//    behind issued rather than retired MMAs.
 
 constexpr int kNvStages = 5;
 constexpr int kNvCopyThreads = 4;
-constexpr int kNvGemmThreads = 32 * (2 + kEpilogueWarps + kNvCopyThreads);    // producer, MMA, 8 epilogue, 4 scale-copy warps
+constexpr int kNvGemmThreads = 32 * (3 + kEpilogueWarps + kNvCopyThreads);    // operand producer, MMA, 8 epilogue, 4 scale-copy warps, scale producer
 constexpr uint32_t kSfaStageBytes = 2048;
 constexpr uint32_t kSfbStageBytes = 4096;
 constexpr uint32_t kNvStageBytes = kStageBytes + kSfaStageBytes + kSfbStageBytes;     // 38 KiB
@@ -459,9 +549,10 @@ template <bool MX> struct BlockScaled {
 };
 
 struct NvGemmSmem {
-    uint64_t full[kNvStages];        // tiles and scale factors of both CTAs landed (leader's barrier)
+    uint64_t full[kNvStages];        // operand tiles of both CTAs landed (leader's barrier)
+    uint64_t sf_full[kNvStages];     // scale factors of both CTAs landed (leader's barrier)
     uint64_t empty[kNvStages];       // the stage's MMAs retired (both CTAs)
-    uint64_t sf_ready[kNvStages];    // the stage's scale factors are in tensor memory (leader)
+    uint64_t sf_ready[kNvStages];    // the stage's scale factors are in tensor memory (both CTAs)
     uint64_t tmem_full;
     uint64_t tmem_empty;
     uint32_t tmem_base;
@@ -521,6 +612,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
     if (threadIdx.x == 0) {
         for (int s = 0; s < kNvStages; s++) {
             mbar_init(&sh->full[s], 1);
+            mbar_init(&sh->sf_full[s], 1);
             mbar_init(&sh->empty[s], 1);
             mbar_init(&sh->sf_ready[s], kNvCopyThreads);
         }
@@ -540,10 +632,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
     cluster_sync();
     tc_fence_after_sync();
     const uint32_t tmem = sh->tmem_base;
+    using BS = BlockScaled<MX>;
+    constexpr int kScaleProducerWarp = 2 + kEpilogueWarps + kNvCopyThreads;
 
     if (warp == 0) {
-        // ---------------- TMA producer ----------------
+        // ---------------- operand producer (both CTAs): A and B tiles ----------------
+        // One thread can issue about one TMA load per 130 cycles; with the two scale loads as
+        // well, four per 512-cycle stage held the whole kernel back, so those have a thread of
+        // their own (below).
         if (lane == 0) {
+            uint32_t full_at[kNvStages];
+#pragma unroll
+            for (int s = 0; s < kNvStages; s++)
+                full_at[s] = leader_addr(&sh->full[s]);
             uint32_t it = 0;
             bool ok = true, aligned = p.wave_sync != nullptr;
             for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters) {
@@ -562,17 +663,43 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
                         break;
                     }
                     uint8_t *st = smem + (size_t)s * kNvStageBytes;
-                    using BS = BlockScaled<MX>;
                     if (rank == 0)
-                        mbar_expect_tx(&sh->full[s], 2 * (kStageBytes + BS::sf_bytes));
-                    // scale factors first: they still have to be copied on to tensor memory
-                    tma_load_pair(st + kStageBytes, &tmap_sfa, 0,
-                                  (int32_t)((((mb * 2 + rank) * p.k_blocks) + kb) * BS::a_blocks), &sh->full[s]);
-                    tma_load_pair(st + kStageBytes + BS::a_blocks * 512, &tmap_sfb, 0,
-                                  (int32_t)(((nb * p.k_blocks) + kb) * BS::b_blocks), &sh->full[s]);
+                        mbar_expect_tx(&sh->full[s], 2 * kStageBytes);
                     const int32_t x = (int32_t)(kb * kRowBytesK);
-                    tma_load_pair(st, &tmap_a, x, row_a, &sh->full[s]);
-                    tma_load_pair(st + kHalfTileBytes, &tmap_b, x, row_b, &sh->full[s]);
+                    tma_load_pair_at(st, &tmap_a, x, row_a, full_at[s]);
+                    tma_load_pair_at(st + kHalfTileBytes, &tmap_b, x, row_b, full_at[s]);
+                }
+            }
+        }
+    } else if (warp == kScaleProducerWarp) {
+        // ---------------- scale-factor producer (both CTAs) ----------------
+        // The stage's scale area in shared memory is free again once the previous round's
+        // copies to tensor memory have completed, which is what sf_ready says.
+        if (lane == 0) {
+            uint32_t sf_full_at[kNvStages];
+#pragma unroll
+            for (int s = 0; s < kNvStages; s++)
+                sf_full_at[s] = leader_addr(&sh->sf_full[s]);
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters) {
+                uint32_t mb, nb;
+                tile_coords(tile, tiles_m, tiles_n, mb, nb);
+                const uint32_t sfa_block0 = (mb * 2 + rank) * p.k_blocks * BS::a_blocks;
+                const uint32_t sfb_block0 = nb * p.k_blocks * BS::b_blocks;
+                for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
+                    const uint32_t s = it % kNvStages, round = it / kNvStages;
+                    if (round > 0 && !mbar_wait(&sh->sf_ready[s], (round - 1) & 1)) {
+                        atomicCAS(p.status, 0u, 0x216u);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t *sf = smem + (size_t)s * kNvStageBytes + kStageBytes;
+                    if (rank == 0)
+                        mbar_expect_tx(&sh->sf_full[s], 2 * BS::sf_bytes);
+                    tma_load_pair_at(sf, &tmap_sfa, 0, (int32_t)(sfa_block0 + kb * BS::a_blocks), sf_full_at[s]);
+                    tma_load_pair_at(sf + BS::a_blocks * 512, &tmap_sfb, 0, (int32_t)(sfb_block0 + kb * BS::b_blocks),
+                                     sf_full_at[s]);
                 }
             }
         }
@@ -592,8 +719,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
                 tc_fence_after_sync();
                 for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
                     const uint32_t s = it % kNvStages, round = it / kNvStages;
-                    // sf_ready implies full: the copy threads waited for the stage before copying
-                    if (!mbar_wait(&sh->sf_ready[s], round & 1)) {
+                    // the scale factors usually arrive first (6 KiB against 64): wait for them, then the tiles
+                    if (!mbar_wait(&sh->sf_ready[s], round & 1) || !mbar_wait(&sh->full[s], round & 1)) {
                         atomicCAS(p.status, 0u, 0x213u);
                         ok = false;
                         break;
@@ -627,7 +754,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
             for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters) {
                 for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
                     const uint32_t s = it % kNvStages, round = it / kNvStages;
-                    if (!mbar_wait(&sh->full[s], round & 1)) {
+                    // the factors have landed, and the MMAs that read this stage's tensor-memory
+                    // columns in the previous round have retired
+                    if (!mbar_wait(&sh->sf_full[s], round & 1) ||
+                        (round > 0 && !mbar_wait(&sh->empty[s], (round - 1) & 1))) {
                         atomicCAS(p.status, 0u, 0x215u);
                         ok = false;
                         break;
@@ -636,20 +766,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
                     const uint32_t sf_s = smem_u32(smem + (size_t)s * kNvStageBytes) + kStageBytes;
                     const uint32_t sf_t = tmem + kNvSfCol + s * kNvSfColsPerStage;
                     // 512-byte blocks of the stage: A's (4 columns each, from column 0), then B's (from column 16)
-                    using BS = BlockScaled<MX>;
                     for (uint32_t blk = me; blk < BS::blocks; blk += kNvCopyThreads) {
                         const uint32_t col = blk < BS::a_blocks ? 4 * blk : 16 + 4 * (blk - BS::a_blocks);
                         tmem_cp_32x128b_warpx4<2>(sf_t + col, make_smem_desc(sf_s + blk * 512, 16, 128, kSwizzleNone));
                     }
-                    // arrives on sf_ready[s] (this CTA) when the copies above have completed in both CTAs
-                    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                                     smem_u32(&sh->sf_ready[s]))
-                                 : "memory");
+                    // arrives on sf_ready[s] in both CTAs when the copies above have completed in both
+                    tc_commit_pair(&sh->sf_ready[s], 3);
                 }
             }
         }
     } else {
-        // ---------------- epilogue warps (as in the dense kernel, one row block) ----------------
+        // ---------------- epilogue warps: one row block, tensor memory released before the stores ----------------
         const uint32_t q = (uint32_t)(warp & 3);
         const uint32_t col_half = (uint32_t)(warp - 2) >> 2;
         uint8_t *box = staging + (size_t)(warp - 2) * kStagingBytes;
@@ -663,8 +790,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
                 break;
             }
             tc_fence_after_sync();
-            drain_warp_tile<CLPK_DT_NVF4>(tmem + col_half * 128 + ((q * 32) << 16), 1, mb * kTileMN + rank * 128 + q * 32,
-                                          nb * kTileMN + col_half * 128, box, &tmap_c, p.alpha, &sh->tmem_empty, lane);
+            drain_warp_tile_early(tmem + col_half * 128 + ((q * 32) << 16), mb * kTileMN + rank * 128 + q * 32,
+                                  nb * kTileMN + col_half * 128, box, &tmap_c, p.alpha, &sh->tmem_empty, lane);
         }
         if (lane == 0)
             bulk_wait<0>();
@@ -846,6 +973,38 @@ int clpk_gemm_workspace_bytes(int dtype, uint32_t m, uint32_t n, uint32_t k, siz
     return CLPK_OK;
 }
 
+// Row-major scale bytes of both operands -> tile order in the workspace (A's blocks, then B's).
+static int pack_scales(const clpk_gemm_args_t *a, cudaStream_t s)
+{
+    const uint32_t words = a->dtype == CLPK_DT_MXF4 ? 2 : 4;   // 32-bit scale words per row per 256 elements of K
+    const size_t sfa_bytes = (size_t)a->m * (a->k / 256) * words * 4, sfb_bytes = (size_t)a->n * (a->k / 256) * words * 4;
+    CLPK_REQUIRE(a->d_sfa && a->d_sfb, "block-scaled FP4 needs d_sfa and d_sfb");
+    CLPK_REQUIRE(a->d_workspace && a->workspace_bytes >= sfa_bytes + sfb_bytes && ((uintptr_t)a->d_workspace % 16) == 0,
+                 "block-scaled FP4 needs a 16-byte aligned workspace of clpk_gemm_workspace_bytes() bytes");
+    CLPK_REQUIRE(((uintptr_t)a->d_sfa % 4) == 0 && ((uintptr_t)a->d_sfb % 4) == 0, "scale arrays must be 4-byte aligned");
+    uint8_t *wsa = static_cast<uint8_t *>(a->d_workspace), *wsb = wsa + sfa_bytes;
+    const uint32_t words_per_row = a->k / 256 * words, kblocks = a->k / 256;
+    const dim3 ga((words_per_row + 31) / 32, a->m / 128), gb((words_per_row + 31) / 32, a->n / 128);
+    pack_scales_kernel<<<ga, 256, 0, s>>>(reinterpret_cast<uint32_t *>(wsa), static_cast<const uint32_t *>(a->d_sfa),
+                                          words_per_row, kblocks, 0, words);
+    pack_scales_kernel<<<gb, 256, 0, s>>>(reinterpret_cast<uint32_t *>(wsb), static_cast<const uint32_t *>(a->d_sfb),
+                                          words_per_row, kblocks, 1, words);
+    CLPK_LAUNCH_CHECK("pack_scales");
+    return CLPK_OK;
+}
+
+int clpk_gemm_pack_scales(const clpk_gemm_args_t *a, void *stream)
+{
+    int rc = require_sm100();
+    if (rc != CLPK_OK)
+        return rc;
+    CLPK_REQUIRE(a, "args is NULL");
+    CLPK_REQUIRE(a->dtype == CLPK_DT_NVF4 || a->dtype == CLPK_DT_MXF4, "only the block-scaled FP4 kinds have scales to pack");
+    CLPK_REQUIRE(a->m % 256 == 0 && a->n % 256 == 0 && a->m > 0 && a->n > 0 && a->k > 0 && a->k % 256 == 0,
+                 "M, N multiples of 256 and K a multiple of 256 (got %u, %u, %u)", a->m, a->n, a->k);
+    return pack_scales(a, as_stream(stream));
+}
+
 int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
 {
     int rc = require_sm100();
@@ -913,18 +1072,15 @@ int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
         const bool mx = a->dtype == CLPK_DT_MXF4;
         const uint32_t words = mx ? 2 : 4;                      // 32-bit scale words per row per 256 elements of K
         const size_t sfa_bytes = (size_t)a->m * (a->k / 256) * words * 4, sfb_bytes = (size_t)a->n * (a->k / 256) * words * 4;
-        CLPK_REQUIRE(a->d_sfa && a->d_sfb, "block-scaled FP4 needs d_sfa and d_sfb");
+        CLPK_REQUIRE((a->d_sfa != nullptr) == (a->d_sfb != nullptr), "d_sfa and d_sfb: give both, or neither when the workspace is already packed");
         CLPK_REQUIRE(a->d_workspace && a->workspace_bytes >= sfa_bytes + sfb_bytes && ((uintptr_t)a->d_workspace % 16) == 0,
                      "block-scaled FP4 needs a 16-byte aligned workspace of clpk_gemm_workspace_bytes() bytes");
         uint8_t *wsa = static_cast<uint8_t *>(a->d_workspace), *wsb = wsa + sfa_bytes;
-        CLPK_REQUIRE(((uintptr_t)a->d_sfa % 4) == 0 && ((uintptr_t)a->d_sfb % 4) == 0, "scale arrays must be 4-byte aligned");
-        const uint32_t words_per_row = a->k / 256 * words, kblocks = a->k / 256;
-        const dim3 ga((words_per_row + 31) / 32, a->m / 128), gb((words_per_row + 31) / 32, a->n / 128);
-        pack_scales_kernel<<<ga, 256, 0, s>>>(reinterpret_cast<uint32_t *>(wsa), static_cast<const uint32_t *>(a->d_sfa),
-                                              words_per_row, kblocks, 0, words);
-        pack_scales_kernel<<<gb, 256, 0, s>>>(reinterpret_cast<uint32_t *>(wsb), static_cast<const uint32_t *>(a->d_sfb),
-                                              words_per_row, kblocks, 1, words);
-        CLPK_LAUNCH_CHECK("pack_scales");
+        if (a->d_sfa) {
+            rc = pack_scales(a, s);
+            if (rc != CLPK_OK)
+                return rc;
+        }
         CUtensorMap tsa, tsb;
         rc = make_scale_map(&tsa, wsa, sfa_bytes / 512, words);
         if (rc != CLPK_OK)

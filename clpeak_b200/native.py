@@ -133,6 +133,7 @@ KERNEL_API = {
     "clpk_mma_flops_per_instr": [_i],
     "clpk_gemm_workspace_bytes": [_i, _u32, _u32, _u32, C.POINTER(C.c_size_t)],
     "clpk_gemm": [C.POINTER(GemmArgs), _vp],
+    "clpk_gemm_pack_scales": [C.POINTER(GemmArgs), _vp],
 }
 _RESTYPES = {
     "clpk_last_error": C.c_char_p,

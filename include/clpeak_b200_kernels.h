@@ -361,7 +361,12 @@ CLPK_API double clpk_mma_flops_per_instr(int kind);
  * FP4 kinds: d_a/d_b are packed e2m1 (K/2 bytes per row); d_sfa/d_sfb are the
  * scale bytes row-major [rows][K/16] (NVF4) or [rows][K/32] (MXF4) as written by
  * clpk_quantize_fp4; the call repacks them into the tensor-core tile order in
- * d_workspace (clpk_gemm_workspace_bytes) before the main kernel. */
+ * d_workspace (clpk_gemm_workspace_bytes) before the main kernel.  Operands that
+ * are multiplied more than once can be repacked once: clpk_gemm_pack_scales does
+ * only the repack (same arguments; d_a, d_b, d_c, d_status unused), and a
+ * clpk_gemm call with d_sfa = d_sfb = NULL takes the workspace as already packed
+ * -- the position cuBLASLt puts its caller in, whose scale arrays must arrive
+ * in tile order (src/cuda/cuda_blas.cpp:456-491 fills them once, before timing). */
 typedef struct clpk_gemm_args {
     int         dtype;
     uint32_t    m, n, k;
@@ -377,6 +382,7 @@ typedef struct clpk_gemm_args {
 } clpk_gemm_args_t;
 
 CLPK_API int clpk_gemm_workspace_bytes(int dtype, uint32_t m, uint32_t n, uint32_t k, size_t *bytes);
+CLPK_API int clpk_gemm_pack_scales(const clpk_gemm_args_t *args, void *stream);
 CLPK_API int clpk_gemm(const clpk_gemm_args_t *args, void *stream);
 
 #ifdef __cplusplus

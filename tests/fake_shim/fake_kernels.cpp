@@ -485,5 +485,6 @@ int clpk_mma_peak(const clpk_mma_peak_args_t *a, void *)
 
 int clpk_gemm_workspace_bytes(int, uint32_t, uint32_t, uint32_t, size_t *bytes) { *bytes = 0; return CLPK_OK; }
 int clpk_gemm(const clpk_gemm_args_t *, void *) { return fail(CLPK_ERR_UNSUPPORTED, "the fake shim has no GEMM"); }
+int clpk_gemm_pack_scales(const clpk_gemm_args_t *, void *) { return fail(CLPK_ERR_UNSUPPORTED, "the fake shim has no GEMM"); }
 
 } // extern "C"

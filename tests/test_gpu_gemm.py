@@ -186,6 +186,36 @@ def test_gemm_nvfp4_tracks_the_unquantised_product(K, orc, cuda, dtype):
     assert np.corrcoef(ref.ravel(), got.ravel())[0, 1] > 0.98
 
 
+@pytest.mark.parametrize("dtype", [N.DT_NVF4, N.DT_MXF4])
+def test_gemm_fp4_scales_packed_once_give_the_same_bits(K, cuda, dtype):
+    """clpk_gemm_pack_scales + clpk_gemm(d_sfa = d_sfb = NULL) is the one-call path split in two."""
+    m, n, k = 512, 768, 1024
+    r = run_nvfp4(K, cuda, m, n, k, dtype)
+    a, sfa, tsa, _ = make_nvfp4_operand(K, cuda, m, k, 40, dtype)
+    b, sfb, tsb, _ = make_nvfp4_operand(K, cuda, n, k, 41, dtype)
+    need = C.c_size_t(0)
+    K.clpk_gemm_workspace_bytes(dtype, m, n, k, C.byref(need))
+    ws = dev_empty(need.value, cuda.uint8)
+    st = dev_empty(1, cuda.int32)
+    c = cuda.full((m * n,), 0x7FC0, dtype=cuda.int16, device="cuda")
+    args = N.GemmArgs(dtype=dtype, m=m, n=n, k=k, d_a=a.data_ptr(), d_b=b.data_ptr(), d_c=c.data_ptr(),
+                      d_sfa=sfa.data_ptr(), d_sfb=sfb.data_ptr(), alpha=r["alpha"], d_workspace=ws.data_ptr(),
+                      workspace_bytes=need.value, d_status=st.data_ptr())
+    K.clpk_gemm_pack_scales(C.byref(args), stream_ptr())
+    args.d_sfa = None
+    args.d_sfb = None
+    for _ in range(2):                              # the packed workspace is not consumed by a call
+        c.fill_(0x7FC0)
+        K.clpk_gemm(C.byref(args), stream_ptr())
+        sync()
+        assert int(to_np(st)[0]) == 0
+        assert np.array_equal(to_np(c).view(np.uint16), r["c"])
+    args.d_sfa = sfa.data_ptr()                     # one scale array without the other is an error
+    with pytest.raises(N.ClpkError) as e:
+        K.clpk_gemm(C.byref(args), stream_ptr())
+    assert e.value.code == N.ERR_BAD_ARG
+
+
 def test_gemm_nvfp4_argument_checks(K, cuda):
     d = dev_empty(64, cuda.uint8)
     args = N.GemmArgs(dtype=N.DT_NVF4, m=256, n=256, k=128, d_a=d.data_ptr(), d_b=d.data_ptr(), d_c=d.data_ptr(),
