@@ -516,12 +516,13 @@ def main():
                      "frac_of_spec": achieved / SPEC["hbm_gbs"], "traffic": ncu_traffic(kernel_symbol)},
         "cpu_baseline": ({"value": cpu["value"], "unit": UNIT, "cores": cpu["cores"], "kind": cpu["kind"],
                           "sample": cpu["sample"], "rows": cpu["rows"],
-                          "other_reference_cpu_rows": (run_reference_cpu_pairs(500) if not args.no_rows else None)}
+                          "other_reference_cpu_rows": (run_reference_cpu_pairs(500) if not args.no_rows else None),
+                          # the same baseline leg also times the reference's own CUDA kernels on this GPU
+                          "reference_cuda_kernels_on_this_gpu": (run_reference_cuda_kernels(200000)
+                                                                 if not args.no_rows else None)}
                          if cpu else None),
         "e2e": e2e, "gpu_launches": 3 * args.steps, "clocks": clocks, "read_checksum": read_xor,
         "rows": rows, "spec_peaks_per_gpu": SPEC,
-        "reference_cuda_kernels_on_this_gpu": (run_reference_cuda_kernels(200000)
-                                                if world == 1 and not args.no_rows else None),
     }
     print(json.dumps(line), flush=True)
     reps.close()
