@@ -428,6 +428,37 @@ def main():
     # checksum of the step's result vs a second, independent pass (copy then read-back XOR)
     read_xor = int(np.bitwise_xor.reduce(parts[:grids[variant["read"]]].cpu().numpy().view(np.uint32)))
 
+    # ---- the timed kernels' results at full size, against torch's own elementwise kernels (untimed) ----
+    def xor_words(t):
+        x = t.view(torch.int64)
+        while x.numel() > 1:
+            h = x.numel() // 2
+            y = x[:h] ^ x[h:2 * h]
+            if x.numel() & 1:
+                y[0] ^= x[-1]
+            x = y
+        w = int(x.item()) & 0xFFFFFFFFFFFFFFFF
+        return (w ^ (w >> 32)) & 0xFFFFFFFF
+
+    checks = {"read_checksum_equals_xor_of_b": read_xor == xor_words(b)}
+    ops["copy"](variant["copy"])
+    torch.cuda.synchronize()
+    checks["copy_equals_source_bitwise"] = bool(torch.equal(a.view(torch.int32), c.view(torch.int32)))
+    ops["triad"](variant["triad"])
+    torch.cuda.synchronize()
+    ok = True
+    piece = 1 << 28                                   # 1 GiB of floats at a time
+    for off in range(0, n_floats, piece):
+        t = c[off:off + piece] * 1.5                  # separate multiply and add, as the kernel and the oracle do
+        t += b[off:off + piece]
+        ok = ok and bool(torch.equal(t.view(torch.int32), a[off:off + piece].view(torch.int32)))
+        del t
+    checks["triad_equals_b_plus_s_times_c_bitwise"] = ok
+    checks["elements_per_array"] = n_floats
+    failed = reps.max_over_ranks(0.0 if all(v for k, v in checks.items() if k != "elements_per_array") else 1.0)
+    checks["all_ranks"] = failed == 0.0
+    torch.cuda.empty_cache()
+
     # ---- end to end: host buffers through the C ABI -------------------------------------------
     e2e = None
     if not args.no_e2e:
@@ -521,7 +552,7 @@ def main():
                           "reference_cuda_kernels_on_this_gpu": (run_reference_cuda_kernels(200000)
                                                                  if not args.no_rows else None)}
                          if cpu else None),
-        "e2e": e2e, "gpu_launches": 3 * args.steps, "clocks": clocks, "read_checksum": read_xor,
+        "e2e": e2e, "gpu_launches": 3 * args.steps, "clocks": clocks, "read_checksum": read_xor, "verified_at_full_size": checks,
         "rows": rows, "spec_peaks_per_gpu": SPEC,
     }
     print(json.dumps(line), flush=True)

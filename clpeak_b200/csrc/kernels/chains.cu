@@ -1,4 +1,6 @@
 // fp32 multiply-add chains, the pointer chase and the launch-latency probe.
+#include <cuda.h>
+
 #include <chrono>
 #include <random>
 #include <vector>
@@ -144,26 +146,84 @@ int clpk_launch_noop(void *stream)
     return CLPK_OK;
 }
 
+// The reference times cuLaunchKernel + cuStreamSynchronize (src/cuda/kernel_latency.cpp:44-63),
+// i.e. the driver's own launch without the runtime's <<<>>> layer on top.  The same two
+// driver entry points are looked up through the runtime here (nothing links libcuda); if the
+// lookup fails the runtime launch is timed instead.
+namespace {
+typedef CUresult (*DrvLaunch)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
+                              void **, void **);
+typedef CUresult (*DrvSync)(CUstream);
+
+struct DriverLaunch {
+    DrvLaunch launch = nullptr;
+    DrvSync sync = nullptr;
+    CUfunction fn = nullptr;
+    bool ok = false;
+};
+
+DriverLaunch driver_launch_of_noop()
+{
+    DriverLaunch d;
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuLaunchKernel", &sym, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+        return d;
+    d.launch = reinterpret_cast<DrvLaunch>(sym);
+    if (cudaGetDriverEntryPoint("cuStreamSynchronize", &sym, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+        return d;
+    d.sync = reinterpret_cast<DrvSync>(sym);
+    cudaFunction_t f = nullptr;
+    if (cudaGetFuncBySymbol(&f, reinterpret_cast<const void *>(clpk::noop_kernel)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return d;
+    }
+    d.fn = reinterpret_cast<CUfunction>(f);
+    d.ok = d.launch && d.sync && d.fn;
+    return d;
+}
+} // namespace
+
 int clpk_launch_latency(uint32_t iters, uint32_t warmup, double *mean_us, void *stream)
 {
     CLPK_REQUIRE(mean_us && iters > 0, "bad arguments");
     cudaStream_t s = as_stream(stream);
-    for (uint32_t w = 0; w < warmup; w++) {
-        noop_kernel<<<1, 1, 0, s>>>();
-        CLPK_LAUNCH_CHECK("noop");
-        CLPK_CUDA(cudaStreamSynchronize(s));
-    }
-    double total_ns = 0.0;
-    for (uint32_t i = 0; i < iters; i++) {
-        const auto t0 = std::chrono::steady_clock::now();
+    const DriverLaunch drv = driver_launch_of_noop();
+    void *no_args[1] = {nullptr};
+    // returns 0 on success; the launch and the wait, exactly what is timed
+    auto once = [&](const char **what, cudaError_t *rt) -> int {
+        if (drv.ok) {
+            const CUresult lr = drv.launch(drv.fn, 1, 1, 1, 1, 1, 1, 0, reinterpret_cast<CUstream>(s), no_args, nullptr);
+            const CUresult sr = drv.sync(reinterpret_cast<CUstream>(s));
+            if (lr != CUDA_SUCCESS || sr != CUDA_SUCCESS) {
+                *what = lr != CUDA_SUCCESS ? "cuLaunchKernel" : "cuStreamSynchronize";
+                *rt = cudaErrorUnknown;
+                return 1;
+            }
+            return 0;
+        }
         noop_kernel<<<1, 1, 0, s>>>();
         const cudaError_t le = cudaGetLastError();
         const cudaError_t se = cudaStreamSynchronize(s);
+        if (le != cudaSuccess || se != cudaSuccess) {
+            *what = le != cudaSuccess ? "launch noop" : "cudaStreamSynchronize";
+            *rt = le != cudaSuccess ? le : se;
+            return 1;
+        }
+        return 0;
+    };
+    const char *what = "";
+    cudaError_t rt = cudaSuccess;
+    for (uint32_t w = 0; w < warmup; w++)
+        if (once(&what, &rt))
+            return cuda_fail(rt, what);
+    double total_ns = 0.0;
+    for (uint32_t i = 0; i < iters; i++) {
+        const auto t0 = std::chrono::steady_clock::now();
+        const int bad = once(&what, &rt);
         const auto t1 = std::chrono::steady_clock::now();
-        if (le != cudaSuccess)
-            return cuda_fail(le, "launch noop");
-        if (se != cudaSuccess)
-            return cuda_fail(se, "cudaStreamSynchronize");
+        if (bad)
+            return cuda_fail(rt, what);
         total_ns += (double)std::chrono::duration_cast<std::chrono::nanoseconds>(t1 - t0).count();
     }
     *mean_us = total_ns / 1000.0 / (double)iters;
