@@ -127,6 +127,18 @@ __device__ __forceinline__ uint32_t leader_addr(const void *p)
     return a;
 }
 
+// Roles that issue TMA or tcgen05 instructions run their loops with the whole warp and let
+// one elected lane issue.  Addresses and descriptors are then warp-uniform values, which is
+// what those instructions take.  With the loop inside `if (lane == 0)` each instruction cost
+// its thread 110-130 cycles (measured with clock64 around it: four MMAs 460 cycles, against
+// 115 this way), and a thread that must issue four MMAs and a commit per 512 tensor-core
+// cycles, or eight and a commit per 1024, was the slowest stage of the pipeline.
+// warp_wait: every lane waits; the verdict is made uniform so that the warp stays together.
+__device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity)
+{
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity) ? 1 : 0) != 0;
+}
+
 // DT: BF16 / F16 -> kind::f16 (K = 16 per instruction); E4M3 / E5M2 -> kind::f8f6f4 (K = 32);
 // TF32 -> kind::tf32 (K = 8, fp32 out); I8 -> kind::i8 (K = 32, int32 out).  Always 128 bytes of K per stage.
 //
@@ -368,7 +380,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
-        if (lane == 0) {
+        {
+            const uint32_t full0 = leader_addr(&sh->full[0]);      // barriers are 8 bytes apart
             uint32_t it = 0;
             bool ok = true, aligned = p.wave_sync != nullptr;
             for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters) {
@@ -380,27 +393,34 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
                 // before: the MMA thread then has work while the slowest producer arrives.
                 const uint32_t align_at = p.k_blocks > p.align_at ? p.align_at : 0u;
                 for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
-                    if (kb == align_at)
-                        wave_align(p, tile / n_clusters, n_tiles, n_clusters, aligned);
+                    if (kb == align_at) {
+                        if (lane == 0)
+                            wave_align(p, tile / n_clusters, n_tiles, n_clusters, aligned);
+                        aligned = __shfl_sync(0xffffffffu, aligned ? 1 : 0, 0) != 0;
+                    }
                     const uint32_t s = it % kDenseStages, round = it / kDenseStages;
-                    if (round > 0 && !mbar_wait(&sh->empty[s], (round - 1) & 1)) {
-                        atomicCAS(p.status, 0u, 0x201u);
+                    if (round > 0 && !warp_wait(&sh->empty[s], (round - 1) & 1)) {
+                        if (lane == 0)
+                            atomicCAS(p.status, 0u, 0x201u);
                         ok = false;
                         break;
                     }
                     uint8_t *st = smem + (size_t)s * kDenseStageBytes;
-                    if (rank == 0)
-                        mbar_expect_tx(&sh->full[s], 2 * kDenseStageBytes);
                     const int32_t x = (int32_t)(kb * p.k_block_elems);
-                    tma_load_pair(st, &tmap_a, x, row_a0, &sh->full[s]);
-                    tma_load_pair(st + kHalfTileBytes, &tmap_a, x, row_a0 + 256, &sh->full[s]);
-                    tma_load_pair(st + 2 * kHalfTileBytes, &tmap_b, x, row_b, &sh->full[s]);
+                    if (elect_one()) {
+                        if (rank == 0)
+                            mbar_expect_tx(&sh->full[s], 2 * kDenseStageBytes);
+                        tma_load_pair_at(st, &tmap_a, x, row_a0, full0 + 8 * s);
+                        tma_load_pair_at(st + kHalfTileBytes, &tmap_a, x, row_a0 + 256, full0 + 8 * s);
+                        tma_load_pair_at(st + 2 * kHalfTileBytes, &tmap_b, x, row_b, full0 + 8 * s);
+                    }
+                    __syncwarp();
                 }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer (leader CTA) ----------------
-        if (rank == 0 && lane == 0) {
+        if (rank == 0) {
             constexpr uint32_t kAFmt = DT == CLPK_DT_BF16 ? kFmtBF16 : DT == CLPK_DT_F16 ? kFmtF16 : DT == CLPK_DT_TF32 ? kFmtTF32
                                      : DT == CLPK_DT_I8 ? kFmtS8 : DT == CLPK_DT_E5M2 ? kFmtE5M2 : kFmtE4M3;
             // the E5M2 variant multiplies e5m2 A by e4m3 B (the pairing the reference's fp8_e5m2 row uses)
@@ -409,42 +429,48 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
             uint32_t it = 0, tcount = 0;
             bool ok = true;
             for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters, tcount++) {
-                if (tcount > 0 && !mbar_wait(&sh->tmem_empty, (tcount - 1) & 1)) {
-                    atomicCAS(p.status, 0u, 0x202u);
+                if (tcount > 0 && !warp_wait(&sh->tmem_empty, (tcount - 1) & 1)) {
+                    if (lane == 0)
+                        atomicCAS(p.status, 0u, 0x202u);
                     break;
                 }
                 tc_fence_after_sync();
                 for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
                     const uint32_t s = it % kDenseStages, round = it / kDenseStages;
-                    if (!mbar_wait(&sh->full[s], round & 1)) {
-                        atomicCAS(p.status, 0u, 0x203u);
+                    if (!warp_wait(&sh->full[s], round & 1)) {
+                        if (lane == 0)
+                            atomicCAS(p.status, 0u, 0x203u);
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
                     const uint32_t base = smem_u32(smem + (size_t)s * kDenseStageBytes);
                     const uint64_t bd = make_smem_desc(base + 2 * kHalfTileBytes, 16, 1024, kSwizzle128B);
+                    if (elect_one()) {
 #pragma unroll
-                    for (uint32_t h = 0; h < 2; h++) {
-                        const uint64_t ad = make_smem_desc(base + h * kHalfTileBytes, 16, 1024, kSwizzle128B);
-                        const uint32_t d = tmem + h * 256;
+                        for (uint32_t h = 0; h < 2; h++) {
+                            const uint64_t ad = make_smem_desc(base + h * kHalfTileBytes, 16, 1024, kSwizzle128B);
+                            const uint32_t d = tmem + h * 256;
 #pragma unroll
-                        for (uint32_t kk = 0; kk < 4; kk++) {
-                            // +32 bytes of K per instruction: +2 in the (>>4) address field
-                            if constexpr (DT == CLPK_DT_E4M3 || DT == CLPK_DT_E5M2)
-                                mma2_f8f6f4_ss(d, ad + 2 * kk, bd + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
-                            else if constexpr (DT == CLPK_DT_TF32)
-                                mma2_tf32_ss(d, ad + 2 * kk, bd + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
-                            else if constexpr (DT == CLPK_DT_I8)
-                                mma2_i8_ss(d, ad + 2 * kk, bd + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
-                            else
-                                mma2_f16_ss(d, ad + 2 * kk, bd + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
+                            for (uint32_t kk = 0; kk < 4; kk++) {
+                                // +32 bytes of K per instruction: +2 in the (>>4) address field
+                                if constexpr (DT == CLPK_DT_E4M3 || DT == CLPK_DT_E5M2)
+                                    mma2_f8f6f4_ss(d, ad + 2 * kk, bd + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
+                                else if constexpr (DT == CLPK_DT_TF32)
+                                    mma2_tf32_ss(d, ad + 2 * kk, bd + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
+                                else if constexpr (DT == CLPK_DT_I8)
+                                    mma2_i8_ss(d, ad + 2 * kk, bd + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
+                                else
+                                    mma2_f16_ss(d, ad + 2 * kk, bd + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
+                            }
                         }
+                        tc_commit_pair(&sh->empty[s], 3);
                     }
-                    tc_commit_pair(&sh->empty[s], 3);
+                    __syncwarp();
                 }
-                if (ok)
+                if (ok && elect_one())
                     tc_commit_pair(&sh->tmem_full, 3);
+                __syncwarp();
             }
         }
     } else {
@@ -496,21 +522,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
 //    (r % 32) * 16 + (r / 32) * 4 + j for row r's j-th factor.  One
 //    tcgen05.cp.cta_group::2.32x128b.warpx4 per block copies it from shared to
 //    tensor memory in both CTAs (4 columns, replicated in the four lane quarters).
-//  * Twelve such copies are needed per stage.  Issued by the MMA thread they sit
-//    in front of the stage's MMAs and cost ~50 ns each (measured: 3.1 PFLOPS
-//    against 5.4 with the copies removed); a copy is mostly issue latency of the
-//    issuing thread, so four dedicated threads (warps 10-13 of the leader CTA) issue
-//    three each, run ahead of the MMA thread by up to the pipeline depth and hand
-//    over through an mbarrier (tcgen05.commit).  Writing the factors through
-//    registers (tcgen05.st from both CTAs) was tried and is slower: the per-stage
-//    cross-CTA mbarrier arrive costs about a microsecond.
-//  * Two producer threads per CTA, each with its own barriers: one loads the A and B
+//  * Twelve such copies are needed per stage.  They are issued by four dedicated warps
+//    (10-13 of the leader CTA, three copies each), which run ahead of the MMA warp by up
+//    to the pipeline depth and hand over through an mbarrier (tcgen05.commit), so that
+//    they never sit in front of a stage's MMAs.  Writing the factors through registers
+//    (tcgen05.st from both CTAs) was tried and is slower: the per-stage cross-CTA
+//    mbarrier arrive costs about a microsecond.
+//  * Two producer warps per CTA, each with its own barriers: one loads the A and B
 //    tiles (full / empty), one the scale factors (sf_full; their shared-memory area is
 //    free again at sf_ready of the previous round, before that round's MMAs have even
-//    run).  A thread issues a TMA load about every 130 cycles, so four loads per
-//    512-cycle stage from one thread paced the whole kernel; and the copies to tensor
-//    memory now start when the 6 KiB of factors have landed instead of after the 64 KiB
-//    of tiles.
+//    run), so the copies to tensor memory start when the 6 KiB of factors have landed
+//    instead of after the 64 KiB of tiles.
 //  * Tensor memory: accumulator in columns [0,256), then one 48-column scale area
 //    per pipeline stage (16 columns A, 32 columns B).  No room is left for a second
 //    accumulator, so a tile's epilogue is not overlapped with the next main loop; the
@@ -520,17 +542,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
 //    elements) has two factors per row per instruction, so one 32-bit word serves
 //    two instructions: the instruction descriptor's scale-factor id picks bytes 0-1
 //    or 2-3.  Half the blocks (2 of A + 4 of B per stage), half the copies.
-//  * What bounds it.  The ring holds five stages = 2560 tensor-core cycles of work, and a
-//    stage's round trip (MMAs retire -> empty -> producer -> TMA through L2, ~1700
-//    cycles under load -> full -> MMA thread) is about that long, so the tensor pipe
-//    runs dry for part of every stage: 64-72 % of cycles busy.  Shared memory (227 KiB)
-//    and tensor memory (512 columns) are both full, so the ring cannot be deepened, and a
-//    512 x 256 tile (which is what gives the dense kernel 1024 cycles per stage) would
-//    need all 512 columns for accumulators.  Tried and measured without effect:
-//    halving the operand bytes per stage (as sharing B between two clusters by
-//    multicast would; 4-6 %), an L2 prefetch cursor ahead of the loads (slower), parked
-//    mbarrier waits, one polling lane per epilogue warp, and letting the copies queue
-//    behind issued rather than retired MMAs.
+//  * What bounds it (clock64 counters in a trace build).  With every role issuing from a
+//    convergent warp the main loop runs at 530-560 cycles per 512-cycle stage; what is
+//    left is between tiles: the MMA warp waits about 3100 cycles per tile for tensor
+//    memory (the queued MMAs drain, tcgen05.commit reaches the epilogue, 128 KiB per CTA
+//    are read out at about 64 bytes per cycle, the release travels back), 7 % of a
+//    K = 16384 tile and 14 % of a K = 8192 one, and it cannot be overlapped without a
+//    second accumulator.  Tried and measured without effect: halving the operand bytes
+//    per stage (as sharing B between two clusters by multicast would; 4-6 %), an L2
+//    prefetch cursor ahead of the loads (slower), parked mbarrier waits, one polling lane
+//    per epilogue warp, and letting the copies queue behind issued rather than retired
+//    MMAs.
 
 constexpr int kNvStages = 5;
 constexpr int kNvCopyThreads = 4;
@@ -637,91 +659,98 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
 
     if (warp == 0) {
         // ---------------- operand producer (both CTAs): A and B tiles ----------------
-        // One thread can issue about one TMA load per 130 cycles; with the two scale loads as
-        // well, four per 512-cycle stage held the whole kernel back, so those have a thread of
-        // their own (below).
-        if (lane == 0) {
-            uint32_t full_at[kNvStages];
-#pragma unroll
-            for (int s = 0; s < kNvStages; s++)
-                full_at[s] = leader_addr(&sh->full[s]);
-            uint32_t it = 0;
-            bool ok = true, aligned = p.wave_sync != nullptr;
-            for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters) {
-                uint32_t mb, nb;
-                tile_coords(tile, tiles_m, tiles_n, mb, nb);
-                const int32_t row_a = (int32_t)(mb * kTileMN + rank * 128);
-                const int32_t row_b = (int32_t)(nb * kTileMN + rank * 128);
-                const uint32_t align_at = p.k_blocks > p.align_at ? p.align_at : 0u;
-                for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
-                    if (kb == align_at)
+        // The scale factors have a producer warp of their own (below): their copies on to tensor
+        // memory can then start when 6 KiB have landed instead of 70.
+        const uint32_t full0 = leader_addr(&sh->full[0]);          // barriers are 8 bytes apart
+        uint32_t it = 0;
+        bool ok = true, aligned = p.wave_sync != nullptr;
+        for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters) {
+            uint32_t mb, nb;
+            tile_coords(tile, tiles_m, tiles_n, mb, nb);
+            const int32_t row_a = (int32_t)(mb * kTileMN + rank * 128);
+            const int32_t row_b = (int32_t)(nb * kTileMN + rank * 128);
+            const uint32_t align_at = p.k_blocks > p.align_at ? p.align_at : 0u;
+            for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
+                if (kb == align_at) {
+                    if (lane == 0)
                         wave_align(p, tile / n_clusters, n_tiles, n_clusters, aligned);
-                    const uint32_t s = it % kNvStages, round = it / kNvStages;
-                    if (round > 0 && !mbar_wait(&sh->empty[s], (round - 1) & 1)) {
+                    aligned = __shfl_sync(0xffffffffu, aligned ? 1 : 0, 0) != 0;
+                }
+                const uint32_t s = it % kNvStages, round = it / kNvStages;
+                if (round > 0 && !warp_wait(&sh->empty[s], (round - 1) & 1)) {
+                    if (lane == 0)
                         atomicCAS(p.status, 0u, 0x211u);
-                        ok = false;
-                        break;
-                    }
-                    uint8_t *st = smem + (size_t)s * kNvStageBytes;
+                    ok = false;
+                    break;
+                }
+                uint8_t *st = smem + (size_t)s * kNvStageBytes;
+                const int32_t x = (int32_t)(kb * kRowBytesK);
+                if (elect_one()) {
                     if (rank == 0)
                         mbar_expect_tx(&sh->full[s], 2 * kStageBytes);
-                    const int32_t x = (int32_t)(kb * kRowBytesK);
-                    tma_load_pair_at(st, &tmap_a, x, row_a, full_at[s]);
-                    tma_load_pair_at(st + kHalfTileBytes, &tmap_b, x, row_b, full_at[s]);
+                    tma_load_pair_at(st, &tmap_a, x, row_a, full0 + 8 * s);
+                    tma_load_pair_at(st + kHalfTileBytes, &tmap_b, x, row_b, full0 + 8 * s);
                 }
+                __syncwarp();
             }
         }
     } else if (warp == kScaleProducerWarp) {
         // ---------------- scale-factor producer (both CTAs) ----------------
         // The stage's scale area in shared memory is free again once the previous round's
         // copies to tensor memory have completed, which is what sf_ready says.
-        if (lane == 0) {
-            uint32_t sf_full_at[kNvStages];
-#pragma unroll
-            for (int s = 0; s < kNvStages; s++)
-                sf_full_at[s] = leader_addr(&sh->sf_full[s]);
-            uint32_t it = 0;
-            bool ok = true;
-            for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters) {
-                uint32_t mb, nb;
-                tile_coords(tile, tiles_m, tiles_n, mb, nb);
-                const uint32_t sfa_block0 = (mb * 2 + rank) * p.k_blocks * BS::a_blocks;
-                const uint32_t sfb_block0 = nb * p.k_blocks * BS::b_blocks;
-                for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
-                    const uint32_t s = it % kNvStages, round = it / kNvStages;
-                    if (round > 0 && !mbar_wait(&sh->sf_ready[s], (round - 1) & 1)) {
+        const uint32_t sf_full0 = leader_addr(&sh->sf_full[0]);
+        uint32_t it = 0;
+        bool ok = true;
+        for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters) {
+            uint32_t mb, nb;
+            tile_coords(tile, tiles_m, tiles_n, mb, nb);
+            const uint32_t sfa_block0 = (mb * 2 + rank) * p.k_blocks * BS::a_blocks;
+            const uint32_t sfb_block0 = nb * p.k_blocks * BS::b_blocks;
+            for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
+                const uint32_t s = it % kNvStages, round = it / kNvStages;
+                if (round > 0 && !warp_wait(&sh->sf_ready[s], (round - 1) & 1)) {
+                    if (lane == 0)
                         atomicCAS(p.status, 0u, 0x216u);
-                        ok = false;
-                        break;
-                    }
-                    uint8_t *sf = smem + (size_t)s * kNvStageBytes + kStageBytes;
+                    ok = false;
+                    break;
+                }
+                uint8_t *sf = smem + (size_t)s * kNvStageBytes + kStageBytes;
+                if (elect_one()) {
                     if (rank == 0)
                         mbar_expect_tx(&sh->sf_full[s], 2 * BS::sf_bytes);
-                    tma_load_pair_at(sf, &tmap_sfa, 0, (int32_t)(sfa_block0 + kb * BS::a_blocks), sf_full_at[s]);
+                    tma_load_pair_at(sf, &tmap_sfa, 0, (int32_t)(sfa_block0 + kb * BS::a_blocks), sf_full0 + 8 * s);
                     tma_load_pair_at(sf + BS::a_blocks * 512, &tmap_sfb, 0, (int32_t)(sfb_block0 + kb * BS::b_blocks),
-                                     sf_full_at[s]);
+                                     sf_full0 + 8 * s);
                 }
+                __syncwarp();
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer (leader CTA) ----------------
-        if (rank == 0 && lane == 0) {
+        // The whole warp runs the loop and waits; one elected lane issues.  Descriptors and
+        // addresses are then warp-uniform values, which is what tcgen05 instructions take:
+        // with the loop inside `if (lane == 0)` every operand had to be moved over from a
+        // per-thread register, and an instruction cost its thread about 110 cycles.
+        if (rank == 0) {
             // MXFP4: instruction kk reads bytes 0-1 (id 0) or 2-3 (id 2) of word kk / 2
             const uint32_t idesc = make_idesc_block_scaled(256, 256, kFmtE2M1, kFmtE2M1, MX ? 1u : 0u, 0, 0);
             const uint32_t idesc_hi = make_idesc_block_scaled(256, 256, kFmtE2M1, kFmtE2M1, 1u, 2, 2);
             uint32_t it = 0, tcount = 0;
             bool ok = true;
             for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters, tcount++) {
-                if (tcount > 0 && !mbar_wait(&sh->tmem_empty, (tcount - 1) & 1)) {
-                    atomicCAS(p.status, 0u, 0x212u);
+                if (tcount > 0 && !__all_sync(0xffffffffu, mbar_wait(&sh->tmem_empty, (tcount - 1) & 1) ? 1 : 0)) {
+                    if (lane == 0)
+                        atomicCAS(p.status, 0u, 0x212u);
                     break;
                 }
                 tc_fence_after_sync();
                 for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
                     const uint32_t s = it % kNvStages, round = it / kNvStages;
                     // the scale factors usually arrive first (6 KiB against 64): wait for them, then the tiles
-                    if (!mbar_wait(&sh->sf_ready[s], round & 1) || !mbar_wait(&sh->full[s], round & 1)) {
-                        atomicCAS(p.status, 0u, 0x213u);
+                    const bool landed = mbar_wait(&sh->sf_ready[s], round & 1) && mbar_wait(&sh->full[s], round & 1);
+                    if (!__all_sync(0xffffffffu, landed ? 1 : 0)) {
+                        if (lane == 0)
+                            atomicCAS(p.status, 0u, 0x213u);
                         ok = false;
                         break;
                     }
@@ -730,25 +759,29 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
                     const uint32_t sfa_t = tmem + kNvSfCol + s * kNvSfColsPerStage, sfb_t = sfa_t + 16;
                     const uint64_t ad = make_smem_desc(base, 16, 1024, kSwizzle128B);
                     const uint64_t bd = make_smem_desc(base + kHalfTileBytes, 16, 1024, kSwizzle128B);
+                    if (elect_one()) {
 #pragma unroll
-                    for (uint32_t kk = 0; kk < 4; kk++) {
-                        if constexpr (MX)
-                            mma2_mxf4_bs(tmem, ad + 2 * kk, bd + 2 * kk, (kk & 1) ? idesc_hi : idesc, sfa_t + 4 * (kk / 2),
-                                         sfb_t + 8 * (kk / 2), (kb | kk) ? 1u : 0u);
-                        else
-                            mma2_nvf4_bs(tmem, ad + 2 * kk, bd + 2 * kk, idesc, sfa_t + 4 * kk, sfb_t + 8 * kk,
-                                         (kb | kk) ? 1u : 0u);
+                        for (uint32_t kk = 0; kk < 4; kk++) {
+                            if constexpr (MX)
+                                mma2_mxf4_bs(tmem, ad + 2 * kk, bd + 2 * kk, (kk & 1) ? idesc_hi : idesc, sfa_t + 4 * (kk / 2),
+                                             sfb_t + 8 * (kk / 2), (kb | kk) ? 1u : 0u);
+                            else
+                                mma2_nvf4_bs(tmem, ad + 2 * kk, bd + 2 * kk, idesc, sfa_t + 4 * kk, sfb_t + 8 * kk,
+                                             (kb | kk) ? 1u : 0u);
+                        }
+                        tc_commit_pair(&sh->empty[s], 3);
                     }
-                    tc_commit_pair(&sh->empty[s], 3);
+                    __syncwarp();
                 }
-                if (ok)
+                if (ok && elect_one())
                     tc_commit_pair(&sh->tmem_full, 3);
+                __syncwarp();
             }
         }
     } else if (warp >= 2 + kEpilogueWarps) {
-        // ---------------- scale-factor copy threads (leader CTA) ----------------
+        // ---------------- scale-factor copy warps (leader CTA) ----------------
         const uint32_t me = (uint32_t)(warp - (2 + kEpilogueWarps));
-        if (rank == 0 && lane == 0) {
+        if (rank == 0) {
             uint32_t it = 0;
             bool ok = true;
             for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters) {
@@ -756,22 +789,26 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
                     const uint32_t s = it % kNvStages, round = it / kNvStages;
                     // the factors have landed, and the MMAs that read this stage's tensor-memory
                     // columns in the previous round have retired
-                    if (!mbar_wait(&sh->sf_full[s], round & 1) ||
-                        (round > 0 && !mbar_wait(&sh->empty[s], (round - 1) & 1))) {
-                        atomicCAS(p.status, 0u, 0x215u);
+                    if (!warp_wait(&sh->sf_full[s], round & 1) ||
+                        (round > 0 && !warp_wait(&sh->empty[s], (round - 1) & 1))) {
+                        if (lane == 0)
+                            atomicCAS(p.status, 0u, 0x215u);
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
                     const uint32_t sf_s = smem_u32(smem + (size_t)s * kNvStageBytes) + kStageBytes;
                     const uint32_t sf_t = tmem + kNvSfCol + s * kNvSfColsPerStage;
-                    // 512-byte blocks of the stage: A's (4 columns each, from column 0), then B's (from column 16)
-                    for (uint32_t blk = me; blk < BS::blocks; blk += kNvCopyThreads) {
-                        const uint32_t col = blk < BS::a_blocks ? 4 * blk : 16 + 4 * (blk - BS::a_blocks);
-                        tmem_cp_32x128b_warpx4<2>(sf_t + col, make_smem_desc(sf_s + blk * 512, 16, 128, kSwizzleNone));
+                    if (elect_one()) {
+                        // 512-byte blocks of the stage: A's (4 columns each, from column 0), then B's (from column 16)
+                        for (uint32_t blk = me; blk < BS::blocks; blk += kNvCopyThreads) {
+                            const uint32_t col = blk < BS::a_blocks ? 4 * blk : 16 + 4 * (blk - BS::a_blocks);
+                            tmem_cp_32x128b_warpx4<2>(sf_t + col, make_smem_desc(sf_s + blk * 512, 16, 128, kSwizzleNone));
+                        }
+                        // arrives on sf_ready[s] in both CTAs when the copies above have completed in both
+                        tc_commit_pair(&sh->sf_ready[s], 3);
                     }
-                    // arrives on sf_ready[s] in both CTAs when the copies above have completed in both
-                    tc_commit_pair(&sh->sf_ready[s], 3);
+                    __syncwarp();
                 }
             }
         }
