@@ -489,7 +489,7 @@ CLPK_DEFINE_MMA_BS(mma2_nvf4_bs, "2", "kind::mxf4nvf4.block_scale.scale_vec::4X"
 CLPK_DEFINE_MMA_BS(mma2_mxf4_bs, "2", "kind::mxf4.block_scale.scale_vec::2X")
 
 // 2:4 sparse A: metadata lives in TMEM.
-#define CLPK_DEFINE_MMA_SP(NAME, KINDSTR)                                                        \
+#define CLPK_DEFINE_MMA_SP(NAME, CTAGROUP, KINDSTR)                                              \
     __device__ __forceinline__ void NAME(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,      \
                                          uint32_t idesc, uint32_t meta_tmem, uint32_t accumulate) \
     {                                                                                            \
@@ -497,17 +497,19 @@ CLPK_DEFINE_MMA_BS(mma2_mxf4_bs, "2", "kind::mxf4.block_scale.scale_vec::2X")
             "{\n\t"                                                                              \
             ".reg .pred p;\n\t"                                                                  \
             "setp.ne.b32 p, %4, 0;\n\t"                                                          \
-            "tcgen05.mma.sp.cta_group::1." KINDSTR " [%0], %1, %2, [%5], %3, p;\n\t"             \
+            "tcgen05.mma.sp.cta_group::" CTAGROUP "." KINDSTR " [%0], %1, %2, [%5], %3, p;\n\t"  \
             "}\n" ::"r"(d_tmem),                                                                 \
             "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(meta_tmem)                \
             : "memory");                                                                         \
     }
 
-CLPK_DEFINE_MMA_SP(mma_f16_sp, "kind::f16")
-CLPK_DEFINE_MMA_SP(mma_f8f6f4_sp, "kind::f8f6f4")
-CLPK_DEFINE_MMA_SP(mma_i8_sp, "kind::i8")
+CLPK_DEFINE_MMA_SP(mma_f16_sp, "1", "kind::f16")
+CLPK_DEFINE_MMA_SP(mma_f8f6f4_sp, "1", "kind::f8f6f4")
+CLPK_DEFINE_MMA_SP(mma_i8_sp, "1", "kind::i8")
+CLPK_DEFINE_MMA_SP(mma2_f8f6f4_sp, "2", "kind::f8f6f4")
+CLPK_DEFINE_MMA_SP(mma2_i8_sp, "2", "kind::i8")
 
-#define CLPK_DEFINE_MMA_SP_BS(NAME, KINDSTR)                                                     \
+#define CLPK_DEFINE_MMA_SP_BS(NAME, CTAGROUP, KINDSTR)                                           \
     __device__ __forceinline__ void NAME(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,      \
                                          uint32_t idesc, uint32_t meta_tmem, uint32_t sfa_tmem,  \
                                          uint32_t sfb_tmem, uint32_t accumulate)                 \
@@ -516,14 +518,16 @@ CLPK_DEFINE_MMA_SP(mma_i8_sp, "kind::i8")
             "{\n\t"                                                                              \
             ".reg .pred p;\n\t"                                                                  \
             "setp.ne.b32 p, %4, 0;\n\t"                                                          \
-            "tcgen05.mma.sp.cta_group::1." KINDSTR " [%0], %1, %2, [%7], %3, [%5], [%6], p;\n\t" \
+            "tcgen05.mma.sp.cta_group::" CTAGROUP "." KINDSTR " [%0], %1, %2, [%7], %3, [%5], [%6], p;\n\t" \
             "}\n" ::"r"(d_tmem),                                                                 \
             "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem), \
             "r"(meta_tmem)                                                                       \
             : "memory");                                                                         \
     }
 
-CLPK_DEFINE_MMA_SP_BS(mma_mxf4_sp_bs, "kind::mxf4.block_scale.scale_vec::2X")
-CLPK_DEFINE_MMA_SP_BS(mma_nvf4_sp_bs, "kind::mxf4nvf4.block_scale.scale_vec::4X")
+CLPK_DEFINE_MMA_SP_BS(mma_mxf4_sp_bs, "1", "kind::mxf4.block_scale.scale_vec::2X")
+CLPK_DEFINE_MMA_SP_BS(mma_nvf4_sp_bs, "1", "kind::mxf4nvf4.block_scale.scale_vec::4X")
+CLPK_DEFINE_MMA_SP_BS(mma2_mxf4_sp_bs, "2", "kind::mxf4.block_scale.scale_vec::2X")
+CLPK_DEFINE_MMA_SP_BS(mma2_nvf4_sp_bs, "2", "kind::mxf4nvf4.block_scale.scale_vec::4X")
 
 } // namespace clpk

@@ -278,9 +278,18 @@ __device__ __forceinline__ void stage_tile_sw128(uint8_t *smem_tile, const uint8
     }
 }
 
-template <int KIND>
+// PAIR: two CTAs run one cta_group::2 instruction (M = 256).  Both stage the same compressed A
+// tile and metadata, each half of B's rows, so each ends with the same 128 x 256 result as a
+// lone CTA.  It matters here more than for the dense kinds: a lone CTA reads 4 KiB of A and
+// 16 KiB of B from shared memory per instruction, 160 cycles at 128 bytes per cycle against the
+// 128 cycles the tensor core needs (measured: 163), a pair 4 + 8 KiB each.
+template <int KIND, bool PAIR>
 __global__ void __launch_bounds__(128) mma_peak_sparse_kernel(PeakParams p, uint32_t meta_cols)
 {
+    constexpr int kGroup = PAIR ? 2 : 1;
+    constexpr int kBRows = PAIR ? kTileN / 2 : kTileN;          // rows of B this CTA stages
+    constexpr uint32_t kM = PAIR ? 256 : kTileM;
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
     constexpr uint32_t kCols = 512;
     constexpr uint32_t kMetaCol = 256, kSpSfaCol = 260, kSpSfbCol = 264;
     constexpr bool kScaled = (KIND == CLPK_MMA_MXF4_SP || KIND == CLPK_MMA_NVF4_SP);
@@ -294,7 +303,7 @@ __global__ void __launch_bounds__(128) mma_peak_sparse_kernel(PeakParams p, uint
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     stage_tile(sA, p.a, kTileM);
-    stage_tile_sw128(sB, p.b, kTileN, kSpBRowBytes);
+    stage_tile_sw128(sB, p.b + (size_t)rank * kBRows * kSpBRowBytes, kBRows, kSpBRowBytes);
     if (threadIdx.x == 0) {
         mbar_init(bar, 1);
         mbar_fence_init();
@@ -302,7 +311,7 @@ __global__ void __launch_bounds__(128) mma_peak_sparse_kernel(PeakParams p, uint
     fence_proxy_async_smem();
     if (warp == 0) {
         __syncwarp();
-        tmem_alloc<1>(tmem_slot, kCols);
+        tmem_alloc<kGroup>(tmem_slot, kCols);
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -334,30 +343,39 @@ __global__ void __launch_bounds__(128) mma_peak_sparse_kernel(PeakParams p, uint
         tmem_st_wait();
         tc_fence_before_sync();
         __syncthreads();
+        if constexpr (PAIR)
+            cluster_sync();             // both CTAs' tiles, metadata, barriers and tensor memory are in place
         tc_fence_after_sync();
     }
 
-    if (threadIdx.x == 0) {
+    if (threadIdx.x == 0 && rank == 0) {
         const uint64_t ad = make_smem_desc(smem_u32(sA), 128, 256, kSwizzleNone);
         const uint64_t bd = make_smem_desc(smem_u32(sB), 16, 1024, kSwizzle128B);
         uint32_t idesc;
         if constexpr (KIND == CLPK_MMA_I8_SP)
-            idesc = make_idesc(kTileM, kTileN, kFmtS8, kFmtS8, kAccS32, true);
+            idesc = make_idesc(kM, kTileN, kFmtS8, kFmtS8, kAccS32, true);
         else if constexpr (KIND == CLPK_MMA_E4M3_SP)
-            idesc = make_idesc(kTileM, kTileN, kFmtE4M3, kFmtE4M3, kAccF32, true);
+            idesc = make_idesc(kM, kTileN, kFmtE4M3, kFmtE4M3, kAccF32, true);
         else
-            idesc = make_idesc_block_scaled(kTileM, kTileN, kFmtE2M1, kFmtE2M1, KIND == CLPK_MMA_MXF4_SP ? 1u : 0u, 0, 0, true);
+            idesc = make_idesc_block_scaled(kM, kTileN, kFmtE2M1, kFmtE2M1, KIND == CLPK_MMA_MXF4_SP ? 1u : 0u, 0, 0, true);
         for (uint32_t i = 0; i < p.n_mma; i++) {
-            if constexpr (KIND == CLPK_MMA_I8_SP)
-                mma_i8_sp(tmem, ad, bd, idesc, tmem + kMetaCol, i ? 1u : 0u);
-            else if constexpr (KIND == CLPK_MMA_E4M3_SP)
-                mma_f8f6f4_sp(tmem, ad, bd, idesc, tmem + kMetaCol, i ? 1u : 0u);
-            else if constexpr (KIND == CLPK_MMA_MXF4_SP)
-                mma_mxf4_sp_bs(tmem, ad, bd, idesc, tmem + kMetaCol, tmem + kSpSfaCol, tmem + kSpSfbCol, i ? 1u : 0u);
-            else
-                mma_nvf4_sp_bs(tmem, ad, bd, idesc, tmem + kMetaCol, tmem + kSpSfaCol, tmem + kSpSfbCol, i ? 1u : 0u);
+            const uint32_t acc = i ? 1u : 0u, meta_t = tmem + kMetaCol, sfa_t = tmem + kSpSfaCol, sfb_t = tmem + kSpSfbCol;
+            if constexpr (KIND == CLPK_MMA_I8_SP) {
+                if constexpr (PAIR) mma2_i8_sp(tmem, ad, bd, idesc, meta_t, acc); else mma_i8_sp(tmem, ad, bd, idesc, meta_t, acc);
+            } else if constexpr (KIND == CLPK_MMA_E4M3_SP) {
+                if constexpr (PAIR) mma2_f8f6f4_sp(tmem, ad, bd, idesc, meta_t, acc); else mma_f8f6f4_sp(tmem, ad, bd, idesc, meta_t, acc);
+            } else if constexpr (KIND == CLPK_MMA_MXF4_SP) {
+                if constexpr (PAIR) mma2_mxf4_sp_bs(tmem, ad, bd, idesc, meta_t, sfa_t, sfb_t, acc);
+                else mma_mxf4_sp_bs(tmem, ad, bd, idesc, meta_t, sfa_t, sfb_t, acc);
+            } else {
+                if constexpr (PAIR) mma2_nvf4_sp_bs(tmem, ad, bd, idesc, meta_t, sfa_t, sfb_t, acc);
+                else mma_nvf4_sp_bs(tmem, ad, bd, idesc, meta_t, sfa_t, sfb_t, acc);
+            }
         }
-        tc_commit(bar);
+        if constexpr (PAIR)
+            tc_commit_pair(bar, 3);
+        else
+            tc_commit(bar);
     }
     __syncwarp();
 
@@ -395,16 +413,41 @@ __global__ void __launch_bounds__(128) mma_peak_sparse_kernel(PeakParams p, uint
 
     tc_fence_before_sync();
     __syncthreads();
+    if constexpr (PAIR)
+        cluster_sync();                 // the peer's shared memory and barrier stay valid until both are done
     if (warp == 0)
-        tmem_dealloc<1>(tmem, kCols);
+        tmem_dealloc<kGroup>(tmem, kCols);
 }
 
 template <int KIND>
 static int launch_peak_sparse(const PeakParams &p, uint32_t grid, uint32_t meta_cols, cudaStream_t s)
 {
     const size_t smem = (size_t)(smem_optin_bytes() * 3 / 5);      // one CTA per SM (512 TMEM columns)
-    CLPK_CUDA(cudaFuncSetAttribute(mma_peak_sparse_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    mma_peak_sparse_kernel<KIND><<<grid, 128, smem, s>>>(p, meta_cols);
+    // CTA pairs by default (a lone CTA is bound by shared-memory reads); CLPK_MMA_PAIR=0 / 1 overrides.
+    bool pair = true;
+    if (const char *e = getenv("CLPK_MMA_PAIR"))
+        pair = e[0] == '1';
+    if (grid % 2 == 0 && pair) {
+        CLPK_CUDA(cudaFuncSetAttribute(mma_peak_sparse_kernel<KIND, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(128);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, mma_peak_sparse_kernel<KIND, true>, p, meta_cols);
+        if (e != cudaSuccess)
+            return cuda_fail(e, "launch mma_peak_sparse (pairs)");
+        return CLPK_OK;
+    }
+    CLPK_CUDA(cudaFuncSetAttribute(mma_peak_sparse_kernel<KIND, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    mma_peak_sparse_kernel<KIND, false><<<grid, 128, smem, s>>>(p, meta_cols);
     CLPK_LAUNCH_CHECK("mma_peak_sparse");
     return CLPK_OK;
 }

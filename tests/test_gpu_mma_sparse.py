@@ -47,6 +47,23 @@ def test_sparse_full_config(K, orc, cuda, kind):
     assert np.all(chk == chk[0])
 
 
+@pytest.mark.parametrize("kind", SP)
+def test_sparse_cta_pairs_and_lone_ctas_compute_the_same_tile(K, orc, cuda, kind, monkeypatch):
+    """cta_group::2 (each CTA stages half of B, both the same compressed A and selectors) against
+    cta_group::1: the same accumulator bits in every tile."""
+    ops = M.make_operands(orc, kind)
+    out = {}
+    for pair in ("0", "1"):
+        monkeypatch.setenv("CLPK_MMA_PAIR", pair)
+        status, tiles, chk = M.run_peak(K, cuda, kind, ops, 5, grid=4, n_out_tiles=4)
+        assert status == 0
+        out[pair] = (tiles.copy(), chk.copy())
+    assert np.array_equal(out["0"][0], out["1"][0]) and np.array_equal(out["0"][1], out["1"][1])
+    want, tol = M.expected_tile(orc, kind, ops, 5)
+    for t in out["1"][0]:
+        M.check_tile(kind, t, want, tol)
+
+
 def test_selectors_matter(K, orc, cuda):
     """Flipping one selector nibble changes exactly one row of the result (int8: exact arithmetic)."""
     ops = M.make_operands(orc, N.MMA_I8_SP)
