@@ -957,6 +957,28 @@ struct B200Harness {
             else
                 out.readings.push_back(ok("float4", bytes / s / 1e9, note, bytes, s));
         }
+        // The same pixels, the same sums per fetch, in an order laid out for the texture path: each
+        // block reads 16 neighbouring 8 x 32 pixel tiles instead of 16 row segments 256 rows apart.
+        const char *tiledNote = "The same image read in small square-ish patches, the order texture hardware is built "
+                                "for (a block of threads reads 16 neighbouring 8 x 32 pixel tiles).";
+        const double st = w.timeLaunches([&] { return clpk_image_bandwidth_tiled(image, buf.as<float>(), blocks, w.stream); }, err);
+        if (st < 0) {
+            out.readings.push_back(bad("float4_tiled", ResultStatus::Error, err, tiledNote));
+        } else {
+            std::vector<float> head(256), tail(256);
+            clpk_memcpy_d2h(head.data(), buf.p, head.size() * 4, w.stream);
+            clpk_memcpy_d2h(tail.data(), buf.as<float>() + (threads - 256), tail.size() * 4, w.stream);
+            clpk_stream_sync(w.stream);
+            bool same = true;
+            for (uint64_t i = 0; i < 256 && same; ++i)
+                same = b200check::sameFloat(head[i], b200check::imageBandwidthTiledReference(i, imgW, imgH, seed)) &&
+                       b200check::sameFloat(tail[i], b200check::imageBandwidthTiledReference(threads - 256 + i, imgW, imgH, seed));
+            const double bytes = (double)IMAGE_FETCH_PER_WI * 4.0 * sizeof(float) * (double)threads;
+            if (!same)
+                out.readings.push_back(bad("float4_tiled", ResultStatus::Error, "sums differ from the host replay", tiledNote));
+            else
+                out.readings.push_back(ok("float4_tiled", bytes / st / 1e9, tiledNote, bytes, st));
+        }
         clpk_image_destroy(image);
     }
 

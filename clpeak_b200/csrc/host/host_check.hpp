@@ -143,6 +143,24 @@ inline float imageBandwidthReference(uint64_t gid, uint64_t threads, uint64_t te
     return ((s[0] + s[1]) + s[2]) + s[3];
 }
 
+// The tiled order: 8 x 32 texel tiles numbered along x; block b's fetch i reads tile (16 b + i) mod
+// tiles; thread t of the block sits at (4 (w % 2) + l % 4, 8 (w / 2) + l / 4) in the tile, w = t / 32, l = t % 32.
+inline float imageBandwidthTiledReference(uint64_t gid, uint32_t width, uint32_t height, uint64_t seed)
+{
+    const uint32_t tilesX = width / 8, nTiles = tilesX * (height / 32);
+    const uint32_t block = (uint32_t)(gid / 256), inBlock = (uint32_t)(gid % 256), w = inBlock / 32, l = inBlock % 32;
+    const uint32_t dx = (w % 2) * 4 + l % 4, dy = (w / 2) * 8 + l / 4;
+    float s[4] = {0, 0, 0, 0};
+    for (uint32_t i = 0; i < 16; ++i) {
+        const uint32_t tile = (uint32_t)(((uint64_t)block * 16 + i) % nTiles);
+        const uint64_t x = (uint64_t)(tile % tilesX) * 8 + dx, y = (uint64_t)(tile / tilesX) * 32 + dy;
+        const uint64_t px = y * width + x;
+        for (int ch = 0; ch < 4; ++ch)
+            s[ch] = s[ch] + clpk_uniform01(seed, 4 * px + (uint64_t)ch);
+    }
+    return ((s[0] + s[1]) + s[2]) + s[3];
+}
+
 inline float seededChain(uint64_t seed, uint64_t item, float y, unsigned iters)
 {
     float x[4];

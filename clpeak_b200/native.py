@@ -123,6 +123,7 @@ KERNEL_API = {
     "clpk_local_bandwidth": [_i, _vp, _u32, _vp],
     "clpk_image_create": [C.POINTER(_vp), _u32, _u32, _u64, _vp],
     "clpk_image_bandwidth": [_vp, _vp, _u32, _vp],
+    "clpk_image_bandwidth_tiled": [_vp, _vp, _u32, _vp],
     "clpk_image_destroy": [_vp],
     "clpk_pointer_chase": [_vp, _u32, _u64, _vp, _vp],
     "clpk_build_chase_cycle": [_vp, _u64, _u64],

@@ -249,6 +249,13 @@ CLPK_API int clpk_image_create(void **image, uint32_t width, uint32_t height, ui
  * src/cuda/cuda_kernels/image_bandwidth.cu).  d_out holds grid*256 floats.  Bytes per
  * launch: 16 * 16 * grid * 256. */
 CLPK_API int clpk_image_bandwidth(void *image, float *d_out, uint32_t grid, void *stream);
+/* The same work in an order that suits the texture path: a warp reads a 4 x 8 patch of
+ * texels, a block an 8 x 32 tile, and fetch i of block b is tile (16 b + i) mod tiles, tiles
+ * numbered along x.  Thread t of the block sits at (x, y) = (4 (w % 2) + l % 4, 8 (w / 2) + l / 4)
+ * inside the tile, w = t / 32, l = t % 32.  Same per-thread sum as clpk_image_bandwidth.  The
+ * image's width must be a multiple of 8 and its height a multiple of 32.  (Additive row: the
+ * reference has only the strided order, src/cuda/cuda_kernels/image_bandwidth.cu:9-25.) */
+CLPK_API int clpk_image_bandwidth_tiled(void *image, float *d_out, uint32_t grid, void *stream);
 CLPK_API int clpk_image_destroy(void *image);
 
 /* ---- latency -------------------------------------------------------------------------------

@@ -53,6 +53,7 @@ _API = {
     "orc_compute_chain": ([_i, _vp, _d, _u64], None),
     "orc_local_bandwidth": ([_i, _vp, _u64], None),
     "orc_image_bandwidth": ([_vp, _u64, _u64, _u64, _u64, _u64], None),
+    "orc_image_bandwidth_tiled": ([_vp, _u64, _u64, _u32, _u32, _u64], None),
     "orc_chase_cycle": ([_vp, _u64, _u64], None),
     "orc_is_single_cycle": ([_vp, _u64], _i),
     "orc_chase": ([_vp, _u32, _u64, C.POINTER(_u32), C.POINTER(_u32)], None),
@@ -168,6 +169,14 @@ def image_bandwidth(n_threads: int, texels: int, seed: int, first: int = 0, coun
     count = n_threads - first if count is None else count
     out = np.empty(count, dtype=np.float32)
     lib().orc_image_bandwidth(ptr(out), first, count, n_threads, texels, seed)
+    return out
+
+
+def image_bandwidth_tiled(n_threads: int, width: int, height: int, seed: int, first: int = 0,
+                          count: int | None = None) -> np.ndarray:
+    count = n_threads - first if count is None else count
+    out = np.empty(count, dtype=np.float32)
+    lib().orc_image_bandwidth_tiled(ptr(out), first, count, width, height, seed)
     return out
 
 

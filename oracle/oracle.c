@@ -601,6 +601,27 @@ void orc_image_bandwidth(float *out, uint64_t first, uint64_t count, uint64_t n_
     }
 }
 
+/* The tiled order of the additive float4_tiled row: 8 x 32 texel tiles numbered along x; block b's
+ * fetch i reads tile (16 b + i) mod tiles; thread t of a block sits at (4 (w % 2) + l % 4,
+ * 8 (w / 2) + l / 4) inside the tile, w = t / 32, l = t % 32.  (No reference counterpart: its
+ * kernel, src/cuda/cuda_kernels/image_bandwidth.cu:9-25, only has the strided order above.) */
+void orc_image_bandwidth_tiled(float *out, uint64_t first, uint64_t count, uint32_t width, uint32_t height, uint64_t seed)
+{
+    const uint32_t tiles_x = width / 8, n_tiles = tiles_x * (height / 32);
+    for (uint64_t t = first; t < first + count; t++) {
+        const uint32_t block = (uint32_t)(t / 256), in_block = (uint32_t)(t % 256), w = in_block / 32, l = in_block % 32;
+        const uint32_t dx = (w % 2) * 4 + l % 4, dy = (w / 2) * 8 + l / 4;
+        float s[4] = {0, 0, 0, 0};
+        for (uint32_t i = 0; i < 16; i++) {
+            const uint32_t tile = (uint32_t)(((uint64_t)block * 16 + i) % n_tiles);
+            const uint64_t x = (uint64_t)(tile % tiles_x) * 8 + dx, y = (uint64_t)(tile / tiles_x) * 32 + dy;
+            const uint64_t px = y * width + x;
+            for (int ch = 0; ch < 4; ch++) s[ch] = s[ch] + orc_uniform01(seed, 4 * px + (uint64_t)ch);
+        }
+        out[t - first] = ((s[0] + s[1]) + s[2]) + s[3];
+    }
+}
+
 void orc_mad_chain(float *out, uint64_t first, uint64_t n_items, uint64_t seed, float y, uint32_t iters)
 {
     for (uint64_t n = 0; n < n_items; n++) {

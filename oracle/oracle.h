@@ -88,6 +88,7 @@ void     orc_compute_chain(int chain, void *out, double a, uint64_t n_threads);
 void     orc_local_bandwidth(int width, float *out, uint64_t n_threads);
 /* threads [first, first + count) of a launch of n_threads */
 void     orc_image_bandwidth(float *out, uint64_t first, uint64_t count, uint64_t n_threads, uint64_t texels, uint64_t seed);
+void     orc_image_bandwidth_tiled(float *out, uint64_t first, uint64_t count, uint32_t width, uint32_t height, uint64_t seed);
 void     orc_mad_chain(float *out, uint64_t first, uint64_t n_items, uint64_t seed, float y, uint32_t iters);
 
 /* ---- pointer chase ---------------------------------------------------------------------- */

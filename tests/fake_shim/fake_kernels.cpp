@@ -346,6 +346,15 @@ int clpk_image_bandwidth(void *image, float *out, uint32_t grid, void *)
     return CLPK_OK;
 }
 
+int clpk_image_bandwidth_tiled(void *image, float *out, uint32_t grid, void *)
+{
+    const FakeImage *im = static_cast<const FakeImage *>(image);
+    const uint64_t n = (uint64_t)grid * 256;
+    for (uint64_t i = 0; i < n; ++i)
+        out[i] = (i < 256 || i + 256 >= n) ? b200check::imageBandwidthTiledReference(i, im->w, im->h, im->seed) : 0.0f;
+    return CLPK_OK;
+}
+
 int clpk_image_destroy(void *image)
 {
     delete static_cast<FakeImage *>(image);

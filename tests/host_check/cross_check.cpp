@@ -61,6 +61,11 @@ int main()
         for (size_t i = 0; i < o.size(); ++i)
             ok = ok && b200check::sameFloat(o[i], b200check::imageBandwidthReference(100 + i, 4096, 1 << 16, 5));
         report("image bandwidth replay equals the oracle", ok);
+        orc_image_bandwidth_tiled(o.data(), 700, 512, 256, 128, 5);          // 512 tiles, 4096 threads wrap 8 times
+        ok = true;
+        for (size_t i = 0; i < o.size(); ++i)
+            ok = ok && b200check::sameFloat(o[i], b200check::imageBandwidthTiledReference(700 + i, 256, 128, 5));
+        report("tiled image bandwidth replay equals the oracle", ok);
     }
 
     // ---- 2:4 pruning ------------------------------------------------------------------------------------

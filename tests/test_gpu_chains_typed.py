@@ -109,6 +109,68 @@ def test_image_bandwidth_small_images_every_thread(K, orc, cuda, shape):
         K.clpk_image_destroy(img)
 
 
+@pytest.mark.parametrize("shape", [(256, 128), (64, 64), (1024, 64), (8, 32), (4096, 32)])
+def test_image_bandwidth_tiled_every_thread(K, orc, cuda, shape):
+    """The tiled order (8 x 32 tiles, 16 neighbouring tiles per block): every thread against the oracle,
+    and the same multiset of texels as the strided order (each read exactly once) when threads * 16 = texels."""
+    w, h = shape
+    stream = cuda.cuda.current_stream().cuda_stream
+    img = make_image(K, w, h, 11, stream)
+    try:
+        threads = max(256, w * h // 16)
+        out = cuda.zeros(threads, dtype=cuda.float32, device="cuda")
+        K.clpk_image_bandwidth_tiled(img, out.data_ptr(), threads // 256, stream)
+        cuda.cuda.synchronize()
+        want = orc.image_bandwidth_tiled(threads, w, h, 11)
+        assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    finally:
+        K.clpk_image_destroy(img)
+
+
+def test_image_bandwidth_tiled_covers_every_texel_once(orc):
+    """Host-only property of the mapping: with threads * 16 = width * height the tiled order visits each texel once."""
+    w, h = 64, 128
+    threads = w * h // 16
+    seen = np.zeros((h, w), dtype=np.int32)
+    tiles_x = w // 8
+    for t in range(threads):
+        b, r = divmod(t, 256)
+        wp, l = divmod(r, 32)
+        for i in range(16):
+            tile = (b * 16 + i) % (tiles_x * (h // 32))
+            seen[(tile // tiles_x) * 32 + (wp // 2) * 8 + l // 4, (tile % tiles_x) * 8 + (wp % 2) * 4 + l % 4] += 1
+    assert (seen == 1).all()
+
+
+def test_image_bandwidth_tiled_rejects_ragged_images(K, cuda):
+    stream = cuda.cuda.current_stream().cuda_stream
+    img = make_image(K, 100, 64, 1, stream)
+    try:
+        out = cuda.zeros(256, dtype=cuda.float32, device="cuda")
+        with pytest.raises(N.ClpkError) as e:
+            K.clpk_image_bandwidth_tiled(img, out.data_ptr(), 1, stream)
+        assert e.value.code == N.ERR_BAD_ARG
+    finally:
+        K.clpk_image_destroy(img)
+
+
+def test_image_bandwidth_tiled_full_size_sampled(K, orc, cuda):
+    w = h = 4096
+    stream = cuda.cuda.current_stream().cuda_stream
+    img = make_image(K, w, h, 5, stream)
+    try:
+        threads = w * h // 16
+        out = cuda.zeros(threads, dtype=cuda.float32, device="cuda")
+        K.clpk_image_bandwidth_tiled(img, out.data_ptr(), threads // 256, stream)
+        cuda.cuda.synchronize()
+        got = out.cpu().numpy()
+        for first in (0, 123456, threads - 512):
+            want = orc.image_bandwidth_tiled(threads, w, h, 5, first=first, count=512)
+            assert np.array_equal(got[first:first + 512].view(np.uint32), want.view(np.uint32))
+    finally:
+        K.clpk_image_destroy(img)
+
+
 def test_image_bandwidth_wraps_when_threads_exceed_texels(K, orc, cuda):
     stream = cuda.cuda.current_stream().cuda_stream
     img = make_image(K, 64, 32, 3, stream)          # 2048 texels, 1024 threads x 16 fetches = 8 passes
