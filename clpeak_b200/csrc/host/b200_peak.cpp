@@ -1079,6 +1079,14 @@ struct B200Harness {
             out.readings.push_back(bad("roundtrip", ResultStatus::Error, shimError("launch"), roundNote));
         else
             out.readings.push_back(ok("roundtrip", mean, roundNote));
+        // What a launch costs once a launch-bound loop is recorded as a CUDA graph and replayed.
+        const char *graphNote = "Per kernel when 1000 empty kernels are recorded once as a CUDA graph and the graph is "
+                                "submitted as a whole -- what a launch costs a program that replays its work.";
+        const uint32_t graphIters = w.latencyIters > 100 ? w.latencyIters / 100 : 1;
+        if (clpk_graph_launch_latency(1000, graphIters, w.warmup, &mean, w.stream) != CLPK_OK)
+            out.readings.push_back(bad("graph_node", ResultStatus::Error, shimError("graph launch"), graphNote));
+        else
+            out.readings.push_back(ok("graph_node", mean, graphNote));
     }
 };
 

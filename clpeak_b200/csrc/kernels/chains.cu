@@ -230,4 +230,59 @@ int clpk_launch_latency(uint32_t iters, uint32_t warmup, double *mean_us, void *
     return CLPK_OK;
 }
 
+// The same empty kernel submitted `nodes` at a time as one CUDA graph: what a launch costs when
+// a launch-bound loop is captured once and replayed (no reference counterpart: its latency test,
+// src/cuda/kernel_latency.cpp:44-63, only has the one-kernel round trip).  mean_us_per_node =
+// (graph launch + synchronise) / nodes, averaged over `iters` replays.
+int clpk_graph_launch_latency(uint32_t nodes, uint32_t iters, uint32_t warmup, double *mean_us_per_node, void *stream)
+{
+    CLPK_REQUIRE(mean_us_per_node && iters > 0 && nodes > 0 && nodes <= 65536, "bad arguments");
+    cudaStream_t own = nullptr, s = as_stream(stream);
+    if (!s) {                                   // the legacy default stream cannot be captured
+        CLPK_CUDA(cudaStreamCreateWithFlags(&own, cudaStreamNonBlocking));
+        s = own;
+    }
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    auto cleanup = [&] {
+        if (exec)
+            cudaGraphExecDestroy(exec);
+        if (graph)
+            cudaGraphDestroy(graph);
+        if (own)
+            cudaStreamDestroy(own);
+    };
+    cudaError_t e = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal);
+    if (e != cudaSuccess) {
+        cleanup();
+        return cuda_fail(e, "cudaStreamBeginCapture");
+    }
+    for (uint32_t i = 0; i < nodes; i++)
+        noop_kernel<<<1, 1, 0, s>>>();
+    e = cudaStreamEndCapture(s, &graph);
+    if (e == cudaSuccess)
+        e = cudaGraphInstantiate(&exec, graph, 0);
+    if (e != cudaSuccess) {
+        cleanup();
+        return cuda_fail(e, "graph capture / instantiate");
+    }
+    double total_ns = 0.0;
+    for (uint32_t i = 0; i < warmup + iters; i++) {
+        const auto t0 = std::chrono::steady_clock::now();
+        e = cudaGraphLaunch(exec, s);
+        if (e == cudaSuccess)
+            e = cudaStreamSynchronize(s);
+        const auto t1 = std::chrono::steady_clock::now();
+        if (e != cudaSuccess) {
+            cleanup();
+            return cuda_fail(e, "cudaGraphLaunch");
+        }
+        if (i >= warmup)
+            total_ns += (double)std::chrono::duration_cast<std::chrono::nanoseconds>(t1 - t0).count();
+    }
+    cleanup();
+    *mean_us_per_node = total_ns / 1000.0 / (double)iters / (double)nodes;
+    return CLPK_OK;
+}
+
 } // extern "C"

@@ -129,6 +129,7 @@ KERNEL_API = {
     "clpk_build_chase_cycle": [_vp, _u64, _u64],
     "clpk_launch_noop": [_vp],
     "clpk_launch_latency": [_u32, _u32, C.POINTER(C.c_double), _vp],
+    "clpk_graph_launch_latency": [_u32, _u32, _u32, C.POINTER(C.c_double), _vp],
     "clpk_mma_peak": [C.POINTER(MmaPeakArgs), _vp],
     "clpk_mma_kind_k": [_i],
     "clpk_mma_flops_per_instr": [_i],

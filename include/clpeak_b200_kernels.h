@@ -276,6 +276,10 @@ CLPK_API int clpk_build_chase_cycle(uint32_t *h_next, uint64_t n, uint64_t seed)
  * (src/cuda/kernel_latency.cpp:44-75).  Synchronous. */
 CLPK_API int clpk_launch_noop(void *stream);
 CLPK_API int clpk_launch_latency(uint32_t iters, uint32_t warmup, double *mean_us, void *stream);
+/* `nodes` empty kernels captured once as a CUDA graph, replayed `iters` times (launch +
+ * synchronise each); the mean per kernel node.  A NULL stream gets a stream of the call's own. */
+CLPK_API int clpk_graph_launch_latency(uint32_t nodes, uint32_t iters, uint32_t warmup, double *mean_us_per_node,
+                                       void *stream);
 
 /* ---- tensor-core peak (tcgen05.mma, accumulator in tensor memory) ------------------------------
  * Takes over the sixteen wmma / mma.sync probes filled in by CudaPeak::runWmma

@@ -396,6 +396,7 @@ int clpk_build_chase_cycle(uint32_t *next, uint64_t n, uint64_t seed)
 
 int clpk_launch_noop(void *) { return CLPK_OK; }
 int clpk_launch_latency(uint32_t, uint32_t, double *mean_us, void *) { *mean_us = 5.0; return CLPK_OK; }
+int clpk_graph_launch_latency(uint32_t, uint32_t, uint32_t, double *mean_us, void *) { *mean_us = 1.0; return CLPK_OK; }
 
 int clpk_mma_kind_k(int kind)
 {

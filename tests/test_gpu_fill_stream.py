@@ -260,3 +260,15 @@ def test_launch_latency(K, cuda):
     mean = C.c_double(0.0)
     K.clpk_launch_latency(200, 3, C.byref(mean), stream_ptr())
     assert 0.5 < mean.value < 1000.0
+
+
+def test_graph_launch_latency_is_below_the_single_launch_round_trip(K, cuda):
+    """1000 empty kernels replayed as one CUDA graph: the per-node cost must undercut launch + synchronise of
+    one kernel, on the caller's stream and on the call's own (NULL) stream; the stream stays usable afterwards."""
+    one, node = C.c_double(0.0), C.c_double(0.0)
+    K.clpk_launch_latency(200, 3, C.byref(one), stream_ptr())
+    for s in (stream_ptr(), None):
+        K.clpk_graph_launch_latency(1000, 20, 2, C.byref(node), s)
+        assert 0.05 < node.value < one.value
+    x = cuda.zeros(16, device="cuda") + 1                   # the captured stream is back to normal work
+    assert float(x.sum()) == 16.0
