@@ -543,11 +543,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
 //    two instructions: the instruction descriptor's scale-factor id picks bytes 0-1
 //    or 2-3.  Half the blocks (2 of A + 4 of B per stage), half the copies.
 //  * What bounds it (clock64 counters in a trace build).  With every role issuing from a
-//    convergent warp the main loop runs at 530-560 cycles per 512-cycle stage, which is
-//    shared-memory bandwidth: per 128-cycle instruction the tensor core reads 8 KiB of
-//    operands per CTA, TMA writes the same 8 KiB (a 256 x 256 tile uses every operand byte
-//    once) and the scale factors add about 1.5 KiB each way, ~150 bytes per cycle asked of
-//    128.  What is left is between tiles: the MMA warp waits about 3100 cycles per tile for tensor
+//    convergent warp the main loop runs at 530-560 cycles per 512-cycle stage (the
+//    counters' own clock reads included).  What is left is between tiles: the MMA warp waits about 3100 cycles per tile for tensor
 //    memory (the queued MMAs drain, tcgen05.commit reaches the epilogue, 128 KiB per CTA
 //    are read out at about 64 bytes per cycle, the release travels back), 7 % of a
 //    K = 16384 tile and 14 % of a K = 8192 one, and it cannot be overlapped without a
