@@ -36,7 +36,6 @@ constexpr uint32_t kHalfTileBytes = 128 * kRowBytesK;       // 16 KiB: 128 rows 
 constexpr uint32_t kStageBytes = 2 * kHalfTileBytes;        // A half + B half (block-scaled kernel)
 constexpr uint32_t kTileMN = 256;
 constexpr int kGemmThreads = 320;                          // dense kernel: producer, MMA, 8 epilogue warps
-constexpr int kGroupN = 8;                                  // tile columns per raster group
 
 struct GemmParams {
     uint32_t m, n, k;
@@ -45,23 +44,11 @@ struct GemmParams {
     void *c;                    // bf16, or fp32 (TF32) / int32 (I8): see out_elem_bytes()
     float alpha;
     uint32_t *status;
-    uint32_t group;             // tile columns per raster group (dense kernel)
+    uint32_t group;             // tile columns per raster group (both kernels)
     unsigned int *wave_sync;    // one counter for this launch, or NULL: see wave_align()
     uint32_t align_at;          // K block of a tile before which the producers meet
     uint32_t align_period;      // ... in every align_period-th wave
 };
-
-__device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uint32_t tiles_n,
-                                            uint32_t &mb, uint32_t &nb)
-{
-    const uint32_t per_group = kGroupN * tiles_m;
-    const uint32_t g = tile / per_group;
-    const uint32_t within = tile - g * per_group;
-    const uint32_t first_n = g * kGroupN;
-    const uint32_t width = (tiles_n - first_n) < (uint32_t)kGroupN ? (tiles_n - first_n) : (uint32_t)kGroupN;
-    mb = within / width;
-    nb = first_n + within % width;
-}
 
 // Output element of a GEMM dtype: fp32 for TF32, int32 for I8, bf16 for everything else.
 template <int DT> struct OutBytes { static constexpr uint32_t value = (DT == CLPK_DT_TF32 || DT == CLPK_DT_I8) ? 4u : 2u; };
@@ -666,7 +653,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
         bool ok = true, aligned = p.wave_sync != nullptr;
         for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters) {
             uint32_t mb, nb;
-            tile_coords(tile, tiles_m, tiles_n, mb, nb);
+            dense_tile_coords(tile, tiles_m, tiles_n, p.group, mb, nb);
             const int32_t row_a = (int32_t)(mb * kTileMN + rank * 128);
             const int32_t row_b = (int32_t)(nb * kTileMN + rank * 128);
             const uint32_t align_at = p.k_blocks > p.align_at ? p.align_at : 0u;
@@ -703,7 +690,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
         bool ok = true;
         for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters) {
             uint32_t mb, nb;
-            tile_coords(tile, tiles_m, tiles_n, mb, nb);
+            dense_tile_coords(tile, tiles_m, tiles_n, p.group, mb, nb);
             const uint32_t sfa_block0 = (mb * 2 + rank) * p.k_blocks * BS::a_blocks;
             const uint32_t sfb_block0 = nb * p.k_blocks * BS::b_blocks;
             for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
@@ -820,7 +807,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
         uint32_t tcount = 0;
         for (uint32_t tile = cluster_id; tile < n_tiles; tile += n_clusters, tcount++) {
             uint32_t mb, nb;
-            tile_coords(tile, tiles_m, tiles_n, mb, nb);
+            dense_tile_coords(tile, tiles_m, tiles_n, p.group, mb, nb);
             if (!__all_sync(0xffffffffu, mbar_wait(&sh->tmem_full, tcount & 1) ? 1 : 0)) {
                 if (lane == 0)
                     atomicCAS(p.status, 0u, 0x214u);
@@ -1095,7 +1082,7 @@ int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
     p.status = a->d_status;
     // waves of ~(SM pairs) tiles that are about square in elements: twice as many 256-wide tile columns
     // as 512-tall tile rows (74 pairs: 12 x 6)
-    p.group = 12;
+    p.group = block_scaled ? 8 : 12;          // block-scaled: 256 x 256 tiles, a wave of 74 is about 8 x 9
     p.wave_sync = nullptr;
     p.align_at = 2;
     p.align_period = block_scaled ? 8 : 1;
