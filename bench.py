@@ -722,10 +722,19 @@ def measure_rows(K, N, torch, stream, time_once, world=1):
                     lib = lambda: torch._scaled_mm(x, y.t(), scale_a=sx, scale_b=sy, out_dtype=torch.bfloat16)
                     what = ("torch._scaled_mm (cuBLASLt), NVFP4: e2m1 + ue4m3 per 16, bf16 out, TN; the same scale "
                             "bytes read in the library's blocked order (timing only)")
-                lms = time_once(lib, reps=5)
+                # Both sit at the power cap, so whoever runs second inherits the other's throttling: alternate
+                # the two for three rounds and compare the best time of each.
+                mine = lambda: K.clpk_gemm(C.byref(ga), stream)
+                ours_ms, lib_ms = [ms], []
+                for _ in range(3):
+                    lib_ms.append(time_once(lib, reps=5))
+                    ours_ms.append(time_once(mine, reps=5))
+                lms = min(lib_ms)
                 ltf = 2.0 * m * m * m / lms / 1e9
-                rows[f"library_cublaslt_{name}_{m}"] = {"TFLOPS": ltf, "ms": lms, "note": what}
-                row["vs_cublas_same_run"] = tf / ltf
+                rows[f"library_cublaslt_{name}_{m}"] = {"TFLOPS": ltf, "ms": lms, "ms_rounds": lib_ms, "note": what}
+                row["ms_rounds"] = ours_ms
+                row["vs_cublas_same_run"] = (2.0 * m * m * m / min(ours_ms) / 1e9) / ltf
+                row["vs_cublas_note"] = "best of alternating rounds on both sides; TFLOPS / ms above are the first round"
             except Exception as e:          # a torch build without that path: report, do not fail the bench
                 rows[f"library_cublaslt_{name}_{m}"] = {"error": repr(e)[:200]}
             x = y = sx = sy = lib = None
