@@ -592,6 +592,21 @@ def measure_small_rows(K, N, torch, stream, time_once):
     mean_us = C.c_double(0.0)
     K.clpk_launch_latency(20000, 200, C.byref(mean_us), stream)
     rows["launch_roundtrip"] = {"us": mean_us.value, "launches": 20000}
+    try:        # additive readings: a kernel node of a replayed CUDA graph; the texture path in tiled order
+        K.clpk_graph_launch_latency(1000, 50, 3, C.byref(mean_us), stream)
+        rows["launch_graph_node"] = {"us": mean_us.value, "nodes_per_graph": 1000, "graph_launches": 50}
+        img = C.c_void_p()
+        K.clpk_image_create(C.byref(img), 4096, 4096, 5, stream)
+        threads = 4096 * 4096 // 16
+        out = torch.empty(threads, dtype=torch.float32, device="cuda")
+        for name, fn in (("texture_float4_reference_order", K.clpk_image_bandwidth),
+                         ("texture_float4_tiled", K.clpk_image_bandwidth_tiled)):
+            ms = time_once(lambda: fn(img, out.data_ptr(), threads // 256, stream), reps=20)
+            rows[name] = {"GBps": 4096 * 4096 * 16 / ms / 1e6, "ms": ms}
+        K.clpk_image_destroy(img)
+        del out
+    except Exception as e:
+        rows["additive_rows_error"] = repr(e)[:200]
     torch.cuda.empty_cache()
     return rows
 
