@@ -17,6 +17,15 @@ the identical, independent workload on its own buffers -- replicas only, no
 data-path collective; torch.distributed is used for the start barrier and the
 max-over-ranks of the device-timed duration.
 
+`e2e_plugin` wall-clocks the product's own plugin call, `clpeak_launch --cuda
+--global-memory-bandwidth` in libclpeak_ffi.so (allocation, seeded fills, kernels, the backend's
+host checks, result rows), on rank 0; with N > 1 it names all N GPUs, which runs the C++
+thread-per-GPU driver while the other ranks idle.
+
+The oracle (oracle/) appears here in two roles only: as the CPU baseline, and as the checker
+of results this file times (sampled GEMM elements, the config-1b sums, the pointer-chase walk).
+It is never the thing measured.
+
 --impl reference times the reference project's own CPU implementation of the
 same metric (its native-CPU backend's global_memory_bandwidth read/copy/triad,
 built unchanged into oracle/_ref/clpeak_ref) on the host cores; when that
@@ -284,6 +293,52 @@ def run_port_cpu(seconds: float):
             "sample": "oracle C port of read/copy/triad, 256 MiB arrays, one pthread per logical core"}
 
 
+def run_plugin(N, devices, extra):
+    """One blocking clpeak_launch through libclpeak_ffi.so; returns rc, wall seconds and the metric events."""
+    lib = N.ffi()
+    events = []
+
+    def cb(_ud, ptr):
+        events.append(json.loads(C.string_at(ptr).decode()))
+        lib.clpeak_free_string(ptr)                 # the callee owns the event string
+
+    keep = N.EVENT_CALLBACK(cb)
+    argv = ["clpeak", "--cuda", "--cuda-device", ",".join(str(d) for d in devices)] + list(extra)
+    arr = (C.c_char_p * len(argv))(*[a.encode() for a in argv])
+    t0 = time.time()
+    rc = lib.clpeak_launch(len(argv), arr, C.cast(keep, C.c_void_p), None)
+    wall = time.time() - t0
+    per_device = {}
+    for e in events:
+        if e.get("t") == "metric":
+            per_device.setdefault(e["device"], {})[f"{e['test']}/{e['metric']}"] = (
+                e["value"] if e["status"] == "ok" else f"{e['status']}: {e['reason']}")
+    return {"rc": rc, "wall_s": wall, "argv": " ".join(argv[1:]), "devices": per_device,
+            "notes": [e["message"].strip() for e in events if e.get("t") == "note"]}
+
+
+def plugin_leg(N, world):
+    """clpeak_launch --cuda --global-memory-bandwidth on the real GPU(s), wall-clocked."""
+    out = run_plugin(N, list(range(world)), ["--global-memory-bandwidth", "--max-time", "200"])
+    names = list(out["devices"])
+    key = "global_memory_bandwidth/"
+    if names:
+        first = out["devices"][names[0]]
+        try:
+            out["value"] = harmonic_stream(first[key + "read"], first[key + "copy"], first[key + "triad"])
+            out["unit"] = UNIT
+        except (KeyError, TypeError):
+            out["value"] = None
+    if world > 1 and len(names) == world + 1:
+        agg = out["devices"][names[-1]]
+        singles = [out["devices"][n] for n in names[:-1]]
+        out["box_aggregate_over_sum_of_gpus"] = {
+            m.split("/")[1]: agg[m] / sum(d[m] for d in singles)
+            for m in (key + "read", key + "copy", key + "triad")
+            if isinstance(agg.get(m), float) and all(isinstance(d.get(m), float) for d in singles)}
+    return out
+
+
 def reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -518,9 +573,32 @@ def main():
             e1.record(); torch.cuda.synchronize()
             return reps.max_over_ranks(e0.elapsed_time(e1) / reps_)
 
-        rows = measure_rows(K, N, torch, stream, lambda fn, reps=3: time_together(fn, reps), world)
+        def clocked(fn, est_ms, seconds):
+            """A loop of at least `seconds` with the SM clock sampled under it: (ms per launch, median MHz)."""
+            n = max(5, int(seconds * 1e3 / max(est_ms, 1e-3)))
+            smp = ClockSampler(local, uuid)
+            smp.start()
+            ms = time_together(fn, n)
+            c = smp.stop()
+            return ms, c.get("sm_mhz"), c.get("reasons")
+
+        rows = measure_rows(K, N, torch, stream, lambda fn, reps=3: time_together(fn, reps), world, clocked,
+                            check=(rank == 0))
         if world == 1:
             rows.update(measure_small_rows(K, N, torch, stream, time_once))
+
+    # ---- the plugin call itself (rank 0; the other ranks have freed their buffers and wait) ----------------
+    plugin = None
+    if not args.no_e2e:
+        del b, parts
+        torch.cuda.empty_cache()
+        reps.barrier()
+        if rank == 0:
+            try:
+                plugin = plugin_leg(N, world)
+            except Exception as e:                      # a missing library is an error of the build, say so
+                plugin = {"error": repr(e)[:300]}
+        reps.barrier()
 
     if rank != 0:
         reps.close()
@@ -552,7 +630,7 @@ def main():
                           "reference_cuda_kernels_on_this_gpu": (run_reference_cuda_kernels(200000)
                                                                  if not args.no_rows else None)}
                          if cpu else None),
-        "e2e": e2e, "gpu_launches": 3 * args.steps, "clocks": clocks, "read_checksum": read_xor, "verified_at_full_size": checks,
+        "e2e": e2e, "e2e_plugin": plugin, "gpu_launches": 3 * args.steps, "clocks": clocks, "read_checksum": read_xor, "verified_at_full_size": checks,
         "rows": rows, "spec_peaks_per_gpu": SPEC,
     }
     print(json.dumps(line), flush=True)
@@ -561,22 +639,37 @@ def main():
 
 
 def measure_small_rows(K, N, torch, stream, time_once):
-    """Configs 1a, 1b, 2b, 2c on this GPU (rank 0, one GPU): chain, read-and-sum, pointer chase, launch roundtrip."""
+    """Configs 1a, 1b, 2b, 2c on this GPU (rank 0, one GPU): chain, read-and-sum, pointer chase, launch roundtrip.
+    The results of 1b and 2b are compared exactly with the oracle's replay at the full configured size."""
     import numpy as np
+    from oracle import binding as orc            # checker only
     rows = {}
     items = 1 << 20
     out = torch.empty(items, dtype=torch.float32, device="cuda")
     ms = time_once(lambda: K.clpk_mad_chain(out.data_ptr(), items, 0, 0.999, 4096, stream), reps=20)
     rows["mad_chain_2^20x4096"] = {"GFLOPS": items * 4 * 4096 * 2 / ms / 1e6, "ms": ms}
+
+    # config 1b: float4 read-and-sum over 256 MiB of uniform[0,1) (seed 1), 16 repeats, sums and checksum exact
     n = (256 << 20) // 4
     src = torch.empty(n, dtype=torch.float32, device="cuda")
     K.clpk_fill_f32(src.data_ptr(), n, 1, N.DIST_UNIFORM01, 0.0, 1.0, stream)
     dst = torch.empty(n // 64, dtype=torch.float32, device="cuda")
     ms = time_once(lambda: K.clpk_global_bandwidth(4, src.data_ptr(), dst.data_ptr(), n, stream), reps=16)
-    rows["read_sum_float4_256MiB"] = {"GBps": n * 4 / ms / 1e6, "ms": ms,
+    g = C.c_int(0)
+    K.clpk_stream_read_grid(N.STREAM_LDG, C.byref(g))
+    parts = torch.zeros(g.value, dtype=torch.int32, device="cuda")
+    K.clpk_stream_read(N.STREAM_LDG, src.data_ptr(), n * 4, parts.data_ptr(), stream)
+    torch.cuda.synchronize()
+    host = orc.fill_f32(n, 1, 0)
+    sums_exact = bool(np.array_equal(dst.cpu().numpy().view(np.uint32), orc.global_bandwidth(4, host).view(np.uint32)))
+    xor_exact = int(np.bitwise_xor.reduce(parts.cpu().numpy().view(np.uint32))) == orc.xor_words(host)
+    rows["read_sum_float4_256MiB"] = {"GBps": n * 4 / ms / 1e6, "ms": ms, "repeats": 16,
+                                      "sums_equal_cpu_replay_bitwise": sums_exact,
+                                      "xor_checksum_equals_cpu": bool(xor_exact), "checked": sums_exact and bool(xor_exact),
                                       "note": "256 MiB is about twice the L2: partly L2-resident between repeats"}
-    del src, dst
-    # pointer chase: 2^28 x uint32 (1 GiB) single cycle, 2^24 dependent hops
+    del src, dst, parts, host
+
+    # config 2b: 2^28 x uint32 (1 GiB) single cycle, 2^24 dependent hops; the walk is replayed on the host
     n_idx, hops = 1 << 28, 1 << 24
     host_next = np.empty(n_idx, dtype=np.uint32)
     K.clpk_build_chase_cycle(host_next.ctypes.data, n_idx, 0xC0FFEE)
@@ -587,11 +680,15 @@ def measure_small_rows(K, N, torch, stream, time_once):
     torch.cuda.synchronize()
     r = res.cpu().numpy().view(np.uint32)
     ns = (int(r[2]) | (int(r[3]) << 32)) / hops
-    rows["pointer_chase_1GiB"] = {"ns_per_hop": ns, "hops": hops, "final_index": int(r[0])}
-    del nxt
+    want_final, want_xor = orc.chase(host_next, 0, hops)
+    rows["pointer_chase_1GiB"] = {"ns_per_hop": ns, "hops": hops, "final_index": int(r[0]), "xor_of_indices": int(r[1]),
+                                  "final_index_equals_cpu_replay": int(r[0]) == want_final,
+                                  "xor_equals_cpu_replay": int(r[1]) == want_xor,
+                                  "checked": int(r[0]) == want_final and int(r[1]) == want_xor}
+    del nxt, host_next
     mean_us = C.c_double(0.0)
-    K.clpk_launch_latency(20000, 200, C.byref(mean_us), stream)
-    rows["launch_roundtrip"] = {"us": mean_us.value, "launches": 20000}
+    K.clpk_launch_latency(100000, 200, C.byref(mean_us), stream)
+    rows["launch_roundtrip"] = {"us": mean_us.value, "launches": 100000}
     try:        # additive readings: a kernel node of a replayed CUDA graph; the texture path in tiled order
         K.clpk_graph_launch_latency(1000, 50, 3, C.byref(mean_us), stream)
         rows["launch_graph_node"] = {"us": mean_us.value, "nodes_per_graph": 1000, "graph_launches": 50}
@@ -611,8 +708,58 @@ def measure_small_rows(K, N, torch, stream, time_once):
     return rows
 
 
-def measure_rows(K, N, torch, stream, time_once, world=1):
-    """Tensor-core peak per dtype (config 3/4) and GEMM (config 5) on this GPU, after the timed region."""
+def check_gemm_samples(torch, N, dt, m, A, B, Cc, sfs, alpha, row_bytes, n_samples=64):
+    """A fixed seeded sample of C elements against the oracle's fp64 dot product of the same quantised operand
+    rows (fetched by D2H).  Tolerance: fp32 accumulation over K terms, K * 2^-23 * sum|a||b|, plus the rounding
+    of the bf16 output, 2^-8 * |c|.  Returns (ok, worst error / tolerance)."""
+    import numpy as np
+    from oracle import binding as orc            # checker only
+    rng = np.random.default_rng(77)
+    ii, jj = rng.integers(0, m, n_samples), rng.integers(0, m, n_samples)
+    sf_row = m // 16 if sfs[0] is not None else 0
+    worst = 0.0
+    c16 = Cc.view(torch.int16)
+    for i, j in zip(ii.tolist(), jj.tolist()):
+        ra = A[i * row_bytes:(i + 1) * row_bytes].cpu().numpy()
+        rb = B[j * row_bytes:(j + 1) * row_bytes].cpu().numpy()
+        sa = sfs[0][i * sf_row:(i + 1) * sf_row].cpu().numpy() if sf_row else None
+        sb = sfs[1][j * sf_row:(j + 1) * sf_row].cpu().numpy() if sf_row else None
+        want, s_abs = orc.gemm_element(dt, ra, rb, m, 0, 0, sa, sb)
+        want *= alpha
+        s_abs *= alpha
+        got = float(np.array([(int(c16[i * m + j].item()) & 0xFFFF) << 16], dtype=np.uint32).view(np.float32)[0])
+        tol = m * 2.0 ** -23 * s_abs + 2.0 ** -8 * abs(want) + 1e-30
+        worst = max(worst, abs(got - want) / tol)
+    return worst <= 1.0, worst
+
+
+def compare_alternating(mine, lib, time_once, rounds=6, reps=5):
+    """Ours and the library, the same number of rounds each, the order swapped every round (both sit at the power
+    cap, so whoever runs second inherits the other's heat).  Returns the two lists of per-launch milliseconds."""
+    ours_ms, lib_ms = [], []
+    for r in range(rounds):
+        if r % 2 == 0:
+            ours_ms.append(time_once(mine, reps=reps))
+            lib_ms.append(time_once(lib, reps=reps))
+        else:
+            lib_ms.append(time_once(lib, reps=reps))
+            ours_ms.append(time_once(mine, reps=reps))
+    return ours_ms, lib_ms
+
+
+def median(xs):
+    xs = sorted(xs)
+    n = len(xs)
+    return xs[n // 2] if n % 2 else 0.5 * (xs[n // 2 - 1] + xs[n // 2])
+
+
+def measure_rows(K, N, torch, stream, time_once, world=1, clocked=None, check=True):
+    """Tensor-core peak per dtype (config 3/4) and GEMM (config 5) on this GPU, after the timed region.
+
+    Every tensor row is given twice: `burst` (5 launches on a GPU that has just idled) and `sustained` (a loop of
+    at least 0.5 s, GEMMs 2 s, with the SM clock sampled under it).  ms x MHz = cycles separates what the kernel
+    does per clock from what the 1000 W cap leaves of the clock: a peak probe at the hardware rate reads 128
+    cycles per instruction (one 128x256xK instruction per 128 clocks per SM)."""
     import numpy as np
     peaks = measured_peaks()
     sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
@@ -622,7 +769,8 @@ def measure_rows(K, N, torch, stream, time_once, world=1):
     # 2:4 sparse kinds: rate counted at the logical K, against twice the dense figure
     sparse_spec = {N.MMA_E4M3_SP: "fp8_tflops", N.MMA_I8_SP: "int8_tops", N.MMA_MXF4_SP: "fp4_tflops",
                    N.MMA_NVF4_SP: "fp4_tflops"}
-    grid, n_mma = 4 * sms, 1 << 14
+    ctas_per_sm = 4
+    grid, n_mma = ctas_per_sm * sms, 1 << 14
     ta = torch.zeros(128 * 32, dtype=torch.uint8, device="cuda")
     tb = torch.zeros(256 * 64, dtype=torch.uint8, device="cuda")
     # selector bytes: groups alternate "keep slots 0,1" (nibble 0x4) and "keep slots 2,3" (nibble 0xE)
@@ -664,16 +812,38 @@ def measure_rows(K, N, torch, stream, time_once, world=1):
         args = N.MmaPeakArgs(kind=kind, d_a=ta.data_ptr(), d_b=tb.data_ptr(), d_sfa=sf.data_ptr(),
                              d_sfb=sf.data_ptr(), d_meta=meta.data_ptr() if kind in sparse_spec else None, n_mma=n_mma, grid=grid, n_out_tiles=0, d_out=None,
                              d_checksum=chk.data_ptr(), d_status=status.data_ptr())
-        ms = time_once(lambda: K.clpk_mma_peak(C.byref(args), stream), reps=5)
+        launch = lambda: K.clpk_mma_peak(C.byref(args), stream)
+        ms = time_once(launch, reps=5)
         if int(status.item()) != 0:
             rows[f"mma_{name}"] = {"error": "device-side wait timed out"}
             continue
         same = bool((chk == chk[0]).all().item())
-        tf = K.raw("clpk_mma_flops_per_instr")(kind) * n_mma * grid / ms / 1e9
+        per_ms = K.raw("clpk_mma_flops_per_instr")(kind) * n_mma * grid / 1e9
+        tf = per_ms / ms
         spec = 2 * SPEC[sparse_spec[kind]] if kind in sparse_spec else SPEC[spec_of[kind]]
-        rows[f"mma_{name}"] = {"T(FL)OPS": tf, "ms": ms, "frac_of_spec": tf / spec, "all_ctas_same_checksum": same,
-                               "box_T(FL)OPS": world * tf}
-    # GEMM, 16384^3 (config 5), bf16 and fp8
+        row = {"T(FL)OPS": tf, "ms": ms, "frac_of_spec": tf / spec, "all_ctas_same_checksum": same,
+               "box_T(FL)OPS": world * tf, "timing": "burst: 5 launches"}
+        if clocked is not None:
+            sms_ms, mhz, reasons = clocked(launch, ms, 0.5)
+            row["sustained"] = {"T(FL)OPS": per_ms / sms_ms, "ms": sms_ms, "frac_of_spec": per_ms / sms_ms / spec,
+                                "seconds": 0.5, "sm_mhz_median": mhz, "reasons": reasons,
+                                "cycles_per_instruction": (sms_ms * 1e-3 * mhz * 1e6 / (n_mma * ctas_per_sm)) if mhz else None}
+        rows[f"mma_{name}"] = row
+
+    # fp64 tensor cores (warp-level DMMA; tcgen05 has no fp64 kind): successor of the reference's wmma_fp64 row
+    try:
+        da = torch.tensor(np.floor(np.linspace(-1, 0.99, 32) * 256) / 256, dtype=torch.float64, device="cuda")
+        db = torch.tensor(np.floor(np.linspace(0.97, -1, 32) * 256) / 256, dtype=torch.float64, device="cuda")
+        dgrid, dn = 8 * sms, 1 << 13
+        launch = lambda: K.clpk_dmma_peak(da.data_ptr(), db.data_ptr(), dn, dgrid, 0, None, None, stream)
+        ms = time_once(launch, reps=5)
+        tf = 512.0 * dn * 64 * dgrid / ms / 1e9
+        rows["dmma_fp64"] = {"TFLOPS": tf, "ms": ms, "frac_of_spec_37TF": tf / 37.0, "box_TFLOPS": world * tf}
+    except Exception as e:
+        rows["dmma_fp64"] = {"error": repr(e)[:200]}
+
+    # GEMM (config 5): M = N = K in {4096, 8192, 16384}; bf16, fp8 e4m3, NVFP4
+    order = 0
     for dt, name, spec in ((N.DT_BF16, "bf16", "bf16_tflops"), (N.DT_E4M3, "fp8_e4m3", "fp8_tflops"),
                            (N.DT_NVF4, "nvf4_e2m1", "fp4_tflops")):
         for m in (4096, 8192, 16384):
@@ -697,9 +867,10 @@ def measure_rows(K, N, torch, stream, time_once, world=1):
             if nv:
                 K.clpk_gemm_workspace_bytes(dt, m, m, m, C.byref(ws_bytes))
                 ws = torch.empty(max(ws_bytes.value, 16), dtype=torch.uint8, device="cuda")
+            alpha = tscale * tscale if nv else 1.0
             ga = N.GemmArgs(dtype=dt, m=m, n=m, k=m, d_a=A.data_ptr(), d_b=B.data_ptr(), d_c=Cc.data_ptr(),
                             d_sfa=sfs[0].data_ptr() if nv else None, d_sfb=sfs[1].data_ptr() if nv else None,
-                            alpha=tscale * tscale if nv else 1.0, d_workspace=ws.data_ptr() if nv else None,
+                            alpha=alpha, d_workspace=ws.data_ptr() if nv else None,
                             workspace_bytes=ws_bytes.value, d_status=status.data_ptr())
             ms_with_pack = None
             if nv:
@@ -709,50 +880,81 @@ def measure_rows(K, N, torch, stream, time_once, world=1):
                 K.clpk_gemm_pack_scales(C.byref(ga), stream)
                 ga.d_sfa = None
                 ga.d_sfb = None
-            ms = time_once(lambda: K.clpk_gemm(C.byref(ga), stream), reps=5)
-            tf = 2.0 * m * m * m / ms / 1e9
-            row = {"TFLOPS": tf, "ms": ms, "frac_of_spec": tf / SPEC[spec], "status": int(status.item()),
-                   "box_TFLOPS": world * tf}
+            mine = lambda: K.clpk_gemm(C.byref(ga), stream)
+            flop = 2.0 * m * m * m
+            ms = time_once(mine, reps=5)
+            row = {"TFLOPS": flop / ms / 1e9, "ms": ms, "frac_of_spec": flop / ms / 1e9 / SPEC[spec],
+                   "status": int(status.item()), "box_TFLOPS": world * flop / ms / 1e9, "timing": "burst: 5 launches"}
             if ms_with_pack is not None:
                 row["ms_including_scale_repack"] = ms_with_pack
             if dt == N.DT_BF16:
-                row["frac_of_measured_cublas_burst"] = tf / peaks["bf16_tflops"]
+                row["frac_of_measured_cublas_burst"] = flop / ms / 1e9 / peaks["bf16_tflops"]
+            if check:
+                Cc.fill_(0x7FC0)                                    # bf16 NaN canary under the result that is checked
+                mine()
+                torch.cuda.synchronize()
+                ok, worst = check_gemm_samples(torch, N, dt, m, A, B, Cc, sfs, alpha, row_bytes)
+                row["checked"] = bool(ok) and int(status.item()) == 0
+                row["check"] = {"samples": 64, "worst_error_over_tolerance": worst,
+                                "tolerance": "K*2^-23*sum|a||b| + 2^-8*|c|, vs fp64 dot of the quantised operands"}
             rows[f"gemm_{name}_{m}"] = row
-            # The vendor library on the very same operand buffers, right after ours (same data, same thermal
-            # state); for comparison only, never on the product path.  The reference's GEMM rows call cuBLASLt
+            # The vendor library on the very same operand buffers (same data, same thermal state); for comparison
+            # only, never on the product path.  The reference's GEMM rows call cuBLASLt
             # (src/cuda/cuda_blas.cpp:264-394, :435-551), which is what torch dispatches to here.
             try:
+                lib_out = torch.empty((m, m), dtype=torch.bfloat16, device="cuda")
                 if dt == N.DT_BF16:
                     x, y = A.view(torch.bfloat16).view(m, m), B.view(torch.bfloat16).view(m, m)
-                    lib, what = (lambda: torch.matmul(x, y.t())), "torch.matmul (cuBLAS), bf16 in / bf16 out, TN"
+                    lib, what = (lambda: torch.matmul(x, y.t(), out=lib_out)), "torch.matmul (cuBLAS), bf16 in / bf16 out, TN"
                 elif dt == N.DT_E4M3:
                     x, y = A.view(torch.float8_e4m3fn).view(m, m), B.view(torch.float8_e4m3fn).view(m, m)
                     one = torch.ones((), dtype=torch.float32, device="cuda")
-                    lib = lambda: torch._scaled_mm(x, y.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+                    lib = lambda: torch._scaled_mm(x, y.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16, out=lib_out)
                     what = "torch._scaled_mm (cuBLASLt), e4m3 in, per-tensor scale, bf16 out, TN"
                 else:
                     x = A.view(torch.float4_e2m1fn_x2).view(m, m // 2)
                     y = B.view(torch.float4_e2m1fn_x2).view(m, m // 2)
                     sx, sy = sfs[0].view(torch.float8_e4m3fn), sfs[1].view(torch.float8_e4m3fn)
-                    lib = lambda: torch._scaled_mm(x, y.t(), scale_a=sx, scale_b=sy, out_dtype=torch.bfloat16)
+                    lib = lambda: torch._scaled_mm(x, y.t(), scale_a=sx, scale_b=sy, out_dtype=torch.bfloat16, out=lib_out)
                     what = ("torch._scaled_mm (cuBLASLt), NVFP4: e2m1 + ue4m3 per 16, bf16 out, TN; the same scale "
                             "bytes read in the library's blocked order (timing only)")
-                # Both sit at the power cap, so whoever runs second inherits the other's throttling: alternate
-                # the two for three rounds and compare the best time of each.
-                mine = lambda: K.clpk_gemm(C.byref(ga), stream)
-                ours_ms, lib_ms = [ms], []
-                for _ in range(3):
-                    lib_ms.append(time_once(lib, reps=5))
-                    ours_ms.append(time_once(mine, reps=5))
-                lms = min(lib_ms)
-                ltf = 2.0 * m * m * m / lms / 1e9
-                rows[f"library_cublaslt_{name}_{m}"] = {"TFLOPS": ltf, "ms": lms, "ms_rounds": lib_ms, "note": what}
+                try:
+                    lib()
+                except TypeError:                   # a torch without out= on this entry point
+                    if dt == N.DT_E4M3:
+                        lib = lambda: torch._scaled_mm(x, y.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+                    elif nv:
+                        lib = lambda: torch._scaled_mm(x, y.t(), scale_a=sx, scale_b=sy, out_dtype=torch.bfloat16)
+                    what += "; output allocated per call by torch's caching allocator"
+                ours_ms, lib_ms = compare_alternating(mine, lib, time_once)
+                lrow = {"TFLOPS_best": flop / min(lib_ms) / 1e9, "TFLOPS_median": flop / median(lib_ms) / 1e9,
+                        "ms_rounds": lib_ms, "note": what}
                 row["ms_rounds"] = ours_ms
-                row["vs_cublas_same_run"] = (2.0 * m * m * m / min(ours_ms) / 1e9) / ltf
-                row["vs_cublas_note"] = "best of alternating rounds on both sides; TFLOPS / ms above are the first round"
+                row["TFLOPS_best_of_rounds"] = flop / min(ours_ms) / 1e9
+                row["TFLOPS_median_of_rounds"] = flop / median(ours_ms) / 1e9
+                row["vs_cublas_median"] = median(lib_ms) / median(ours_ms)
+                row["vs_cublas_best"] = min(lib_ms) / min(ours_ms)
+                row["vs_cublas_note"] = ("6 alternating rounds of 5 launches on each side, order swapped every round; "
+                                         "ratio of medians and of bests (library time / our time)")
+                if clocked is not None:
+                    # >= 2 s of each, clock sampled under the loop; which side goes first alternates per row
+                    first_ours = order % 2 == 0
+                    order += 1
+                    res = {}
+                    for who in (("ours", "lib") if first_ours else ("lib", "ours")):
+                        fn, est = (mine, median(ours_ms)) if who == "ours" else (lib, median(lib_ms))
+                        sms_ms, mhz, reasons = clocked(fn, est, 2.0)
+                        res[who] = {"TFLOPS": flop / sms_ms / 1e9, "ms": sms_ms, "sm_mhz_median": mhz, "reasons": reasons,
+                                    "mega_cycles": sms_ms * 1e-3 * mhz if mhz else None}
+                    row["sustained"] = dict(res["ours"], seconds=2.0, ran="first" if first_ours else "second")
+                    lrow["sustained"] = dict(res["lib"], seconds=2.0, ran="second" if first_ours else "first")
+                    row["vs_cublas_sustained"] = res["lib"]["ms"] / res["ours"]["ms"]
+                    if res["ours"]["mega_cycles"] and res["lib"]["mega_cycles"]:
+                        row["vs_cublas_sustained_in_cycles"] = res["lib"]["mega_cycles"] / res["ours"]["mega_cycles"]
+                rows[f"library_cublaslt_{name}_{m}"] = lrow
             except Exception as e:          # a torch build without that path: report, do not fail the bench
                 rows[f"library_cublaslt_{name}_{m}"] = {"error": repr(e)[:200]}
-            x = y = sx = sy = lib = None
+            x = y = sx = sy = lib = lib_out = None
             del A, B, Cc, sfs, ws
             torch.cuda.empty_cache()
     return rows

@@ -10,7 +10,9 @@
 // opens device scopes in index order, streams the first device's readings as they
 // arrive and replays the others, then adds a box-aggregate pseudo device when
 // more than one GPU ran.  Nothing is exchanged between GPUs: replicas only.
+#include <algorithm>
 #include <atomic>
+#include <chrono>
 #include <cmath>
 #include <condition_variable>
 #include <cstring>
@@ -37,6 +39,7 @@ constexpr double kSpecFp8Tflops = 4500.0;
 constexpr double kSpecFp4Tflops = 9000.0;
 constexpr double kSpecInt8Tops = 4500.0;
 constexpr double kSpecFp32Gflops = 80000.0;
+constexpr double kSpecFp64Tflops = 37.0;    // HGX B200: 296 TFLOPS FP64 tensor core per board
 
 std::string pct(double value, double peak, const char *what)
 {
@@ -77,6 +80,11 @@ struct B200Worker {
     void *stream = nullptr;
     unsigned warmup = 2, targetUs = DEFAULT_TARGET_TIME_US, forcedIters = 0;
     unsigned latencyIters = 2000;
+    // The device threads meet here immediately before every timed batch (after this GPU's warm-ups
+    // and probe launch), so that the timed regions of all GPUs overlap and every GPU is measured
+    // under the power and thermal load of a full box.  Null when a single GPU runs.
+    StartGate *batchGate = nullptr;
+    std::chrono::milliseconds batchGateTimeout{20000};
 
     // results handed to the calling thread, in plan order
     std::mutex m;
@@ -110,6 +118,8 @@ struct B200Worker {
             float ms = 0;
             if (!ok || !batch(1, ms)) break;
             const unsigned iters = pickIters((double)ms * 1000.0, targetUs, forcedIters);
+            if (batchGate)
+                batchGate->arrive(batchGateTimeout);
             if (!batch(iters, ms)) break;
             result = (double)ms * 1e-3 / iters;
         } while (false);
@@ -563,6 +573,63 @@ struct B200Harness {
         const double work = clpk_mma_flops_per_instr(kind) * nMma * grid;
         const double t = work / s / 1e12;
         out.readings.push_back(ok(row.metric, t, note + "  " + pct(t, row.spec, row.specName), work, s));
+    }
+
+    // fp64 tensor cores: no tcgen05 kind exists, so this is the warp-level DMMA path (mma.sync.m8n8k4.f64),
+    // the successor of wmma_fp64 (src/cuda/wmma.cpp:131-138).  Operands are multiples of 2^-8 so that the
+    // expected accumulators are exact in fp64 whatever order the hardware adds the four products in.
+    static void tensorFp64(B200Worker &w, B200TestResult &out)
+    {
+        out.spec = {"wmma_fp64", "DMMA fp64xfp64+fp64 8x8x4", "tflops", Category::Unknown,
+                    "Tensor cores on full 64-bit numbers, for scientific computing.  Blackwell's tcgen05 instructions "
+                    "have no 64-bit form, so this is the warp-level instruction the earlier generations introduced."};
+        const uint32_t grid = 8u * (uint32_t)w.info.numSMs, nMma = 1u << 13;
+        const std::string note = "2^13 dependent instructions on each of " + std::to_string(CLPK_DMMA_CHAINS) +
+                                 " accumulators per warp, " + std::to_string(CLPK_DMMA_WARPS) + " warps on each of " +
+                                 std::to_string(grid) + " CTAs; seeded operands (multiples of 2^-8 in [-1,1)), "
+                                 "accumulators compared exactly with the host.";
+        auto fail = [&](const std::string &why) { out.readings.push_back(bad("wmma_fp64", ResultStatus::Error, why, note)); };
+        double hA[32], hB[32];
+        for (int i = 0; i < 32; ++i) {
+            hA[i] = std::floor((double)clpk_uniform_pm1(2, (uint64_t)i) * 256.0) / 256.0;
+            hB[i] = std::floor((double)clpk_uniform_pm1(2, 32 + (uint64_t)i) * 256.0) / 256.0;
+        }
+        const uint32_t outTiles = 2;
+        DeviceBuffer dA, dB, dOut, dChk;
+        if (!dA.alloc(sizeof hA) || !dB.alloc(sizeof hB) || !dOut.alloc(outTiles * CLPK_DMMA_WARPS * 64 * sizeof(double)) ||
+            !dChk.alloc(grid * 4))
+            return fail("Failed to allocate buffers");
+        if (clpk_memcpy_h2d(dA.p, hA, sizeof hA, w.stream) != CLPK_OK || clpk_memcpy_h2d(dB.p, hB, sizeof hB, w.stream) != CLPK_OK)
+            return fail(shimError("operand upload"));
+        std::string err;
+        const double s = w.timeLaunches([&] {
+            return clpk_dmma_peak(dA.as<double>(), dB.as<double>(), nMma, grid, outTiles, dOut.as<double>(),
+                                  dChk.as<uint32_t>(), w.stream);
+        }, err);
+        if (s < 0)
+            return fail(err);
+        std::vector<double> tiles((size_t)outTiles * CLPK_DMMA_WARPS * 64);
+        std::vector<uint32_t> chk(grid);
+        clpk_memcpy_d2h(tiles.data(), dOut.p, tiles.size() * sizeof(double), w.stream);
+        clpk_memcpy_d2h(chk.data(), dChk.p, chk.size() * 4, w.stream);
+        if (clpk_stream_sync(w.stream) != CLPK_OK)
+            return fail(shimError("read back"));
+        for (uint32_t c : chk)
+            if (c != chk[0])
+                return fail("CTAs disagree on the accumulator checksum");
+        for (uint32_t t = 0; t < outTiles; ++t)
+            for (int wp = 0; wp < CLPK_DMMA_WARPS; ++wp)
+                for (int r = 0; r < 8; ++r)
+                    for (int c = 0; c < 8; ++c) {
+                        double want = b200check::dmmaExpected(hA, hB, nMma, wp, r, c);
+                        const double got = tiles[((size_t)t * CLPK_DMMA_WARPS + wp) * 64 + r * 8 + c];
+                        if (got != want)
+                            return fail("accumulator check failed: warp " + std::to_string(wp) + " (" + std::to_string(r) + "," +
+                                        std::to_string(c) + ") = " + std::to_string(got) + ", host " + std::to_string(want));
+                    }
+        const double work = 512.0 * nMma * CLPK_DMMA_CHAINS * CLPK_DMMA_WARPS * grid;
+        const double t = work / s / 1e12;
+        out.readings.push_back(ok("wmma_fp64", t, note + "  " + pct(t, kSpecFp64Tflops, "fp64 tensor TFLOPS"), work, s));
     }
 
     static void tensorNotBuilt(B200TestResult &out, const char *tag, const char *display, const char *metric,
@@ -1223,7 +1290,7 @@ int CudaPeak::runAll()
                 continue;
             plan.push_back([row](B200Worker &w, B200TestResult &o) { H::tensorPeak(w, o, row); });
             if (row.kind == CLPK_MMA_TF32)
-                plan.push_back([](B200Worker &, B200TestResult &o) { H::tensorNotBuilt(o, "wmma_fp64", "fp64 tensor path", "wmma_fp64", "tflops", "tcgen05 has no fp64 kind"); });
+                plan.push_back(H::tensorFp64);
         }
         for (const auto &row : H::sparseRows(false))
             plan.push_back([row](B200Worker &w, B200TestResult &o) { H::tensorSparse(w, o, row); });
@@ -1263,12 +1330,21 @@ int CudaPeak::runAll()
         plan.push_back(H::kernelLatency);
 
     // ---- run: one thread per GPU, start gate before every test ---------------------------------------------
-    StartGate gate((int)workers.size());
+    // Two gates: `gate` lines the threads up at the start of each test (allocation and operand
+    // generation take different times per GPU), `batchGate` again right before each timed batch.
+    // A thread that errors out of a test early never reaches that test's batch gate; the others
+    // give up on it after batchGateTimeout, the gate is marked broken and later batches start
+    // unsynchronised (the per-test gate keeps working).
+    StartGate gate((int)workers.size()), batchGate((int)workers.size());
     const auto gateTimeout = std::chrono::milliseconds(barrierTimeoutMs);
     std::vector<std::thread> threads;
     for (auto &wp : workers) {
         B200Worker *w = wp.get();
-        threads.emplace_back([w, &plan, &gate, gateTimeout] {
+        if (workers.size() > 1) {
+            w->batchGate = &batchGate;
+            w->batchGateTimeout = std::min(gateTimeout, std::chrono::milliseconds(20000));
+        }
+        threads.emplace_back([w, &plan, &gate, &batchGate, gateTimeout] {
             bool alive = clpk_set_device(w->device) == CLPK_OK && clpk_stream_create(&w->stream) == CLPK_OK;
             if (!alive)
                 w->fatal = shimError("device init");
@@ -1285,6 +1361,7 @@ int CudaPeak::runAll()
                 w->push(std::move(r));
             }
             gate.leave();
+            batchGate.leave();
             if (w->stream)
                 clpk_stream_destroy(w->stream);
             {
@@ -1337,6 +1414,8 @@ int CudaPeak::runAll()
         t.join();
     if (gate.broken())
         log->note("CUDA: a device thread missed the start gate; the remaining tests ran unsynchronised\n");
+    if (batchGate.broken())
+        log->note("CUDA: a device thread missed a timed-batch gate; later batches started unsynchronised\n");
 
     // ---- box aggregate ------------------------------------------------------------------------------------------------
     if (many && !clpeak::cancelRequested()) {

@@ -327,6 +327,19 @@ inline std::string checkHalfAccumTile(const uint8_t *a, const uint8_t *b, const 
 // largest |x0|+|x1| of every four pairs); ties go to the lower index.  compressed
 // is [rows][k/2] in K order, meta one nibble per group (first | second << 2), low
 // nibble first.
+// Expected sum of one warp's accumulator chains of the fp64 tensor probe (clpk_dmma_peak): chain j of warp w
+// starts at w*CHAINS + j and adds A*B n times.  Exact for operands that are multiples of 2^-8 in [-1,1).
+inline double dmmaExpected(const double *a, const double *b, uint32_t nMma, int warp, int row, int col)
+{
+    double p = 0;
+    for (int k = 0; k < 4; ++k)
+        p += a[row * 4 + k] * b[col * 4 + k];
+    double init = 0;
+    for (int j = 0; j < CLPK_DMMA_CHAINS; ++j)
+        init += (double)(warp * CLPK_DMMA_CHAINS + j);
+    return init + (double)CLPK_DMMA_CHAINS * (double)nMma * p;
+}
+
 inline void pruneTile(const std::vector<float> &dense, int rows, int k, bool pairs, std::vector<float> &compressed,
                       std::vector<uint8_t> &meta)
 {

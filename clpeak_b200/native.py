@@ -131,6 +131,7 @@ KERNEL_API = {
     "clpk_launch_latency": [_u32, _u32, C.POINTER(C.c_double), _vp],
     "clpk_graph_launch_latency": [_u32, _u32, _u32, C.POINTER(C.c_double), _vp],
     "clpk_mma_peak": [C.POINTER(MmaPeakArgs), _vp],
+    "clpk_dmma_peak": [_vp, _vp, _u32, _u32, _u32, _vp, _vp, _vp],
     "clpk_mma_kind_k": [_i],
     "clpk_mma_flops_per_instr": [_i],
     "clpk_gemm_workspace_bytes": [_i, _u32, _u32, _u32, C.POINTER(C.c_size_t)],

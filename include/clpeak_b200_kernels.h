@@ -352,6 +352,21 @@ CLPK_API int clpk_mma_peak(const clpk_mma_peak_args_t *args, void *stream);
 CLPK_API int clpk_mma_kind_k(int kind);
 CLPK_API double clpk_mma_flops_per_instr(int kind);
 
+/* fp64 tensor-core peak.  Takes the place of wmma_fp64
+ * (src/cuda/cuda_kernels/wmma_fp64.cu:15-46; row at src/cuda/wmma.cpp:131-138).  tcgen05 has
+ * no fp64 kind, so this is the warp-level mma.sync.m8n8k4.f64 path: CLPK_DMMA_WARPS warps
+ * per CTA, CLPK_DMMA_CHAINS independent accumulator tiles per warp, n_mma dependent
+ * instructions D = A*B + D per chain.  d_a is A [8][4] row-major, d_b is B as [8][4]: row n
+ * holds column n of B.  Chain j of warp w starts at w*CLPK_DMMA_CHAINS + j in every element.
+ * d_out receives, for each of the first n_out_tiles CTAs and each of its warps, the
+ * element-wise sum of that warp's chains: [n_out_tiles][CLPK_DMMA_WARPS][8][8] doubles.
+ * d_checksum[grid] (may be NULL) is a hash of each CTA's tiles; all CTAs must agree.
+ * Work: 8*8*4*2 = 512 flop per instruction per warp, the reference's count. */
+#define CLPK_DMMA_WARPS   8
+#define CLPK_DMMA_CHAINS  8
+CLPK_API int clpk_dmma_peak(const double *d_a, const double *d_b, uint32_t n_mma, uint32_t grid,
+                            uint32_t n_out_tiles, double *d_out, uint32_t *d_checksum, void *stream);
+
 /* ---- GEMM (takes the place of cuBLASLt in CudaPeak::runCublas) -----------------------------------
  * C[M][N] = A[M][K] * B[N][K]^T: A row-major, B "column-major K x N" = N rows
  * of K contiguous elements -- the reference's TN layout

@@ -62,6 +62,7 @@ _API = {
     "orc_prune_pairs_2to4": ([_vp, _vp, _vp, _vp, _u64, _u64], None),
     "orc_mma_tile_sp": ([_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp], None),
     "orc_gemm_element": ([_i, _vp, _vp, _vp, _vp, _u64, _u64, _u64, C.POINTER(_d)], _d),
+    "orc_dmma_tiles": ([_vp, _vp, _u32, _i, _i, _vp], None),
     "orc_pick_iters": ([_d, C.c_uint, C.c_uint, C.c_uint], C.c_uint),
 }
 
@@ -237,3 +238,9 @@ def mma_tile_sp(kind: int, a_comp: np.ndarray, meta: np.ndarray, b: np.ndarray, 
     lib().orc_mma_tile_sp(kind, ptr(a_comp), ptr(meta), ptr(b), ptr(sfa) if sfa is not None else None,
                           ptr(sfb) if sfb is not None else None, ptr(p), ptr(s))
     return p, s
+
+
+def dmma_tiles(a: np.ndarray, b: np.ndarray, n_mma: int, warps: int, chains: int) -> np.ndarray:
+    out = np.empty((warps, 8, 8), dtype=np.float64)
+    lib().orc_dmma_tiles(ptr(a), ptr(b), n_mma, warps, chains, ptr(out))
+    return out

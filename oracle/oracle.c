@@ -871,3 +871,25 @@ unsigned orc_pick_iters(double per_iter_us, unsigned target_us, unsigned forced,
     if (want > (double)max_iters) want = (double)max_iters;
     return (unsigned)want;
 }
+
+/* fp64 tensor probe (clpk_dmma_peak): the successor of src/cuda/cuda_kernels/wmma_fp64.cu:15-46 (4 chains of
+ * 1024 m8n8k4 instructions per warp on constant fragments) with seeded tiles.  Chain j of warp w starts at
+ * w*chains + j in every element and runs n_mma instructions D = A*B + D; each instruction is replayed as
+ * four fused multiply-adds in k order.  out[warps][8][8] = element-wise sum of a warp's chains.  For operands
+ * that are multiples of 2^-8 in [-1,1) every step is exact, so the k order does not matter. */
+void orc_dmma_tiles(const double *a, const double *b, uint32_t n_mma, int warps, int chains, double *out)
+{
+    for (int w = 0; w < warps; w++)
+        for (int r = 0; r < 8; r++)
+            for (int c = 0; c < 8; c++) {
+                double sum = 0.0;
+                for (int j = 0; j < chains; j++) {
+                    double d = (double)(w * chains + j);
+                    for (uint32_t i = 0; i < n_mma; i++)
+                        for (int k = 0; k < 4; k++)
+                            d = fma(a[r * 4 + k], b[c * 4 + k], d);
+                    sum = j == 0 ? d : sum + d;
+                }
+                out[(w * 8 + r) * 8 + c] = sum;
+            }
+}

@@ -120,6 +120,10 @@ void     orc_mma_tile_sp(int kind, const void *a_comp, const uint8_t *meta, cons
 double   orc_gemm_element(int dtype, const void *a, const void *b, const uint8_t *sfa, const uint8_t *sfb,
                           uint64_t k, uint64_t i, uint64_t j, double *abs_sum);
 
+/* fp64 tensor probe: expected [warps][8][8] chain sums of clpk_dmma_peak (successor of
+ * src/cuda/cuda_kernels/wmma_fp64.cu:15-46). */
+void     orc_dmma_tiles(const double *a, const double *b, uint32_t n_mma, int warps, int chains, double *out);
+
 /* pickIters, src/common/common.cpp:35-45. */
 unsigned orc_pick_iters(double per_iter_us, unsigned target_us, unsigned forced, unsigned max_iters);
 

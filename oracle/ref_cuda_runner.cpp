@@ -21,7 +21,17 @@
 // `mma.sync` forms, int4) are reported as skipped; their kernels do not assemble for sm_100a.
 //
 // usage: ref_cuda_runner <cubin dir> [--budget-us N (default 500000)] [--filter substring] [--csv file]
-// Prints one JSON object per row on stdout.  --csv also writes the rows as a result file of the
+//        ref_cuda_runner <cubin dir> --dump <test>/<label> <out file> [--blocks N] [--arg X]
+//                                    [--input file] [--dim W H]
+// The second form is the parity pin: it launches ONE reference kernel once on a small grid and
+// writes the bytes of its output buffer to <out file>, so that a test can compare the
+// reference's own result with the CPU oracle and with this backend's kernel on the same
+// inputs.  Rows: the shader-core chains (single_precision_compute/float ...
+// integer_compute_int8_dp/int8_dp8; --arg replaces the scalar the reference's host passes),
+// global_memory_bandwidth/{float,float2,float4} (--input: raw fp32, blocks*256*16*width values),
+// local_memory_bandwidth/{float,float2,float4}, image_memory_bandwidth/float4 (--dim W H,
+// --input: W*H*4 raw fp32; the grid is W*H/16/256 blocks as in src/cuda/image_bandwidth.cpp:20-107).
+// The first form prints one JSON object per row on stdout.  --csv also writes the rows as a result file of the
 // reference's CSV schema (format_version 2; writer src/common/result_store.cpp:264), with the
 // reference's test tags and metric labels, so that `clpeak --cuda --compare <file>` lines the
 // two backends up row by row.
@@ -382,6 +392,171 @@ void run_kernel_latency(const Gpu &g)
     cuModuleUnload(mod);
 }
 
+// ---- --dump: one launch of one reference kernel, output buffer written to a file ------------------
+
+bool read_file(const char *path, std::vector<char> &bytes)
+{
+    std::FILE *f = std::fopen(path, "rb");
+    if (!f)
+        return false;
+    std::fseek(f, 0, SEEK_END);
+    const long n = std::ftell(f);
+    std::fseek(f, 0, SEEK_SET);
+    bytes.resize(n > 0 ? (size_t)n : 0);
+    const bool ok = bytes.empty() || std::fread(bytes.data(), 1, bytes.size(), f) == bytes.size();
+    std::fclose(f);
+    return ok;
+}
+
+bool write_file(const char *path, const void *p, size_t n)
+{
+    std::FILE *f = std::fopen(path, "wb");
+    if (!f)
+        return false;
+    const bool ok = std::fwrite(p, 1, n, f) == n;
+    return std::fclose(f) == 0 && ok;
+}
+
+struct DumpArgs {
+    const char *row = nullptr, *out = nullptr, *input = nullptr;
+    unsigned blocks = 2;
+    bool have_arg = false;
+    double arg = 0;
+    int w = 0, h = 0;
+};
+
+int launch_and_dump(const Gpu &g, CUfunction fn, unsigned grid, unsigned block, void **args, CUdeviceptr out,
+                    size_t out_bytes, const char *path)
+{
+    DRV(cuMemsetD8(out, 0xA5, out_bytes));       // a kernel that writes nothing cannot pass for one that does
+    DRV(cuLaunchKernel(fn, grid, 1, 1, block, 1, 1, 0, g.stream, args, nullptr));
+    DRV(cuStreamSynchronize(g.stream));
+    std::vector<char> host(out_bytes);
+    DRV(cuMemcpyDtoH(host.data(), out, out_bytes));
+    if (!write_file(path, host.data(), out_bytes)) {
+        std::fprintf(stderr, "cannot write %s\n", path);
+        return 5;
+    }
+    std::printf("{\"dump\": \"%s\", \"grid\": %u, \"block\": %u, \"bytes\": %zu}\n", path, grid, block, out_bytes);
+    return 0;
+}
+
+int run_dump(const Gpu &g, const DumpArgs &d)
+{
+    const std::string row = d.row;
+    const size_t slash = row.find('/');
+    if (slash == std::string::npos) {
+        std::fprintf(stderr, "--dump wants <test>/<label>\n");
+        return 2;
+    }
+    const std::string test = row.substr(0, slash), label = row.substr(slash + 1);
+    CUmodule mod;
+    CUfunction fn;
+    std::vector<char> input;
+    if (d.input && !read_file(d.input, input)) {
+        std::fprintf(stderr, "cannot read %s\n", d.input);
+        return 5;
+    }
+    const int width = label == "float" ? 1 : label == "float2" ? 2 : label == "float4" ? 4 : 0;
+    int rc = 2;
+
+    if (test == "global_memory_bandwidth" && width) {
+        const size_t in_bytes = (size_t)d.blocks * 256 * 16 * width * sizeof(float);
+        if (input.size() != in_bytes) {
+            std::fprintf(stderr, "--input must hold %zu bytes for %u blocks\n", in_bytes, d.blocks);
+            return 2;
+        }
+        const std::string kernel = "global_bandwidth_v" + std::to_string(width);
+        if (!load_kernel(g, "global_bandwidth", kernel.c_str(), &mod, &fn))
+            return 6;
+        CUdeviceptr in = 0, out = 0;
+        const size_t out_bytes = (size_t)d.blocks * 256 * sizeof(float);
+        DRV(cuMemAlloc(&in, in_bytes));
+        DRV(cuMemAlloc(&out, out_bytes));
+        DRV(cuMemcpyHtoD(in, input.data(), in_bytes));
+        void *args[2] = {&in, &out};
+        rc = launch_and_dump(g, fn, d.blocks, 256, args, out, out_bytes, d.out);
+        cuMemFree(in);
+        cuMemFree(out);
+    } else if (test == "local_memory_bandwidth" && width) {
+        const std::string kernel = "local_bandwidth_v" + std::to_string(width);
+        if (!load_kernel(g, "local_bandwidth", kernel.c_str(), &mod, &fn))
+            return 6;
+        CUdeviceptr out = 0;
+        const size_t out_bytes = (size_t)d.blocks * 256 * sizeof(float);
+        DRV(cuMemAlloc(&out, out_bytes));
+        void *args[1] = {&out};
+        rc = launch_and_dump(g, fn, d.blocks, 256, args, out, out_bytes, d.out);
+        cuMemFree(out);
+    } else if (test == "image_memory_bandwidth" && width == 4) {
+        const size_t texels = (size_t)d.w * d.h;
+        if (d.w <= 0 || d.h <= 0 || texels % (16 * 256) != 0 || input.size() != texels * 16) {
+            std::fprintf(stderr, "--dim W H with W*H a multiple of 4096, --input of W*H*16 bytes\n");
+            return 2;
+        }
+        if (!load_kernel(g, "image_bandwidth", "image_bandwidth", &mod, &fn))
+            return 6;
+        CUDA_ARRAY_DESCRIPTOR ad = {};
+        ad.Width = (size_t)d.w;
+        ad.Height = (size_t)d.h;
+        ad.Format = CU_AD_FORMAT_FLOAT;
+        ad.NumChannels = 4;
+        CUarray arr;
+        DRV(cuArrayCreate(&arr, &ad));
+        CUDA_MEMCPY2D cp = {};
+        cp.srcMemoryType = CU_MEMORYTYPE_HOST;
+        cp.srcHost = input.data();
+        cp.srcPitch = (size_t)d.w * 16;
+        cp.dstMemoryType = CU_MEMORYTYPE_ARRAY;
+        cp.dstArray = arr;
+        cp.WidthInBytes = (size_t)d.w * 16;
+        cp.Height = (size_t)d.h;
+        DRV(cuMemcpy2D(&cp));
+        CUDA_RESOURCE_DESC rd = {};
+        rd.resType = CU_RESOURCE_TYPE_ARRAY;
+        rd.res.array.hArray = arr;
+        CUDA_TEXTURE_DESC td = {};
+        td.addressMode[0] = td.addressMode[1] = CU_TR_ADDRESS_MODE_CLAMP;
+        td.filterMode = CU_TR_FILTER_MODE_POINT;
+        CUtexObject tex = 0;
+        DRV(cuTexObjectCreate(&tex, &rd, &td, nullptr));
+        const unsigned grid = (unsigned)(texels / 16 / 256);
+        const size_t out_bytes = (size_t)grid * 256 * sizeof(float);
+        CUdeviceptr out = 0;
+        DRV(cuMemAlloc(&out, out_bytes));
+        int w = d.w, h = d.h;
+        void *args[4] = {&tex, &out, &w, &h};
+        rc = launch_and_dump(g, fn, grid, 256, args, out, out_bytes, d.out);
+        cuMemFree(out);
+        cuTexObjectDestroy(tex);
+        cuArrayDestroy(arr);
+    } else {
+        const ComputeRow *r = nullptr;
+        for (const ComputeRow &c : kComputeRows)
+            if (test == c.test && label == c.label && !c.skip && c.block == 256)
+                r = &c;
+        if (!r) {
+            std::fprintf(stderr, "no dumpable row %s\n", d.row);
+            return 2;
+        }
+        if (!load_kernel(g, r->module, r->kernel, &mod, &fn))
+            return 6;
+        const size_t out_bytes = (size_t)d.blocks * r->out_per_block * r->elem_bytes;
+        CUdeviceptr out = 0;
+        DRV(cuMemAlloc(&out, out_bytes));
+        const double a = d.have_arg ? d.arg : r->arg;
+        float af = (float)a;
+        double ad = a;
+        int ai = (int)(long long)a;
+        void *scalar = r->arg_kind == Arg::F32 ? (void *)&af : r->arg_kind == Arg::F64 ? (void *)&ad : (void *)&ai;
+        void *args[2] = {&out, scalar};
+        rc = launch_and_dump(g, fn, d.blocks, r->block, args, out, out_bytes, d.out);
+        cuMemFree(out);
+    }
+    cuModuleUnload(mod);
+    return rc;
+}
+
 const char *category_of(const std::string &unit)
 {
     if (unit == "gflops" || unit == "tflops")
@@ -416,15 +591,32 @@ bool write_csv(const char *path, const char *device, int driver)
 int main(int argc, char **argv)
 {
     if (argc < 2) {
-        std::fprintf(stderr, "usage: %s <cubin dir> [--budget-us N] [--filter substring] [--csv file]\n", argv[0]);
+        std::fprintf(stderr, "usage: %s <cubin dir> [--budget-us N] [--filter substring] [--csv file]\n"
+                             "       %s <cubin dir> --dump <test>/<label> <out file> [--blocks N] [--arg X] [--input file] [--dim W H]\n",
+                     argv[0], argv[0]);
         return 2;
     }
     Gpu g;
     g.dir = argv[1];
     const char *filter = nullptr, *csv = nullptr;
+    DumpArgs dump;
     for (int i = 2; i < argc; i++) {
         const bool has_value = i + 1 < argc;
-        if (!std::strcmp(argv[i], "--budget-us") && has_value && std::atol(argv[i + 1]) > 0)
+        if (!std::strcmp(argv[i], "--dump") && i + 2 < argc) {
+            dump.row = argv[++i];
+            dump.out = argv[++i];
+        } else if (!std::strcmp(argv[i], "--blocks") && has_value && std::atol(argv[i + 1]) > 0 &&
+                   std::atol(argv[i + 1]) <= 65536)
+            dump.blocks = (unsigned)std::atol(argv[++i]);
+        else if (!std::strcmp(argv[i], "--arg") && has_value) {
+            dump.have_arg = true;
+            dump.arg = std::strtod(argv[++i], nullptr);
+        } else if (!std::strcmp(argv[i], "--input") && has_value)
+            dump.input = argv[++i];
+        else if (!std::strcmp(argv[i], "--dim") && i + 2 < argc) {
+            dump.w = std::atoi(argv[++i]);
+            dump.h = std::atoi(argv[++i]);
+        } else if (!std::strcmp(argv[i], "--budget-us") && has_value && std::atol(argv[i + 1]) > 0)
             g.budget_us = (unsigned)std::atol(argv[++i]);
         else if (!std::strcmp(argv[i], "--filter") && has_value)
             filter = argv[++i];
@@ -451,6 +643,13 @@ int main(int argc, char **argv)
     if (major != 10) {
         std::fprintf(stderr, "the cubins are built for sm_100a; this device is sm_%d%d\n", major, minor);
         return 4;
+    }
+
+    if (dump.row) {
+        const int drc = run_dump(g, dump);
+        cuStreamDestroy(g.stream);
+        cuDevicePrimaryCtxRelease(g.dev);
+        return drc;
     }
 
     if (wanted(filter, "global_memory_bandwidth", "float float2 float4"))

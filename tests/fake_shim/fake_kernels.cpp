@@ -493,6 +493,24 @@ int clpk_mma_peak(const clpk_mma_peak_args_t *a, void *)
     return CLPK_OK;
 }
 
+int clpk_dmma_peak(const double *a, const double *b, uint32_t n_mma, uint32_t grid, uint32_t n_out_tiles, double *out,
+                   uint32_t *checksum, void *)
+{
+    if (!a || !b || n_out_tiles > grid) return fail(CLPK_ERR_BAD_ARG, "dmma arguments");
+    for (uint32_t t = 0; t < n_out_tiles; ++t)
+        for (int w = 0; w < CLPK_DMMA_WARPS; ++w)
+            for (int r = 0; r < 8; ++r)
+                for (int c = 0; c < 8; ++c) {
+                    double p = 0, init = 0;
+                    for (int k = 0; k < 4; ++k) p += a[r * 4 + k] * b[c * 4 + k];
+                    for (int j = 0; j < CLPK_DMMA_CHAINS; ++j) init += w * CLPK_DMMA_CHAINS + j;
+                    out[((size_t)t * CLPK_DMMA_WARPS + w) * 64 + r * 8 + c] = init + (double)CLPK_DMMA_CHAINS * n_mma * p;
+                }
+    if (checksum)
+        for (uint32_t c = 0; c < grid; ++c) checksum[c] = 0x1234u;
+    return CLPK_OK;
+}
+
 int clpk_gemm_workspace_bytes(int, uint32_t, uint32_t, uint32_t, size_t *bytes) { *bytes = 0; return CLPK_OK; }
 int clpk_gemm(const clpk_gemm_args_t *, void *) { return fail(CLPK_ERR_UNSUPPORTED, "the fake shim has no GEMM"); }
 int clpk_gemm_pack_scales(const clpk_gemm_args_t *, void *) { return fail(CLPK_ERR_UNSUPPORTED, "the fake shim has no GEMM"); }

@@ -61,6 +61,7 @@ def test_launch_streams_events_and_writes_xml(ffi, one_device, tmp_path):
     assert by[("wmma_bf16", "wmma_bf16")]["unit"] == "tflops" and by[("wmma_bf16", "wmma_bf16")]["category"] == "fp_compute"
     assert by[("wmma_int8_k32", "int8_k32")]["unit"] == "tops" and by[("wmma_int8_k32", "int8_k32")]["category"] == "int_compute"
     assert by[("wmma_int4", "int4")]["status"] == "unsupported" and by[("wmma_int4", "int4")]["value"] == 0
+    assert by[("wmma_fp64", "wmma_fp64")]["status"] == "ok" and by[("wmma_fp64", "wmma_fp64")]["unit"] == "tflops"
     # the 2:4 sparse rows prune on the host, run, and pass the host's own tile check (exact for int8)
     for key, unit, cat in ((("wmma_int8_sparse", "int8_sparse"), "tops", "int_compute"),
                            (("wmma_mxf4_sparse", "mxf4_sparse"), "tflops", "fp_compute"),
