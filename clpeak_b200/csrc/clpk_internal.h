@@ -22,6 +22,14 @@ int require_sm100();
 int num_sms();          // of the current device (cached per device)
 int smem_optin_bytes(); // of the current device
 
+// Value of a CLPK_TUNE_* knob, or -1 when neither the environment (read once) nor
+// clpk_set_tuning has set it.
+int tuning(int knob);
+
+// fp32 (CUDA cores) and fp64 (DMMA) GEMMs, simt_gemm.cu; dtype is CLPK_DT_F32 or CLPK_DT_F64.
+int launch_simt_gemm(int dtype, const void *a, const void *b, void *c, uint32_t m, uint32_t n, uint32_t k, float alpha,
+                     cudaStream_t s);
+
 inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
 
 } // namespace clpk

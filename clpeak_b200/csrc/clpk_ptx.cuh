@@ -165,34 +165,6 @@ __device__ __forceinline__ void tma_prefetch_desc(const void *tmap)
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
 
-// 2-D tile load, this CTA's shared memory and barrier.  No multicast.
-__device__ __forceinline__ void tma_load_2d(void *smem_dst, const void *tmap, int32_t x, int32_t y,
-                                            uint64_t *bar)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-        "[%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(smem_dst)),
-        "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y)
-        : "memory");
-}
-
-// Same, but the completion bytes are signalled on the barrier at the same
-// offset in CTA `bar_cta` of the cluster (used by the CTA pair of a 2-SM MMA,
-// where the leader's barrier collects both CTAs' loads).
-__device__ __forceinline__ void tma_load_2d_bar_cta(void *smem_dst, const void *tmap, int32_t x,
-                                                    int32_t y, uint64_t *bar, uint32_t bar_cta)
-{
-    uint32_t remote_bar;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
-                 : "=r"(remote_bar)
-                 : "r"(smem_u32(bar)), "r"(bar_cta));
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-        "[%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(smem_dst)),
-        "l"(tmap), "r"(remote_bar), "r"(x), "r"(y)
-        : "memory");
-}
-
 __device__ __forceinline__ void tma_store_2d(const void *tmap, const void *smem_src, int32_t x,
                                              int32_t y)
 {

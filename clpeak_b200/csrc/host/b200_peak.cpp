@@ -661,9 +661,11 @@ struct B200Harness {
         const uint32_t d = gemmDim(w);
         const int dt = r.dtype;
         const bool nv = dt == CLPK_DT_NVF4, mx = dt == CLPK_DT_MXF4, scaled = nv || mx;
-        const bool wideOut = dt == CLPK_DT_TF32 || dt == CLPK_DT_I8;
+        const bool wideOut = dt == CLPK_DT_TF32 || dt == CLPK_DT_I8 || dt == CLPK_DT_F32;
         const uint32_t sfBlock = nv ? 16 : 32;
-        const char *outName = dt == CLPK_DT_TF32 ? "fp32 out" : dt == CLPK_DT_I8 ? "int32 accumulate and out" : "fp32 accumulate, bf16 out";
+        const char *outName = dt == CLPK_DT_TF32 ? "fp32 out" : dt == CLPK_DT_I8 ? "int32 accumulate and out"
+                            : dt == CLPK_DT_F32 ? "fp32 throughout, on the CUDA cores (FFMA)"
+                            : dt == CLPK_DT_F64 ? "fp64 throughout, on the warp-level DMMA instruction" : "fp32 accumulate, bf16 out";
         const std::string note = "M=N=K=" + std::to_string(d) + ", A row-major, B column-major, " +
                                  (dt == CLPK_DT_I8 ? "uniform[-8,7] operands, " : "N(0,0.02) operands, ") +
                                  (nv ? "e2m1 with ue4m3 block scales and fp32 tensor scales (put in tile order once, before timing), " : "") +
@@ -672,15 +674,16 @@ struct B200Harness {
                                  "; sampled elements checked against a host dot product.";
         auto fail = [&](const std::string &why) { out.readings.push_back(bad(r.metric, ResultStatus::Error, why, note)); };
         const uint64_t n = (uint64_t)d * d;
-        const uint64_t rowBytes = scaled ? d / 2 : dt == CLPK_DT_TF32 ? 4ull * d
+        const uint64_t rowBytes = scaled ? d / 2 : dt == CLPK_DT_F64 ? 8ull * d : (dt == CLPK_DT_TF32 || dt == CLPK_DT_F32) ? 4ull * d
                                 : (dt == CLPK_DT_F16 || dt == CLPK_DT_BF16) ? 2ull * d : d;
+        const uint64_t outBytes = dt == CLPK_DT_F64 ? 8 : wideOut ? 4 : 2;
         // N(0, 0.02): |x| < 0.12, so a tensor scale of 2^-15 keeps x / scale / 6 within ue4m3's range (448).
         const float tensorScale = nv ? std::ldexp(1.0f, -15) : 1.0f;
         size_t wsBytes = 0;
         if (scaled && clpk_gemm_workspace_bytes(dt, d, d, d, &wsBytes) != CLPK_OK)
             return fail(shimError("workspace size"));
         DeviceBuffer tmp, A, B, C, st, sfa, sfb, ws;
-        if (!tmp.alloc(n * 4) || !A.alloc(d * rowBytes) || !B.alloc(d * rowBytes) || !C.alloc(n * (wideOut ? 4 : 2)) || !st.alloc(4) ||
+        if (!tmp.alloc(n * 4) || !A.alloc(d * rowBytes) || !B.alloc(d * rowBytes) || !C.alloc(n * outBytes) || !st.alloc(4) ||
             (scaled && (!sfa.alloc(n / sfBlock) || !sfb.alloc(n / sfBlock) || !ws.alloc(wsBytes))))
             return fail("Failed to allocate matrices");
         auto operand = [&](DeviceBuffer &dst, DeviceBuffer &sf, uint64_t seed, bool isB) {
@@ -689,6 +692,8 @@ struct B200Harness {
             int rc = clpk_fill_f32(tmp.as<float>(), n, seed, CLPK_DIST_NORMAL, 0.0f, 0.02f, w.stream);
             if (scaled)
                 return rc | clpk_quantize_fp4(dst.as<uint8_t>(), sf.as<uint8_t>(), tmp.as<float>(), d, d, dt, tensorScale, w.stream);
+            if (dt == CLPK_DT_F32)
+                return rc | clpk_memcpy_d2d(dst.p, tmp.p, n * 4, w.stream);
             return rc | clpk_convert_f32(dst.p, tmp.as<float>(), n, (dt == CLPK_DT_E5M2 && isB) ? CLPK_DT_E4M3 : dt, w.stream);
         };
         int rc = operand(A, sfa, 40, false);
@@ -718,13 +723,16 @@ struct B200Harness {
         for (int sidx = 0; sidx < 16 && verdict.empty(); ++sidx) {
             const uint64_t i = clpk_rand64(77, 2 * sidx) % d, j = clpk_rand64(77, 2 * sidx + 1) % d;
             uint32_t cWord = 0;
+            double cDouble = 0;
             clpk_memcpy_d2h(rowA.data(), A.as<uint8_t>() + i * rowBytes, rowBytes, w.stream);
             clpk_memcpy_d2h(rowB.data(), B.as<uint8_t>() + j * rowBytes, rowBytes, w.stream);
             if (scaled) {
                 clpk_memcpy_d2h(rowSfa.data(), sfa.as<uint8_t>() + i * sfRow, sfRow, w.stream);
                 clpk_memcpy_d2h(rowSfb.data(), sfb.as<uint8_t>() + j * sfRow, sfRow, w.stream);
             }
-            if (wideOut)
+            if (dt == CLPK_DT_F64)
+                clpk_memcpy_d2h(&cDouble, C.as<double>() + i * d + j, 8, w.stream);
+            else if (wideOut)
                 clpk_memcpy_d2h(&cWord, C.as<uint32_t>() + i * d + j, 4, w.stream);
             else
                 clpk_memcpy_d2h(&cWord, C.as<uint16_t>() + i * d + j, 2, w.stream);
@@ -737,7 +745,10 @@ struct B200Harness {
             if (dt == CLPK_DT_I8) {
                 got = (double)(int32_t)cWord;
                 tol = 0.0;
-            } else if (dt == CLPK_DT_TF32) {
+            } else if (dt == CLPK_DT_F64) {
+                got = cDouble;
+                tol = d * std::ldexp(1.0, -51) * sAbs + 1e-300;      // K fp64 roundings on each side of the comparison
+            } else if (dt == CLPK_DT_TF32 || dt == CLPK_DT_F32) {
                 got = clpk_bits_f32(cWord);
                 tol = d * std::ldexp(1.0, -23) * sAbs + 1e-30;
             } else {
@@ -764,9 +775,9 @@ struct B200Harness {
                     "what a well-tuned library routine reaches, as opposed to the bare instruction rate of the rows above.  "
                     "The reference calls cuBLASLt here; this backend runs its own warp-specialised 2-CTA tcgen05 kernel."};
         // the reference's row order (src/cuda/cuda_blas.cpp:567-676)
-        for (const char *m : {"fp32", "fp64"})
-            out.readings.push_back(bad(m, ResultStatus::Unsupported, "shader-core GEMM: no tcgen05 kind for this type, not built in the B200 backend"));
         static const GemmRow rows[] = {
+            {"fp32", CLPK_DT_F32, kSpecFp32Gflops / 1000.0, "fp32 TFLOPS (CUDA cores)", ""},
+            {"fp64", CLPK_DT_F64, kSpecFp64Tflops, "fp64 tensor TFLOPS", ""},
             {"tf32", CLPK_DT_TF32, kSpecBf16Tflops / 2, "dense tf32 TFLOPS", ""},
             {"fp16", CLPK_DT_F16, kSpecBf16Tflops, "dense fp16 TFLOPS", ""},
             {"bf16", CLPK_DT_BF16, kSpecBf16Tflops, "dense bf16 TFLOPS", ""},

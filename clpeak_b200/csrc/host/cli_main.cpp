@@ -23,16 +23,22 @@ int main(int argc, char **argv)
 
     ResultStore rows;
     DeviceInfoStore devices;
-    int status = 0;
+    int status = 0, ran = 0;
     for (const auto &b : clpeakBackends()) {
         if (opts.*(b.skip))
             continue;
+        ++ran;
         std::unique_ptr<Peak> peak = b.create();
         peak->log.reset(new LoggerText(std::cout, opts.compareFile, opts.describe));
         peak->applyOptions(opts);
         status |= peak->runAll();
         rows.insert(rows.end(), peak->log->results.begin(), peak->log->results.end());
         devices.insert(devices.end(), peak->log->devices.begin(), peak->log->devices.end());
+    }
+    if (opts.namedAbsentBackend) {
+        std::cerr << "clpeak: the native CPU backend is not built into this binary (CUDA backend only)\n";
+        if (ran == 0)
+            status |= 1;
     }
     if (opts.enableJson && !saveJson(rows, opts.jsonFile, devices)) status |= 1;
     if (opts.enableCsv && !saveCsv(rows, opts.csvFile)) status |= 1;

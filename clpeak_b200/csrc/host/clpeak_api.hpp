@@ -417,6 +417,9 @@ struct CliOptions {
     bool listDevices = false;
     bool verbose = false;
     bool describe = false;
+    // --cpu was given, but this build registers no native CPU backend (backend_table.hpp): the
+    // front ends say so and report a non-zero status when nothing else was selected.
+    bool namedAbsentBackend = false;
 
     CliOptions()
     {

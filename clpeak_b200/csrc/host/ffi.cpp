@@ -201,16 +201,25 @@ int clpeak_launch(int argc, const char **argv, ClpeakEventCallback on_event, voi
 
     ResultStore rows;
     DeviceInfoStore devices;
-    int status = 0;
+    int status = 0, ran = 0;
     for (const auto &b : clpeakBackends()) {
         if (opts.*(b.skip) || clpeak::cancelRequested())
             continue;
+        ++ran;
         std::unique_ptr<Peak> peak = b.create();
         peak->log.reset(new LoggerFfi(on_event, user_data));
         peak->applyOptions(opts);
         status |= peak->runAll();
         rows.insert(rows.end(), peak->log->results.begin(), peak->log->results.end());
         devices.insert(devices.end(), peak->log->devices.begin(), peak->log->devices.end());
+    }
+    if (opts.namedAbsentBackend) {
+        LogEvent note;
+        note.kind = LogEvent::Kind::Note;
+        note.message = "the native CPU backend is not built into this library (CUDA backend only)";
+        deliver(on_event, user_data, eventJson(note));
+        if (ran == 0)
+            status |= 1;
     }
     if (opts.enableJson && !saveJson(rows, opts.jsonFile, devices)) status |= 1;
     if (opts.enableCsv && !saveCsv(rows, opts.csvFile)) status |= 1;

@@ -441,6 +441,12 @@ inline double gemmElement(int dtype, const void *a, const void *b, uint64_t k, u
         } else if (dtype == CLPK_DT_I8) {
             va = static_cast<const int8_t *>(a)[i * k + x];
             vb = static_cast<const int8_t *>(b)[j * k + x];
+        } else if (dtype == CLPK_DT_F32) {
+            va = static_cast<const float *>(a)[i * k + x];
+            vb = static_cast<const float *>(b)[j * k + x];
+        } else if (dtype == CLPK_DT_F64) {
+            va = static_cast<const double *>(a)[i * k + x];
+            vb = static_cast<const double *>(b)[j * k + x];
         } else if (dtype == CLPK_DT_TF32) {
             va = clpk_bits_f32(static_cast<const uint32_t *>(a)[i * k + x] & 0xFFFFE000u);
             vb = clpk_bits_f32(static_cast<const uint32_t *>(b)[j * k + x] & 0xFFFFE000u);

@@ -27,7 +27,7 @@ const char *kHelp = R"( clpeak [OPTIONS]   (B200 / sm_100a CUDA backend)
   -i, --iters num             force a fixed iter count (overrides --max-time calibration)
   -w, --warmup num            number of warm-up kernel runs before timing (default: 2)
   --max-time ms               per-test time budget for the timed phase (default: 500 ms)
-  --max-time-cpu ms           per-test time budget for the CPU backend (default: 2000 ms)
+  --max-time-cpu ms           per-test time budget for the CPU backend (accepted, unused: no CPU backend here)
   --verbose                   print backend debug logs
   --describe                  explain what each test and each reading measures
   --list-devices              list available devices for every backend and exit
@@ -38,7 +38,8 @@ const char *kHelp = R"( clpeak [OPTIONS]   (B200 / sm_100a CUDA backend)
 
  BACKEND SELECTION (default: run every available backend):
   --cuda / --no-cuda          run only / skip the CUDA backend
-  --cpu  / --no-cpu           run only / skip the native CPU backend
+  --cpu  / --no-cpu           accepted for scripts written for a full clpeak build; this build carries
+                              the CUDA backend only, so --cpu alone runs nothing and exits non-zero
   --cuda-device list          comma-separated CUDA device indices (default: all, run concurrently)
 
  CATEGORY SELECTION (--<cat> runs only the named categories, --no-<cat> removes one):
@@ -171,7 +172,7 @@ Outcome parse(int argc, char **argv, CliOptions &o, std::string &err)
         if (s == "--list-devices") { o.listDevices = true; continue; }
         if (s == "--cuda") { wantCuda = onlyNamedBackends = true; continue; }
         if (s == "--no-cuda") { o.skipCuda = true; continue; }
-        if (s == "--cpu") { wantCpu = onlyNamedBackends = true; continue; }
+        if (s == "--cpu") { wantCpu = onlyNamedBackends = o.namedAbsentBackend = true; continue; }
         if (s == "--no-cpu") { o.skipCpu = true; continue; }
 
         if (s == "-i" || s == "--iters") {

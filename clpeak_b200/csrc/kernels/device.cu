@@ -1,6 +1,10 @@
 // Device, memory, stream and event plumbing behind the C ABI.
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
+
+#include <atomic>
+#include <mutex>
 
 #include "../clpk_internal.h"
 
@@ -81,11 +85,45 @@ int smem_optin_bytes()
     return g_dev[dev].smem_optin;
 }
 
+static std::atomic<int> g_tune[CLPK_TUNE_COUNT];
+static std::once_flag g_tune_once;
+
+static void load_tuning_from_environment()
+{
+    static const char *names[CLPK_TUNE_COUNT] = {"CLPK_GEMM_NO_ALIGN", "CLPK_GEMM_ALIGN_AT", "CLPK_GEMM_GROUP",
+                                                 "CLPK_MMA_PAIR", "CLPK_GEMM_FP4_TILE", "CLPK_MMA_LONE_LANE"};
+    for (int k = 0; k < CLPK_TUNE_COUNT; k++) {
+        const char *e = getenv(names[k]);
+        g_tune[k].store((e && e[0]) ? atoi(e) : -1);
+    }
+}
+
+int tuning(int knob)
+{
+    std::call_once(g_tune_once, load_tuning_from_environment);
+    return (knob >= 0 && knob < CLPK_TUNE_COUNT) ? g_tune[knob].load(std::memory_order_relaxed) : -1;
+}
+
 } // namespace clpk
 
 using namespace clpk;
 
 extern "C" {
+
+int clpk_set_tuning(int knob, int value)
+{
+    CLPK_REQUIRE(knob >= 0 && knob < CLPK_TUNE_COUNT, "unknown tuning knob %d", knob);
+    (void)tuning(knob);                    // the environment is read first, so that it cannot overwrite this later
+    g_tune[knob].store(value < 0 ? -1 : value);
+    return CLPK_OK;
+}
+
+int clpk_get_tuning(int knob, int *value)
+{
+    CLPK_REQUIRE(knob >= 0 && knob < CLPK_TUNE_COUNT && value, "unknown tuning knob %d or NULL value", knob);
+    *value = tuning(knob);
+    return CLPK_OK;
+}
 
 const char *clpk_last_error(void) { return g_err; }
 const char *clpk_version(void) { return "clpeak-b200 0.1 (sm_100a)"; }

@@ -60,6 +60,9 @@ __global__ void convert_kernel(void *dst, const float *src, uint64_t n, int dtyp
             reinterpret_cast<uint32_t *>(dst)[i] = b & 0xFFFFE000u;
             break;
         }
+        case CLPK_DT_F64:
+            reinterpret_cast<double *>(dst)[i] = (double)x;
+            break;
         case CLPK_DT_I8: {
             int v = __float2int_rn(x);
             v = v < -128 ? -128 : (v > 127 ? 127 : v);
@@ -176,7 +179,8 @@ int clpk_convert_f32(void *d_dst, const float *d_src, uint64_t n, int dtype, voi
 {
     CLPK_REQUIRE((d_dst && d_src) || n == 0, "NULL buffer");
     CLPK_REQUIRE(dtype == CLPK_DT_F16 || dtype == CLPK_DT_BF16 || dtype == CLPK_DT_E4M3 ||
-                     dtype == CLPK_DT_E5M2 || dtype == CLPK_DT_I8 || dtype == CLPK_DT_TF32 || dtype == CLPK_DT_E2M1,
+                     dtype == CLPK_DT_E5M2 || dtype == CLPK_DT_I8 || dtype == CLPK_DT_TF32 || dtype == CLPK_DT_E2M1 ||
+                     dtype == CLPK_DT_F64,
                  "clpk_convert_f32: dtype %d has no plain conversion", dtype);
     if (n == 0)
         return CLPK_OK;

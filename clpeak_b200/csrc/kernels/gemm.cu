@@ -8,13 +8,16 @@
 //    N = 256), two row blocks sharing one B tile; each CTA holds 256 x 256 of the
 //    accumulator, i.e. all of its tensor memory.  The MMA reads both CTAs' shared
 //    memory.  No TMA multicast anywhere: each CTA fetches what it needs itself.
-//  * Warp roles (192 threads): warp 0 TMA producer, warp 1 MMA issuer (leader
-//    CTA only) and TMEM owner, warps 2-5 epilogue (TMEM -> registers -> output
-//    type -> global).
+//  * Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer (leader
+//    CTA only) and TMEM owner, warps 2-9 epilogue (TMEM -> registers -> output
+//    type -> swizzled staging box in shared memory -> TMA store).  The roles
+//    that issue TMA or tcgen05 instructions run their loops as whole warps and
+//    let one elected lane issue.
 //  * K is consumed in blocks of 128 bytes per row (64 x 16-bit, 128 x 8-bit),
-//    the width of one 128-byte-swizzled TMA box; a stage is 32 KiB of A and
-//    16 KiB of B per CTA.  Both CTAs' loads signal the leader's "full"
-//    barrier; tcgen05.commit releases a stage in both CTAs at once.
+//    the width of one 128-byte-swizzled TMA box; a stage is two 16 KiB A
+//    sub-tiles (one per row block) and this CTA's 16 KiB half of B, four
+//    stages.  Both CTAs' loads signal the leader's "full" barrier;
+//    tcgen05.commit releases a stage in both CTAs at once.
 //  * Every mbarrier wait is bounded; on expiry the status word is set and all
 //    roles fall through to the common exit, which frees tensor memory.
 //
@@ -242,20 +245,22 @@ __device__ __forceinline__ void drain_warp_tile(uint32_t taddr0, uint32_t row_bl
 // and tensor memory is released before anything is written out.  Two rounds of two
 // tcgen05.ld (64 fp32 registers in flight, 32 packed ones kept) rather than one of four,
 // which would not fit the register file.
+// ROUNDS = boxes of 64 columns this warp owns: 2 (a 128-column share) or 1 (a 64-column share).
+template <int ROUNDS>
 __device__ __forceinline__ void drain_warp_tile_early(uint32_t taddr0, uint32_t row0, uint32_t col0, uint8_t *box,
                                                       const CUtensorMap *tmap_c, float alpha, uint64_t *empty_bar,
                                                       int lane)
 {
     uint8_t *my_row = box + lane * 128;
     const uint32_t sw = (uint32_t)(lane & 7);
-    uint32_t w[2][32];
+    uint32_t w[ROUNDS][32];
 #pragma unroll
-    for (uint32_t b = 0; b < 2; b++) {
+    for (uint32_t b = 0; b < ROUNDS; b++) {
         uint32_t r0[32], r1[32];
         tmem_ld_32x32b_x32(taddr0 + b * 64, r0);
         tmem_ld_32x32b_x32(taddr0 + b * 64 + 32, r1);
         tmem_ld_wait();
-        if (b == 1) {
+        if (b == ROUNDS - 1) {
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0)
@@ -270,7 +275,7 @@ __device__ __forceinline__ void drain_warp_tile_early(uint32_t taddr0, uint32_t 
         }
     }
 #pragma unroll
-    for (uint32_t b = 0; b < 2; b++) {
+    for (uint32_t b = 0; b < ROUNDS; b++) {
         // the previous box must have been read out of shared memory by its store
         if (lane == 0)
             bulk_wait_read<0>();
@@ -541,31 +546,47 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
 //    per epilogue warp, and letting the copies queue behind issued rather than retired
 //    MMAs.
 
-constexpr int kNvStages = 5;
+constexpr int kNvMaxStages = 6;
 constexpr int kNvCopyThreads = 4;
 constexpr int kNvGemmThreads = 32 * (3 + kEpilogueWarps + kNvCopyThreads);    // operand producer, MMA, 8 epilogue, 4 scale-copy warps, scale producer
-constexpr uint32_t kSfaStageBytes = 2048;
-constexpr uint32_t kSfbStageBytes = 4096;
-constexpr uint32_t kNvStageBytes = kStageBytes + kSfaStageBytes + kSfbStageBytes;     // 38 KiB
-constexpr uint32_t kNvSfCol = 256, kNvSfColsPerStage = 48;
+constexpr uint32_t kNvSfCol = 256;                             // first scale column: after the accumulator(s)
 
-template <bool MX> struct BlockScaled {
+// TN = width of the cluster tile in columns of C.
+//   TN = 256: 256 x 256 tile, ONE accumulator (256 columns) and five 48-column scale areas.  Every operand
+//             byte is used for 256 outputs, the least L2 traffic per flop; the epilogue of a tile is exposed.
+//   TN = 128: 256 x 128 tile, TWO accumulators (2 x 128 columns) and six 32-column scale areas, 448 columns
+//             in all.  The epilogue of tile t drains one accumulator while the main loop of tile t + 1 fills
+//             the other; the price is half again as many operand bytes per flop (A is re-read for every 128
+//             columns instead of every 256) and instructions half as long.
+template <bool MX, int TN> struct BlockScaled {
     static constexpr uint32_t a_blocks = MX ? 2 : 4;            // 512-byte scale blocks of A per stage (per CTA)
-    static constexpr uint32_t b_blocks = MX ? 4 : 8;            // ... of B (all 256 columns)
+    static constexpr uint32_t b_blocks = (MX ? 4 : 8) * TN / 256; // ... of B (all TN columns)
     static constexpr uint32_t blocks = a_blocks + b_blocks;
     static constexpr uint32_t sf_bytes = blocks * 512;
     static constexpr uint32_t sf_per_kblock = MX ? 8 : 16;      // factors per row per 256 elements of K
+    static constexpr uint32_t b_rows = TN / 2;                  // rows of B this CTA stages
+    static constexpr uint32_t b_tile_bytes = b_rows * kRowBytesK;
+    static constexpr uint32_t tile_bytes = kHalfTileBytes + b_tile_bytes;          // A half + this CTA's part of B
+    static constexpr uint32_t stage_bytes = tile_bytes + 2048 + 4096 * TN / 256;   // + room for NVFP4's scale blocks
+    static constexpr int stages = TN == 256 ? 5 : 6;
+    static constexpr uint32_t n_acc = 256 / TN;                 // accumulators in tensor memory
+    static constexpr uint32_t sf_cols = 16 + TN / 8;            // tensor-memory columns per stage: 16 for A, 4 per 128 columns of B per instruction
+    static constexpr uint32_t b_cols_per_instr = TN / 32;       // scale columns of B per instruction (NVFP4)
+    static constexpr size_t smem_bytes = (size_t)stages * stage_bytes + kEpilogueWarps * kStagingBytes + 512 + 1024;
+    static_assert(kNvSfCol + stages * sf_cols <= 512, "tensor memory columns");
+    static_assert(stages <= kNvMaxStages, "barrier arrays");
 };
 
 struct NvGemmSmem {
-    uint64_t full[kNvStages];        // operand tiles of both CTAs landed (leader's barrier)
-    uint64_t sf_full[kNvStages];     // scale factors of both CTAs landed (leader's barrier)
-    uint64_t empty[kNvStages];       // the stage's MMAs retired (both CTAs)
-    uint64_t sf_ready[kNvStages];    // the stage's scale factors are in tensor memory (both CTAs)
-    uint64_t tmem_full;
-    uint64_t tmem_empty;
+    uint64_t full[kNvMaxStages];     // operand tiles of both CTAs landed (leader's barrier)
+    uint64_t sf_full[kNvMaxStages];  // scale factors of both CTAs landed (leader's barrier)
+    uint64_t empty[kNvMaxStages];    // the stage's MMAs retired (both CTAs)
+    uint64_t sf_ready[kNvMaxStages]; // the stage's scale factors are in tensor memory (both CTAs)
+    uint64_t tmem_full[2];           // per accumulator
+    uint64_t tmem_empty[2];
     uint32_t tmem_base;
 };
+static_assert(sizeof(NvGemmSmem) <= 512, "NvGemmSmem");
 
 // Row-major scale bytes [rows][k / block] -> 512-byte blocks in tensor-memory order, one
 // 32-bit word (four factors) per row per block.  NVFP4: 16 factors per row per stage =
@@ -600,7 +621,7 @@ __global__ void __launch_bounds__(256) pack_scales_kernel(uint32_t *__restrict__
     }
 }
 
-template <bool MX>
+template <bool MX, int TN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
     gemm_block_scaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
@@ -608,6 +629,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
 {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    using BS = BlockScaled<MX, TN>;
+    constexpr int kNvStages = BS::stages;
+    constexpr uint32_t kNvStageBytes = BS::stage_bytes, kNvSfColsPerStage = BS::sf_cols;
     uint8_t *staging = smem + (size_t)kNvStages * kNvStageBytes;                 // one 4 KiB box per epilogue warp
     NvGemmSmem *sh = reinterpret_cast<NvGemmSmem *>(staging + kEpilogueWarps * kStagingBytes);
 
@@ -615,7 +639,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
     const uint32_t rank = cluster_ctarank();
     const uint32_t cluster_id = blockIdx.x >> 1;
     const uint32_t n_clusters = gridDim.x >> 1;
-    const uint32_t tiles_m = p.m / kTileMN, tiles_n = p.n / kTileMN;
+    const uint32_t tiles_m = p.m / kTileMN, tiles_n = p.n / TN;
     const uint32_t n_tiles = tiles_m * tiles_n;
 
     if (threadIdx.x == 0) {
@@ -625,8 +649,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
             mbar_init(&sh->empty[s], 1);
             mbar_init(&sh->sf_ready[s], kNvCopyThreads);
         }
-        mbar_init(&sh->tmem_full, 1);
-        mbar_init(&sh->tmem_empty, 2 * kEpilogueWarps);
+        for (int acc = 0; acc < 2; acc++) {
+            mbar_init(&sh->tmem_full[acc], 1);
+            mbar_init(&sh->tmem_empty[acc], 2 * kEpilogueWarps);
+        }
         mbar_fence_init();
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
@@ -641,7 +667,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
     cluster_sync();
     tc_fence_after_sync();
     const uint32_t tmem = sh->tmem_base;
-    using BS = BlockScaled<MX>;
     constexpr int kScaleProducerWarp = 2 + kEpilogueWarps + kNvCopyThreads;
 
     if (warp == 0) {
@@ -655,7 +680,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
             uint32_t mb, nb;
             dense_tile_coords(tile, tiles_m, tiles_n, p.group, mb, nb);
             const int32_t row_a = (int32_t)(mb * kTileMN + rank * 128);
-            const int32_t row_b = (int32_t)(nb * kTileMN + rank * 128);
+            const int32_t row_b = (int32_t)(nb * TN + rank * BS::b_rows);
             const uint32_t align_at = p.k_blocks > p.align_at ? p.align_at : 0u;
             for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
                 if (kb == align_at) {
@@ -674,7 +699,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
                 const int32_t x = (int32_t)(kb * kRowBytesK);
                 if (elect_one()) {
                     if (rank == 0)
-                        mbar_expect_tx(&sh->full[s], 2 * kStageBytes);
+                        mbar_expect_tx(&sh->full[s], 2 * BS::tile_bytes);
                     tma_load_pair_at(st, &tmap_a, x, row_a, full0 + 8 * s);
                     tma_load_pair_at(st + kHalfTileBytes, &tmap_b, x, row_b, full0 + 8 * s);
                 }
@@ -701,7 +726,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
                     ok = false;
                     break;
                 }
-                uint8_t *sf = smem + (size_t)s * kNvStageBytes + kStageBytes;
+                uint8_t *sf = smem + (size_t)s * kNvStageBytes + BS::tile_bytes;
                 if (elect_one()) {
                     if (rank == 0)
                         mbar_expect_tx(&sh->sf_full[s], 2 * BS::sf_bytes);
@@ -720,17 +745,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
         // per-thread register, and an instruction cost its thread about 110 cycles.
         if (rank == 0) {
             // MXFP4: instruction kk reads bytes 0-1 (id 0) or 2-3 (id 2) of word kk / 2
-            const uint32_t idesc = make_idesc_block_scaled(256, 256, kFmtE2M1, kFmtE2M1, MX ? 1u : 0u, 0, 0);
-            const uint32_t idesc_hi = make_idesc_block_scaled(256, 256, kFmtE2M1, kFmtE2M1, 1u, 2, 2);
+            const uint32_t idesc = make_idesc_block_scaled(256, TN, kFmtE2M1, kFmtE2M1, MX ? 1u : 0u, 0, 0);
+            const uint32_t idesc_hi = make_idesc_block_scaled(256, TN, kFmtE2M1, kFmtE2M1, 1u, 2, 2);
             uint32_t it = 0, tcount = 0;
             bool ok = true;
             for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters, tcount++) {
-                if (tcount > 0 && !__all_sync(0xffffffffu, mbar_wait(&sh->tmem_empty, (tcount - 1) & 1) ? 1 : 0)) {
+                // accumulator `acc` is free again when the epilogue of its previous tile has read it out
+                const uint32_t acc = tcount % BS::n_acc, use = tcount / BS::n_acc;
+                if (use > 0 && !__all_sync(0xffffffffu, mbar_wait(&sh->tmem_empty[acc], (use - 1) & 1) ? 1 : 0)) {
                     if (lane == 0)
                         atomicCAS(p.status, 0u, 0x212u);
                     break;
                 }
                 tc_fence_after_sync();
+                const uint32_t d_t = tmem + acc * TN;
                 for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
                     const uint32_t s = it % kNvStages, round = it / kNvStages;
                     // the scale factors usually arrive first (6 KiB against 64): wait for them, then the tiles
@@ -750,10 +778,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
 #pragma unroll
                         for (uint32_t kk = 0; kk < 4; kk++) {
                             if constexpr (MX)
-                                mma2_mxf4_bs(tmem, ad + 2 * kk, bd + 2 * kk, (kk & 1) ? idesc_hi : idesc, sfa_t + 4 * (kk / 2),
-                                             sfb_t + 8 * (kk / 2), (kb | kk) ? 1u : 0u);
+                                mma2_mxf4_bs(d_t, ad + 2 * kk, bd + 2 * kk, (kk & 1) ? idesc_hi : idesc, sfa_t + 4 * (kk / 2),
+                                             sfb_t + BS::b_cols_per_instr * (kk / 2), (kb | kk) ? 1u : 0u);
                             else
-                                mma2_nvf4_bs(tmem, ad + 2 * kk, bd + 2 * kk, idesc, sfa_t + 4 * kk, sfb_t + 8 * kk,
+                                mma2_nvf4_bs(d_t, ad + 2 * kk, bd + 2 * kk, idesc, sfa_t + 4 * kk, sfb_t + BS::b_cols_per_instr * kk,
                                              (kb | kk) ? 1u : 0u);
                         }
                         tc_commit_pair(&sh->empty[s], 3);
@@ -761,7 +789,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
                     __syncwarp();
                 }
                 if (ok && elect_one())
-                    tc_commit_pair(&sh->tmem_full, 3);
+                    tc_commit_pair(&sh->tmem_full[acc], 3);
                 __syncwarp();
             }
         }
@@ -784,7 +812,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
                         break;
                     }
                     tc_fence_after_sync();
-                    const uint32_t sf_s = smem_u32(smem + (size_t)s * kNvStageBytes) + kStageBytes;
+                    const uint32_t sf_s = smem_u32(smem + (size_t)s * kNvStageBytes) + BS::tile_bytes;
                     const uint32_t sf_t = tmem + kNvSfCol + s * kNvSfColsPerStage;
                     if (elect_one()) {
                         // 512-byte blocks of the stage: A's (4 columns each, from column 0), then B's (from column 16)
@@ -808,14 +836,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
         for (uint32_t tile = cluster_id; tile < n_tiles; tile += n_clusters, tcount++) {
             uint32_t mb, nb;
             dense_tile_coords(tile, tiles_m, tiles_n, p.group, mb, nb);
-            if (!__all_sync(0xffffffffu, mbar_wait(&sh->tmem_full, tcount & 1) ? 1 : 0)) {
+            const uint32_t acc = tcount % BS::n_acc, use = tcount / BS::n_acc;
+            if (!__all_sync(0xffffffffu, mbar_wait(&sh->tmem_full[acc], use & 1) ? 1 : 0)) {
                 if (lane == 0)
                     atomicCAS(p.status, 0u, 0x214u);
                 break;
             }
             tc_fence_after_sync();
-            drain_warp_tile_early(tmem + col_half * 128 + ((q * 32) << 16), mb * kTileMN + rank * 128 + q * 32,
-                                  nb * kTileMN + col_half * 128, box, &tmap_c, p.alpha, &sh->tmem_empty, lane);
+            drain_warp_tile_early<TN / 128>(tmem + acc * TN + col_half * (TN / 2) + ((q * 32) << 16), mb * kTileMN + rank * 128 + q * 32,
+                                            nb * TN + col_half * (TN / 2), box, &tmap_c, p.alpha, &sh->tmem_empty[acc], lane);
         }
         if (lane == 0)
             bulk_wait<0>();
@@ -852,8 +881,8 @@ static int get_encode_fn(EncodeTiledFn *out)
     return CLPK_OK;
 }
 
-// Row-major [rows][row_bytes] operand, box = 128 rows x 128 bytes, 128-byte swizzle.
-static int make_operand_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t row_bytes)
+// Row-major [rows][row_bytes] operand, box = box_rows (128 unless said otherwise) x 128 bytes, 128-byte swizzle.
+static int make_operand_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows = 128)
 {
     EncodeTiledFn enc;
     int rc = get_encode_fn(&enc);
@@ -861,7 +890,7 @@ static int make_operand_map(CUtensorMap *map, const void *base, uint64_t rows, u
         return rc;
     const cuuint64_t dims[2] = {row_bytes, rows};
     const cuuint64_t strides[1] = {row_bytes};
-    const cuuint32_t box[2] = {kRowBytesK, 128};
+    const cuuint32_t box[2] = {kRowBytesK, box_rows};
     const cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -919,15 +948,19 @@ static int make_scale_map(CUtensorMap *map, const void *base, uint64_t n_rows, u
     return CLPK_OK;
 }
 
-constexpr size_t kNvGemmSmemBytes = (size_t)kNvStages * kNvStageBytes + kEpilogueWarps * kStagingBytes + sizeof(NvGemmSmem) + 1024;
 
 constexpr size_t kGemmSmemBytes = (size_t)kDenseStages * kDenseStageBytes + kEpilogueWarps * kStagingBytes + sizeof(DenseSmem) + 1024;
 
-// One wave counter per launch, from a small ring so that launches on different streams
-// do not share one; zeroed in stream order before the kernel.
+// One wave counter per launch, from a ring of 32 per device so that launches on different streams
+// do not share one; zeroed in stream order before the kernel.  The slot index comes from one
+// process-wide counter, so a slot is handed out again 32 launches later: with more than 32 aligned
+// GEMMs in flight at once on one device (across streams) two running kernels would share a counter.
+// That costs alignment, not correctness -- a producer that does not see its wave complete within
+// 40 us stops taking part -- but callers that want the alignment keep at most 32 in flight.
 constexpr int kSyncSlots = 32;
 __device__ unsigned int g_wave_sync[kSyncSlots];
 static std::atomic<unsigned> g_next_sync_slot{0};
+static thread_local int g_last_aligned = -1;
 
 // Launches a persistent cluster kernel whose last parameter is GemmParams: cooperatively with a
 // fresh wave counter when the alignment is on, plainly (and unaligned) otherwise.
@@ -937,11 +970,11 @@ static int launch_persistent(Kernel kernel, const char *what, int threads, size_
 {
     CLPK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int grid = (num_sms() / 2) * 2;
-    const char *off = getenv("CLPK_GEMM_NO_ALIGN");
     p.wave_sync = nullptr;
+    g_last_aligned = 0;
     // nothing to keep in step in the first two waves: small problems skip the counter and its memset
     const bool worth_aligning = n_tiles > 2u * (uint32_t)(grid / 2) * p.align_period;
-    if (worth_aligning && !(off && off[0] == '1')) {
+    if (worth_aligning && tuning(CLPK_TUNE_GEMM_NO_ALIGN) != 1) {
         unsigned int *base = nullptr;
         CLPK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&base), g_wave_sync));
         p.wave_sync = base + g_next_sync_slot.fetch_add(1) % kSyncSlots;
@@ -957,9 +990,16 @@ static int launch_persistent(Kernel kernel, const char *what, int threads, size_
         attr[0].val.cooperative = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        if (cudaLaunchKernelEx(&cfg, kernel, maps..., p) == cudaSuccess)
+        const cudaError_t ce = cudaLaunchKernelEx(&cfg, kernel, maps..., p);
+        if (ce == cudaSuccess) {
+            g_last_aligned = 1;
             return CLPK_OK;
-        (void)cudaGetLastError();       // not co-schedulable here: run without the alignment
+        }
+        // Only "the grid cannot be co-resident here" (another context holds SMs, MPS limits) is a
+        // reason to run without the alignment; anything else is a real error and is reported as one.
+        if (ce != cudaErrorCooperativeLaunchTooLarge && ce != cudaErrorLaunchOutOfResources)
+            return cuda_fail(ce, what);
+        (void)cudaGetLastError();
         p.wave_sync = nullptr;
     }
     cudaLaunchConfig_t plain = {};
@@ -986,6 +1026,8 @@ using namespace clpk;
 
 extern "C" {
 
+int clpk_gemm_last_launch_aligned(void) { return g_last_aligned; }
+
 int clpk_gemm_workspace_bytes(int dtype, uint32_t m, uint32_t n, uint32_t k, size_t *bytes)
 {
     CLPK_REQUIRE(bytes, "bytes is NULL");
@@ -995,6 +1037,21 @@ int clpk_gemm_workspace_bytes(int dtype, uint32_t m, uint32_t n, uint32_t k, siz
     if (dtype == CLPK_DT_MXF4)              // packed into 4-byte words of which each instruction uses two bytes
         *bytes = ((size_t)m + n) * (k / 32);
     return CLPK_OK;
+}
+
+// Width of the block-scaled kernel's cluster tile for a problem: 256 (one accumulator, least operand
+// traffic) or 128 (two accumulators, the epilogue overlaps the next tile).  The GEMM_FP4_TILE knob
+// forces one; the choice also fixes the order of B's scale blocks in the workspace, so a workspace
+// packed by clpk_gemm_pack_scales belongs to the knob setting it was packed under.
+static uint32_t fp4_tile_n(uint32_t m, uint32_t n, uint32_t k)
+{
+    const int t = tuning(CLPK_TUNE_GEMM_FP4_TILE);
+    if (t == 1)
+        return 256;
+    if (t == 2)
+        return 128;
+    (void)m; (void)n; (void)k;
+    return 256;
 }
 
 // Row-major scale bytes of both operands -> tile order in the workspace (A's blocks, then B's).
@@ -1011,8 +1068,10 @@ static int pack_scales(const clpk_gemm_args_t *a, cudaStream_t s)
     const dim3 ga((words_per_row + 31) / 32, a->m / 128), gb((words_per_row + 31) / 32, a->n / 128);
     pack_scales_kernel<<<ga, 256, 0, s>>>(reinterpret_cast<uint32_t *>(wsa), static_cast<const uint32_t *>(a->d_sfa),
                                           words_per_row, kblocks, 0, words);
+    // B's blocks: per 256 columns [k block][instruction][column half] for the 256-wide tile, per 128 columns
+    // [k block][instruction] (A's order) for the 128-wide one
     pack_scales_kernel<<<gb, 256, 0, s>>>(reinterpret_cast<uint32_t *>(wsb), static_cast<const uint32_t *>(a->d_sfb),
-                                          words_per_row, kblocks, 1, words);
+                                          words_per_row, kblocks, fp4_tile_n(a->m, a->n, a->k) == 256 ? 1 : 0, words);
     CLPK_LAUNCH_CHECK("pack_scales");
     return CLPK_OK;
 }
@@ -1036,6 +1095,12 @@ int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
         return rc;
     CLPK_REQUIRE(a, "args is NULL");
     CLPK_REQUIRE(a->d_a && a->d_b && a->d_c && a->d_status, "NULL buffer");
+    if (a->dtype == CLPK_DT_F32 || a->dtype == CLPK_DT_F64) {
+        // no tcgen05 kind for these: the CUDA-core fp32 and DMMA fp64 kernels of simt_gemm.cu
+        CLPK_CUDA(cudaMemsetAsync(a->d_status, 0, sizeof(uint32_t), as_stream(stream)));
+        g_last_aligned = 0;
+        return launch_simt_gemm(a->dtype, a->d_a, a->d_b, a->d_c, a->m, a->n, a->k, a->alpha, as_stream(stream));
+    }
     CLPK_REQUIRE(a->m % 256 == 0 && a->n % 256 == 0 && a->m > 0 && a->n > 0,
                  "M and N must be positive multiples of 256 (got %u, %u)", a->m, a->n);
     CLPK_REQUIRE(a->k > 0, "K must be positive");
@@ -1086,10 +1151,10 @@ int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
     p.wave_sync = nullptr;
     p.align_at = 2;
     p.align_period = block_scaled ? 8 : 1;
-    if (const char *e = getenv("CLPK_GEMM_ALIGN_AT"))
-        p.align_at = (uint32_t)atoi(e);
-    if (const char *e = getenv("CLPK_GEMM_GROUP"))
-        p.group = (uint32_t)atoi(e) > 0 ? (uint32_t)atoi(e) : p.group;
+    if (const int t = tuning(CLPK_TUNE_GEMM_ALIGN_AT); t >= 0)
+        p.align_at = (uint32_t)t;
+    if (const int t = tuning(CLPK_TUNE_GEMM_GROUP); t > 0)
+        p.group = (uint32_t)t;
 
 
     if (block_scaled) {
@@ -1105,20 +1170,35 @@ int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
             if (rc != CLPK_OK)
                 return rc;
         }
+        const uint32_t tn = fp4_tile_n(a->m, a->n, a->k);
         CUtensorMap tsa, tsb;
         rc = make_scale_map(&tsa, wsa, sfa_bytes / 512, words);
         if (rc != CLPK_OK)
             return rc;
-        rc = make_scale_map(&tsb, wsb, sfb_bytes / 512, 2 * words);
+        rc = make_scale_map(&tsb, wsb, sfb_bytes / 512, words * tn / 128);
         if (rc != CLPK_OK)
             return rc;
         CUtensorMap tc;
         rc = make_output_map(&tc, a->d_c, a->m, a->n, a->dtype);
         if (rc != CLPK_OK)
             return rc;
-        const uint32_t n_tiles = (a->m / kTileMN) * (a->n / kTileMN);
-        return mx ? launch_persistent(gemm_block_scaled_kernel<true>, "gemm_mxf4", kNvGemmThreads, kNvGemmSmemBytes, s, p, n_tiles, ta, tb, tsa, tsb, tc)
-                  : launch_persistent(gemm_block_scaled_kernel<false>, "gemm_nvf4", kNvGemmThreads, kNvGemmSmemBytes, s, p, n_tiles, ta, tb, tsa, tsb, tc);
+        const uint32_t n_tiles = (a->m / kTileMN) * (a->n / tn);
+        if (tn == 128) {
+            rc = make_operand_map(&tb, a->d_b, a->n, row_bytes, 64);       // each CTA stages 64 rows of B per stage
+            if (rc != CLPK_OK)
+                return rc;
+            if (tuning(CLPK_TUNE_GEMM_GROUP) <= 0)
+                p.group *= 2;                                              // the same panel width in elements
+            p.align_period *= 2;
+            return mx ? launch_persistent(gemm_block_scaled_kernel<true, 128>, "gemm_mxf4 (256x128)", kNvGemmThreads,
+                                          BlockScaled<true, 128>::smem_bytes, s, p, n_tiles, ta, tb, tsa, tsb, tc)
+                      : launch_persistent(gemm_block_scaled_kernel<false, 128>, "gemm_nvf4 (256x128)", kNvGemmThreads,
+                                          BlockScaled<false, 128>::smem_bytes, s, p, n_tiles, ta, tb, tsa, tsb, tc);
+        }
+        return mx ? launch_persistent(gemm_block_scaled_kernel<true, 256>, "gemm_mxf4", kNvGemmThreads,
+                                      BlockScaled<true, 256>::smem_bytes, s, p, n_tiles, ta, tb, tsa, tsb, tc)
+                  : launch_persistent(gemm_block_scaled_kernel<false, 256>, "gemm_nvf4", kNvGemmThreads,
+                                      BlockScaled<false, 256>::smem_bytes, s, p, n_tiles, ta, tb, tsa, tsb, tc);
     }
     CUtensorMap tc;
     rc = make_output_map(&tc, a->d_c, a->m, a->n, a->dtype);

@@ -52,6 +52,8 @@ struct PeakParams {
     uint32_t *out;
     uint32_t *checksum;
     uint32_t *status;
+    unsigned long long *clock;  // optional: CTA 0 stores {SM cycles, nanoseconds} from its first issue to its last retire
+    uint32_t lone_lane;         // 1: the issue loop runs in one thread (the form kept for comparison)
 };
 
 // Copy a [rows][32 B] row-major tile into the core-matrix layout.
@@ -191,17 +193,33 @@ __global__ void __launch_bounds__(128) mma_peak_kernel(PeakParams p)
         tc_fence_after_sync();
     }
 
-    if (threadIdx.x == 0 && rank == 0) {
+    // The issue loop runs in the whole of warp 0 and one elected lane issues: inside `if (lane == 0)`
+    // every tcgen05.mma costs its thread about as long as the tensor core needs for it, so a lone
+    // issuer cannot run ahead of the pipe; as a convergent warp an issue takes a quarter of that.
+    unsigned long long c0 = 0, t0 = 0;
+    if (warp == 0 && rank == 0) {
         const uint64_t ad = make_smem_desc(smem_u32(sA), 128, 256, kSwizzleNone);
         const uint64_t bd = make_smem_desc(smem_u32(sB), 128, 256, kSwizzleNone);
         const uint32_t sfa = tmem + kSfaCol, sfb = tmem + kSfbCol;
-        issue_mma<KIND, PAIR>(tmem, ad, bd, sfa, sfb, 0u);
-        for (uint32_t i = 1; i < p.n_mma; i++)
-            issue_mma<KIND, PAIR>(tmem, ad, bd, sfa, sfb, 1u);
-        if constexpr (PAIR)
-            tc_commit_pair(bar, 3);
-        else
-            tc_commit(bar);
+        c0 = clock64();
+        t0 = globaltimer_ns();
+        if (p.lone_lane) {
+            if (lane == 0) {
+                issue_mma<KIND, PAIR>(tmem, ad, bd, sfa, sfb, 0u);
+                for (uint32_t i = 1; i < p.n_mma; i++)
+                    issue_mma<KIND, PAIR>(tmem, ad, bd, sfa, sfb, 1u);
+                if constexpr (PAIR) tc_commit_pair(bar, 3); else tc_commit(bar);
+            }
+        } else {
+            if (elect_one())
+                issue_mma<KIND, PAIR>(tmem, ad, bd, sfa, sfb, 0u);
+            for (uint32_t i = 1; i < p.n_mma; i++)
+                if (elect_one())
+                    issue_mma<KIND, PAIR>(tmem, ad, bd, sfa, sfb, 1u);
+            if (elect_one()) {
+                if constexpr (PAIR) tc_commit_pair(bar, 3); else tc_commit(bar);
+            }
+        }
     }
     __syncwarp();
 
@@ -209,6 +227,10 @@ __global__ void __launch_bounds__(128) mma_peak_kernel(PeakParams p)
     // warp-aligned instruction and the checksum uses a CTA barrier.
     const int done = __syncthreads_and(mbar_wait(bar, 0) ? 1 : 0);
     tc_fence_after_sync();
+    if (p.clock && blockIdx.x == 0 && threadIdx.x == 0) {
+        p.clock[0] = clock64() - c0;
+        p.clock[1] = globaltimer_ns() - t0;
+    }
     if (!done && threadIdx.x == 0)
         atomicCAS(p.status, 0u, 0x100u + (uint32_t)KIND);
 
@@ -348,9 +370,12 @@ __global__ void __launch_bounds__(128) mma_peak_sparse_kernel(PeakParams p, uint
         tc_fence_after_sync();
     }
 
-    if (threadIdx.x == 0 && rank == 0) {
+    unsigned long long c0 = 0, t0 = 0;
+    if (warp == 0 && rank == 0) {
         const uint64_t ad = make_smem_desc(smem_u32(sA), 128, 256, kSwizzleNone);
         const uint64_t bd = make_smem_desc(smem_u32(sB), 16, 1024, kSwizzle128B);
+        c0 = clock64();
+        t0 = globaltimer_ns();
         uint32_t idesc;
         if constexpr (KIND == CLPK_MMA_I8_SP)
             idesc = make_idesc(kM, kTileN, kFmtS8, kFmtS8, kAccS32, true);
@@ -360,6 +385,9 @@ __global__ void __launch_bounds__(128) mma_peak_sparse_kernel(PeakParams p, uint
             idesc = make_idesc_block_scaled(kM, kTileN, kFmtE2M1, kFmtE2M1, KIND == CLPK_MMA_MXF4_SP ? 1u : 0u, 0, 0, true);
         for (uint32_t i = 0; i < p.n_mma; i++) {
             const uint32_t acc = i ? 1u : 0u, meta_t = tmem + kMetaCol, sfa_t = tmem + kSpSfaCol, sfb_t = tmem + kSpSfbCol;
+            // whole warp in the loop, one lane issues (see the dense kernel); lone_lane keeps lane 0 alone
+            if (!(p.lone_lane ? lane == 0 : elect_one() != 0))
+                continue;
             if constexpr (KIND == CLPK_MMA_I8_SP) {
                 if constexpr (PAIR) mma2_i8_sp(tmem, ad, bd, idesc, meta_t, acc); else mma_i8_sp(tmem, ad, bd, idesc, meta_t, acc);
             } else if constexpr (KIND == CLPK_MMA_E4M3_SP) {
@@ -372,15 +400,18 @@ __global__ void __launch_bounds__(128) mma_peak_sparse_kernel(PeakParams p, uint
                 else mma_nvf4_sp_bs(tmem, ad, bd, idesc, meta_t, sfa_t, sfb_t, acc);
             }
         }
-        if constexpr (PAIR)
-            tc_commit_pair(bar, 3);
-        else
-            tc_commit(bar);
+        if (p.lone_lane ? lane == 0 : elect_one() != 0) {
+            if constexpr (PAIR) tc_commit_pair(bar, 3); else tc_commit(bar);
+        }
     }
     __syncwarp();
 
     const int done = __syncthreads_and(mbar_wait(bar, 0) ? 1 : 0);
     tc_fence_after_sync();
+    if (p.clock && blockIdx.x == 0 && threadIdx.x == 0) {
+        p.clock[0] = clock64() - c0;
+        p.clock[1] = globaltimer_ns() - t0;
+    }
     if (!done && threadIdx.x == 0)
         atomicCAS(p.status, 0u, 0x100u + (uint32_t)KIND);
 
@@ -423,10 +454,10 @@ template <int KIND>
 static int launch_peak_sparse(const PeakParams &p, uint32_t grid, uint32_t meta_cols, cudaStream_t s)
 {
     const size_t smem = (size_t)(smem_optin_bytes() * 3 / 5);      // one CTA per SM (512 TMEM columns)
-    // CTA pairs by default (a lone CTA is bound by shared-memory reads); CLPK_MMA_PAIR=0 / 1 overrides.
+    // CTA pairs by default (a lone CTA is bound by shared-memory reads); the MMA_PAIR knob overrides.
     bool pair = true;
-    if (const char *e = getenv("CLPK_MMA_PAIR"))
-        pair = e[0] == '1';
+    if (const int t = tuning(CLPK_TUNE_MMA_PAIR); t >= 0)
+        pair = t == 1;
     if (grid % 2 == 0 && pair) {
         CLPK_CUDA(cudaFuncSetAttribute(mma_peak_sparse_kernel<KIND, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         cudaLaunchConfig_t cfg = {};
@@ -486,10 +517,10 @@ static int launch_peak(const PeakParams &p, uint32_t grid, cudaStream_t s)
     const int optin = smem_optin_bytes();
     const size_t smem = KindTraits<KIND>::scaled ? (size_t)(optin * 3 / 5) : (size_t)(optin * 2 / 5);
     // CTA pairs (cta_group::2) where they measured faster on B200 -- int8 +1.5..4 %, MXFP4 / NVFP4 +2..4 %;
-    // fp16 / bf16 / fp8 lose 4..7 % as pairs and stay solo.  CLPK_MMA_PAIR=0 / 1 overrides for every kind.
+    // fp16 / bf16 / fp8 lose 4..7 % as pairs and stay solo.  The MMA_PAIR knob (0 / 1) overrides for every kind.
     bool pair = KIND == CLPK_MMA_I8 || KIND == CLPK_MMA_MXF4 || KIND == CLPK_MMA_NVF4;
-    if (const char *e = getenv("CLPK_MMA_PAIR"))
-        pair = e[0] == '1';
+    if (const int t = tuning(CLPK_TUNE_MMA_PAIR); t >= 0)
+        pair = t == 1;
     if (grid % 2 == 0 && pair) {
         CLPK_CUDA(cudaFuncSetAttribute(mma_peak_kernel<KIND, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         cudaLaunchConfig_t cfg = {};
@@ -567,6 +598,8 @@ int clpk_mma_peak(const clpk_mma_peak_args_t *a, void *stream)
     p.out = static_cast<uint32_t *>(a->d_out);
     p.checksum = a->d_checksum;
     p.status = a->d_status;
+    p.clock = a->d_clock;
+    p.lone_lane = tuning(CLPK_TUNE_MMA_LONE_LANE) == 1 ? 1u : 0u;
     switch (a->kind) {
     case CLPK_MMA_E4M3_SP: return launch_peak_sparse<CLPK_MMA_E4M3_SP>(p, a->grid, (uint32_t)ki.k / 32, s);
     case CLPK_MMA_I8_SP:   return launch_peak_sparse<CLPK_MMA_I8_SP>(p, a->grid, (uint32_t)ki.k / 32, s);

@@ -1,0 +1,237 @@
+// The two GEMM rows that have no tcgen05 kind: fp32 on the CUDA cores and fp64 on the
+// warp-level DMMA path.  They take the place of the reference's cuBLASLt "fp32" and
+// "fp64" rows (src/cuda/cuda_blas.cpp:567-581) behind the same clpk_gemm entry point:
+// C[M][N] = alpha * A[M][K] * B[N][K]^T, both operands K-contiguous, C row-major in the
+// operand type.
+//
+// fp32 (sgemm_kernel).  128 x 128 x 16 tile per CTA of 256 threads, 8 x 8 outputs per
+// thread as four 4 x 4 blocks so that every shared-memory read is a conflict-free
+// 128-bit load; operands are transposed into shared memory ([k][m]) on the way in, the
+// next k block travels global -> registers while the current one is multiplied, two
+// shared-memory buffers.  Bound: FFMA issue, 128 FMA / clock / SM (B200: 148 SMs x 128
+// x 2 x 1.965 GHz = 74.4 TFLOPS); the inner loop issues 64 FFMA per 4 LDS.128.
+//
+// fp64 (dgemm_kernel).  128 x 128 x 16 tile per CTA of 256 threads = 8 warps in a 2 x 4
+// grid, 64 x 32 outputs per warp = 8 x 4 m8n8k4 accumulator tiles (128 registers of
+// accumulators per thread).  Operands go global -> shared with cp.async (16 bytes), three
+// stages; rows are padded to 20 doubles so that the fragment reads (lane -> row lane/4,
+// k lane%4) fall in 16 distinct 8-byte banks per half warp.  Bound: the DMMA pipe, 64
+// fp64 FMA / clock / SM, the same rate as the scalar DFMA pipe (37.2 TFLOPS at 1.965 GHz).
+//
+// CTAs walk C in groups of 16 tile rows so that the operand panels a wave of CTAs needs
+// stay in L2.  Work 2*M*N*K flop; minimum HBM bytes (M*K + N*K + M*N) * element.
+#include <cuda_pipeline.h>
+
+#include "../clpk_internal.h"
+
+namespace clpk {
+
+constexpr int kSimtTile = 128;
+constexpr int kSimtBK = 16;
+constexpr int kRasterGroup = 16;
+
+// blockIdx.x -> (tile row, tile column), column-major inside groups of kRasterGroup tile rows
+__device__ __forceinline__ void raster(uint32_t tiles_m, uint32_t tiles_n, uint32_t *tm, uint32_t *tn)
+{
+    const uint32_t per_group = kRasterGroup * tiles_n;
+    const uint32_t g = blockIdx.x / per_group, r = blockIdx.x % per_group;
+    const uint32_t rows = min((uint32_t)kRasterGroup, tiles_m - g * kRasterGroup);
+    *tm = g * kRasterGroup + r % rows;
+    *tn = r / rows;
+}
+
+// ---------------------------------------------------------------------------------------------
+// fp32
+// ---------------------------------------------------------------------------------------------
+
+constexpr int kSgemmPad = 4;
+constexpr int kSgemmLd = kSimtTile + kSgemmPad;          // floats per k row of a shared tile
+
+__global__ void __launch_bounds__(256, 2)
+sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__restrict__ C, uint32_t M, uint32_t N,
+             uint32_t K, float alpha)
+{
+    __shared__ __align__(16) float sA[2][kSimtBK][kSgemmLd];
+    __shared__ __align__(16) float sB[2][kSimtBK][kSgemmLd];
+    uint32_t tm, tn;
+    raster(M / kSimtTile, N / kSimtTile, &tm, &tn);
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const float *gA = A + (size_t)tm * kSimtTile * K, *gB = B + (size_t)tn * kSimtTile * K;
+
+    // global -> registers: 128 rows x 16 floats per operand = 512 float4, two per thread
+    const int lrow = tid >> 2, lk = (tid & 3) * 4;
+    float4 ra[2], rb[2];
+    auto fetch = [&](uint32_t k0) {
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            ra[h] = *reinterpret_cast<const float4 *>(gA + (size_t)(lrow + 64 * h) * K + k0 + lk);
+            rb[h] = *reinterpret_cast<const float4 *>(gB + (size_t)(lrow + 64 * h) * K + k0 + lk);
+        }
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int r = lrow + 64 * h;
+            sA[buf][lk + 0][r] = ra[h].x; sA[buf][lk + 1][r] = ra[h].y; sA[buf][lk + 2][r] = ra[h].z; sA[buf][lk + 3][r] = ra[h].w;
+            sB[buf][lk + 0][r] = rb[h].x; sB[buf][lk + 1][r] = rb[h].y; sB[buf][lk + 2][r] = rb[h].z; sB[buf][lk + 3][r] = rb[h].w;
+        }
+    };
+
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            acc[i][j] = 0.0f;
+
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    const uint32_t nk = K / kSimtBK;
+    for (uint32_t kb = 0; kb < nk; kb++) {
+        const int cur = kb & 1;
+        if (kb + 1 < nk)
+            fetch((kb + 1) * kSimtBK);
+#pragma unroll
+        for (int k = 0; k < kSimtBK; k++) {
+            const float4 a0 = *reinterpret_cast<const float4 *>(&sA[cur][k][ty * 4]);
+            const float4 a1 = *reinterpret_cast<const float4 *>(&sA[cur][k][64 + ty * 4]);
+            const float4 b0 = *reinterpret_cast<const float4 *>(&sB[cur][k][tx * 4]);
+            const float4 b1 = *reinterpret_cast<const float4 *>(&sB[cur][k][64 + tx * 4]);
+            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        if (kb + 1 < nk) {
+            stash(cur ^ 1);
+            __syncthreads();
+        }
+    }
+
+    float *gC = C + (size_t)tm * kSimtTile * N + (size_t)tn * kSimtTile;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int r = (i < 4 ? 0 : 64) + ty * 4 + (i & 3);
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const float4 v = make_float4(alpha * acc[i][4 * h], alpha * acc[i][4 * h + 1], alpha * acc[i][4 * h + 2],
+                                         alpha * acc[i][4 * h + 3]);
+            *reinterpret_cast<float4 *>(gC + (size_t)r * N + 64 * h + tx * 4) = v;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// fp64
+// ---------------------------------------------------------------------------------------------
+
+constexpr int kDgemmLd = kSimtBK + 4;                    // doubles per row of a shared tile (160 bytes)
+constexpr int kDgemmStages = 3;
+constexpr size_t kDgemmStageDoubles = 2 * (size_t)kSimtTile * kDgemmLd;
+constexpr size_t kDgemmSmemBytes = kDgemmStages * kDgemmStageDoubles * sizeof(double);
+
+__device__ __forceinline__ void dmma_m8n8k4(double &d0, double &d1, double a, double b)
+{
+    asm("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0, %1}, {%2}, {%3}, {%0, %1};"
+        : "+d"(d0), "+d"(d1)
+        : "d"(a), "d"(b));
+}
+
+__global__ void __launch_bounds__(256, 1)
+dgemm_kernel(const double *__restrict__ A, const double *__restrict__ B, double *__restrict__ C, uint32_t M, uint32_t N,
+             uint32_t K, double alpha)
+{
+    extern __shared__ __align__(16) double dsm[];
+    uint32_t tm, tn;
+    raster(M / kSimtTile, N / kSimtTile, &tm, &tn);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = (warp >> 2) * 64, wn = (warp & 3) * 32;          // this warp's 64 x 32 corner inside the tile
+    const double *gA = A + (size_t)tm * kSimtTile * K, *gB = B + (size_t)tn * kSimtTile * K;
+
+    // one stage = A tile then B tile, [128][kDgemmLd] doubles each; 16-byte chunks: 128 rows x 8 per operand
+    auto load_stage = [&](int stage, uint32_t k0) {
+        double *sa = dsm + (size_t)stage * kDgemmStageDoubles, *sb = sa + (size_t)kSimtTile * kDgemmLd;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int c = tid + 256 * i, r = c >> 3, kc = (c & 7) * 2;
+            __pipeline_memcpy_async(sa + r * kDgemmLd + kc, gA + (size_t)r * K + k0 + kc, 16);
+            __pipeline_memcpy_async(sb + r * kDgemmLd + kc, gB + (size_t)r * K + k0 + kc, 16);
+        }
+    };
+
+    double acc[8][4][2];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            acc[i][j][0] = acc[i][j][1] = 0.0;
+
+    const uint32_t nk = K / kSimtBK;
+#pragma unroll
+    for (int s = 0; s < kDgemmStages - 1; s++) {
+        if ((uint32_t)s < nk)
+            load_stage(s, s * kSimtBK);
+        __pipeline_commit();
+    }
+    const int fr = lane >> 2, fk = lane & 3;                        // fragment row (or column of B) and k of this lane
+    for (uint32_t kb = 0; kb < nk; kb++) {
+        __pipeline_wait_prior(kDgemmStages - 2);
+        __syncthreads();                                            // stage kb has landed; stage kb-1 is free for reuse
+        if (kb + kDgemmStages - 1 < nk)
+            load_stage((kb + kDgemmStages - 1) % kDgemmStages, (kb + kDgemmStages - 1) * kSimtBK);
+        __pipeline_commit();
+        const double *sa = dsm + (size_t)(kb % kDgemmStages) * kDgemmStageDoubles, *sb = sa + (size_t)kSimtTile * kDgemmLd;
+#pragma unroll
+        for (int k4 = 0; k4 < kSimtBK; k4 += 4) {
+            double a[8], b[4];
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+                a[i] = sa[(wm + 8 * i + fr) * kDgemmLd + k4 + fk];
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                b[j] = sb[(wn + 8 * j + fr) * kDgemmLd + k4 + fk];
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    dmma_m8n8k4(acc[i][j][0], acc[i][j][1], a[i], b[j]);
+        }
+    }
+    __pipeline_wait_prior(0);
+
+    // accumulator tile (i, j): this lane holds row lane/4, columns 2*(lane%4) and the next one
+    double *gC = C + ((size_t)tm * kSimtTile + wm) * N + (size_t)tn * kSimtTile + wn;
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            *reinterpret_cast<double2 *>(gC + (size_t)(8 * i + fr) * N + 8 * j + 2 * fk) =
+                make_double2(alpha * acc[i][j][0], alpha * acc[i][j][1]);
+}
+
+int launch_simt_gemm(int dtype, const void *a, const void *b, void *c, uint32_t m, uint32_t n, uint32_t k, float alpha,
+                     cudaStream_t s)
+{
+    CLPK_REQUIRE(m % kSimtTile == 0 && n % kSimtTile == 0 && m > 0 && n > 0, "M and N must be multiples of %d", kSimtTile);
+    CLPK_REQUIRE(k % kSimtBK == 0 && k > 0, "K must be a multiple of %d", kSimtBK);
+    CLPK_REQUIRE(((uintptr_t)a % 16) == 0 && ((uintptr_t)b % 16) == 0 && ((uintptr_t)c % 16) == 0, "operands must be 16-byte aligned");
+    const uint64_t tiles = (uint64_t)(m / kSimtTile) * (n / kSimtTile);
+    CLPK_REQUIRE(tiles <= 0x7FFFFFFFull, "too many tiles");
+    if (dtype == CLPK_DT_F32) {
+        sgemm_kernel<<<(unsigned)tiles, 256, 0, s>>>(static_cast<const float *>(a), static_cast<const float *>(b),
+                                                     static_cast<float *>(c), m, n, k, alpha);
+        CLPK_LAUNCH_CHECK("sgemm");
+    } else {
+        CLPK_CUDA(cudaFuncSetAttribute(dgemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDgemmSmemBytes));
+        dgemm_kernel<<<(unsigned)tiles, 256, kDgemmSmemBytes, s>>>(static_cast<const double *>(a), static_cast<const double *>(b),
+                                                                    static_cast<double *>(c), m, n, k, (double)alpha);
+        CLPK_LAUNCH_CHECK("dgemm");
+    }
+    return CLPK_OK;
+}
+
+} // namespace clpk

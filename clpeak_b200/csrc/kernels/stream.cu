@@ -14,6 +14,7 @@
 // read n, copy 2n, triad 3n bytes for n-byte arrays; GPUs do not
 // write-allocate, so these are the true DRAM bytes.
 #include <atomic>
+#include <mutex>
 
 #include "../clpk_internal.h"
 #include "../clpk_ptx.cuh"
@@ -521,14 +522,19 @@ __global__ void __launch_bounds__(192) stream_triad_tma(float *__restrict__ a,
 // Per-device status word for the TMA kernels (timeouts are reported through
 // the return code of the *next* synchronising call via clpk_stream_status()).
 static uint32_t *g_status[64] = {nullptr};
+static std::mutex g_lazy_mutex;          // first use of a device by two host threads at once allocates once
 
 static int status_word(uint32_t **out)
 {
     int dev = 0;
     CLPK_CUDA(cudaGetDevice(&dev));
+    CLPK_REQUIRE(dev >= 0 && dev < 64, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lk(g_lazy_mutex);
     if (!g_status[dev]) {
-        CLPK_CUDA(cudaMalloc(&g_status[dev], sizeof(uint32_t)));
-        CLPK_CUDA(cudaMemset(g_status[dev], 0, sizeof(uint32_t)));
+        uint32_t *w = nullptr;
+        CLPK_CUDA(cudaMalloc(&w, sizeof(uint32_t)));
+        CLPK_CUDA(cudaMemset(w, 0, sizeof(uint32_t)));
+        g_status[dev] = w;
     }
     *out = g_status[dev];
     return CLPK_OK;
@@ -564,8 +570,11 @@ static int tile_counter(cudaStream_t s, unsigned long long **out)
     int dev = 0;
     CLPK_CUDA(cudaGetDevice(&dev));
     CLPK_REQUIRE(dev >= 0 && dev < 64, "device ordinal %d out of range", dev);
-    if (!g_counters[dev])
-        CLPK_CUDA(cudaMalloc(&g_counters[dev], kCounterRing * sizeof(unsigned long long)));
+    {
+        std::lock_guard<std::mutex> lk(g_lazy_mutex);
+        if (!g_counters[dev])
+            CLPK_CUDA(cudaMalloc(&g_counters[dev], kCounterRing * sizeof(unsigned long long)));
+    }
     *out = g_counters[dev] + g_next_counter.fetch_add(1) % kCounterRing;
     CLPK_CUDA(cudaMemsetAsync(*out, 0, sizeof(unsigned long long), s));
     return CLPK_OK;

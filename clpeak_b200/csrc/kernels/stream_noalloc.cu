@@ -2,12 +2,13 @@
 //
 // clpk_stream_read() hands its per-CTA partial XORs back in a buffer the caller
 // allocates.  Some callers cannot allocate device memory at the moment they
-// need the checksum: code running inside a CUDA-graph capture or on a
-// latency-critical path where cudaMalloc's implicit device synchronisation is
-// not acceptable, a plugin whose host forbids allocator calls after start-up,
-// or a process running with its memory pool already handed out in full.  For
-// them this entry point keeps the partials in a fixed array that lives in the
-// library's own device image.
+// need the checksum: code on a latency-critical path where cudaMalloc's implicit
+// device synchronisation is not acceptable, a plugin whose host forbids
+// allocator calls after start-up, or a process running with its memory pool
+// already handed out in full.  For them this entry point keeps the partials in
+// a fixed array that lives in the library's own device image.  The first call
+// on a device looks the array's device address up (cudaGetSymbolAddress); make
+// that first call before any stream capture.
 //
 // The array (kMaxCtas partial words plus a ticket counter, 16.25 KiB) exists
 // once per GPU that loads the library and stays until the process exits.  Every
@@ -15,6 +16,8 @@
 // two host threads -- race on it and must be serialised by the caller.  The
 // array keeps the last call's partials; the only word that has to start at zero,
 // the ticket, is cleared by a memset at the head of every call.
+#include <atomic>
+
 #include "../clpk_internal.h"
 
 namespace clpk {
@@ -87,9 +90,11 @@ __global__ void __launch_bounds__(kThreads) stream_checksum_static(const uint4 *
     }
 }
 
-// Device address of the scratch array on the current device, resolved once per
-// device with that device current.
-static uint32_t *g_scratch_ptr[64] = {nullptr};
+// Device address of the scratch array on the current device, resolved with that
+// device current.  Two host threads making their first call on one device at the
+// same moment both resolve it and both store the same value; the slots are atomic
+// so that this is not a data race.
+static std::atomic<uint32_t *> g_scratch_ptr[64];
 
 static int scratch_for_device(uint32_t **out)
 {
@@ -99,12 +104,12 @@ static int scratch_for_device(uint32_t **out)
         set_error("device index %d out of range", dev);
         return CLPK_ERR_BAD_ARG;
     }
-    if (!g_scratch_ptr[dev]) {
-        uint32_t *ptr = nullptr;
+    uint32_t *ptr = g_scratch_ptr[dev].load(std::memory_order_acquire);
+    if (!ptr) {
         CLPK_CUDA(cudaGetSymbolAddress((void **)&ptr, g_read_scratch));
-        g_scratch_ptr[dev] = ptr;
+        g_scratch_ptr[dev].store(ptr, std::memory_order_release);
     }
-    *out = g_scratch_ptr[dev];
+    *out = ptr;
     return CLPK_OK;
 }
 

@@ -17,7 +17,8 @@ OK, ERR_CUDA, ERR_BAD_ARG, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_NO_DEVICE, ERR_TOO_
 
 DIST_UNIFORM01, DIST_UNIFORM_PM1, DIST_NORMAL = 0, 1, 2
 (DT_F32, DT_F16, DT_BF16, DT_E4M3, DT_E5M2, DT_I8, DT_MXF4, DT_NVF4, DT_MXF4_B64, DT_NVF4_B32, DT_TF32,
- DT_E2M1) = range(12)
+ DT_E2M1, DT_F64) = range(13)
+TUNE_GEMM_NO_ALIGN, TUNE_GEMM_ALIGN_AT, TUNE_GEMM_GROUP, TUNE_MMA_PAIR, TUNE_GEMM_FP4_TILE, TUNE_MMA_LONE_LANE = range(6)
 STREAM_LDG, STREAM_TMA, STREAM_WIDE = 0, 1, 2
 STREAM_VARIANTS = (STREAM_LDG, STREAM_TMA, STREAM_WIDE)
 (MMA_F16, MMA_BF16, MMA_E4M3, MMA_E5M2, MMA_I8, MMA_MXF4, MMA_NVF4,
@@ -63,6 +64,7 @@ class MmaPeakArgs(C.Structure):
         ("d_meta", C.c_void_p),
         ("n_mma", C.c_uint32), ("grid", C.c_uint32), ("n_out_tiles", C.c_uint32),
         ("d_out", C.c_void_p), ("d_checksum", C.c_void_p), ("d_status", C.c_void_p),
+        ("d_clock", C.c_void_p),
     ]
 
 
@@ -137,6 +139,9 @@ KERNEL_API = {
     "clpk_gemm_workspace_bytes": [_i, _u32, _u32, _u32, C.POINTER(C.c_size_t)],
     "clpk_gemm": [C.POINTER(GemmArgs), _vp],
     "clpk_gemm_pack_scales": [C.POINTER(GemmArgs), _vp],
+    "clpk_gemm_last_launch_aligned": [],
+    "clpk_set_tuning": [_i, _i],
+    "clpk_get_tuning": [_i, C.POINTER(_i)],
 }
 _RESTYPES = {
     "clpk_last_error": C.c_char_p,

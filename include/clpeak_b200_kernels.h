@@ -93,6 +93,28 @@ CLPK_API int clpk_event_elapsed_ms(void *start, void *stop, float *ms);
  * holds none of the previous kernel's data.  d_scratch must hold `bytes`. */
 CLPK_API int clpk_flush_l2(void *d_scratch, size_t bytes, void *stream);
 
+/* ---- tuning knobs ---------------------------------------------------------------------------
+ * Scheduling choices that do not change any result.  Each knob's default is what measured
+ * fastest; the environment variable of the same name (CLPK_GEMM_NO_ALIGN, ...) is read ONCE,
+ * at the first use of any knob in the process, and replaces the default; clpk_set_tuning
+ * replaces both from then on (value < 0: back to "not set").  clpk_get_tuning returns -1 for
+ * a knob that is not set.  No reference counterpart (cuBLASLt picks its own schedule).
+ *   GEMM_NO_ALIGN  1 = the producers of the persistent GEMM do not meet once per wave
+ *   GEMM_ALIGN_AT  k block at which they meet (default 2)
+ *   GEMM_GROUP     raster group width in tile columns (default 12 dense, 8 block-scaled)
+ *   MMA_PAIR       peak probes as CTA pairs (1) or lone CTAs (0); default per kind
+ *   GEMM_FP4_TILE  block-scaled GEMM tile: 0 = by size, 1 = 256x256 one accumulator,
+ *                  2 = 256x128 two accumulators (the epilogue overlaps the next tile) */
+#define CLPK_TUNE_GEMM_NO_ALIGN 0
+#define CLPK_TUNE_GEMM_ALIGN_AT 1
+#define CLPK_TUNE_GEMM_GROUP    2
+#define CLPK_TUNE_MMA_PAIR      3
+#define CLPK_TUNE_GEMM_FP4_TILE 4
+#define CLPK_TUNE_MMA_LONE_LANE 5   /* 1 = the peak probes issue from one thread instead of an elected lane of a whole warp */
+#define CLPK_TUNE_COUNT         6
+CLPK_API int clpk_set_tuning(int knob, int value);
+CLPK_API int clpk_get_tuning(int knob, int *value);
+
 /* ---- seeded operand generation ----------------------------------------------
  * Replaces populate() (src/common/common.cpp:76-95, a sequential xorshift32
  * fill on the host) with counter-based device fills: element i of stream
@@ -118,6 +140,7 @@ CLPK_API int clpk_fill_i8(int8_t *d_dst, uint64_t n, uint64_t seed, void *stream
 #define CLPK_DT_NVF4_B32 9   /* as NVF4 with one ue4m3 scale per 32: the dense B operand of NVF4_SP */
 #define CLPK_DT_TF32  10  /* fp32 word rounded (nearest even) to 10 mantissa bits, low 13 bits clear       */
 #define CLPK_DT_E2M1  11  /* plain e2m1, two per byte (element 2i in the low nibble), saturating at +-6   */
+#define CLPK_DT_F64   12  /* double; clpk_convert_f32 widens exactly                                      */
 
 /* Round-to-nearest-even conversion of n floats to a plain (unscaled) format:
  * F16, BF16, E4M3 / E5M2 (saturating to the largest finite value), I8
@@ -343,6 +366,9 @@ typedef struct clpk_mma_peak_args {
     void       *d_out;        /* n_out_tiles * 128*256 * 4 bytes                              */
     uint32_t   *d_checksum;   /* grid words, may be NULL                                      */
     uint32_t   *d_status;     /* one word, zeroed by the call                                 */
+    unsigned long long *d_clock; /* optional, two words: CTA 0 stores the SM cycles (clock64) and the
+                                  * nanoseconds (%globaltimer) between its first issue and the retirement
+                                  * of its last instruction; cycles / ns is the SM clock the run really had */
 } clpk_mma_peak_args_t;
 
 CLPK_API int clpk_mma_peak(const clpk_mma_peak_args_t *args, void *stream);
@@ -373,6 +399,9 @@ CLPK_API int clpk_dmma_peak(const double *d_a, const double *d_b, uint32_t n_mma
  * (src/cuda/cuda_blas.cpp:275-287).  Accumulation in tensor memory, no epilogue
  * beyond the multiplication by `alpha` (the product of the NVF4 tensor scales).
  *   dtype            A / B elements                  accumulate   C element
+ *   CLPK_DT_F32      fp32, CUDA cores (FFMA)         fp32         fp32   the reference's "fp32" row
+ *   CLPK_DT_F64      fp64, mma.sync.m8n8k4 (DMMA)    fp64         fp64   the reference's "fp64" row
+ *                    (src/cuda/cuda_blas.cpp:567-581); M, N multiples of 128, K of 16
  *   CLPK_DT_BF16     bf16                            fp32         bf16
  *   CLPK_DT_F16      fp16                            fp32         bf16
  *   CLPK_DT_TF32     fp32 words (19 bits read)       fp32         fp32
@@ -410,6 +439,10 @@ typedef struct clpk_gemm_args {
 CLPK_API int clpk_gemm_workspace_bytes(int dtype, uint32_t m, uint32_t n, uint32_t k, size_t *bytes);
 CLPK_API int clpk_gemm_pack_scales(const clpk_gemm_args_t *args, void *stream);
 CLPK_API int clpk_gemm(const clpk_gemm_args_t *args, void *stream);
+/* 1 if the calling thread's last clpk_gemm launch ran with the per-wave producer meeting (a
+ * cooperative launch), 0 if it ran without (small problem, knob, or the cooperative launch did
+ * not fit), -1 before any launch.  Lets a benchmark record which schedule it timed. */
+CLPK_API int clpk_gemm_last_launch_aligned(void);
 
 #ifdef __cplusplus
 }

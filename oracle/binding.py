@@ -104,7 +104,7 @@ def fill_i8(n: int, seed: int, first: int = 0) -> np.ndarray:
     return out
 
 
-_DT_NP = {1: np.uint16, 2: np.uint16, 3: np.uint8, 4: np.uint8, 5: np.int8, 10: np.uint32}
+_DT_NP = {1: np.uint16, 2: np.uint16, 3: np.uint8, 4: np.uint8, 5: np.int8, 10: np.uint32, 12: np.float64}
 
 
 def convert_f32(src: np.ndarray, dtype: int) -> np.ndarray:

@@ -18,7 +18,7 @@
 
 /* dtype / kind numbering mirrors include/clpeak_b200_kernels.h */
 enum { DT_F32 = 0, DT_F16 = 1, DT_BF16 = 2, DT_E4M3 = 3, DT_E5M2 = 4, DT_I8 = 5, DT_MXF4 = 6, DT_NVF4 = 7,
-       DT_MXF4_B64 = 8, DT_NVF4_B32 = 9, DT_TF32 = 10, DT_E2M1 = 11 };
+       DT_MXF4_B64 = 8, DT_NVF4_B32 = 9, DT_TF32 = 10, DT_E2M1 = 11, DT_F64 = 12 };
 
 static int fp4_block(int dtype) { return dtype == DT_MXF4 ? 32 : dtype == DT_NVF4 ? 16 : dtype == DT_MXF4_B64 ? 64 : 32; }
 static int fp4_is_mx(int dtype) { return dtype == DT_MXF4 || dtype == DT_MXF4_B64; }
@@ -287,6 +287,7 @@ void orc_convert_f32(void *dst, const float *src, uint64_t n, int dtype)
         case DT_E4M3: ((uint8_t *)dst)[i] = orc_f32_to_e4m3(src[i]); break;
         case DT_E5M2: ((uint8_t *)dst)[i] = orc_f32_to_e5m2(src[i]); break;
         case DT_I8:   ((int8_t *)dst)[i] = orc_f32_to_i8(src[i]); break;
+        case DT_F64:  ((double *)dst)[i] = (double)src[i]; break;
         case DT_TF32: {     /* nearest even at bit 13; infinities and NaNs keep their class */
             uint32_t b; memcpy(&b, &src[i], 4);
             if ((b & 0x7F800000u) != 0x7F800000u) b += 0xFFFu + ((b >> 13) & 1u);
@@ -842,6 +843,9 @@ double orc_gemm_element(int dtype, const void *a, const void *b, const uint8_t *
         /* the reference's "fp8_e5m2" GEMM row multiplies e5m2 A by e4m3 B (src/cuda/cuda_blas.cpp:632-638) */
         case DT_E5M2: va = orc_e5m2_to_f32(((const uint8_t *)a)[i * k + x]);  vb = orc_e4m3_to_f32(((const uint8_t *)b)[j * k + x]); break;
         case DT_I8:   va = ((const int8_t *)a)[i * k + x];                    vb = ((const int8_t *)b)[j * k + x]; break;
+        /* the reference's "fp32" and "fp64" GEMM rows (src/cuda/cuda_blas.cpp:567-581): plain float / double operands */
+        case DT_F32:  va = ((const float *)a)[i * k + x];                     vb = ((const float *)b)[j * k + x]; break;
+        case DT_F64:  va = ((const double *)a)[i * k + x];                    vb = ((const double *)b)[j * k + x]; break;
         case DT_TF32: {   /* the multiplier reads sign, exponent and 10 mantissa bits of each fp32 word */
             uint32_t wa = ((const uint32_t *)a)[i * k + x] & 0xFFFFE000u, wb = ((const uint32_t *)b)[j * k + x] & 0xFFFFE000u;
             float fa, fb; memcpy(&fa, &wa, 4); memcpy(&fb, &wb, 4);

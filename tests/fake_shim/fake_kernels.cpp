@@ -511,6 +511,9 @@ int clpk_dmma_peak(const double *a, const double *b, uint32_t n_mma, uint32_t gr
     return CLPK_OK;
 }
 
+int clpk_gemm_last_launch_aligned(void) { return -1; }
+int clpk_set_tuning(int, int) { return CLPK_OK; }
+int clpk_get_tuning(int, int *value) { if (value) *value = -1; return CLPK_OK; }
 int clpk_gemm_workspace_bytes(int, uint32_t, uint32_t, uint32_t, size_t *bytes) { *bytes = 0; return CLPK_OK; }
 int clpk_gemm(const clpk_gemm_args_t *, void *) { return fail(CLPK_ERR_UNSUPPORTED, "the fake shim has no GEMM"); }
 int clpk_gemm_pack_scales(const clpk_gemm_args_t *, void *) { return fail(CLPK_ERR_UNSUPPORTED, "the fake shim has no GEMM"); }

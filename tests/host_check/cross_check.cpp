@@ -7,6 +7,7 @@
 #include <vector>
 
 #include "host_check.hpp"
+#include "clpeak_api.hpp"
 #include "../../oracle/oracle.h"
 
 static int g_failed = 0;
@@ -165,6 +166,29 @@ int main()
             std::snprintf(name, sizeof name, "GEMM element, dtype %d, equals the oracle", dt);
             report(name, ok);
         }
+    }
+    // ---- the product's buffer fill and launch-count rule (host/core.cpp) ------------------------------------
+    {
+        // populate: the reference's xorshift32 stream from 0xDEADBEEF as finite floats
+        // (src/common/common.cpp:76-95); the oracle's copy is pinned to that stream by the CPU tests
+        std::vector<float> mine(100003), theirs(100003);
+        populate(mine.data(), mine.size());
+        orc_populate_reference(theirs.data(), theirs.size());
+        bool ok = std::memcmp(mine.data(), theirs.data(), mine.size() * sizeof(float)) == 0;
+        uint32_t first;
+        std::memcpy(&first, mine.data(), 4);
+        uint32_t s0 = 0xDEADBEEFu;
+        s0 ^= s0 << 13; s0 ^= s0 >> 17; s0 ^= s0 << 5;
+        ok = ok && first == ((s0 & 0x7F7FFFFFu) | 0x00800000u);
+        // (the mask keeps bit 23 set, so one pattern in 128 has the exponent 0xFF: the stream does
+        // contain infinities and NaNs, in the reference as here)
+        report("product populate() equals the reference stream", ok);
+        ok = true;
+        const double per[] = {0.2, 1.0, 37.5, 1e3, 5e5, 4e6};
+        for (double us : per)
+            for (unsigned forced : {0u, 7u})
+                ok = ok && pickIters(us, 500000u, forced) == orc_pick_iters(us, 500000u, forced, 10000u);
+        report("product pickIters() equals the oracle's restatement", ok);
     }
     return g_failed;
 }

@@ -116,7 +116,11 @@ def test_selection_grammar(ffi, one_device):
     assert only_latency == ["kernel_launch_latency"]
     assert tests_run(["--latency", "--no-memory-latency"]) == ["kernel_launch_latency"]
     assert tests_run(["--no-cuda"]) == []
-    assert tests_run(["--cpu"]) == []                         # positive backend flag: only the named backends
+    # --cpu names a backend this build does not carry: nothing runs, a note says why, the status is non-zero
+    rc, ev = ffi.launch(["--cpu"] + FAST)
+    assert rc == 1 and [e["t"] for e in ev] == ["note", "done"] and "CPU backend is not built" in ev[0]["message"]
+    rc, ev = ffi.launch(["--cpu", "--cuda", "--kernel-launch-latency"] + FAST)
+    assert rc == 0 and any(e["t"] == "note" for e in ev) and any(e["t"] == "metric" for e in ev)
     assert tests_run(["--cuda", "--int-compute", "--no-cublas"]) == [
         "integer_compute", "integer_compute_int8_dp", "wmma_int4", "wmma_int8", "wmma_int8_k32", "wmma_int8_sparse"]
     assert tests_run(["--half-precision-compute", "--double-precision-compute", "--mixed-precision-compute",

@@ -110,6 +110,20 @@ def test_gemm_4096_sampled(K, orc, cuda, dtype):
     check_samples(orc, dtype, a, b, c, m, n, k, samples)
 
 
+@pytest.mark.parametrize("dtype", [N.DT_BF16, N.DT_E4M3])
+def test_gemm_8192_sampled(K, orc, cuda, dtype):
+    """The middle size of the GEMM configuration (M = N = K = 8192): 16 x 32 tiles, several waves."""
+    m = n = k = 8192
+    d_a, d_b = make_gemm_operands(K, cuda, dtype, m, n, k)
+    d_c = run_gemm(K, cuda, dtype, m, n, k, d_a, d_b)
+    a = to_np(d_a).view(NP_DT[dtype])
+    b = to_np(d_b).view(NP_DT[dtype])
+    c = c_view(dtype, d_c)
+    rng = np.random.default_rng(3)
+    samples = list(zip(rng.integers(0, m, 200), rng.integers(0, n, 200))) + [(0, 0), (m - 1, n - 1), (511, 256), (512, 255)]
+    check_samples(orc, dtype, a, b, c, m, n, k, samples)
+
+
 def test_gemm_rejects_ragged(K, cuda):
     d = dev_empty(16, cuda.int16)
     args = N.GemmArgs(dtype=N.DT_BF16, m=250, n=256, k=128, d_a=d.data_ptr(), d_b=d.data_ptr(), d_c=d.data_ptr(),
@@ -176,6 +190,53 @@ def test_gemm_nvfp4(K, orc, cuda, m, n, k, dtype):
 
 
 @pytest.mark.parametrize("dtype", [N.DT_NVF4, N.DT_MXF4])
+@pytest.mark.parametrize("m", [4096, 8192])
+def test_gemm_fp4_config_sizes_sampled(K, orc, cuda, dtype, m):
+    """The block-scaled GEMM at the sizes the GEMM configuration names (4096 and 8192 cubed; 16384 cubed is
+    checked by the benchmark itself on the result it times)."""
+    r = run_nvfp4(K, cuda, m, m, m, dtype)
+    assert not np.any(r["c"] == 0x7FC0)
+    rng = np.random.default_rng(6)
+    samples = list(zip(rng.integers(0, m, 150), rng.integers(0, m, 150))) + [(0, 0), (m - 1, m - 1), (255, 256), (256, 255)]
+    worst = 0.0
+    for (i, j) in samples:
+        want, s_abs = orc.gemm_element(dtype, r["a"], r["b"], m, int(i), int(j), r["sfa"], r["sfb"])
+        want *= r["alpha"]
+        s_abs *= r["alpha"]
+        got = float(bf16_to_f64(r["c"][i * m + j: i * m + j + 1])[0])
+        tol = m * 2.0 ** -23 * s_abs + 2.0 ** -8 * abs(want) + 1e-30
+        worst = max(worst, abs(got - want) / tol)
+    assert worst <= 1.0, f"worst sampled error is {worst:.3g}x the stated tolerance"
+
+
+@pytest.mark.parametrize("dtype", [N.DT_NVF4, N.DT_MXF4])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 256), (256, 768, 1024), (1024, 512, 2304), (4096, 4096, 4096)])
+def test_gemm_fp4_both_tile_shapes_give_the_same_bits(K, orc, cuda, dtype, m, n, k):
+    """The 256 x 128 two-accumulator tile (the epilogue of one tile overlaps the main loop of the next) against
+    the 256 x 256 single-accumulator tile: every element of C is one cluster's sum over K in the same order
+    either way, so the outputs are bit-identical; the wide one is checked against the oracle elsewhere, the
+    narrow one here as well."""
+    try:
+        K.clpk_set_tuning(N.TUNE_GEMM_FP4_TILE, 1)
+        wide = run_nvfp4(K, cuda, m, n, k, dtype)
+        K.clpk_set_tuning(N.TUNE_GEMM_FP4_TILE, 2)
+        narrow = run_nvfp4(K, cuda, m, n, k, dtype)
+    finally:
+        K.clpk_set_tuning(N.TUNE_GEMM_FP4_TILE, -1)
+    assert not np.any(narrow["c"] == 0x7FC0), "some of C was never written"
+    rng = np.random.default_rng(8)
+    worst = 0.0
+    for (i, j) in list(zip(rng.integers(0, m, 60), rng.integers(0, n, 60))) + [(0, 0), (m - 1, n - 1), (255, 127), (128, 128)]:
+        want, s_abs = orc.gemm_element(dtype, narrow["a"], narrow["b"], k, int(i), int(j), narrow["sfa"], narrow["sfb"])
+        want *= narrow["alpha"]
+        s_abs *= narrow["alpha"]
+        got = float(bf16_to_f64(narrow["c"][i * n + j: i * n + j + 1])[0])
+        worst = max(worst, abs(got - want) / (k * 2.0 ** -23 * s_abs + 2.0 ** -8 * abs(want) + 1e-30))
+    assert worst <= 1.0, f"worst sampled error is {worst:.3g}x the stated tolerance"
+    assert np.array_equal(wide["c"], narrow["c"])
+
+
+@pytest.mark.parametrize("dtype", [N.DT_NVF4, N.DT_MXF4])
 def test_gemm_nvfp4_tracks_the_unquantised_product(K, orc, cuda, dtype):
     """End-to-end sanity of the whole recipe (quantiser + scales + tensor scale): C correlates with fp32 A.B^T."""
     m = n = 256
@@ -233,21 +294,26 @@ def test_gemm_nvfp4_argument_checks(K, cuda):
 # ---- scheduling knobs do not change the numbers ---------------------------------------------
 
 @pytest.mark.parametrize("dtype", [N.DT_BF16, N.DT_I8])
-def test_gemm_is_bitwise_the_same_with_and_without_producer_alignment(K, cuda, dtype, monkeypatch):
+def test_gemm_is_bitwise_the_same_with_and_without_producer_alignment(K, cuda, dtype):
     """The per-wave meeting of the producers and the raster group width only move work in time and
     across SM pairs; every element of C is still one cluster's sum over K in the same order."""
     m, n, k = 8192, 8192, 256                # 512 tiles on 74 clusters: seven waves, so the producers do meet
     d_a, d_b = make_gemm_operands(K, cuda, dtype, m, n, k)
-    monkeypatch.delenv("CLPK_GEMM_NO_ALIGN", raising=False)
-    monkeypatch.delenv("CLPK_GEMM_GROUP", raising=False)
+    knobs = (N.TUNE_GEMM_NO_ALIGN, N.TUNE_GEMM_GROUP, N.TUNE_GEMM_ALIGN_AT)
+    for knob in knobs:
+        K.clpk_set_tuning(knob, -1)
     base = to_np(run_gemm(K, cuda, dtype, m, n, k, d_a, d_b)).copy()
-    for env in ({"CLPK_GEMM_NO_ALIGN": "1"}, {"CLPK_GEMM_GROUP": "3"}, {"CLPK_GEMM_ALIGN_AT": "0"}):
-        for key, val in env.items():
-            monkeypatch.setenv(key, val)
-        other = to_np(run_gemm(K, cuda, dtype, m, n, k, d_a, d_b))
-        assert np.array_equal(base.view(np.uint8), other.view(np.uint8)), env
-        for key in env:
-            monkeypatch.delenv(key)
+    assert K.raw("clpk_gemm_last_launch_aligned")() == 1          # seven waves: the producers do meet
+    try:
+        for knob, val in ((N.TUNE_GEMM_NO_ALIGN, 1), (N.TUNE_GEMM_GROUP, 3), (N.TUNE_GEMM_ALIGN_AT, 0)):
+            K.clpk_set_tuning(knob, val)
+            other = to_np(run_gemm(K, cuda, dtype, m, n, k, d_a, d_b))
+            assert K.raw("clpk_gemm_last_launch_aligned")() == (0 if knob == N.TUNE_GEMM_NO_ALIGN else 1)
+            assert np.array_equal(base.view(np.uint8), other.view(np.uint8)), (knob, val)
+            K.clpk_set_tuning(knob, -1)
+    finally:
+        for knob in knobs:
+            K.clpk_set_tuning(knob, -1)
 
 
 def test_gemm_many_waves_small_k(K, orc, cuda):
@@ -262,3 +328,64 @@ def test_gemm_many_waves_small_k(K, orc, cuda):
     rng = np.random.default_rng(9)
     samples = list(zip(rng.integers(0, m, 400), rng.integers(0, n, 400))) + [(m - 1, n - 1), (0, 0), (511, 255), (512, 256)]
     check_samples(orc, N.DT_BF16, a, b, c, m, n, k, samples)
+
+
+# ---- fp32 (CUDA cores) and fp64 (DMMA): the rows without a tcgen05 kind --------------------------------
+
+def run_simt_gemm(K, cuda, dtype, m, n, k, alpha=1.0):
+    """A, B ~ N(0, 0.02) generated on the device as fp32; the fp64 operands are those floats widened."""
+    wide = dtype == N.DT_F64
+    tdt = cuda.float64 if wide else cuda.float32
+    ops = []
+    for rows, seed in ((m, 40), (n, 41)):
+        f = dev_empty(rows * k, cuda.float32)
+        K.clpk_fill_f32(f.data_ptr(), rows * k, seed, N.DIST_NORMAL, 0.0, 0.02, stream_ptr())
+        if wide:
+            q = dev_empty(rows * k, cuda.float64)
+            K.clpk_convert_f32(q.data_ptr(), f.data_ptr(), rows * k, N.DT_F64, stream_ptr())
+            f = q
+        ops.append(f)
+    c = cuda.full((m * n,), float("nan"), dtype=tdt, device="cuda")
+    st = dev_empty(1, cuda.int32)
+    args = N.GemmArgs(dtype=dtype, m=m, n=n, k=k, d_a=ops[0].data_ptr(), d_b=ops[1].data_ptr(), d_c=c.data_ptr(),
+                      d_sfa=None, d_sfb=None, alpha=alpha, d_workspace=None, workspace_bytes=0, d_status=st.data_ptr())
+    K.clpk_gemm(C.byref(args), stream_ptr())
+    sync()
+    assert int(to_np(st)[0]) == 0
+    return to_np(ops[0]), to_np(ops[1]), to_np(c)
+
+
+@pytest.mark.parametrize("dtype", [N.DT_F32, N.DT_F64])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 16), (256, 384, 64), (384, 128, 1040), (2048, 2048, 512)])
+def test_simt_gemm_against_the_oracle(K, orc, cuda, dtype, m, n, k):
+    """Every element of the small cases, samples of the large one, against the oracle's fp64 dot product.
+    Tolerance: K sequential roundings of the accumulator, K * u * sum|a||b| with u = 2^-23 (fp32; one extra
+    bit over the unit roundoff for the host's own accumulation) or 2^-51 (fp64)."""
+    a, b, c = run_simt_gemm(K, cuda, dtype, m, n, k)
+    assert not np.isnan(c).any(), "some of C was never written"
+    u = 2.0 ** -51 if dtype == N.DT_F64 else 2.0 ** -23
+    if m * n <= 256 * 384:
+        want = a.reshape(m, k).astype(np.float64) @ b.reshape(n, k).astype(np.float64).T
+        s_abs = np.abs(a.reshape(m, k)).astype(np.float64) @ np.abs(b.reshape(n, k)).astype(np.float64).T
+        assert np.all(np.abs(c.reshape(m, n).astype(np.float64) - want) <= k * u * s_abs + 1e-300)
+    rng = np.random.default_rng(4)
+    samples = list(zip(rng.integers(0, m, 150), rng.integers(0, n, 150))) + [(0, 0), (m - 1, n - 1), (127, 0), (0, 127)]
+    worst = 0.0
+    for i, j in samples:
+        want, s_abs = orc.gemm_element(dtype, a, b, k, int(i), int(j))
+        worst = max(worst, abs(float(c[i * n + j]) - want) / (k * u * s_abs + 1e-300))
+    assert worst <= 1.0, f"worst sampled error is {worst:.3g}x the stated tolerance"
+
+
+@pytest.mark.parametrize("dtype", [N.DT_F32, N.DT_F64])
+def test_simt_gemm_alpha_and_argument_checks(K, orc, cuda, dtype):
+    a, b, c1 = run_simt_gemm(K, cuda, dtype, 128, 256, 64)
+    _, _, c2 = run_simt_gemm(K, cuda, dtype, 128, 256, 64, alpha=0.5)
+    assert np.array_equal(c2, c1 * 0.5)                        # a power of two scales exactly
+    d = dev_empty(64, cuda.float64)
+    for m, n, k in ((100, 128, 16), (128, 128, 8), (128, 64, 16)):
+        args = N.GemmArgs(dtype=dtype, m=m, n=n, k=k, d_a=d.data_ptr(), d_b=d.data_ptr(), d_c=d.data_ptr(), alpha=1.0,
+                          d_status=d.data_ptr())
+        with pytest.raises(N.ClpkError) as e:
+            K.clpk_gemm(C.byref(args), None)
+        assert e.value.code == N.ERR_BAD_ARG

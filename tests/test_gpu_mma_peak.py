@@ -41,6 +41,27 @@ def test_full_config_all_ctas_agree(K, orc, cuda, kind):
     assert int(chk[0]) == int(np.bitwise_xor.reduce(tiles[0].view(np.uint32).ravel()))
 
 
+@pytest.mark.parametrize("kind", [N.MMA_BF16, N.MMA_E4M3])
+def test_doubling_an_operand_doubles_every_accumulator_bit_for_bit(K, orc, cuda, kind):
+    """A truncating binary adder is blind to a common power of two: with A replaced by 2A (exact in the
+    operand format) every accumulator of the full 2^14-instruction run must be exactly twice what it was.
+    A wrong low-order accumulate that the tolerance of the full run would let through does not survive this."""
+    ops = M.make_operands(orc, kind)
+    if kind == N.MMA_BF16:
+        fa = (ops["a"].astype(np.uint32) << 16).view(np.float32)
+    else:
+        L = orc.lib()
+        fa = np.array([L.orc_e4m3_to_f32(int(v)) for v in ops["a"].ravel()], dtype=np.float32).reshape(ops["a"].shape)
+    twice = orc.convert_f32(fa * np.float32(2.0), M.DENSE_DT[kind]).reshape(ops["a"].shape)
+    n_mma = 1 << 14
+    _, base, _ = M.run_peak(K, cuda, kind, ops, n_mma, grid=2, n_out_tiles=1)
+    _, dbl, _ = M.run_peak(K, cuda, kind, dict(ops, a=twice), n_mma, grid=2, n_out_tiles=1)
+    b = base[0].view(np.float32)
+    assert np.isfinite(b).all() and not np.any((b != 0) & (np.abs(b) < 2.0 ** -100))     # nothing near the subnormals
+    assert np.count_nonzero(b) > b.size // 2
+    assert np.array_equal(dbl[0].view(np.float32), b * np.float32(2.0))
+
+
 @pytest.mark.parametrize("n_mma", [1, 2, 3])
 def test_fp16_accumulate_tile(K, orc, cuda, n_mma):
     """kind::f16 with a 16-bit accumulator: one half per 32-bit tensor-memory cell, low 16 bits."""
@@ -73,15 +94,18 @@ def test_tf32_ignores_the_low_mantissa_bits(K, orc, cuda):
 
 
 @pytest.mark.parametrize("kind", DENSE + SCALED)
-def test_cta_pairs_and_lone_ctas_compute_the_same_tile(K, orc, cuda, kind, monkeypatch):
+def test_cta_pairs_and_lone_ctas_compute_the_same_tile(K, orc, cuda, kind):
     """cta_group::2 (two CTAs share B) against cta_group::1: same accumulator bits, tile by tile."""
     ops = M.make_operands(orc, kind)
     out = {}
-    for pair in ("0", "1"):
-        monkeypatch.setenv("CLPK_MMA_PAIR", pair)
-        status, tiles, chk = M.run_peak(K, cuda, kind, ops, 5, grid=4, n_out_tiles=4)
-        assert status == 0
-        out[pair] = (tiles.copy(), chk.copy())
+    try:
+        for pair in ("0", "1"):
+            K.clpk_set_tuning(N.TUNE_MMA_PAIR, int(pair))
+            status, tiles, chk = M.run_peak(K, cuda, kind, ops, 5, grid=4, n_out_tiles=4)
+            assert status == 0
+            out[pair] = (tiles.copy(), chk.copy())
+    finally:
+        K.clpk_set_tuning(N.TUNE_MMA_PAIR, -1)
     assert np.array_equal(out["0"][0], out["1"][0]) and np.array_equal(out["0"][1], out["1"][1])
     want, tol = M.expected_tile(orc, kind, ops, 5)
     for t in out["1"][0]:

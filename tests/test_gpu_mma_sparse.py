@@ -48,16 +48,19 @@ def test_sparse_full_config(K, orc, cuda, kind):
 
 
 @pytest.mark.parametrize("kind", SP)
-def test_sparse_cta_pairs_and_lone_ctas_compute_the_same_tile(K, orc, cuda, kind, monkeypatch):
+def test_sparse_cta_pairs_and_lone_ctas_compute_the_same_tile(K, orc, cuda, kind):
     """cta_group::2 (each CTA stages half of B, both the same compressed A and selectors) against
     cta_group::1: the same accumulator bits in every tile."""
     ops = M.make_operands(orc, kind)
     out = {}
-    for pair in ("0", "1"):
-        monkeypatch.setenv("CLPK_MMA_PAIR", pair)
-        status, tiles, chk = M.run_peak(K, cuda, kind, ops, 5, grid=4, n_out_tiles=4)
-        assert status == 0
-        out[pair] = (tiles.copy(), chk.copy())
+    try:
+        for pair in ("0", "1"):
+            K.clpk_set_tuning(N.TUNE_MMA_PAIR, int(pair))
+            status, tiles, chk = M.run_peak(K, cuda, kind, ops, 5, grid=4, n_out_tiles=4)
+            assert status == 0
+            out[pair] = (tiles.copy(), chk.copy())
+    finally:
+        K.clpk_set_tuning(N.TUNE_MMA_PAIR, -1)
     assert np.array_equal(out["0"][0], out["1"][0]) and np.array_equal(out["0"][1], out["1"][1])
     want, tol = M.expected_tile(orc, kind, ops, 5)
     for t in out["1"][0]:

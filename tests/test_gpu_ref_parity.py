@@ -62,7 +62,7 @@ def same_bits_nan_aware(got, want, ftype, what):
 
 
 # label of the reference row -> (test tag, CLPK_CHAIN_* or None for compute_sp, start values)
-FLOAT_STARTS = [1.3, 0.25, -0.75, 1e-3]
+FLOAT_STARTS = [1.3, 0.25, -0.75, -0.5, 1e-3]
 INT_STARTS = [3, 4, 125, -7]
 CHAINS = [
     ("single_precision_compute/float", None, FLOAT_STARTS),
@@ -83,6 +83,7 @@ CHAINS = [
 def test_chain_reference_kernel_equals_oracle_equals_ours(K, orc, cuda, ref, tmp_path, row, chain, starts):
     blocks = 3
     stream = cuda.cuda.current_stream().cuda_stream
+    finite_outputs = 0
     for a in starts:
         wide = chain == N.CHAIN_DOUBLE
         theirs = ref(row, tmp_path, dtype=np.uint64 if wide else np.uint32, blocks=blocks, arg=a)
@@ -105,10 +106,11 @@ def test_chain_reference_kernel_equals_oracle_equals_ours(K, orc, cuda, ref, tmp
             same_bits_nan_aware(theirs, want, ftype, what + ": reference kernel vs oracle")
             same_bits_nan_aware(ours, want, ftype, what + ": this backend vs oracle")
             same_bits_nan_aware(ours, theirs, ftype, what + ": this backend vs reference kernel")
-    # at least one start keeps real numbers in the output, so the comparison is not inf == inf throughout
+            finite_outputs += int(np.isfinite(want.astype(np.float64)).sum())
+    # some start keeps real numbers in the output (thread 0 adds c = 0, so a start below one in magnitude
+    # decays instead of running away): the comparison is not inf == inf throughout
     if chain is None or chain < N.CHAIN_INT32:
-        finite = np.isfinite(want.astype(np.float64))
-        assert finite.any(), f"{row}: every output of the last start is non-finite"
+        assert finite_outputs > 0, f"{row}: every output of every start is non-finite"
 
 
 @pytest.mark.parametrize("width", [1, 2, 4])
@@ -129,9 +131,16 @@ def test_global_bandwidth_reference_kernel_equals_oracle_equals_ours(K, orc, cud
     K.clpk_global_bandwidth(width, d_in.data_ptr(), d_out.data_ptr(), n, cuda.cuda.current_stream().cuda_stream)
     cuda.cuda.synchronize()
     ours = d_out.cpu().numpy()
-    assert np.array_equal(theirs, want.view(np.uint32)), "reference kernel vs oracle"
-    assert np.array_equal(ours.view(np.uint32), want.view(np.uint32)), "this backend vs oracle"
-    assert np.isfinite(want).all() and len(np.unique(want)) > blocks * 200
+    # The reference's stream sets bit 23 of every pattern, so one value in 128 has the exponent 0xFF
+    # (infinity or NaN) and many sums are NaN; a generated NaN's payload is not part of the contract.
+    same_bits_nan_aware(theirs, want, np.float32, "reference kernel vs oracle")
+    same_bits_nan_aware(ours, want, np.float32, "this backend vs oracle")
+    same_bits_nan_aware(ours, theirs, np.float32, "this backend vs reference kernel")
+    finite = want[np.isfinite(want)]
+    assert len(np.unique(finite)) > blocks * (200 if source == "uniform" else 100)
+    if source == "uniform":
+        assert np.isfinite(want).all()
+        assert np.array_equal(theirs, want.view(np.uint32)) and np.array_equal(ours.view(np.uint32), want.view(np.uint32))
 
 
 @pytest.mark.parametrize("width", [1, 2, 4])
