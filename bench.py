@@ -781,6 +781,7 @@ def measure_rows(K, N, torch, stream, time_once, world=1, clocked=None, check=Tr
     sf = torch.full((256 * 4,), 0x38, dtype=torch.uint8, device="cuda")
     chk = torch.empty(grid, dtype=torch.int32, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    clk = torch.zeros(2, dtype=torch.int64, device="cuda")       # CTA 0's {SM cycles, ns} of the last launch
     for kind, name in N.MMA_KIND_NAMES.items():
         if kind not in spec_of and kind not in sparse_spec:
             continue
@@ -811,7 +812,7 @@ def measure_rows(K, N, torch, stream, time_once, world=1, clocked=None, check=Tr
             K.clpk_quantize_fp4(tb.data_ptr(), sf.data_ptr(), f.data_ptr(), 256, 64, dt, 1.0, stream)
         args = N.MmaPeakArgs(kind=kind, d_a=ta.data_ptr(), d_b=tb.data_ptr(), d_sfa=sf.data_ptr(),
                              d_sfb=sf.data_ptr(), d_meta=meta.data_ptr() if kind in sparse_spec else None, n_mma=n_mma, grid=grid, n_out_tiles=0, d_out=None,
-                             d_checksum=chk.data_ptr(), d_status=status.data_ptr())
+                             d_checksum=chk.data_ptr(), d_status=status.data_ptr(), d_clock=clk.data_ptr())
         launch = lambda: K.clpk_mma_peak(C.byref(args), stream)
         ms = time_once(launch, reps=5)
         if int(status.item()) != 0:
@@ -825,9 +826,14 @@ def measure_rows(K, N, torch, stream, time_once, world=1, clocked=None, check=Tr
                "box_T(FL)OPS": world * tf, "timing": "burst: 5 launches"}
         if clocked is not None:
             sms_ms, mhz, reasons = clocked(launch, ms, 0.5)
+            cyc, ns = (int(v) for v in clk.cpu().tolist())
+            true_mhz = cyc / ns * 1e3 if ns else None
             row["sustained"] = {"T(FL)OPS": per_ms / sms_ms, "ms": sms_ms, "frac_of_spec": per_ms / sms_ms / spec,
-                                "seconds": 0.5, "sm_mhz_median": mhz, "reasons": reasons,
-                                "cycles_per_instruction": (sms_ms * 1e-3 * mhz * 1e6 / (n_mma * ctas_per_sm)) if mhz else None}
+                                "seconds": 0.5, "sm_mhz_nvml_median": mhz, "reasons": reasons,
+                                # clock64 / %globaltimer of CTA 0 inside the last launch: the clock the kernel really had
+                                "sm_mhz_in_kernel": true_mhz,
+                                "cycles_per_instruction": (sms_ms * 1e-3 * true_mhz * 1e6 / (n_mma * ctas_per_sm)) if true_mhz else None,
+                                "rate_at_max_clock_T(FL)OPS": (per_ms / sms_ms * 1965.0 / true_mhz) if true_mhz else None}
         rows[f"mma_{name}"] = row
 
     # fp64 tensor cores (warp-level DMMA; tcgen05 has no fp64 kind): successor of the reference's wmma_fp64 row
@@ -841,6 +847,40 @@ def measure_rows(K, N, torch, stream, time_once, world=1, clocked=None, check=Tr
         rows["dmma_fp64"] = {"TFLOPS": tf, "ms": ms, "frac_of_spec_37TF": tf / 37.0, "box_TFLOPS": world * tf}
     except Exception as e:
         rows["dmma_fp64"] = {"error": repr(e)[:200]}
+
+    # the reference's fp32 and fp64 GEMM rows (CUDA cores / DMMA), 8192^3, with the library beside them
+    for dt, tdt, name, spec_tf in ((N.DT_F32, torch.float32, "fp32", 75.0), (N.DT_F64, torch.float64, "fp64", 37.0)):
+        try:
+            m = 8192
+            a = torch.empty(m * m, dtype=torch.float32, device="cuda")
+            K.clpk_fill_f32(a.data_ptr(), m * m, 40, N.DIST_NORMAL, 0.0, 0.02, stream)
+            b = torch.empty(m * m, dtype=torch.float32, device="cuda")
+            K.clpk_fill_f32(b.data_ptr(), m * m, 41, N.DIST_NORMAL, 0.0, 0.02, stream)
+            a, b = a.to(tdt).view(m, m), b.to(tdt).view(m, m)
+            c = torch.empty(m, m, dtype=tdt, device="cuda")
+            o = torch.empty(m, m, dtype=tdt, device="cuda")
+            ga = N.GemmArgs(dtype=dt, m=m, n=m, k=m, d_a=a.data_ptr(), d_b=b.data_ptr(), d_c=c.data_ptr(), alpha=1.0,
+                            d_status=status.data_ptr())
+            mine = lambda: K.clpk_gemm(C.byref(ga), stream)
+            tf32_was = torch.backends.cuda.matmul.allow_tf32
+            torch.backends.cuda.matmul.allow_tf32 = False
+            lib = lambda: torch.matmul(a, b.t(), out=o)
+            ours_ms, lib_ms = compare_alternating(mine, lib, time_once, rounds=4, reps=3)
+            torch.backends.cuda.matmul.allow_tf32 = tf32_was
+            flop = 2.0 * m ** 3
+            # both sides accumulate K products in the operand type; they agree to rounding
+            err = float((c - o).abs().max().item())
+            scale = float(o.abs().max().item())
+            tol = m * (2.0 ** -23 if dt == N.DT_F32 else 2.0 ** -52) * scale * 4
+            rows[f"gemm_{name}_{m}"] = {"TFLOPS": flop / median(ours_ms) / 1e9, "ms_rounds": ours_ms,
+                                        "frac_of_spec": flop / median(ours_ms) / 1e9 / spec_tf,
+                                        "vs_cublas_median": median(lib_ms) / median(ours_ms),
+                                        "checked": err <= tol, "max_abs_difference_from_library": err}
+            rows[f"library_cublas_{name}_{m}"] = {"TFLOPS_median": flop / median(lib_ms) / 1e9, "ms_rounds": lib_ms}
+            del a, b, c, o
+        except Exception as e:
+            rows[f"gemm_{name}_8192"] = {"error": repr(e)[:200]}
+        torch.cuda.empty_cache()
 
     # GEMM (config 5): M = N = K in {4096, 8192, 16384}; bf16, fp8 e4m3, NVFP4
     order = 0
@@ -946,6 +986,11 @@ def measure_rows(K, N, torch, stream, time_once, world=1, clocked=None, check=Tr
                         sms_ms, mhz, reasons = clocked(fn, est, 2.0)
                         res[who] = {"TFLOPS": flop / sms_ms / 1e9, "ms": sms_ms, "sm_mhz_median": mhz, "reasons": reasons,
                                     "mega_cycles": sms_ms * 1e-3 * mhz if mhz else None}
+                        if who == "ours":
+                            cyc, ns = C.c_ulonglong(0), C.c_ulonglong(0)
+                            K.clpk_gemm_last_clock(C.byref(cyc), C.byref(ns), stream)
+                            if ns.value:
+                                res[who]["sm_mhz_in_kernel"] = cyc.value / ns.value * 1e3
                     row["sustained"] = dict(res["ours"], seconds=2.0, ran="first" if first_ours else "second")
                     lrow["sustained"] = dict(res["lib"], seconds=2.0, ran="second" if first_ours else "first")
                     row["vs_cublas_sustained"] = res["lib"]["ms"] / res["ours"]["ms"]

@@ -51,6 +51,7 @@ struct GemmParams {
     unsigned int *wave_sync;    // one counter for this launch, or NULL: see wave_align()
     uint32_t align_at;          // K block of a tile before which the producers meet
     uint32_t align_period;      // ... in every align_period-th wave
+    unsigned long long *clock;  // two words: CTA 0 stores the SM cycles and nanoseconds it ran for (clpk_gemm_last_clock)
 };
 
 // Output element of a GEMM dtype: fp32 for TF32, int32 for I8, bf16 for everything else.
@@ -369,6 +370,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
     cluster_sync();
     tc_fence_after_sync();
     const uint32_t tmem = sh->tmem_base;
+    const unsigned long long clk0 = clock64(), ns0 = globaltimer_ns();
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -493,6 +495,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
     tc_fence_before_sync();
     __syncthreads();
     cluster_sync();
+    if (blockIdx.x == 0 && threadIdx.x == 0 && p.clock) {
+        p.clock[0] = clock64() - clk0;
+        p.clock[1] = globaltimer_ns() - ns0;
+    }
     if (warp == 1)
         tmem_dealloc<2>(tmem, 512);
 }
@@ -667,6 +673,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
     cluster_sync();
     tc_fence_after_sync();
     const uint32_t tmem = sh->tmem_base;
+    const unsigned long long clk0 = clock64(), ns0 = globaltimer_ns();
     constexpr int kScaleProducerWarp = 2 + kEpilogueWarps + kNvCopyThreads;
 
     if (warp == 0) {
@@ -853,6 +860,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
     tc_fence_before_sync();
     __syncthreads();
     cluster_sync();
+    if (blockIdx.x == 0 && threadIdx.x == 0 && p.clock) {
+        p.clock[0] = clock64() - clk0;
+        p.clock[1] = globaltimer_ns() - ns0;
+    }
     if (warp == 1)
         tmem_dealloc<2>(tmem, 512);
 }
@@ -961,6 +972,8 @@ constexpr int kSyncSlots = 32;
 __device__ unsigned int g_wave_sync[kSyncSlots];
 static std::atomic<unsigned> g_next_sync_slot{0};
 static thread_local int g_last_aligned = -1;
+// {SM cycles, nanoseconds} CTA 0 of the last GEMM launch on this device ran for (both tensor kernels write it).
+__device__ unsigned long long g_gemm_clock[2];
 
 // Launches a persistent cluster kernel whose last parameter is GemmParams: cooperatively with a
 // fresh wave counter when the alignment is on, plainly (and unaligned) otherwise.
@@ -972,6 +985,7 @@ static int launch_persistent(Kernel kernel, const char *what, int threads, size_
     const int grid = (num_sms() / 2) * 2;
     p.wave_sync = nullptr;
     g_last_aligned = 0;
+    CLPK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&p.clock), g_gemm_clock));
     // nothing to keep in step in the first two waves: small problems skip the counter and its memset
     const bool worth_aligning = n_tiles > 2u * (uint32_t)(grid / 2) * p.align_period;
     if (worth_aligning && tuning(CLPK_TUNE_GEMM_NO_ALIGN) != 1) {
@@ -1027,6 +1041,19 @@ using namespace clpk;
 extern "C" {
 
 int clpk_gemm_last_launch_aligned(void) { return g_last_aligned; }
+
+int clpk_gemm_last_clock(unsigned long long *h_cycles, unsigned long long *h_ns, void *stream)
+{
+    CLPK_REQUIRE(h_cycles && h_ns, "NULL output");
+    unsigned long long v[2] = {0, 0};
+    void *sym = nullptr;
+    CLPK_CUDA(cudaGetSymbolAddress(&sym, g_gemm_clock));
+    CLPK_CUDA(cudaMemcpyAsync(v, sym, sizeof v, cudaMemcpyDeviceToHost, as_stream(stream)));
+    CLPK_CUDA(cudaStreamSynchronize(as_stream(stream)));
+    *h_cycles = v[0];
+    *h_ns = v[1];
+    return CLPK_OK;
+}
 
 int clpk_gemm_workspace_bytes(int dtype, uint32_t m, uint32_t n, uint32_t k, size_t *bytes)
 {

@@ -140,6 +140,7 @@ KERNEL_API = {
     "clpk_gemm": [C.POINTER(GemmArgs), _vp],
     "clpk_gemm_pack_scales": [C.POINTER(GemmArgs), _vp],
     "clpk_gemm_last_launch_aligned": [],
+    "clpk_gemm_last_clock": [C.POINTER(C.c_ulonglong), C.POINTER(C.c_ulonglong), _vp],
     "clpk_set_tuning": [_i, _i],
     "clpk_get_tuning": [_i, C.POINTER(_i)],
 }

@@ -443,6 +443,11 @@ CLPK_API int clpk_gemm(const clpk_gemm_args_t *args, void *stream);
  * cooperative launch), 0 if it ran without (small problem, knob, or the cooperative launch did
  * not fit), -1 before any launch.  Lets a benchmark record which schedule it timed. */
 CLPK_API int clpk_gemm_last_launch_aligned(void);
+/* SM cycles (clock64) and nanoseconds (%globaltimer) that CTA 0 of the last tensor-core GEMM
+ * launched on the current device ran for; cycles / ns is the SM clock the kernel really had, which
+ * under the power cap is well below the nominal one.  Waits for `stream`.  The fp32 / fp64 kernels
+ * do not write it. */
+CLPK_API int clpk_gemm_last_clock(unsigned long long *h_cycles, unsigned long long *h_ns, void *stream);
 
 #ifdef __cplusplus
 }

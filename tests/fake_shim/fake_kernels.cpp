@@ -512,6 +512,7 @@ int clpk_dmma_peak(const double *a, const double *b, uint32_t n_mma, uint32_t gr
 }
 
 int clpk_gemm_last_launch_aligned(void) { return -1; }
+int clpk_gemm_last_clock(unsigned long long *c, unsigned long long *n, void *) { *c = 0; *n = 0; return CLPK_OK; }
 int clpk_set_tuning(int, int) { return CLPK_OK; }
 int clpk_get_tuning(int, int *value) { if (value) *value = -1; return CLPK_OK; }
 int clpk_gemm_workspace_bytes(int, uint32_t, uint32_t, uint32_t, size_t *bytes) { *bytes = 0; return CLPK_OK; }
