@@ -356,7 +356,7 @@ def run_simt_gemm(K, cuda, dtype, m, n, k, alpha=1.0):
 
 
 @pytest.mark.parametrize("dtype", [N.DT_F32, N.DT_F64])
-@pytest.mark.parametrize("m,n,k", [(128, 128, 16), (256, 384, 64), (384, 128, 1040), (2048, 2048, 512)])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 16), (256, 384, 64), (384, 128, 1040), (2048, 2048, 512), (4096, 4096, 4096)])
 def test_simt_gemm_against_the_oracle(K, orc, cuda, dtype, m, n, k):
     """Every element of the small cases, samples of the large one, against the oracle's fp64 dot product.
     Tolerance: K sequential roundings of the accumulator, K * u * sum|a||b| with u = 2^-23 (fp32; one extra
