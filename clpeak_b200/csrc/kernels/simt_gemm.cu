@@ -8,12 +8,13 @@
 // thread as four 4 x 4 blocks so that every shared-memory read is a conflict-free
 // 128-bit load; operands are transposed into shared memory ([k][m]) on the way in, the
 // next k block travels global -> registers while the current one is multiplied, two
-// shared-memory buffers.  Bound: FFMA issue, 128 FMA / clock / SM (B200: 148 SMs x 128
-// x 2 x 1.965 GHz = 74.4 TFLOPS); the inner loop issues 64 FFMA per 4 LDS.128.
+// shared-memory buffers.  The multiply is sm_100's packed fma.rn.f32x2 (two FMAs per
+// issued instruction).  Bound: the fp32 pipe, 128 FMA / clock / SM (B200: 148 SMs x 128
+// x 2 x 1.965 GHz = 74.4 TFLOPS); the inner loop issues 32 packed FMAs per 4 LDS.128.
 //
-// fp64 (dgemm_kernel).  128 x 128 x 16 tile per CTA of 256 threads = 8 warps in a 2 x 4
-// grid, 64 x 32 outputs per warp = 8 x 4 m8n8k4 accumulator tiles (128 registers of
-// accumulators per thread).  Operands go global -> shared with cp.async (16 bytes), three
+// fp64 (dgemm_kernel).  128 x 64 x 16 tile per CTA of 128 threads = 4 warps in a 2 x 2
+// grid, two CTAs per SM, 64 x 32 outputs per warp = 8 x 4 m8n8k4 accumulator tiles (128
+// registers of accumulators per thread).  Operands go global -> shared with cp.async (16 bytes), three
 // stages; rows are padded to 20 doubles so that the fragment reads (lane -> row lane/4,
 // k lane%4) fall in 16 distinct 8-byte banks per half warp.  Bound: the DMMA pipe, 64
 // fp64 FMA / clock / SM, the same rate as the scalar DFMA pipe (37.2 TFLOPS at 1.965 GHz).
@@ -43,6 +44,26 @@ __device__ __forceinline__ void raster(uint32_t tiles_m, uint32_t tiles_n, uint3
 // ---------------------------------------------------------------------------------------------
 // fp32
 // ---------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi)
+{
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+
+__device__ __forceinline__ float2 unpack2(unsigned long long v)
+{
+    float2 r;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(v));
+    return r;
+}
+
+// d = a * b + d on two packed fp32 lanes, each rounded to nearest even like fmaf
+__device__ __forceinline__ void ffma2(unsigned long long &d, unsigned long long a, unsigned long long b)
+{
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(b));
+}
 
 constexpr int kSgemmPad = 4;
 constexpr int kSgemmLd = kSimtTile + kSgemmPad;          // floats per k row of a shared tile
@@ -77,12 +98,15 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
         }
     };
 
-    float acc[8][8];
+    // Accumulators as pairs of neighbouring columns: sm_100's packed fma.rn.f32x2 does two FMAs per issued
+    // instruction (same rounding as two scalar FMAs), which halves the issue slots the multiply needs and leaves
+    // room for the shared-memory loads next to it.
+    unsigned long long acc[8][4];
 #pragma unroll
     for (int i = 0; i < 8; i++)
 #pragma unroll
-        for (int j = 0; j < 8; j++)
-            acc[i][j] = 0.0f;
+        for (int j = 0; j < 4; j++)
+            acc[i][j] = 0ull;
 
     fetch(0);
     stash(0);
@@ -99,12 +123,14 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
             const float4 b0 = *reinterpret_cast<const float4 *>(&sB[cur][k][tx * 4]);
             const float4 b1 = *reinterpret_cast<const float4 *>(&sB[cur][k][64 + tx * 4]);
             const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            const unsigned long long b[4] = {pack2(b0.x, b0.y), pack2(b0.z, b0.w), pack2(b1.x, b1.y), pack2(b1.z, b1.w)};
 #pragma unroll
-            for (int i = 0; i < 8; i++)
+            for (int i = 0; i < 8; i++) {
+                const unsigned long long aa = pack2(a[i], a[i]);
 #pragma unroll
-                for (int j = 0; j < 8; j++)
-                    acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                for (int j = 0; j < 4; j++)
+                    ffma2(acc[i][j], aa, b[j]);
+            }
         }
         if (kb + 1 < nk) {
             stash(cur ^ 1);
@@ -118,8 +144,8 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
         const int r = (i < 4 ? 0 : 64) + ty * 4 + (i & 3);
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            const float4 v = make_float4(alpha * acc[i][4 * h], alpha * acc[i][4 * h + 1], alpha * acc[i][4 * h + 2],
-                                         alpha * acc[i][4 * h + 3]);
+            const float2 lo = unpack2(acc[i][2 * h]), hi = unpack2(acc[i][2 * h + 1]);
+            const float4 v = make_float4(alpha * lo.x, alpha * lo.y, alpha * hi.x, alpha * hi.y);
             *reinterpret_cast<float4 *>(gC + (size_t)r * N + 64 * h + tx * 4) = v;
         }
     }
@@ -131,8 +157,13 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
 
 constexpr int kDgemmLd = kSimtBK + 4;                    // doubles per row of a shared tile (160 bytes)
 constexpr int kDgemmStages = 3;
-constexpr size_t kDgemmStageDoubles = 2 * (size_t)kSimtTile * kDgemmLd;
-constexpr size_t kDgemmSmemBytes = kDgemmStages * kDgemmStageDoubles * sizeof(double);
+// CN = columns of C per CTA.  64: four warps and two CTAs per SM, whose barriers and pipeline fills overlap each
+// other; with 128 (eight warps, one CTA per SM) the DMMA pipe idled at every CTA-wide barrier (87 % busy in ncu).
+template <int CN> struct Dgemm {
+    static constexpr int threads = 2 * CN;
+    static constexpr size_t stage_doubles = (size_t)(kSimtTile + CN) * kDgemmLd;
+    static constexpr size_t smem_bytes = kDgemmStages * stage_doubles * sizeof(double);
+};
 
 __device__ __forceinline__ void dmma_m8n8k4(double &d0, double &d1, double a, double b)
 {
@@ -141,24 +172,32 @@ __device__ __forceinline__ void dmma_m8n8k4(double &d0, double &d1, double a, do
         : "d"(a), "d"(b));
 }
 
-__global__ void __launch_bounds__(256, 1)
+template <int CN>
+__global__ void __launch_bounds__(Dgemm<CN>::threads, 128 / CN)
 dgemm_kernel(const double *__restrict__ A, const double *__restrict__ B, double *__restrict__ C, uint32_t M, uint32_t N,
              uint32_t K, double alpha)
 {
     extern __shared__ __align__(16) double dsm[];
+    constexpr int kThreads = Dgemm<CN>::threads;
+    constexpr size_t kDgemmStageDoubles = Dgemm<CN>::stage_doubles;
     uint32_t tm, tn;
-    raster(M / kSimtTile, N / kSimtTile, &tm, &tn);
+    raster(M / kSimtTile, N / CN, &tm, &tn);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int wm = (warp >> 2) * 64, wn = (warp & 3) * 32;          // this warp's 64 x 32 corner inside the tile
-    const double *gA = A + (size_t)tm * kSimtTile * K, *gB = B + (size_t)tn * kSimtTile * K;
+    constexpr int kWarpsN = CN / 32;
+    const int wm = (warp / kWarpsN) * 64, wn = (warp % kWarpsN) * 32;   // this warp's 64 x 32 corner inside the tile
+    const double *gA = A + (size_t)tm * kSimtTile * K, *gB = B + (size_t)tn * CN * K;
 
-    // one stage = A tile then B tile, [128][kDgemmLd] doubles each; 16-byte chunks: 128 rows x 8 per operand
+    // one stage = A tile [128][kDgemmLd] then B tile [CN][kDgemmLd]; 16-byte chunks, 8 per row
     auto load_stage = [&](int stage, uint32_t k0) {
         double *sa = dsm + (size_t)stage * kDgemmStageDoubles, *sb = sa + (size_t)kSimtTile * kDgemmLd;
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const int c = tid + 256 * i, r = c >> 3, kc = (c & 7) * 2;
+        for (int i = 0; i < kSimtTile * 8 / kThreads; i++) {
+            const int c = tid + kThreads * i, r = c >> 3, kc = (c & 7) * 2;
             __pipeline_memcpy_async(sa + r * kDgemmLd + kc, gA + (size_t)r * K + k0 + kc, 16);
+        }
+#pragma unroll
+        for (int i = 0; i < CN * 8 / kThreads; i++) {
+            const int c = tid + kThreads * i, r = c >> 3, kc = (c & 7) * 2;
             __pipeline_memcpy_async(sb + r * kDgemmLd + kc, gB + (size_t)r * K + k0 + kc, 16);
         }
     };
@@ -204,7 +243,7 @@ dgemm_kernel(const double *__restrict__ A, const double *__restrict__ B, double 
     __pipeline_wait_prior(0);
 
     // accumulator tile (i, j): this lane holds row lane/4, columns 2*(lane%4) and the next one
-    double *gC = C + ((size_t)tm * kSimtTile + wm) * N + (size_t)tn * kSimtTile + wn;
+    double *gC = C + ((size_t)tm * kSimtTile + wm) * N + (size_t)tn * CN + wn;
 #pragma unroll
     for (int i = 0; i < 8; i++)
 #pragma unroll
@@ -219,16 +258,17 @@ int launch_simt_gemm(int dtype, const void *a, const void *b, void *c, uint32_t 
     CLPK_REQUIRE(m % kSimtTile == 0 && n % kSimtTile == 0 && m > 0 && n > 0, "M and N must be multiples of %d", kSimtTile);
     CLPK_REQUIRE(k % kSimtBK == 0 && k > 0, "K must be a multiple of %d", kSimtBK);
     CLPK_REQUIRE(((uintptr_t)a % 16) == 0 && ((uintptr_t)b % 16) == 0 && ((uintptr_t)c % 16) == 0, "operands must be 16-byte aligned");
-    const uint64_t tiles = (uint64_t)(m / kSimtTile) * (n / kSimtTile);
-    CLPK_REQUIRE(tiles <= 0x7FFFFFFFull, "too many tiles");
+    uint64_t tiles = (uint64_t)(m / kSimtTile) * (n / kSimtTile);
+    CLPK_REQUIRE(tiles <= 0x3FFFFFFFull, "too many tiles");
     if (dtype == CLPK_DT_F32) {
         sgemm_kernel<<<(unsigned)tiles, 256, 0, s>>>(static_cast<const float *>(a), static_cast<const float *>(b),
                                                      static_cast<float *>(c), m, n, k, alpha);
         CLPK_LAUNCH_CHECK("sgemm");
     } else {
-        CLPK_CUDA(cudaFuncSetAttribute(dgemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDgemmSmemBytes));
-        dgemm_kernel<<<(unsigned)tiles, 256, kDgemmSmemBytes, s>>>(static_cast<const double *>(a), static_cast<const double *>(b),
-                                                                    static_cast<double *>(c), m, n, k, (double)alpha);
+        // 128 x 64 CTA tiles: 34.2-34.5 TFLOPS at 4096^3 / 8192^3 against 31.9-32.1 with 128 x 128 tiles of 8 warps
+        CLPK_CUDA(cudaFuncSetAttribute(dgemm_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Dgemm<64>::smem_bytes));
+        dgemm_kernel<64><<<(unsigned)(2 * tiles), Dgemm<64>::threads, Dgemm<64>::smem_bytes, s>>>(
+            static_cast<const double *>(a), static_cast<const double *>(b), static_cast<double *>(c), m, n, k, (double)alpha);
         CLPK_LAUNCH_CHECK("dgemm");
     }
     return CLPK_OK;
