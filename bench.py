@@ -593,12 +593,13 @@ def main():
         del b, parts
         torch.cuda.empty_cache()
         reps.barrier()
+        torch.cuda.synchronize()
         if rank == 0:
             try:
                 plugin = plugin_leg(N, world)
             except Exception as e:                      # a missing library is an error of the build, say so
                 plugin = {"error": repr(e)[:300]}
-        reps.barrier()
+        reps.host_barrier()                             # a CPU-side wait: an NCCL barrier would spin on the other GPUs
 
     if rank != 0:
         reps.close()

@@ -531,26 +531,32 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
 //    free again at sf_ready of the previous round, before that round's MMAs have even
 //    run), so the copies to tensor memory start when the 6 KiB of factors have landed
 //    instead of after the 64 KiB of tiles.
-//  * Tensor memory: accumulator in columns [0,256), then one 48-column scale area
+//  * Tensor memory (256-wide tile): accumulator in columns [0,256), then one 48-column scale area
 //    per pipeline stage (16 columns A, 32 columns B).  No room is left for a second
 //    accumulator, so a tile's epilogue is not overlapped with the next main loop; the
 //    epilogue therefore reads all of its columns and releases tensor memory before it
-//    writes anything out (drain_warp_tile_early).
+//    writes anything out (drain_warp_tile_early).  The 128-wide tile (TN = 128) has two
+//    128-column accumulators and overlaps the epilogue completely.
 //  * MXFP4 (MX = true: kind::mxf4.block_scale.scale_vec::2X, one ue8m0 scale per 32
 //    elements) has two factors per row per instruction, so one 32-bit word serves
 //    two instructions: the instruction descriptor's scale-factor id picks bytes 0-1
 //    or 2-3.  Half the blocks (2 of A + 4 of B per stage), half the copies.
-//  * What bounds it (clock64 counters in a trace build).  With every role issuing from a
-//    convergent warp the main loop runs at 530-560 cycles per 512-cycle stage (the
-//    counters' own clock reads included).  What is left is between tiles: the MMA warp waits about 3100 cycles per tile for tensor
-//    memory (the queued MMAs drain, tcgen05.commit reaches the epilogue, 128 KiB per CTA
-//    are read out at about 64 bytes per cycle, the release travels back), 7 % of a
-//    K = 16384 tile and 14 % of a K = 8192 one, and it cannot be overlapped without a
-//    second accumulator.  Tried and measured without effect: halving the operand bytes
-//    per stage (as sharing B between two clusters by multicast would; 4-6 %), an L2
-//    prefetch cursor ahead of the loads (slower), parked mbarrier waits, one polling lane
-//    per epilogue warp, and letting the copies queue behind issued rather than retired
-//    MMAs.
+//  * What bounds it, with cycles counted at the clock CTA 0 really had (clock64 and
+//    %globaltimer around the whole kernel, clpk_gemm_last_clock): a fit over 4096^3,
+//    8192^3 and 16384^3 gives 669 cycles per 512-cycle stage, 1130 per tile and 9000 per
+//    launch -- the time goes in the main loop, not at the tile hand-over.  Releasing the
+//    accumulator before the epilogue has read it (timing only) changes nothing; the
+//    128-wide tile, which hides the epilogue, is 35 % slower; two N = 128 instructions per
+//    K step on the 256-wide tile cost 7 %.  A stage moves 38 KiB into shared memory (TMA)
+//    and 38 KiB out of it (32 KiB operands to the tensor core, 6 KiB scale factors to
+//    tensor memory): 76 KiB per 669 cycles = 116 bytes per cycle through a data pipe that
+//    takes one 128-byte wavefront per cycle (ncu: the reads alone fill 42 % of it over the
+//    whole launch).  A 256 x 256 x 256 FP4 stage needs 64 KiB of operand traffic per 512
+//    tensor-core cycles before its scale factors, so this shape is bound by the
+//    shared-memory data pipe at about 80 % of the tensor peak.  Tried and measured without
+//    effect: an L2 prefetch cursor ahead of the loads (slower), parked mbarrier waits, one
+//    polling lane per epilogue warp, letting the copies queue behind issued rather than
+//    retired MMAs, raster group widths from 4 to 32.
 
 constexpr int kNvMaxStages = 6;
 constexpr int kNvCopyThreads = 4;

@@ -21,6 +21,7 @@ class Replicas:
         self.local_world = int(os.environ.get("LOCAL_WORLD_SIZE", str(self.world)))
         self.device = device
         self._dist = None
+        self._host_group = None
         if self.world > 1:
             import torch.distributed as dist
             if not dist.is_initialized():
@@ -29,6 +30,9 @@ class Replicas:
                     kw["device_id"] = device
                 dist.init_process_group(backend or "nccl", **kw)
             self._dist = dist
+            # A second, CPU-only group for waits that must not occupy the GPUs: an NCCL barrier is a kernel
+            # that spins on every waiting rank's GPU until the last rank arrives.
+            self._host_group = dist.new_group(backend="gloo") if dist.get_backend() != "gloo" else None
 
     @property
     def active(self) -> bool:
@@ -37,6 +41,12 @@ class Replicas:
     def barrier(self) -> None:
         if self._dist is not None:
             self._dist.barrier()
+
+    def host_barrier(self) -> None:
+        """Wait for all ranks on the host only (gloo): the GPUs of the waiting ranks stay idle, so that one rank
+        can meanwhile run something on all of them."""
+        if self._dist is not None:
+            self._dist.barrier(group=self._host_group)
 
     def max_over_ranks(self, value: float) -> float:
         """The slowest replica's figure (a time): what every box-level rate divides by."""

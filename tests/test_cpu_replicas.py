@@ -16,6 +16,7 @@ WORKER = textwrap.dedent("""
     r = Replicas("gloo")
     assert r.active and r.world == 2
     r.barrier()
+    r.host_barrier()                                   # the CPU-only wait used while one rank drives every GPU
     local_ms = 10.0 if r.rank == 0 else 25.0          # rank 1 is the slow replica
     rate, ms = r.whole_job_rate(1000.0, local_ms)
     mx = r.max_over_ranks(float(r.rank))
@@ -61,6 +62,7 @@ def test_single_replica_needs_no_process_group(monkeypatch):
     r = Replicas("gloo")
     assert not r.active and r.world == 1 and r.rank == 0
     r.barrier()
+    r.host_barrier()
     rate, ms = r.whole_job_rate(500.0, 5.0)
     assert ms == 5.0 and rate == 500.0 / 0.005
     r.close()
