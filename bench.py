@@ -925,7 +925,9 @@ def measure_rows(K, N, torch, stream, time_once, world=1, clocked=None, check=Tr
             flop = 2.0 * m * m * m
             ms = time_once(mine, reps=5)
             row = {"TFLOPS": flop / ms / 1e9, "ms": ms, "frac_of_spec": flop / ms / 1e9 / SPEC[spec],
-                   "status": int(status.item()), "box_TFLOPS": world * flop / ms / 1e9, "timing": "burst: 5 launches"}
+                   "status": int(status.item()), "box_TFLOPS": world * flop / ms / 1e9, "timing": "burst: 5 launches",
+                   # 1: cooperative launch with the per-wave producer meeting; 0: plain launch (small problem or no co-residency)
+                   "producers_aligned": K.raw("clpk_gemm_last_launch_aligned")()}
             if ms_with_pack is not None:
                 row["ms_including_scale_repack"] = ms_with_pack
             if dt == N.DT_BF16:

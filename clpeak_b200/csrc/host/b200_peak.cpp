@@ -50,6 +50,21 @@ std::string pct(double value, double peak, const char *what)
     return ss.str();
 }
 
+// "... N cycles per instruction at X MHz": the kernel's own clock64 / %globaltimer span of CTA 0 turns the
+// measured time into tensor-core cycles, which separates the instruction rate from the clock the power cap allows.
+std::string cyclesNote(double secondsPerLaunch, const unsigned long long clock[2], double instructionsPerSm)
+{
+    if (clock[1] == 0 || instructionsPerSm <= 0)
+        return "";
+    const double mhz = (double)clock[0] / (double)clock[1] * 1e3;
+    std::ostringstream ss;
+    ss.setf(std::ios::fixed);
+    ss.precision(1);
+    ss << "  About " << secondsPerLaunch * mhz * 1e6 / instructionsPerSm << " cycles per instruction (128 is the tensor core's rate) at the "
+       << (long long)(mhz + 0.5) << " MHz the SMs ran at under the power cap.";
+    return ss.str();
+}
+
 std::string shimError(const char *what)
 {
     return std::string(what) + ": " + clpk_last_error();
@@ -372,9 +387,9 @@ struct B200Harness {
 
         // operands: generated and quantised on the device, copied back for the check
         const size_t aBytes = 128 * 32, bBytes = 256 * 32;
-        DeviceBuffer f32, dA, dB, dSfa, dSfb, dOut, dChk, dStatus;
+        DeviceBuffer f32, dA, dB, dSfa, dSfb, dOut, dChk, dStatus, dClock;
         if (!f32.alloc(256 * 64 * sizeof(float)) || !dA.alloc(aBytes) || !dB.alloc(bBytes) || !dSfa.alloc(128 * 4) ||
-            !dSfb.alloc(256 * 4) || !dOut.alloc(128 * 256 * 4) || !dChk.alloc(grid * 4) || !dStatus.alloc(4))
+            !dSfb.alloc(256 * 4) || !dOut.alloc(128 * 256 * 4) || !dChk.alloc(grid * 4) || !dStatus.alloc(4) || !dClock.alloc(16))
             return fail("Failed to allocate buffers");
         int rc = CLPK_OK;
         auto gen = [&](void *dst, void *sf, int rows, uint64_t first) {
@@ -409,6 +424,8 @@ struct B200Harness {
         a.d_a = dA.p; a.d_b = dB.p; a.d_sfa = dSfa.p; a.d_sfb = dSfb.p;
         a.n_mma = nMma; a.grid = grid; a.n_out_tiles = 1;
         a.d_out = dOut.p; a.d_checksum = dChk.as<uint32_t>(); a.d_status = dStatus.as<uint32_t>();
+        a.d_clock = dClock.as<unsigned long long>();
+        clpk_memset(dClock.p, 0, 16, w.stream);
 
         std::string err;
         const double s = w.timeLaunches([&] { return clpk_mma_peak(&a, w.stream); }, err);
@@ -418,6 +435,8 @@ struct B200Harness {
         std::vector<uint8_t> hA(aBytes), hB(bBytes), hSfa(128 * 4), hSfb(256 * 4);
         std::vector<uint32_t> tile(128 * 256), chk(grid);
         uint32_t status = 0;
+        unsigned long long clock[2] = {0, 0};
+        clpk_memcpy_d2h(clock, dClock.p, sizeof clock, w.stream);
         clpk_memcpy_d2h(hA.data(), dA.p, aBytes, w.stream);
         clpk_memcpy_d2h(hB.data(), dB.p, bBytes, w.stream);
         clpk_memcpy_d2h(hSfa.data(), dSfa.p, hSfa.size(), w.stream);
@@ -452,7 +471,8 @@ struct B200Harness {
 
         const double work = clpk_mma_flops_per_instr(kind) * nMma * grid;
         const double t = work / s / 1e12;
-        out.readings.push_back(ok(row.metric, t, note + "  " + pct(t, row.spec, row.specName), work, s));
+        out.readings.push_back(ok(row.metric, t, note + "  " + pct(t, row.spec, row.specName) +
+                                                     cyclesNote(s, clock, (double)nMma * grid / w.info.numSMs), work, s));
     }
 
     // 2:4 structured-sparse kinds (tcgen05.mma.sp): a dense float tile is generated on the device, pruned on the
@@ -489,9 +509,10 @@ struct B200Harness {
         auto fail = [&](const std::string &why) { out.readings.push_back(bad(row.metric, ResultStatus::Error, why, note)); };
 
         const size_t aBytes = 128 * 32, bBytes = 256 * 64, metaBytes = 128 * 8;   // K/2 x 8-bit = K/2 x 2 x 4-bit
-        DeviceBuffer f32, dA, dB, dSfa, dSfb, dMeta, dOut, dChk, dStatus;
+        DeviceBuffer f32, dA, dB, dSfa, dSfb, dMeta, dOut, dChk, dStatus, dClock;
         if (!f32.alloc(256 * 128 * sizeof(float)) || !dA.alloc(aBytes) || !dB.alloc(bBytes) || !dSfa.alloc(128 * 4) ||
-            !dSfb.alloc(256 * 4) || !dMeta.alloc(metaBytes) || !dOut.alloc(128 * 256 * 4) || !dChk.alloc(grid * 4) || !dStatus.alloc(4))
+            !dSfb.alloc(256 * 4) || !dMeta.alloc(metaBytes) || !dOut.alloc(128 * 256 * 4) || !dChk.alloc(grid * 4) || !dStatus.alloc(4) ||
+            !dClock.alloc(16))
             return fail("Failed to allocate buffers");
 
         // A: dense on the device -> host prune -> compressed floats back -> device quantise
@@ -541,6 +562,8 @@ struct B200Harness {
         a.d_a = dA.p; a.d_b = dB.p; a.d_sfa = dSfa.p; a.d_sfb = dSfb.p; a.d_meta = dMeta.p;
         a.n_mma = nMma; a.grid = grid; a.n_out_tiles = 1;
         a.d_out = dOut.p; a.d_checksum = dChk.as<uint32_t>(); a.d_status = dStatus.as<uint32_t>();
+        a.d_clock = dClock.as<unsigned long long>();
+        clpk_memset(dClock.p, 0, 16, w.stream);
 
         std::string err;
         const double s = w.timeLaunches([&] { return clpk_mma_peak(&a, w.stream); }, err);
@@ -550,6 +573,8 @@ struct B200Harness {
         std::vector<uint8_t> hA(aBytes), hB(bBytes), hSfa(128 * (size_t)nsf), hSfb(256 * (size_t)nsf);
         std::vector<uint32_t> tile(128 * 256), chk(grid);
         uint32_t status = 0;
+        unsigned long long clock[2] = {0, 0};
+        clpk_memcpy_d2h(clock, dClock.p, sizeof clock, w.stream);
         clpk_memcpy_d2h(hA.data(), dA.p, aBytes, w.stream);
         clpk_memcpy_d2h(hB.data(), dB.p, bBytes, w.stream);
         clpk_memcpy_d2h(hSfa.data(), dSfa.p, hSfa.size(), w.stream);
@@ -572,7 +597,8 @@ struct B200Harness {
 
         const double work = clpk_mma_flops_per_instr(kind) * nMma * grid;
         const double t = work / s / 1e12;
-        out.readings.push_back(ok(row.metric, t, note + "  " + pct(t, row.spec, row.specName), work, s));
+        out.readings.push_back(ok(row.metric, t, note + "  " + pct(t, row.spec, row.specName) +
+                                                     cyclesNote(s, clock, (double)nMma * grid / w.info.numSMs), work, s));
     }
 
     // fp64 tensor cores: no tcgen05 kind exists, so this is the warp-level DMMA path (mma.sync.m8n8k4.f64),
@@ -765,7 +791,11 @@ struct B200Harness {
             return fail("result check failed: " + verdict);
         const double work = 2.0 * d * d * d;
         const double t = work / s / 1e12;
-        out.readings.push_back(ok(r.metric, t, note + "  " + pct(t, r.spec, r.specName), work, s));
+        std::string clockNote;
+        unsigned long long cyc = 0, ns = 0;
+        if (dt != CLPK_DT_F32 && dt != CLPK_DT_F64 && clpk_gemm_last_clock(&cyc, &ns, w.stream) == CLPK_OK && ns > 0)
+            clockNote = "  SM clock inside the last launch: " + std::to_string((long long)((double)cyc / (double)ns * 1e3 + 0.5)) + " MHz.";
+        out.readings.push_back(ok(r.metric, t, note + "  " + pct(t, r.spec, r.specName) + clockNote, work, s));
     }
 
     static void gemmFp(B200Worker &w, B200TestResult &out)
