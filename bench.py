@@ -687,6 +687,17 @@ def measure_small_rows(K, N, torch, stream, time_once):
                                   "xor_equals_cpu_replay": int(r[1]) == want_xor,
                                   "checked": int(r[0]) == want_final and int(r[1]) == want_xor}
     del nxt, host_next
+    # pinned host <-> device copies of the reference's transfer size (512 MiB, src/cuda/transfer_bandwidth.cpp:43-95)
+    nb = 512 << 20
+    hbuf = torch.empty(nb, dtype=torch.uint8).pin_memory()
+    hbuf.copy_(torch.arange(nb, dtype=torch.int64).to(torch.uint8))
+    hback = torch.empty(nb, dtype=torch.uint8).pin_memory()
+    dbuf = torch.empty(nb, dtype=torch.uint8, device="cuda")
+    h2d = time_once(lambda: K.clpk_memcpy_h2d(dbuf.data_ptr(), hbuf.data_ptr(), nb, stream), reps=5)
+    d2h = time_once(lambda: K.clpk_memcpy_d2h(hback.data_ptr(), dbuf.data_ptr(), nb, stream), reps=5)
+    rows["transfer_pinned_512MiB"] = {"h2d_GBps": nb / h2d / 1e6, "d2h_GBps": nb / d2h / 1e6,
+                                      "checked": bool(torch.equal(hbuf, hback))}
+    del hbuf, hback, dbuf
     mean_us = C.c_double(0.0)
     K.clpk_launch_latency(100000, 200, C.byref(mean_us), stream)
     rows["launch_roundtrip"] = {"us": mean_us.value, "launches": 100000}
