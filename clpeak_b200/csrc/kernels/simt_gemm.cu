@@ -4,13 +4,20 @@
 // C[M][N] = alpha * A[M][K] * B[N][K]^T, both operands K-contiguous, C row-major in the
 // operand type.
 //
-// fp32 (sgemm_kernel).  128 x 256 x 16 tile per CTA of 256 threads, 8 x 16 outputs per
-// thread as 4 x 4 blocks so that every shared-memory read is a conflict-free
+// fp32 (sgemm_kernel).  128 x 128 x 16 tile per CTA of 256 threads, 8 x 8 outputs per
+// thread as four 4 x 4 blocks so that every shared-memory read is a conflict-free
 // 128-bit load; operands are transposed into shared memory ([k][m]) on the way in, the
 // next k block travels global -> registers while the current one is multiplied, two
 // shared-memory buffers.  The multiply is sm_100's packed fma.rn.f32x2 (two FMAs per
 // issued instruction).  Bound: the fp32 pipe, 128 FMA / clock / SM (B200: 148 SMs x 128
-// x 2 x 1.965 GHz = 74.4 TFLOPS); the inner loop issues 64 packed FMAs per 6 LDS.128.
+// x 2 x 1.965 GHz = 74.4 TFLOPS); the inner loop issues 32 packed FMAs per 4 LDS.128.
+// Per k step a warp pulls 32 x 64 bytes of fragments out of shared memory (every thread
+// needs its own copy in registers): 2 KiB at 128 bytes per clock = 16 clocks per 64 clocks
+// of multiply on its scheduler, i.e. with four schedulers the fragment traffic of an SM
+// takes as long as its multiplies, and the fp32 pipe measures 74 % busy.  8 x 16 outputs
+// per thread (3 KiB per 128 clocks) was tried: one CTA of 216-register threads per SM, and
+// slower (50.6 against 54.0 TFLOPS at 8192^3) -- the second CTA's warps are worth more
+// than the better ratio.
 //
 // fp64 (dgemm_kernel).  128 x 64 x 16 tile per CTA of 128 threads = 4 warps in a 2 x 2
 // grid, two CTAs per SM, 64 x 32 outputs per warp = 8 x 4 m8n8k4 accumulator tiles (128
@@ -66,58 +73,46 @@ __device__ __forceinline__ void ffma2(unsigned long long &d, unsigned long long 
 }
 
 constexpr int kSgemmPad = 4;
-constexpr int kSgemmTileN = 256;                         // columns of C per CTA (rows: kSimtTile = 128)
-constexpr int kSgemmLdA = kSimtTile + kSgemmPad;         // floats per k row of the shared A tile
-constexpr int kSgemmLdB = kSgemmTileN + kSgemmPad;       // ... of the shared B tile
-constexpr size_t kSgemmSmemBytes = 2 * (size_t)kSimtBK * (kSgemmLdA + kSgemmLdB) * sizeof(float);
+constexpr int kSgemmLd = kSimtTile + kSgemmPad;          // floats per k row of a shared tile
 
-// 8 x 16 outputs per thread.  Every thread needs its own copy of the fragments in registers, so per k step a warp
-// pulls 32 x (8 + 16) x 4 bytes = 3 KiB out of shared memory at 128 bytes per clock for 128 clocks of multiply;
-// with 8 x 8 outputs per thread (2 KiB per 64 clocks) the fragment traffic took exactly as long as the
-// multiplies and the fp32 pipe stayed at 74 %.
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(256, 2)
 sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__restrict__ C, uint32_t M, uint32_t N,
              uint32_t K, float alpha)
 {
-    extern __shared__ __align__(16) float ssm[];
-    float (*sA)[kSimtBK][kSgemmLdA] = reinterpret_cast<float (*)[kSimtBK][kSgemmLdA]>(ssm);
-    float (*sB)[kSimtBK][kSgemmLdB] = reinterpret_cast<float (*)[kSimtBK][kSgemmLdB]>(ssm + 2 * kSimtBK * kSgemmLdA);
+    __shared__ __align__(16) float sA[2][kSimtBK][kSgemmLd];
+    __shared__ __align__(16) float sB[2][kSimtBK][kSgemmLd];
     uint32_t tm, tn;
-    raster(M / kSimtTile, N / kSgemmTileN, &tm, &tn);
+    raster(M / kSimtTile, N / kSimtTile, &tm, &tn);
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-    const float *gA = A + (size_t)tm * kSimtTile * K, *gB = B + (size_t)tn * kSgemmTileN * K;
+    const float *gA = A + (size_t)tm * kSimtTile * K, *gB = B + (size_t)tn * kSimtTile * K;
 
-    // global -> registers: A 128 rows x 16 floats = 512 float4 (two per thread), B 256 rows = 1024 float4 (four)
+    // global -> registers: 128 rows x 16 floats per operand = 512 float4, two per thread
     const int lrow = tid >> 2, lk = (tid & 3) * 4;
-    float4 ra[2], rb[4];
+    float4 ra[2], rb[2];
     auto fetch = [&](uint32_t k0) {
 #pragma unroll
-        for (int h = 0; h < 2; h++)
+        for (int h = 0; h < 2; h++) {
             ra[h] = *reinterpret_cast<const float4 *>(gA + (size_t)(lrow + 64 * h) * K + k0 + lk);
-#pragma unroll
-        for (int h = 0; h < 4; h++)
             rb[h] = *reinterpret_cast<const float4 *>(gB + (size_t)(lrow + 64 * h) * K + k0 + lk);
+        }
     };
     auto stash = [&](int buf) {
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const int r = lrow + 64 * h;
             sA[buf][lk + 0][r] = ra[h].x; sA[buf][lk + 1][r] = ra[h].y; sA[buf][lk + 2][r] = ra[h].z; sA[buf][lk + 3][r] = ra[h].w;
-        }
-#pragma unroll
-        for (int h = 0; h < 4; h++) {
-            const int r = lrow + 64 * h;
             sB[buf][lk + 0][r] = rb[h].x; sB[buf][lk + 1][r] = rb[h].y; sB[buf][lk + 2][r] = rb[h].z; sB[buf][lk + 3][r] = rb[h].w;
         }
     };
 
     // Accumulators as pairs of neighbouring columns: sm_100's packed fma.rn.f32x2 does two FMAs per issued
-    // instruction (same rounding as two scalar FMAs).
-    unsigned long long acc[8][8];
+    // instruction (same rounding as two scalar FMAs), which halves the issue slots the multiply needs and leaves
+    // room for the shared-memory loads next to it.
+    unsigned long long acc[8][4];
 #pragma unroll
     for (int i = 0; i < 8; i++)
 #pragma unroll
-        for (int j = 0; j < 8; j++)
+        for (int j = 0; j < 4; j++)
             acc[i][j] = 0ull;
 
     fetch(0);
@@ -132,19 +127,15 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
         for (int k = 0; k < kSimtBK; k++) {
             const float4 a0 = *reinterpret_cast<const float4 *>(&sA[cur][k][ty * 4]);
             const float4 a1 = *reinterpret_cast<const float4 *>(&sA[cur][k][64 + ty * 4]);
+            const float4 b0 = *reinterpret_cast<const float4 *>(&sB[cur][k][tx * 4]);
+            const float4 b1 = *reinterpret_cast<const float4 *>(&sB[cur][k][64 + tx * 4]);
             const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-            unsigned long long b[8];
-#pragma unroll
-            for (int h = 0; h < 4; h++) {
-                const float4 bv = *reinterpret_cast<const float4 *>(&sB[cur][k][64 * h + tx * 4]);
-                b[2 * h] = pack2(bv.x, bv.y);
-                b[2 * h + 1] = pack2(bv.z, bv.w);
-            }
+            const unsigned long long b[4] = {pack2(b0.x, b0.y), pack2(b0.z, b0.w), pack2(b1.x, b1.y), pack2(b1.z, b1.w)};
 #pragma unroll
             for (int i = 0; i < 8; i++) {
                 const unsigned long long aa = pack2(a[i], a[i]);
 #pragma unroll
-                for (int j = 0; j < 8; j++)
+                for (int j = 0; j < 4; j++)
                     ffma2(acc[i][j], aa, b[j]);
             }
         }
@@ -154,12 +145,12 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
         }
     }
 
-    float *gC = C + (size_t)tm * kSimtTile * N + (size_t)tn * kSgemmTileN;
+    float *gC = C + (size_t)tm * kSimtTile * N + (size_t)tn * kSimtTile;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         const int r = (i < 4 ? 0 : 64) + ty * 4 + (i & 3);
 #pragma unroll
-        for (int h = 0; h < 4; h++) {
+        for (int h = 0; h < 2; h++) {
             const float2 lo = unpack2(acc[i][2 * h]), hi = unpack2(acc[i][2 * h + 1]);
             const float4 v = make_float4(alpha * lo.x, alpha * lo.y, alpha * hi.x, alpha * hi.y);
             *reinterpret_cast<float4 *>(gC + (size_t)r * N + 64 * h + tx * 4) = v;
@@ -272,15 +263,13 @@ int launch_simt_gemm(int dtype, const void *a, const void *b, void *c, uint32_t 
                      cudaStream_t s)
 {
     CLPK_REQUIRE(m % kSimtTile == 0 && n % kSimtTile == 0 && m > 0 && n > 0, "M and N must be multiples of %d", kSimtTile);
-    CLPK_REQUIRE(dtype != CLPK_DT_F32 || n % kSgemmTileN == 0, "fp32: N must be a multiple of %d", kSgemmTileN);
     CLPK_REQUIRE(k % kSimtBK == 0 && k > 0, "K must be a multiple of %d", kSimtBK);
     CLPK_REQUIRE(((uintptr_t)a % 16) == 0 && ((uintptr_t)b % 16) == 0 && ((uintptr_t)c % 16) == 0, "operands must be 16-byte aligned");
     uint64_t tiles = (uint64_t)(m / kSimtTile) * (n / kSimtTile);
     CLPK_REQUIRE(tiles <= 0x3FFFFFFFull, "too many tiles");
     if (dtype == CLPK_DT_F32) {
-        CLPK_CUDA(cudaFuncSetAttribute(sgemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSgemmSmemBytes));
-        sgemm_kernel<<<(unsigned)(tiles / 2), 256, kSgemmSmemBytes, s>>>(static_cast<const float *>(a), static_cast<const float *>(b),
-                                                                         static_cast<float *>(c), m, n, k, alpha);
+        sgemm_kernel<<<(unsigned)tiles, 256, 0, s>>>(static_cast<const float *>(a), static_cast<const float *>(b),
+                                                     static_cast<float *>(c), m, n, k, alpha);
         CLPK_LAUNCH_CHECK("sgemm");
     } else {
         // 128 x 64 CTA tiles: 34.2-34.5 TFLOPS at 4096^3 / 8192^3 against 31.9-32.1 with 128 x 128 tiles of 8 warps
