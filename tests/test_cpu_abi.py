@@ -64,3 +64,41 @@ def test_status_helpers_need_no_gpu(K):
     assert K.raw("clpk_mma_flops_per_instr")(1) == 2.0 * 128 * 256 * 16
     assert K.raw("clpk_mma_flops_per_instr")(9) == 2.0 * 128 * 256 * 128      # sparse: logical K
     assert b"sm_100a" in K.raw("clpk_version")()
+
+
+def test_tuning_knobs_environment_once_then_setter(tmp_path):
+    """The CLPK_* environment variables give a knob its default and are read once per process; clpk_set_tuning
+    replaces the value afterwards; a negative value means "not set"; unknown knobs are refused.  Run in a child
+    process so that the variables are in place before the library's first use of them."""
+    import os
+    import sys
+    code = """
+import ctypes as C, os, sys
+sys.path.insert(0, sys.argv[1])
+from clpeak_b200 import native as N
+K = N.kernels()
+v = C.c_int(99)
+K.clpk_get_tuning(N.TUNE_GEMM_GROUP, C.byref(v)); assert v.value == 5, v.value          # from the environment
+K.clpk_get_tuning(N.TUNE_MMA_PAIR, C.byref(v)); assert v.value == -1                     # not set anywhere
+os.environ["CLPK_GEMM_GROUP"] = "9"                                                      # too late: read once
+K.clpk_get_tuning(N.TUNE_GEMM_GROUP, C.byref(v)); assert v.value == 5
+K.clpk_set_tuning(N.TUNE_GEMM_GROUP, 16)
+K.clpk_get_tuning(N.TUNE_GEMM_GROUP, C.byref(v)); assert v.value == 16
+K.clpk_set_tuning(N.TUNE_GEMM_GROUP, -3)
+K.clpk_get_tuning(N.TUNE_GEMM_GROUP, C.byref(v)); assert v.value == -1
+for bad in (-1, 6, 1000):
+    try:
+        K.clpk_set_tuning(bad, 1)
+    except N.ClpkError as e:
+        assert e.code == N.ERR_BAD_ARG
+    else:
+        raise AssertionError("knob %d accepted" % bad)
+assert K.raw("clpk_gemm_last_launch_aligned")() == -1                                    # nothing launched yet
+print("ok")
+"""
+    script = tmp_path / "knobs.py"
+    script.write_text(code)
+    env = dict(os.environ, CLPK_GEMM_GROUP="5")
+    env.pop("CLPK_MMA_PAIR", None)
+    r = subprocess.run([sys.executable, str(script), str(ROOT)], env=env, capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and r.stdout.strip().endswith("ok"), r.stdout + r.stderr

@@ -389,3 +389,22 @@ def test_simt_gemm_alpha_and_argument_checks(K, orc, cuda, dtype):
         with pytest.raises(N.ClpkError) as e:
             K.clpk_gemm(C.byref(args), None)
         assert e.value.code == N.ERR_BAD_ARG
+
+
+def test_gemm_reports_the_clock_it_ran_at(K, cuda):
+    """clpk_gemm_last_clock: CTA 0's clock64 / %globaltimer span of the last tensor-core GEMM; the quotient is an SM
+    clock, which on a B200 lies between the idle floor and the 1.965 GHz maximum, and the span is close to the
+    launch's CUDA-event duration."""
+    m = n = k = 4096
+    d_a, d_b = make_gemm_operands(K, cuda, N.DT_BF16, m, n, k)
+    run_gemm(K, cuda, N.DT_BF16, m, n, k, d_a, d_b)                      # warm
+    e0, e1 = cuda.cuda.Event(enable_timing=True), cuda.cuda.Event(enable_timing=True)
+    e0.record()
+    run_gemm(K, cuda, N.DT_BF16, m, n, k, d_a, d_b)
+    e1.record()
+    cuda.cuda.synchronize()
+    cyc, ns = C.c_ulonglong(0), C.c_ulonglong(0)
+    K.clpk_gemm_last_clock(C.byref(cyc), C.byref(ns), stream_ptr())
+    mhz = cyc.value / ns.value * 1e3
+    assert 500.0 < mhz < 2100.0, mhz
+    assert 50e3 < ns.value < e0.elapsed_time(e1) * 1e6                    # the kernel's span lies inside the bracketed call

@@ -126,3 +126,28 @@ def test_rejects_bad_arguments(K, cuda):
     with pytest.raises(N.ClpkError) as e:
         K.clpk_mma_peak(C.byref(args), None)
     assert e.value.code == N.ERR_BAD_ARG
+
+
+def test_probe_reports_cycles_and_time_of_cta_0(K, orc, cuda):
+    """d_clock: {SM cycles, nanoseconds} around CTA 0's issue loop.  Two co-resident bf16 CTAs share the tensor pipe,
+    so CTA 0's 2^14 instructions take about 2 x 128 cycles each; the quotient cycles / ns is a plausible SM clock."""
+    import ctypes as C
+    from tests.gpu_util import dev_empty, dev_from, stream_ptr, sync, to_np
+    ops = M.make_operands(orc, N.MMA_BF16)
+    sms = cuda.cuda.get_device_properties(0).multi_processor_count
+    n_mma, grid = 1 << 14, 4 * sms
+    d_a, d_b = dev_from(ops["a"].view(np.uint8)), dev_from(ops["b"].view(np.uint8))
+    d_chk, d_status = dev_empty(grid, cuda.int32), dev_empty(1, cuda.int32)
+    d_clock = cuda.zeros(2, dtype=cuda.int64, device="cuda")
+    args = N.MmaPeakArgs(kind=N.MMA_BF16, d_a=d_a.data_ptr(), d_b=d_b.data_ptr(), n_mma=n_mma, grid=grid, n_out_tiles=0,
+                         d_checksum=d_chk.data_ptr(), d_status=d_status.data_ptr(), d_clock=d_clock.data_ptr())
+    try:
+        K.clpk_set_tuning(N.TUNE_MMA_PAIR, 0)
+        K.clpk_mma_peak(C.byref(args), stream_ptr())
+        sync()
+    finally:
+        K.clpk_set_tuning(N.TUNE_MMA_PAIR, -1)
+    cyc, ns = (int(v) for v in to_np(d_clock))
+    assert int(to_np(d_status)[0]) == 0
+    assert 500.0 < cyc / ns * 1e3 < 2100.0
+    assert 250.0 <= cyc / n_mma <= 275.0, cyc / n_mma
