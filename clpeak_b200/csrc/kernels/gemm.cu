@@ -488,8 +488,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
             drain_warp_tile<DT>(tmem + col_half * 128 + ((q * 32) << 16), 2, mb * kDenseTileM + rank * 128 + q * 32,
                                 nb * kTileMN + col_half * 128, box, &tmap_c, p.alpha, &sh->tmem_empty, lane);
         }
+        // The staging box must have been read before this CTA's shared memory goes away; the writes themselves
+        // complete like any other store before the grid is reported finished, so they are not waited for here
+        // (that wait was about a microsecond at the end of every launch).
         if (lane == 0)
-            bulk_wait<0>();
+            bulk_wait_read<0>();
     }
 
     tc_fence_before_sync();
@@ -859,8 +862,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
             drain_warp_tile_early<TN / 128>(tmem + acc * TN + col_half * (TN / 2) + ((q * 32) << 16), mb * kTileMN + rank * 128 + q * 32,
                                             nb * TN + col_half * (TN / 2), box, &tmap_c, p.alpha, &sh->tmem_empty[acc], lane);
         }
+        // The staging box must have been read before this CTA's shared memory goes away; the writes themselves
+        // complete like any other store before the grid is reported finished, so they are not waited for here
+        // (that wait was about a microsecond at the end of every launch).
         if (lane == 0)
-            bulk_wait<0>();
+            bulk_wait_read<0>();
     }
 
     tc_fence_before_sync();
