@@ -37,6 +37,22 @@ __device__ __forceinline__ uint32_t elect_one()
     return pred;
 }
 
+// ---- programmatic dependent launch -----------------------------------------------
+// A kernel launched with cudaLaunchAttributeProgrammaticStreamSerialization may start while the kernel before it
+// in the stream is still running.  griddep_wait() blocks until that kernel has completed and its memory
+// operations are visible (a no-op in a kernel launched without the attribute); griddep_launch_dependents() lets
+// the kernel after this one begin to launch as soon as this one's CTAs make room.
+
+__device__ __forceinline__ void griddep_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+__device__ __forceinline__ void griddep_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---- mbarrier ---------------------------------------------------------------
 
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)

@@ -91,7 +91,7 @@ static std::once_flag g_tune_once;
 static void load_tuning_from_environment()
 {
     static const char *names[CLPK_TUNE_COUNT] = {"CLPK_GEMM_NO_ALIGN", "CLPK_GEMM_ALIGN_AT", "CLPK_GEMM_GROUP",
-                                                 "CLPK_MMA_PAIR", "CLPK_GEMM_FP4_TILE", "CLPK_MMA_LONE_LANE"};
+                                                 "CLPK_MMA_PAIR", "CLPK_GEMM_FP4_TILE", "CLPK_MMA_LONE_LANE", "CLPK_GEMM_NO_PDL"};
     for (int k = 0; k < CLPK_TUNE_COUNT; k++) {
         const char *e = getenv(names[k]);
         g_tune[k].store((e && e[0]) ? atoi(e) : -1);

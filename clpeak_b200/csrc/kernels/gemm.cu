@@ -52,7 +52,21 @@ struct GemmParams {
     uint32_t align_at;          // K block of a tile before which the producers meet
     uint32_t align_period;      // ... in every align_period-th wave
     unsigned long long *clock;  // two words: CTA 0 stores the SM cycles and nanoseconds it ran for (clpk_gemm_last_clock)
+    uint32_t zero_status;       // 1: the kernel clears *status itself (launches that may overlap the previous kernel's tail)
 };
+
+// Launches of a small GEMM repeat every 40-100 us, and 6-7 us of each are the CTA's set-up (barriers, tensor
+// memory, descriptor prefetch) and the launch gap.  The plain (non-cooperative) launches therefore carry the
+// programmatic-serialisation attribute: a CTA of launch i + 1 takes an SM as soon as launch i's CTA there has
+// exited, does its set-up, and then waits here until launch i has completed as a whole and its writes are visible.
+// Nothing of global memory is read or written before that point.
+__device__ __forceinline__ void join_previous_launch(const GemmParams &p)
+{
+    griddep_wait();
+    if (p.zero_status && blockIdx.x == 0 && threadIdx.x == 0)
+        *p.status = 0u;
+    griddep_launch_dependents();
+}
 
 // Output element of a GEMM dtype: fp32 for TF32, int32 for I8, bf16 for everything else.
 template <int DT> struct OutBytes { static constexpr uint32_t value = (DT == CLPK_DT_TF32 || DT == CLPK_DT_I8) ? 4u : 2u; };
@@ -370,6 +384,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
     cluster_sync();
     tc_fence_after_sync();
     const uint32_t tmem = sh->tmem_base;
+    join_previous_launch(p);
     const unsigned long long clk0 = clock64(), ns0 = globaltimer_ns();
 
     if (warp == 0) {
@@ -682,6 +697,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
     cluster_sync();
     tc_fence_after_sync();
     const uint32_t tmem = sh->tmem_base;
+    join_previous_launch(p);
     const unsigned long long clk0 = clock64(), ns0 = globaltimer_ns();
     constexpr int kScaleProducerWarp = 2 + kEpilogueWarps + kNvCopyThreads;
 
@@ -996,6 +1012,7 @@ static int launch_persistent(Kernel kernel, const char *what, int threads, size_
     CLPK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int grid = (num_sms() / 2) * 2;
     p.wave_sync = nullptr;
+    p.zero_status = 0;
     g_last_aligned = 0;
     CLPK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&p.clock), g_gemm_clock));
     // nothing to keep in step in the first two waves: small problems skip the counter and its memset
@@ -1005,6 +1022,7 @@ static int launch_persistent(Kernel kernel, const char *what, int threads, size_
         CLPK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&base), g_wave_sync));
         p.wave_sync = base + g_next_sync_slot.fetch_add(1) % kSyncSlots;
         CLPK_CUDA(cudaMemsetAsync(p.wave_sync, 0, sizeof(unsigned int), s));
+        CLPK_CUDA(cudaMemsetAsync(p.status, 0, sizeof(uint32_t), s));
         // cooperative: every CTA is resident before any runs, so the wave counter can fill up
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)grid);
@@ -1028,11 +1046,19 @@ static int launch_persistent(Kernel kernel, const char *what, int threads, size_
         (void)cudaGetLastError();
         p.wave_sync = nullptr;
     }
+    // No stream operation between two such launches (the kernel clears the status word itself), so that the
+    // programmatic serialisation can overlap this launch's set-up with the tail of the one before.
+    p.zero_status = 1;
     cudaLaunchConfig_t plain = {};
     plain.gridDim = dim3((unsigned)grid);
     plain.blockDim = dim3((unsigned)threads);
     plain.dynamicSmemBytes = smem;
     plain.stream = s;
+    cudaLaunchAttribute pdl[1];
+    pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl[0].val.programmaticStreamSerializationAllowed = tuning(CLPK_TUNE_GEMM_NO_PDL) == 1 ? 0 : 1;
+    plain.attrs = pdl;
+    plain.numAttrs = 1;
     const cudaError_t e = cudaLaunchKernelEx(&plain, kernel, maps..., p);
     if (e != cudaSuccess)
         return cuda_fail(e, what);
@@ -1162,7 +1188,6 @@ int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
         return CLPK_ERR_UNSUPPORTED;
     }
     cudaStream_t s = as_stream(stream);
-    CLPK_CUDA(cudaMemsetAsync(a->d_status, 0, sizeof(uint32_t), s));
 
     const uint64_t row_bytes = (uint64_t)a->k * elem_bits / 8;
     CLPK_REQUIRE(((uint64_t)a->k * elem_bits) % (8 * kRowBytesK) == 0,

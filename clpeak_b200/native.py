@@ -18,7 +18,7 @@ OK, ERR_CUDA, ERR_BAD_ARG, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_NO_DEVICE, ERR_TOO_
 DIST_UNIFORM01, DIST_UNIFORM_PM1, DIST_NORMAL = 0, 1, 2
 (DT_F32, DT_F16, DT_BF16, DT_E4M3, DT_E5M2, DT_I8, DT_MXF4, DT_NVF4, DT_MXF4_B64, DT_NVF4_B32, DT_TF32,
  DT_E2M1, DT_F64) = range(13)
-TUNE_GEMM_NO_ALIGN, TUNE_GEMM_ALIGN_AT, TUNE_GEMM_GROUP, TUNE_MMA_PAIR, TUNE_GEMM_FP4_TILE, TUNE_MMA_LONE_LANE = range(6)
+TUNE_GEMM_NO_ALIGN, TUNE_GEMM_ALIGN_AT, TUNE_GEMM_GROUP, TUNE_MMA_PAIR, TUNE_GEMM_FP4_TILE, TUNE_MMA_LONE_LANE, TUNE_GEMM_NO_PDL = range(7)
 STREAM_LDG, STREAM_TMA, STREAM_WIDE = 0, 1, 2
 STREAM_VARIANTS = (STREAM_LDG, STREAM_TMA, STREAM_WIDE)
 (MMA_F16, MMA_BF16, MMA_E4M3, MMA_E5M2, MMA_I8, MMA_MXF4, MMA_NVF4,

@@ -104,14 +104,19 @@ CLPK_API int clpk_flush_l2(void *d_scratch, size_t bytes, void *stream);
  *   GEMM_GROUP     raster group width in tile columns (default 12 dense, 8 block-scaled)
  *   MMA_PAIR       peak probes as CTA pairs (1) or lone CTAs (0); default per kind
  *   GEMM_FP4_TILE  block-scaled GEMM tile: 0 = by size, 1 = 256x256 one accumulator,
- *                  2 = 256x128 two accumulators (the epilogue overlaps the next tile) */
+ *                  2 = 256x128 two accumulators (the epilogue overlaps the next tile)
+ *   MMA_LONE_LANE  1 = the peak probes issue from one thread instead of an elected lane of a whole warp
+ *   GEMM_NO_PDL    1 = GEMMs too small for the per-wave alignment are launched plainly; by default they carry
+ *                  the programmatic-serialisation attribute, so that a launch's set-up overlaps the tail of
+ *                  the kernel before it in the stream (it waits for that kernel before touching memory) */
 #define CLPK_TUNE_GEMM_NO_ALIGN 0
 #define CLPK_TUNE_GEMM_ALIGN_AT 1
 #define CLPK_TUNE_GEMM_GROUP    2
 #define CLPK_TUNE_MMA_PAIR      3
 #define CLPK_TUNE_GEMM_FP4_TILE 4
 #define CLPK_TUNE_MMA_LONE_LANE 5   /* 1 = the peak probes issue from one thread instead of an elected lane of a whole warp */
-#define CLPK_TUNE_COUNT         6
+#define CLPK_TUNE_GEMM_NO_PDL   6   /* 1 = small GEMMs are launched without programmatic stream serialisation */
+#define CLPK_TUNE_COUNT         7
 CLPK_API int clpk_set_tuning(int knob, int value);
 CLPK_API int clpk_get_tuning(int knob, int *value);
 

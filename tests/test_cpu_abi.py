@@ -86,7 +86,7 @@ K.clpk_set_tuning(N.TUNE_GEMM_GROUP, 16)
 K.clpk_get_tuning(N.TUNE_GEMM_GROUP, C.byref(v)); assert v.value == 16
 K.clpk_set_tuning(N.TUNE_GEMM_GROUP, -3)
 K.clpk_get_tuning(N.TUNE_GEMM_GROUP, C.byref(v)); assert v.value == -1
-for bad in (-1, 6, 1000):
+for bad in (-1, 7, 1000):
     try:
         K.clpk_set_tuning(bad, 1)
     except N.ClpkError as e:
