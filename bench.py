@@ -794,6 +794,20 @@ def measure_rows(K, N, torch, stream, time_once, world=1, clocked=None, check=Tr
     chk = torch.empty(grid, dtype=torch.int32, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     clk = torch.zeros(2, dtype=torch.int64, device="cuda")       # CTA 0's {SM cycles, ns} of the last launch
+    # fp64 tensor cores (warp-level DMMA; tcgen05 has no fp64 kind): successor of the reference's wmma_fp64 row.
+    # Measured first: this pipe runs at the full SM clock, which a GPU that has just run the tcgen05 rows at its
+    # power cap does not offer for the next second or so
+    try:
+        da = torch.tensor(np.floor(np.linspace(-1, 0.99, 32) * 256) / 256, dtype=torch.float64, device="cuda")
+        db = torch.tensor(np.floor(np.linspace(0.97, -1, 32) * 256) / 256, dtype=torch.float64, device="cuda")
+        dgrid, dn = 8 * sms, 1 << 13
+        launch = lambda: K.clpk_dmma_peak(da.data_ptr(), db.data_ptr(), dn, dgrid, 0, None, None, stream)
+        ms = time_once(launch, reps=5)
+        tf = 512.0 * dn * 64 * dgrid / ms / 1e9
+        rows["dmma_fp64"] = {"TFLOPS": tf, "ms": ms, "frac_of_spec_37TF": tf / 37.0, "box_TFLOPS": world * tf}
+    except Exception as e:
+        rows["dmma_fp64"] = {"error": repr(e)[:200]}
+
     for kind, name in N.MMA_KIND_NAMES.items():
         if kind not in spec_of and kind not in sparse_spec:
             continue
@@ -847,18 +861,6 @@ def measure_rows(K, N, torch, stream, time_once, world=1, clocked=None, check=Tr
                                 "cycles_per_instruction": (sms_ms * 1e-3 * true_mhz * 1e6 / (n_mma * ctas_per_sm)) if true_mhz else None,
                                 "rate_at_max_clock_T(FL)OPS": (per_ms / sms_ms * 1965.0 / true_mhz) if true_mhz else None}
         rows[f"mma_{name}"] = row
-
-    # fp64 tensor cores (warp-level DMMA; tcgen05 has no fp64 kind): successor of the reference's wmma_fp64 row
-    try:
-        da = torch.tensor(np.floor(np.linspace(-1, 0.99, 32) * 256) / 256, dtype=torch.float64, device="cuda")
-        db = torch.tensor(np.floor(np.linspace(0.97, -1, 32) * 256) / 256, dtype=torch.float64, device="cuda")
-        dgrid, dn = 8 * sms, 1 << 13
-        launch = lambda: K.clpk_dmma_peak(da.data_ptr(), db.data_ptr(), dn, dgrid, 0, None, None, stream)
-        ms = time_once(launch, reps=5)
-        tf = 512.0 * dn * 64 * dgrid / ms / 1e9
-        rows["dmma_fp64"] = {"TFLOPS": tf, "ms": ms, "frac_of_spec_37TF": tf / 37.0, "box_TFLOPS": world * tf}
-    except Exception as e:
-        rows["dmma_fp64"] = {"error": repr(e)[:200]}
 
     # the reference's fp32 and fp64 GEMM rows (CUDA cores / DMMA), 8192^3, with the library beside them
     for dt, tdt, name, spec_tf in ((N.DT_F32, torch.float32, "fp32", 75.0), (N.DT_F64, torch.float64, "fp64", 37.0)):
