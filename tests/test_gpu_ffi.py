@@ -285,3 +285,23 @@ def test_transfer_bandwidth_bytes_arrive_intact(K, cuda):
         K.clpk_free_host(h_src)
         K.clpk_free_host(h_dst)
         K.clpk_stream_destroy(stream)
+
+
+def test_device_info_describes_a_b200(K, cuda):
+    """clpk_device_info / clpk_device_count behind CudaDevice::init and CudaPeak::enumerate
+    (src/cuda/cuda_device.cpp:40-120, src/cuda/cuda_peak.cpp:221-275) against what torch reports."""
+    n = C.c_int(0)
+    K.clpk_device_count(C.byref(n))
+    assert n.value == cuda.cuda.device_count() >= 1
+    info = N.DeviceInfo()
+    K.clpk_device_info(0, C.byref(info))
+    props = cuda.cuda.get_device_properties(0)
+    assert info.name.decode() == props.name and "B200" in props.name
+    assert (info.cc_major, info.cc_minor) == (10, 0) == (props.major, props.minor)
+    assert info.num_sms == props.multi_processor_count >= 100
+    assert info.total_mem_bytes == props.total_memory > 100 << 30
+    assert info.smem_optin_bytes >= 227 * 1024 and info.l2_bytes >= 64 << 20
+    assert info.sm_clock_khz >= 1_000_000 and info.mem_bus_bits >= 4096
+    assert info.driver_version >= 12000 and info.runtime_version >= 12000
+    with pytest.raises(N.ClpkError):
+        K.clpk_device_info(n.value, C.byref(info))                # one past the last device
