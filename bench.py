@@ -583,7 +583,7 @@ def main():
             return ms, c.get("sm_mhz"), c.get("reasons")
 
         rows = measure_rows(K, N, torch, stream, lambda fn, reps=3: time_together(fn, reps), world, clocked,
-                            check=(rank == 0))
+                            all_ranks_ok=lambda ok: reps.max_over_ranks(0.0 if ok else 1.0) == 0.0)
         if world == 1:
             rows.update(measure_small_rows(K, N, torch, stream, time_once))
 
@@ -765,7 +765,7 @@ def median(xs):
     return xs[n // 2] if n % 2 else 0.5 * (xs[n // 2 - 1] + xs[n // 2])
 
 
-def measure_rows(K, N, torch, stream, time_once, world=1, clocked=None, check=True):
+def measure_rows(K, N, torch, stream, time_once, world=1, clocked=None, all_ranks_ok=lambda ok: ok):
     """Tensor-core peak per dtype (config 3/4) and GEMM (config 5) on this GPU, after the timed region.
 
     Every tensor row is given twice: `burst` (5 launches on a GPU that has just idled) and `sustained` (a loop of
@@ -945,14 +945,14 @@ def measure_rows(K, N, torch, stream, time_once, world=1, clocked=None, check=Tr
                 row["ms_including_scale_repack"] = ms_with_pack
             if dt == N.DT_BF16:
                 row["frac_of_measured_cublas_burst"] = flop / ms / 1e9 / peaks["bf16_tflops"]
-            if check:
-                Cc.fill_(0x7FC0)                                    # bf16 NaN canary under the result that is checked
-                mine()
-                torch.cuda.synchronize()
-                ok, worst = check_gemm_samples(torch, N, dt, m, A, B, Cc, sfs, alpha, row_bytes)
-                row["checked"] = bool(ok) and int(status.item()) == 0
-                row["check"] = {"samples": 64, "worst_error_over_tolerance": worst,
-                                "tolerance": "K*2^-23*sum|a||b| + 2^-8*|c|, vs fp64 dot of the quantised operands"}
+            # every replica checks the C it has just timed; the row is "checked" only if all of them agree
+            Cc.fill_(0x7FC0)                                        # bf16 NaN canary under the result that is checked
+            mine()
+            torch.cuda.synchronize()
+            ok, worst = check_gemm_samples(torch, N, dt, m, A, B, Cc, sfs, alpha, row_bytes)
+            row["checked"] = all_ranks_ok(bool(ok) and int(status.item()) == 0)
+            row["check"] = {"samples": 64, "worst_error_over_tolerance": worst, "replicas": world,
+                            "tolerance": "K*2^-23*sum|a||b| + 2^-8*|c|, vs fp64 dot of the quantised operands"}
             rows[f"gemm_{name}_{m}"] = row
             # The vendor library on the very same operand buffers (same data, same thermal state); for comparison
             # only, never on the product path.  The reference's GEMM rows call cuBLASLt
