@@ -362,7 +362,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
     const uint32_t rank = cluster_ctarank();
     const uint32_t cluster_id = blockIdx.x >> 1;
     const uint32_t n_clusters = gridDim.x >> 1;
-    const uint32_t tiles_m = (p.m + kDenseTileM - 1) / kDenseTileM, tiles_n = p.n / kTileMN;
+    const uint32_t tiles_m = (p.m + kDenseTileM - 1) / kDenseTileM, tiles_n = (p.n + kTileMN - 1) / kTileMN;
     const uint32_t n_tiles = tiles_m * tiles_n;
 
     if (threadIdx.x == 0) {
@@ -1068,7 +1068,7 @@ static int launch_persistent(Kernel kernel, const char *what, int threads, size_
 template <int DT>
 static int launch_gemm(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, const GemmParams &p, cudaStream_t s)
 {
-    const uint32_t n_tiles = ((p.m + kDenseTileM - 1) / kDenseTileM) * (p.n / kTileMN);
+    const uint32_t n_tiles = ((p.m + kDenseTileM - 1) / kDenseTileM) * ((p.n + kTileMN - 1) / kTileMN);
     return launch_persistent(gemm_kernel<DT>, "gemm", kGemmThreads, kGemmSmemBytes, s, p, n_tiles, ta, tb, tc);
 }
 
@@ -1166,11 +1166,13 @@ int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
         g_last_aligned = 0;
         return launch_simt_gemm(a->dtype, a->d_a, a->d_b, a->d_c, a->m, a->n, a->k, a->alpha, as_stream(stream));
     }
-    CLPK_REQUIRE(a->m % 256 == 0 && a->n % 256 == 0 && a->m > 0 && a->n > 0,
-                 "M and N must be positive multiples of 256 (got %u, %u)", a->m, a->n);
-    CLPK_REQUIRE(a->k > 0, "K must be positive");
+    CLPK_REQUIRE(a->m > 0 && a->n > 0 && a->k > 0, "M, N and K must be positive");
     const bool block_scaled = a->dtype == CLPK_DT_NVF4 || a->dtype == CLPK_DT_MXF4;
-    CLPK_REQUIRE(!block_scaled || a->k % 256 == 0, "block-scaled FP4 needs K to be a multiple of 256 (got %u)", a->k);
+    // The dense kinds take ragged shapes: TMA fills what a box reads beyond the operands with zeros and clips what
+    // a box would store beyond C, so a partial tile costs a whole one but needs no code.  The block-scaled kinds
+    // keep whole tiles (their scale factors are repacked per 128 rows and 256 elements of K).
+    CLPK_REQUIRE(!block_scaled || (a->m % 256 == 0 && a->n % 256 == 0 && a->k % 256 == 0),
+                 "block-scaled FP4 needs M, N and K to be multiples of 256 (got %u, %u, %u)", a->m, a->n, a->k);
     CLPK_REQUIRE(((uintptr_t)a->d_a % 16) == 0 && ((uintptr_t)a->d_b % 16) == 0 && ((uintptr_t)a->d_c % 16) == 0,
                  "operands must be 16-byte aligned");
     uint32_t elem_bits;
@@ -1190,8 +1192,10 @@ int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
     cudaStream_t s = as_stream(stream);
 
     const uint64_t row_bytes = (uint64_t)a->k * elem_bits / 8;
-    CLPK_REQUIRE(((uint64_t)a->k * elem_bits) % (8 * kRowBytesK) == 0,
-                 "K = %u: a row of %u-bit elements must be a multiple of 128 bytes", a->k, elem_bits);
+    CLPK_REQUIRE(((uint64_t)a->k * elem_bits) % (8 * 16) == 0,
+                 "K = %u: a row of %u-bit elements must be a multiple of 16 bytes (the pitch of a TMA tensor map)", a->k, elem_bits);
+    const uint32_t out_bytes = (a->dtype == CLPK_DT_TF32 || a->dtype == CLPK_DT_I8) ? 4u : 2u;
+    CLPK_REQUIRE(((uint64_t)a->n * out_bytes) % 16 == 0, "N = %u: a row of C must be a multiple of 16 bytes", a->n);
     CUtensorMap ta, tb;
     rc = make_operand_map(&ta, a->d_a, a->m, row_bytes);
     if (rc != CLPK_OK)
@@ -1205,7 +1209,7 @@ int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
     p.n = a->n;
     p.k = a->k;
     p.k_block_elems = kRowBytesK;          // x coordinate is in bytes: the maps are typed UINT8
-    p.k_blocks = (uint32_t)(row_bytes / kRowBytesK);
+    p.k_blocks = (uint32_t)((row_bytes + kRowBytesK - 1) / kRowBytesK);
     p.c = a->d_c;
     p.alpha = a->alpha;
     p.status = a->d_status;

@@ -124,13 +124,55 @@ def test_gemm_8192_sampled(K, orc, cuda, dtype):
     check_samples(orc, dtype, a, b, c, m, n, k, samples)
 
 
-def test_gemm_rejects_ragged(K, cuda):
-    d = dev_empty(16, cuda.int16)
-    args = N.GemmArgs(dtype=N.DT_BF16, m=250, n=256, k=128, d_a=d.data_ptr(), d_b=d.data_ptr(), d_c=d.data_ptr(),
-                      alpha=1.0, d_status=d.data_ptr())
-    with pytest.raises(N.ClpkError) as e:
-        K.clpk_gemm(C.byref(args), None)
-    assert e.value.code == N.ERR_BAD_ARG
+@pytest.mark.parametrize("dtype", [N.DT_BF16, N.DT_E4M3, N.DT_TF32, N.DT_I8])
+@pytest.mark.parametrize("m,n,k", [(8, 8, 16), (200, 328, 80), (513, 264, 1040), (1000, 1016, 528), (2304, 1800, 144)])
+def test_gemm_ragged_shapes_every_element(K, orc, cuda, dtype, m, n, k):
+    """Shapes that are not whole tiles: TMA zero-fills what a box reads beyond A and B and clips what a box would
+    store beyond C.  int8, bf16 and tf32 compare every element of C, e4m3 a sample with the four corners; the canary
+    after C must stay (nothing is written beyond it) and none may remain inside it."""
+    d_a, d_b = make_gemm_operands(K, cuda, dtype, m, n, k)
+    wide = dtype in WIDE_OUT
+    pad = 4096
+    d_c = cuda.full((m * n + pad,), 0x7FC00000 if wide else 0x7FC0, dtype=cuda.int32 if wide else cuda.int16, device="cuda")
+    d_status = dev_empty(1, cuda.int32)
+    args = N.GemmArgs(dtype=dtype, m=m, n=n, k=k, d_a=d_a.data_ptr(), d_b=d_b.data_ptr(), d_c=d_c.data_ptr(), alpha=1.0,
+                      d_status=d_status.data_ptr())
+    K.clpk_gemm(C.byref(args), stream_ptr())
+    sync()
+    assert int(to_np(d_status)[0]) == 0
+    c_all = to_np(d_c)
+    canary = 0x7FC00000 if wide else 0x7FC0
+    assert np.all(c_all[m * n:].view(np.uint32 if wide else np.uint16) == canary), "the kernel wrote beyond C"
+    c = c_all[:m * n].view(np.uint32 if wide else np.uint16)
+    assert not np.any(c == canary), "some of C was never written"
+    a = to_np(d_a).view(NP_DT[dtype])
+    b = to_np(d_b).view(NP_DT[dtype])
+    if dtype == N.DT_I8:
+        want = a.reshape(m, k).astype(np.int64) @ b.reshape(n, k).astype(np.int64).T
+        assert np.array_equal(c.view(np.int32).reshape(m, n), want.astype(np.int32))
+        return
+    if dtype in (N.DT_BF16, N.DT_TF32):
+        fa = (bf16_to_f64(a) if dtype == N.DT_BF16 else a.view(np.float32).astype(np.float64)).reshape(m, k)
+        fb = (bf16_to_f64(b) if dtype == N.DT_BF16 else b.view(np.float32).astype(np.float64)).reshape(n, k)
+        want, s = fa @ fb.T, np.abs(fa) @ np.abs(fb).T
+        got = (bf16_to_f64(c) if dtype == N.DT_BF16 else c.view(np.float32).astype(np.float64)).reshape(m, n)
+        tol = k * 2.0 ** -23 * s + (2.0 ** -8 * np.abs(want) if dtype == N.DT_BF16 else 0.0) + 1e-30
+        worst = float(np.max(np.abs(got - want) / tol))
+        assert worst <= 1.0, f"worst error over all of C is {worst:.3g}x the stated tolerance"
+        return
+    rng = np.random.default_rng(11)
+    samples = list(zip(rng.integers(0, m, 300), rng.integers(0, n, 300))) + [(0, 0), (m - 1, n - 1), (m - 1, 0), (0, n - 1)]
+    check_samples(orc, dtype, a, b, c, m, n, k, samples)
+
+
+def test_gemm_rejects_misaligned_rows(K, cuda):
+    d = dev_empty(4096, cuda.int16)
+    for m, n, k in ((256, 256, 100), (256, 250, 128)):           # a row of A or of C that is not a multiple of 16 bytes
+        args = N.GemmArgs(dtype=N.DT_BF16, m=m, n=n, k=k, d_a=d.data_ptr(), d_b=d.data_ptr(), d_c=d.data_ptr(),
+                          alpha=1.0, d_status=d.data_ptr())
+        with pytest.raises(N.ClpkError) as e:
+            K.clpk_gemm(C.byref(args), None)
+        assert e.value.code == N.ERR_BAD_ARG
 
 
 # ---- NVFP4 ---------------------------------------------------------------------------------
