@@ -83,7 +83,14 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
     __shared__ __align__(16) float sB[2][kSimtBK][kSgemmLd];
     uint32_t tm, tn;
     raster(M / kSimtTile, N / kSimtTile, &tm, &tn);
-    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    // A warp is 8 (rows) x 4 (columns) threads, the CTA 2 x 4 warps.  A 128-bit shared-memory load takes two passes
+    // of the data pipe per warp when every group of four consecutive lanes asks for at most two different 16-byte
+    // words, and four passes otherwise (measured with a one-warp probe: lane / 2, lane / 4 and lane % 2 cost two
+    // passes, lane % 4 and lane % 8 four).  So bit 0 of the lane picks the column and bit 1 the row: inside a group
+    // of four lanes both fragments have two distinct addresses.
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int lx = (lane & 1) | ((lane >> 1) & 2), ly = ((lane >> 1) & 1) | ((lane >> 2) & 6);
+    const int tx = (warp & 3) * 4 + lx, ty = (warp >> 2) * 8 + ly;
     const float *gA = A + (size_t)tm * kSimtTile * K, *gB = B + (size_t)tn * kSimtTile * K;
 
     // global -> registers: 128 rows x 16 floats per operand = 512 float4, two per thread
@@ -99,7 +106,9 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
     auto stash = [&](int buf) {
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            const int r = lrow + 64 * h;
+            // k rows 8..15 keep their columns with bit 3 flipped: a warp stores 8 consecutive rows r for four k
+            // (lk = 0, 4, 8, 12), and 8 k rows of 132 floats are a multiple of 32 banks apart
+            const int r = (lrow + 64 * h) ^ (lk & 8);
             sA[buf][lk + 0][r] = ra[h].x; sA[buf][lk + 1][r] = ra[h].y; sA[buf][lk + 2][r] = ra[h].z; sA[buf][lk + 3][r] = ra[h].w;
             sB[buf][lk + 0][r] = rb[h].x; sB[buf][lk + 1][r] = rb[h].y; sB[buf][lk + 2][r] = rb[h].z; sB[buf][lk + 3][r] = rb[h].w;
         }
@@ -125,10 +134,11 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
             fetch((kb + 1) * kSimtBK);
 #pragma unroll
         for (int k = 0; k < kSimtBK; k++) {
-            const float4 a0 = *reinterpret_cast<const float4 *>(&sA[cur][k][ty * 4]);
-            const float4 a1 = *reinterpret_cast<const float4 *>(&sA[cur][k][64 + ty * 4]);
-            const float4 b0 = *reinterpret_cast<const float4 *>(&sB[cur][k][tx * 4]);
-            const float4 b1 = *reinterpret_cast<const float4 *>(&sB[cur][k][64 + tx * 4]);
+            const int fa = (ty * 4) ^ (k & 8), fb = (tx * 4) ^ (k & 8);
+            const float4 a0 = *reinterpret_cast<const float4 *>(&sA[cur][k][fa]);
+            const float4 a1 = *reinterpret_cast<const float4 *>(&sA[cur][k][64 + fa]);
+            const float4 b0 = *reinterpret_cast<const float4 *>(&sB[cur][k][fb]);
+            const float4 b1 = *reinterpret_cast<const float4 *>(&sB[cur][k][64 + fb]);
             const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
             const unsigned long long b[4] = {pack2(b0.x, b0.y), pack2(b0.z, b0.w), pack2(b1.x, b1.y), pack2(b1.z, b1.w)};
 #pragma unroll
