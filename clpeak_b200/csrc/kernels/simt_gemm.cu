@@ -72,15 +72,24 @@ __device__ __forceinline__ void ffma2(unsigned long long &d, unsigned long long 
     asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(b));
 }
 
-constexpr int kSgemmPad = 4;
-constexpr int kSgemmLd = kSimtTile + kSgemmPad;          // floats per k row of a shared tile
+constexpr int kSgemmLd = kSimtTile + 4;               // floats per k row of a shared tile
+constexpr int kSgemmThreads = 256;
+constexpr size_t kSgemmTileFloats = (size_t)kSimtBK * kSgemmLd;                // one operand, one buffer: [k][row]
+constexpr size_t kSgemmStagingFloats = 4 * 4 * (size_t)kSgemmThreads;          // four 16-byte chunks per thread
+constexpr size_t kSgemmSmemBytes = (4 * kSgemmTileFloats + 2 * kSgemmStagingFloats) * sizeof(float);
 
-__global__ void __launch_bounds__(256, 2)
+__device__ __forceinline__ void cp_async_16(float *dst_shared, const float *src)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_shared)), "l"(src) : "memory");
+}
+
+__global__ void __launch_bounds__(kSgemmThreads, 2)
 sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__restrict__ C, uint32_t M, uint32_t N,
              uint32_t K, float alpha)
 {
-    __shared__ __align__(16) float sA[2][kSimtBK][kSgemmLd];
-    __shared__ __align__(16) float sB[2][kSimtBK][kSgemmLd];
+    extern __shared__ __align__(16) float ssm[];
+    float *const tiles = ssm;                                   // [buffer][A, B][k][kSgemmLd]
+    float *const staging = ssm + 4 * kSgemmTileFloats;          // [buffer][chunk][thread] of float4
     uint32_t tm, tn;
     raster(M / kSimtTile, N / kSimtTile, &tm, &tn);
     // A warp is 8 (rows) x 4 (columns) threads, the CTA 2 x 4 warps.  A 128-bit shared-memory load takes two passes
@@ -90,33 +99,38 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
     // of four lanes both fragments have two distinct addresses.
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int lx = (lane & 1) | ((lane >> 1) & 2), ly = ((lane >> 1) & 1) | ((lane >> 2) & 6);
-    const int tx = (warp & 3) * 4 + lx, ty = (warp >> 2) * 8 + ly;
-    const float *gA = A + (size_t)tm * kSimtTile * K, *gB = B + (size_t)tn * kSimtTile * K;
+    const int fa = ((warp >> 2) * 8 + ly) * 4, fb = ((warp & 3) * 4 + lx) * 4;
 
-    // global -> registers: 128 rows x 16 floats per operand = 512 float4, two per thread
+    // Operands travel global -> staging (asynchronous 16-byte copies, two k blocks ahead) -> registers -> tile
+    // (transposed: [row][k] in memory, [k][row] in the tile).  Every thread moves the same four chunks through both
+    // hops -- rows lrow and lrow + 64 of A and of B, floats lk .. lk + 3 of the k block -- so only its own copies
+    // have to have landed before it transposes, and nothing read from global memory is held in registers across
+    // the multiply (with the loads going straight to registers the warps stood at the tile stores waiting for
+    // them: 53 against 64 TFLOPS for the same loop without the operand traffic).
     const int lrow = tid >> 2, lk = (tid & 3) * 4;
-    float4 ra[2], rb[2];
-    auto fetch = [&](uint32_t k0) {
+    const float *src[4] = {A + ((size_t)tm * kSimtTile + lrow) * K + lk, A + ((size_t)tm * kSimtTile + lrow + 64) * K + lk,
+                           B + ((size_t)tn * kSimtTile + lrow) * K + lk, B + ((size_t)tn * kSimtTile + lrow + 64) * K + lk};
+    auto fetch = [&](uint32_t kb) {                              // k block kb into staging buffer kb % 2
+        float *st = staging + (kb & 1) * kSgemmStagingFloats + tid * 4;
 #pragma unroll
-        for (int h = 0; h < 2; h++) {
-            ra[h] = *reinterpret_cast<const float4 *>(gA + (size_t)(lrow + 64 * h) * K + k0 + lk);
-            rb[h] = *reinterpret_cast<const float4 *>(gB + (size_t)(lrow + 64 * h) * K + k0 + lk);
-        }
+        for (int c = 0; c < 4; c++)
+            cp_async_16(st + c * 4 * kSgemmThreads, src[c] + (size_t)kb * kSimtBK);
     };
-    auto stash = [&](int buf) {
+    auto transpose = [&](uint32_t kb) {                          // staging buffer kb % 2 into tile buffer kb % 2
+        const float *st = staging + (kb & 1) * kSgemmStagingFloats + tid * 4;
+        float *sA = tiles + (kb & 1) * 2 * kSgemmTileFloats, *sB = sA + kSgemmTileFloats;
 #pragma unroll
-        for (int h = 0; h < 2; h++) {
-            // k rows 8..15 keep their columns with bit 3 flipped: a warp stores 8 consecutive rows r for four k
+        for (int c = 0; c < 4; c++) {
+            const float4 v = *reinterpret_cast<const float4 *>(st + c * 4 * kSgemmThreads);
+            // k rows 8..15 keep their columns with bit 3 flipped: a warp stores 8 consecutive rows for four k
             // (lk = 0, 4, 8, 12), and 8 k rows of 132 floats are a multiple of 32 banks apart
-            const int r = (lrow + 64 * h) ^ (lk & 8);
-            sA[buf][lk + 0][r] = ra[h].x; sA[buf][lk + 1][r] = ra[h].y; sA[buf][lk + 2][r] = ra[h].z; sA[buf][lk + 3][r] = ra[h].w;
-            sB[buf][lk + 0][r] = rb[h].x; sB[buf][lk + 1][r] = rb[h].y; sB[buf][lk + 2][r] = rb[h].z; sB[buf][lk + 3][r] = rb[h].w;
+            float *dst = (c < 2 ? sA : sB) + lk * kSgemmLd + ((lrow + 64 * (c & 1)) ^ (lk & 8));
+            dst[0] = v.x; dst[kSgemmLd] = v.y; dst[2 * kSgemmLd] = v.z; dst[3 * kSgemmLd] = v.w;
         }
     };
 
     // Accumulators as pairs of neighbouring columns: sm_100's packed fma.rn.f32x2 does two FMAs per issued
-    // instruction (same rounding as two scalar FMAs), which halves the issue slots the multiply needs and leaves
-    // room for the shared-memory loads next to it.
+    // instruction with the rounding of two scalar FMAs.
     unsigned long long acc[8][4];
 #pragma unroll
     for (int i = 0; i < 8; i++)
@@ -124,21 +138,28 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
         for (int j = 0; j < 4; j++)
             acc[i][j] = 0ull;
 
-    fetch(0);
-    stash(0);
-    __syncthreads();
     const uint32_t nk = K / kSimtBK;
+    fetch(0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    if (nk > 1)
+        fetch(1);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    transpose(0);
+    __syncthreads();
     for (uint32_t kb = 0; kb < nk; kb++) {
-        const int cur = kb & 1;
-        if (kb + 1 < nk)
-            fetch((kb + 1) * kSimtBK);
+        // staging buffer kb % 2 was emptied into the tile before the last barrier: refill it two k blocks ahead
+        if (kb + 2 < nk)
+            fetch(kb + 2);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const float *sA = tiles + (kb & 1) * 2 * kSgemmTileFloats, *sB = sA + kSgemmTileFloats;
 #pragma unroll
         for (int k = 0; k < kSimtBK; k++) {
-            const int fa = (ty * 4) ^ (k & 8), fb = (tx * 4) ^ (k & 8);
-            const float4 a0 = *reinterpret_cast<const float4 *>(&sA[cur][k][fa]);
-            const float4 a1 = *reinterpret_cast<const float4 *>(&sA[cur][k][64 + fa]);
-            const float4 b0 = *reinterpret_cast<const float4 *>(&sB[cur][k][fb]);
-            const float4 b1 = *reinterpret_cast<const float4 *>(&sB[cur][k][64 + fb]);
+            const int ca = fa ^ (k & 8), cb = fb ^ (k & 8);
+            const float4 a0 = *reinterpret_cast<const float4 *>(sA + k * kSgemmLd + ca);
+            const float4 a1 = *reinterpret_cast<const float4 *>(sA + k * kSgemmLd + 64 + ca);
+            const float4 b0 = *reinterpret_cast<const float4 *>(sB + k * kSgemmLd + cb);
+            const float4 b1 = *reinterpret_cast<const float4 *>(sB + k * kSgemmLd + 64 + cb);
             const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
             const unsigned long long b[4] = {pack2(b0.x, b0.y), pack2(b0.z, b0.w), pack2(b1.x, b1.y), pack2(b1.z, b1.w)};
 #pragma unroll
@@ -150,7 +171,8 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
             }
         }
         if (kb + 1 < nk) {
-            stash(cur ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");      // k block kb + 1 is in staging (kb + 2 may still fly)
+            transpose(kb + 1);
             __syncthreads();
         }
     }
@@ -158,12 +180,12 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
     float *gC = C + (size_t)tm * kSimtTile * N + (size_t)tn * kSimtTile;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-        const int r = (i < 4 ? 0 : 64) + ty * 4 + (i & 3);
+        const int r = (i < 4 ? 0 : 64) + fa + (i & 3);
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const float2 lo = unpack2(acc[i][2 * h]), hi = unpack2(acc[i][2 * h + 1]);
             const float4 v = make_float4(alpha * lo.x, alpha * lo.y, alpha * hi.x, alpha * hi.y);
-            *reinterpret_cast<float4 *>(gC + (size_t)r * N + 64 * h + tx * 4) = v;
+            *reinterpret_cast<float4 *>(gC + (size_t)r * N + 64 * h + fb) = v;
         }
     }
 }
@@ -278,8 +300,9 @@ int launch_simt_gemm(int dtype, const void *a, const void *b, void *c, uint32_t 
     uint64_t tiles = (uint64_t)(m / kSimtTile) * (n / kSimtTile);
     CLPK_REQUIRE(tiles <= 0x3FFFFFFFull, "too many tiles");
     if (dtype == CLPK_DT_F32) {
-        sgemm_kernel<<<(unsigned)tiles, 256, 0, s>>>(static_cast<const float *>(a), static_cast<const float *>(b),
-                                                     static_cast<float *>(c), m, n, k, alpha);
+        CLPK_CUDA(cudaFuncSetAttribute(sgemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSgemmSmemBytes));
+        sgemm_kernel<<<(unsigned)tiles, kSgemmThreads, kSgemmSmemBytes, s>>>(
+            static_cast<const float *>(a), static_cast<const float *>(b), static_cast<float *>(c), m, n, k, alpha);
         CLPK_LAUNCH_CHECK("sgemm");
     } else {
         // 128 x 64 CTA tiles: 34.2-34.5 TFLOPS at 4096^3 / 8192^3 against 31.9-32.1 with 128 x 128 tiles of 8 warps
