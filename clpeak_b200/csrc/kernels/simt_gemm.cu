@@ -73,9 +73,10 @@ __device__ __forceinline__ void ffma2(unsigned long long &d, unsigned long long 
 }
 
 constexpr int kSgemmLd = kSimtTile + 4;               // floats per k row of a shared tile
-constexpr int kSgemmThreads = 256;
+constexpr int kSgemmThreads = 128;
+constexpr int kSgemmChunks = 2 * kSimtTile * kSimtBK / 4 / kSgemmThreads;      // 16-byte chunks per thread and k block
 constexpr size_t kSgemmTileFloats = (size_t)kSimtBK * kSgemmLd;                // one operand, one buffer: [k][row]
-constexpr size_t kSgemmStagingFloats = 4 * 4 * (size_t)kSgemmThreads;          // four 16-byte chunks per thread
+constexpr size_t kSgemmStagingFloats = kSgemmChunks * 4 * (size_t)kSgemmThreads;
 constexpr size_t kSgemmSmemBytes = (4 * kSgemmTileFloats + 2 * kSgemmStagingFloats) * sizeof(float);
 
 __device__ __forceinline__ void cp_async_16(float *dst_shared, const float *src)
@@ -92,50 +93,54 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
     float *const staging = ssm + 4 * kSgemmTileFloats;          // [buffer][chunk][thread] of float4
     uint32_t tm, tn;
     raster(M / kSimtTile, N / kSimtTile, &tm, &tn);
-    // A warp is 8 (rows) x 4 (columns) threads, the CTA 2 x 4 warps.  A 128-bit shared-memory load takes two passes
-    // of the data pipe per warp when every group of four consecutive lanes asks for at most two different 16-byte
-    // words, and four passes otherwise (measured with a one-warp probe: lane / 2, lane / 4 and lane % 2 cost two
-    // passes, lane % 4 and lane % 8 four).  So bit 0 of the lane picks the column and bit 1 the row: inside a group
-    // of four lanes both fragments have two distinct addresses.
+    // Four warps in a 2 x 2 grid, 64 x 64 outputs per warp, a warp 8 (rows) x 4 (columns) threads, 8 rows x 16
+    // columns per thread as 4 x 4 blocks.  A 128-bit shared-memory load takes two passes of the data pipe per warp
+    // when every group of four consecutive lanes asks for at most two different 16-byte words, and four passes
+    // otherwise (measured with a one-warp probe: lane / 2, lane / 4 and lane % 2 cost two passes, lane % 4 and
+    // lane % 8 four).  So lane bits 0 and 2 pick the column block and bits 1, 3, 4 the row block: inside a group of
+    // four lanes both fragments have two distinct addresses.
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int lx = (lane & 1) | ((lane >> 1) & 2), ly = ((lane >> 1) & 1) | ((lane >> 2) & 6);
-    const int fa = ((warp >> 2) * 8 + ly) * 4, fb = ((warp & 3) * 4 + lx) * 4;
+    const int fa = (warp >> 1) * 64 + ly * 4, fb = (warp & 1) * 64 + lx * 4;
 
     // Operands travel global -> staging (asynchronous 16-byte copies, two k blocks ahead) -> registers -> tile
-    // (transposed: [row][k] in memory, [k][row] in the tile).  Every thread moves the same four chunks through both
-    // hops -- rows lrow and lrow + 64 of A and of B, floats lk .. lk + 3 of the k block -- so only its own copies
-    // have to have landed before it transposes, and nothing read from global memory is held in registers across
-    // the multiply (with the loads going straight to registers the warps stood at the tile stores waiting for
-    // them: 53 against 64 TFLOPS for the same loop without the operand traffic).
+    // (transposed: [row][k] in memory, [k][row] in the tile).  Every thread moves the same chunks through both
+    // hops -- rows lrow + 32 c of A and of B, floats lk .. lk + 3 of the k block -- so only its own copies have to
+    // have landed before it transposes, and nothing read from global memory is held in registers across the
+    // multiply (with the loads going straight to registers the warps stood at the tile stores waiting for them:
+    // 53 against 64 TFLOPS for the same loop without the operand traffic).
     const int lrow = tid >> 2, lk = (tid & 3) * 4;
-    const float *src[4] = {A + ((size_t)tm * kSimtTile + lrow) * K + lk, A + ((size_t)tm * kSimtTile + lrow + 64) * K + lk,
-                           B + ((size_t)tn * kSimtTile + lrow) * K + lk, B + ((size_t)tn * kSimtTile + lrow + 64) * K + lk};
+    const float *srcA = A + ((size_t)tm * kSimtTile + lrow) * K + lk, *srcB = B + ((size_t)tn * kSimtTile + lrow) * K + lk;
     auto fetch = [&](uint32_t kb) {                              // k block kb into staging buffer kb % 2
         float *st = staging + (kb & 1) * kSgemmStagingFloats + tid * 4;
 #pragma unroll
-        for (int c = 0; c < 4; c++)
-            cp_async_16(st + c * 4 * kSgemmThreads, src[c] + (size_t)kb * kSimtBK);
+        for (int c = 0; c < 4; c++) {
+            cp_async_16(st + c * 4 * kSgemmThreads, srcA + (size_t)c * 32 * K + (size_t)kb * kSimtBK);
+            cp_async_16(st + (4 + c) * 4 * kSgemmThreads, srcB + (size_t)c * 32 * K + (size_t)kb * kSimtBK);
+        }
     };
     auto transpose = [&](uint32_t kb) {                          // staging buffer kb % 2 into tile buffer kb % 2
         const float *st = staging + (kb & 1) * kSgemmStagingFloats + tid * 4;
         float *sA = tiles + (kb & 1) * 2 * kSgemmTileFloats, *sB = sA + kSgemmTileFloats;
 #pragma unroll
-        for (int c = 0; c < 4; c++) {
+        for (int c = 0; c < 8; c++) {
             const float4 v = *reinterpret_cast<const float4 *>(st + c * 4 * kSgemmThreads);
             // k rows 8..15 keep their columns with bit 3 flipped: a warp stores 8 consecutive rows for four k
             // (lk = 0, 4, 8, 12), and 8 k rows of 132 floats are a multiple of 32 banks apart
-            float *dst = (c < 2 ? sA : sB) + lk * kSgemmLd + ((lrow + 64 * (c & 1)) ^ (lk & 8));
+            float *dst = (c < 4 ? sA : sB) + lk * kSgemmLd + ((lrow + 32 * (c & 3)) ^ (lk & 8));
             dst[0] = v.x; dst[kSgemmLd] = v.y; dst[2 * kSgemmLd] = v.z; dst[3 * kSgemmLd] = v.w;
         }
     };
 
     // Accumulators as pairs of neighbouring columns: sm_100's packed fma.rn.f32x2 does two FMAs per issued
-    // instruction with the rounding of two scalar FMAs.
-    unsigned long long acc[8][4];
+    // instruction with the rounding of two scalar FMAs.  8 rows x 8 pairs with the row value duplicated into a
+    // fresh register pair just before its eight FMAs runs at 71 of 74 TFLOPS from registers alone with 8 warps per
+    // SM; 16 rows x 4 pairs at 51 (register-bank conflicts between the operand pairs).
+    unsigned long long acc[8][8];
 #pragma unroll
     for (int i = 0; i < 8; i++)
 #pragma unroll
-        for (int j = 0; j < 4; j++)
+        for (int j = 0; j < 8; j++)
             acc[i][j] = 0ull;
 
     const uint32_t nk = K / kSimtBK;
@@ -156,17 +161,24 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
 #pragma unroll
         for (int k = 0; k < kSimtBK; k++) {
             const int ca = fa ^ (k & 8), cb = fb ^ (k & 8);
-            const float4 a0 = *reinterpret_cast<const float4 *>(sA + k * kSgemmLd + ca);
-            const float4 a1 = *reinterpret_cast<const float4 *>(sA + k * kSgemmLd + 64 + ca);
-            const float4 b0 = *reinterpret_cast<const float4 *>(sB + k * kSgemmLd + cb);
-            const float4 b1 = *reinterpret_cast<const float4 *>(sB + k * kSgemmLd + 64 + cb);
-            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-            const unsigned long long b[4] = {pack2(b0.x, b0.y), pack2(b0.z, b0.w), pack2(b1.x, b1.y), pack2(b1.z, b1.w)};
+            float a[8];
+            unsigned long long b[8];
+#pragma unroll
+            for (int q = 0; q < 2; q++) {
+                const float4 v = *reinterpret_cast<const float4 *>(sA + k * kSgemmLd + ca + 32 * q);
+                a[4 * q] = v.x; a[4 * q + 1] = v.y; a[4 * q + 2] = v.z; a[4 * q + 3] = v.w;
+            }
+#pragma unroll
+            for (int h = 0; h < 4; h++) {
+                const float4 v = *reinterpret_cast<const float4 *>(sB + k * kSgemmLd + cb + 16 * h);
+                b[2 * h] = pack2(v.x, v.y);
+                b[2 * h + 1] = pack2(v.z, v.w);
+            }
 #pragma unroll
             for (int i = 0; i < 8; i++) {
                 const unsigned long long aa = pack2(a[i], a[i]);
 #pragma unroll
-                for (int j = 0; j < 4; j++)
+                for (int j = 0; j < 8; j++)
                     ffma2(acc[i][j], aa, b[j]);
             }
         }
@@ -180,12 +192,12 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
     float *gC = C + (size_t)tm * kSimtTile * N + (size_t)tn * kSimtTile;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-        const int r = (i < 4 ? 0 : 64) + fa + (i & 3);
+        const int r = fa + 32 * (i >> 2) + (i & 3);
 #pragma unroll
-        for (int h = 0; h < 2; h++) {
+        for (int h = 0; h < 4; h++) {
             const float2 lo = unpack2(acc[i][2 * h]), hi = unpack2(acc[i][2 * h + 1]);
             const float4 v = make_float4(alpha * lo.x, alpha * lo.y, alpha * hi.x, alpha * hi.y);
-            *reinterpret_cast<float4 *>(gC + (size_t)r * N + 64 * h + fb) = v;
+            *reinterpret_cast<float4 *>(gC + (size_t)r * N + fb + 16 * h) = v;
         }
     }
 }
