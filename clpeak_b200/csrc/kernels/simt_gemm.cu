@@ -4,20 +4,27 @@
 // C[M][N] = alpha * A[M][K] * B[N][K]^T, both operands K-contiguous, C row-major in the
 // operand type.
 //
-// fp32 (sgemm_kernel).  128 x 128 x 16 tile per CTA of 256 threads, 8 x 8 outputs per
-// thread as four 4 x 4 blocks so that every shared-memory read is a conflict-free
-// 128-bit load; operands are transposed into shared memory ([k][m]) on the way in, the
-// next k block travels global -> registers while the current one is multiplied, two
-// shared-memory buffers.  The multiply is sm_100's packed fma.rn.f32x2 (two FMAs per
-// issued instruction).  Bound: the fp32 pipe, 128 FMA / clock / SM (B200: 148 SMs x 128
-// x 2 x 1.965 GHz = 74.4 TFLOPS); the inner loop issues 32 packed FMAs per 4 LDS.128.
-// Per k step a warp pulls 32 x 64 bytes of fragments out of shared memory (every thread
-// needs its own copy in registers): 2 KiB at 128 bytes per clock = 16 clocks per 64 clocks
-// of multiply on its scheduler, i.e. with four schedulers the fragment traffic of an SM
-// takes as long as its multiplies, and the fp32 pipe measures 74 % busy.  8 x 16 outputs
-// per thread (3 KiB per 128 clocks) was tried: one CTA of 216-register threads per SM, and
-// slower (50.6 against 54.0 TFLOPS at 8192^3) -- the second CTA's warps are worth more
-// than the better ratio.
+// fp32 (sgemm_kernel).  128 x 128 x 16 tile per CTA of 128 threads = 4 warps in a 2 x 2
+// grid, two CTAs per SM, 8 rows x 16 columns of outputs per thread.  The multiply is
+// sm_100's packed fma.rn.f32x2 (two FMAs per issued instruction) on accumulator pairs of
+// neighbouring columns, the row value duplicated into a fresh register pair just before
+// its eight FMAs.  Which shape the packed FMA likes was measured from registers alone: 8
+// rows x 8 pairs with that duplication runs at 71 of 74 TFLOPS with 8 warps per SM, 16
+// rows x 4 pairs at 51, pairs over two neighbouring k (no duplication at all) at 52 --
+// the operand pairs collide in the register banks.  Operands are transposed into shared
+// memory ([k][row]) so that both fragments are 128-bit loads: global -> staging buffer by
+// asynchronous 16-byte copies two k blocks ahead, staging -> registers -> tile by the
+// thread that copied them, one barrier per k block.  Fragment loads are laid out for two
+// passes of the shared-memory data pipe per 128-bit load (see the kernel).  Bound: the
+// fp32 pipe, 128 FMA / clock / SM (B200: 148 SMs x 128 x 2 x 1.965 GHz = 74.4 TFLOPS).
+// Measured 62.6 TFLOPS at 8192^3 (0.84 of the pipe, 0.95 of cuBLAS) and 60.8 at 4096^3
+// (1.07 of cuBLAS: 1024 tiles are 3.5 waves of 296 CTAs, and a CTA alone on its SM runs
+// twice as fast).  The same loop runs at 68.4 without the transposition, 65.2 without the
+// fragment loads and 69.6 with neither; moving the transposition under the multiplies
+// (with or without a branch) and 128-bit tile stores changed nothing.  Earlier shapes:
+// 256 threads x (8 x 8) with the next k block held in registers across the multiply,
+// 54.0 (the warps stood at the tile stores waiting for the global loads); the same through
+// the staging buffer, 58.9.
 //
 // fp64 (dgemm_kernel).  128 x 64 x 16 tile per CTA of 128 threads = 4 warps in a 2 x 2
 // grid, two CTAs per SM, 64 x 32 outputs per warp = 8 x 4 m8n8k4 accumulator tiles (128
