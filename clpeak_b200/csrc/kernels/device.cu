@@ -23,6 +23,9 @@ void set_error(const char *fmt, ...)
 int cuda_fail(cudaError_t e, const char *what)
 {
     set_error("%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+    // The runtime also keeps a failed call's code as its "last error"; this failure is reported here, so take it
+    // back out, or the next kernel launch's check would report it a second time (a sticky error stays whatever we do).
+    (void)cudaGetLastError();
     if (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver ||
         e == cudaErrorInitializationError)
         return CLPK_ERR_NO_DEVICE;

@@ -17,6 +17,7 @@ import xml.etree.ElementTree as ET
 import pytest
 
 from clpeak_b200 import native as N
+from tests.gpu_util import dev_empty, stream_ptr, sync
 
 pytestmark = pytest.mark.gpu
 
@@ -305,3 +306,7 @@ def test_device_info_describes_a_b200(K, cuda):
     assert info.driver_version >= 12000 and info.runtime_version >= 12000
     with pytest.raises(N.ClpkError):
         K.clpk_device_info(n.value, C.byref(info))                # one past the last device
+    # a failure that has been reported does not come back at the next launch
+    d = dev_empty(4, cuda.float32)
+    K.clpk_fill_f32(d.data_ptr(), 4, 1, N.DIST_UNIFORM01, 0.0, 1.0, stream_ptr())
+    sync()
