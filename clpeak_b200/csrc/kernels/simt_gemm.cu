@@ -34,10 +34,13 @@
 // k lane%4) fall in 16 distinct 8-byte banks per half warp.  Bound: the DMMA pipe, 64
 // fp64 FMA / clock / SM, the same rate as the scalar DFMA pipe (37.2 TFLOPS at 1.965 GHz).
 //
+// Both take any M, N > 0 and any K that keeps operand rows 16-byte aligned (a multiple of 4
+// floats, 2 doubles): a second instantiation of each kernel zero-fills the chunks a tile
+// reaches beyond A or B (cp.async with a source size of 0) and skips the stores beyond C;
+// whole tiles and k blocks take the instantiation without the checks.
+//
 // CTAs walk C in groups of 16 tile rows so that the operand panels a wave of CTAs needs
 // stay in L2.  Work 2*M*N*K flop; minimum HBM bytes (M*K + N*K + M*N) * element.
-#include <cuda_pipeline.h>
-
 #include "../clpk_internal.h"
 
 namespace clpk {
@@ -87,11 +90,22 @@ constexpr size_t kSgemmTileFloats = (size_t)kSimtBK * kSgemmLd;                /
 constexpr size_t kSgemmStagingFloats = kSgemmChunks * 4 * (size_t)kSgemmThreads;
 constexpr size_t kSgemmSmemBytes = (4 * kSgemmTileFloats + 2 * kSgemmStagingFloats) * sizeof(float);
 
-__device__ __forceinline__ void cp_async_16(float *dst_shared, const float *src)
+__device__ __forceinline__ void cp_async_16(void *dst_shared, const void *src)
 {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_shared)), "l"(src) : "memory");
 }
 
+// the same copy, or 16 bytes of zeros when the chunk lies outside the operand (nothing is read then)
+__device__ __forceinline__ void cp_async_16_or_zeros(void *dst_shared, const void *src, bool inside)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_shared)), "l"(src),
+                 "r"(inside ? 16u : 0u)
+                 : "memory");
+}
+
+// RAGGED: M, N need not be multiples of the tile nor K of the k block (K a multiple of 4, so that rows stay 16-byte
+// aligned): chunks outside the operands arrive as zeros, stores outside C are skipped.
+template <bool RAGGED>
 __global__ void __launch_bounds__(kSgemmThreads, 2)
 sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__restrict__ C, uint32_t M, uint32_t N,
              uint32_t K, float alpha)
@@ -100,7 +114,7 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
     float *const tiles = ssm;                                   // [buffer][A, B][k][kSgemmLd]
     float *const staging = ssm + 4 * kSgemmTileFloats;          // [buffer][chunk][thread] of float4
     uint32_t tm, tn;
-    raster(M / kSimtTile, N / kSimtTile, &tm, &tn);
+    raster((M + kSimtTile - 1) / kSimtTile, (N + kSimtTile - 1) / kSimtTile, &tm, &tn);
     // Four warps in a 2 x 2 grid, 64 x 64 outputs per warp, a warp 8 (rows) x 4 (columns) threads, 8 rows x 16
     // columns per thread as 4 x 4 blocks.  A 128-bit shared-memory load takes two passes of the data pipe per warp
     // when every group of four consecutive lanes asks for at most two different 16-byte words, and four passes
@@ -123,8 +137,15 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
         float *st = staging + (kb & 1) * kSgemmStagingFloats + tid * 4;
 #pragma unroll
         for (int c = 0; c < 4; c++) {
-            cp_async_16(st + c * 4 * kSgemmThreads, srcA + (size_t)c * 32 * K + (size_t)kb * kSimtBK);
-            cp_async_16(st + (4 + c) * 4 * kSgemmThreads, srcB + (size_t)c * 32 * K + (size_t)kb * kSimtBK);
+            if (RAGGED) {
+                const bool in_k = kb * kSimtBK + lk < K;
+                const bool in_a = in_k && tm * kSimtTile + lrow + 32 * c < M, in_b = in_k && tn * kSimtTile + lrow + 32 * c < N;
+                cp_async_16_or_zeros(st + c * 4 * kSgemmThreads, in_a ? srcA + (size_t)c * 32 * K + (size_t)kb * kSimtBK : A, in_a);
+                cp_async_16_or_zeros(st + (4 + c) * 4 * kSgemmThreads, in_b ? srcB + (size_t)c * 32 * K + (size_t)kb * kSimtBK : B, in_b);
+            } else {
+                cp_async_16(st + c * 4 * kSgemmThreads, srcA + (size_t)c * 32 * K + (size_t)kb * kSimtBK);
+                cp_async_16(st + (4 + c) * 4 * kSgemmThreads, srcB + (size_t)c * 32 * K + (size_t)kb * kSimtBK);
+            }
         }
     };
     auto transpose = [&](uint32_t kb) {                          // staging buffer kb % 2 into tile buffer kb % 2
@@ -151,7 +172,7 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
         for (int j = 0; j < 8; j++)
             acc[i][j] = 0ull;
 
-    const uint32_t nk = K / kSimtBK;
+    const uint32_t nk = (K + kSimtBK - 1) / kSimtBK;
     fetch(0);
     asm volatile("cp.async.commit_group;" ::: "memory");
     if (nk > 1)
@@ -205,7 +226,21 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
         for (int h = 0; h < 4; h++) {
             const float2 lo = unpack2(acc[i][2 * h]), hi = unpack2(acc[i][2 * h + 1]);
             const float4 v = make_float4(alpha * lo.x, alpha * lo.y, alpha * hi.x, alpha * hi.y);
-            *reinterpret_cast<float4 *>(gC + (size_t)r * N + fb + 16 * h) = v;
+            if (!RAGGED) {
+                *reinterpret_cast<float4 *>(gC + (size_t)r * N + fb + 16 * h) = v;
+            } else if (tm * kSimtTile + r < M) {
+                const uint32_t col = tn * kSimtTile + fb + 16 * h;
+                float *dst = gC + (size_t)r * N + fb + 16 * h;
+                if ((N & 3) == 0 && col < N) {
+                    *reinterpret_cast<float4 *>(dst) = v;
+                } else {
+                    const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int t = 0; t < 4; t++)
+                        if (col + t < N)
+                            dst[t] = e[t];
+                }
+            }
         }
     }
 }
@@ -231,7 +266,7 @@ __device__ __forceinline__ void dmma_m8n8k4(double &d0, double &d1, double a, do
         : "d"(a), "d"(b));
 }
 
-template <int CN>
+template <int CN, bool RAGGED>
 __global__ void __launch_bounds__(Dgemm<CN>::threads, 128 / CN)
 dgemm_kernel(const double *__restrict__ A, const double *__restrict__ B, double *__restrict__ C, uint32_t M, uint32_t N,
              uint32_t K, double alpha)
@@ -240,7 +275,7 @@ dgemm_kernel(const double *__restrict__ A, const double *__restrict__ B, double 
     constexpr int kThreads = Dgemm<CN>::threads;
     constexpr size_t kDgemmStageDoubles = Dgemm<CN>::stage_doubles;
     uint32_t tm, tn;
-    raster(M / kSimtTile, N / CN, &tm, &tn);
+    raster((M + kSimtTile - 1) / kSimtTile, (N + CN - 1) / CN, &tm, &tn);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     constexpr int kWarpsN = CN / 32;
     const int wm = (warp / kWarpsN) * 64, wn = (warp % kWarpsN) * 32;   // this warp's 64 x 32 corner inside the tile
@@ -252,12 +287,22 @@ dgemm_kernel(const double *__restrict__ A, const double *__restrict__ B, double 
 #pragma unroll
         for (int i = 0; i < kSimtTile * 8 / kThreads; i++) {
             const int c = tid + kThreads * i, r = c >> 3, kc = (c & 7) * 2;
-            __pipeline_memcpy_async(sa + r * kDgemmLd + kc, gA + (size_t)r * K + k0 + kc, 16);
+            if (RAGGED) {
+                const bool inside = tm * kSimtTile + r < M && k0 + kc < K;
+                cp_async_16_or_zeros(sa + r * kDgemmLd + kc, inside ? gA + (size_t)r * K + k0 + kc : A, inside);
+            } else {
+                cp_async_16(sa + r * kDgemmLd + kc, gA + (size_t)r * K + k0 + kc);
+            }
         }
 #pragma unroll
         for (int i = 0; i < CN * 8 / kThreads; i++) {
             const int c = tid + kThreads * i, r = c >> 3, kc = (c & 7) * 2;
-            __pipeline_memcpy_async(sb + r * kDgemmLd + kc, gB + (size_t)r * K + k0 + kc, 16);
+            if (RAGGED) {
+                const bool inside = tn * CN + r < N && k0 + kc < K;
+                cp_async_16_or_zeros(sb + r * kDgemmLd + kc, inside ? gB + (size_t)r * K + k0 + kc : B, inside);
+            } else {
+                cp_async_16(sb + r * kDgemmLd + kc, gB + (size_t)r * K + k0 + kc);
+            }
         }
     };
 
@@ -268,20 +313,20 @@ dgemm_kernel(const double *__restrict__ A, const double *__restrict__ B, double 
         for (int j = 0; j < 4; j++)
             acc[i][j][0] = acc[i][j][1] = 0.0;
 
-    const uint32_t nk = K / kSimtBK;
+    const uint32_t nk = (K + kSimtBK - 1) / kSimtBK;
 #pragma unroll
     for (int s = 0; s < kDgemmStages - 1; s++) {
         if ((uint32_t)s < nk)
             load_stage(s, s * kSimtBK);
-        __pipeline_commit();
+        asm volatile("cp.async.commit_group;" ::: "memory");
     }
     const int fr = lane >> 2, fk = lane & 3;                        // fragment row (or column of B) and k of this lane
     for (uint32_t kb = 0; kb < nk; kb++) {
-        __pipeline_wait_prior(kDgemmStages - 2);
+        asm volatile("cp.async.wait_group %0;" ::"n"(kDgemmStages - 2) : "memory");
         __syncthreads();                                            // stage kb has landed; stage kb-1 is free for reuse
         if (kb + kDgemmStages - 1 < nk)
             load_stage((kb + kDgemmStages - 1) % kDgemmStages, (kb + kDgemmStages - 1) * kSimtBK);
-        __pipeline_commit();
+        asm volatile("cp.async.commit_group;" ::: "memory");
         const double *sa = dsm + (size_t)(kb % kDgemmStages) * kDgemmStageDoubles, *sb = sa + (size_t)kSimtTile * kDgemmLd;
 #pragma unroll
         for (int k4 = 0; k4 < kSimtBK; k4 += 4) {
@@ -299,7 +344,7 @@ dgemm_kernel(const double *__restrict__ A, const double *__restrict__ B, double 
                     dmma_m8n8k4(acc[i][j][0], acc[i][j][1], a[i], b[j]);
         }
     }
-    __pipeline_wait_prior(0);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
 
     // accumulator tile (i, j): this lane holds row lane/4, columns 2*(lane%4) and the next one
     double *gC = C + ((size_t)tm * kSimtTile + wm) * N + (size_t)tn * CN + wn;
@@ -307,27 +352,48 @@ dgemm_kernel(const double *__restrict__ A, const double *__restrict__ B, double 
     for (int i = 0; i < 8; i++)
 #pragma unroll
         for (int j = 0; j < 4; j++)
-            *reinterpret_cast<double2 *>(gC + (size_t)(8 * i + fr) * N + 8 * j + 2 * fk) =
-                make_double2(alpha * acc[i][j][0], alpha * acc[i][j][1]);
+        {
+            double *dst = gC + (size_t)(8 * i + fr) * N + 8 * j + 2 * fk;
+            const double2 v = make_double2(alpha * acc[i][j][0], alpha * acc[i][j][1]);
+            if (!RAGGED) {
+                *reinterpret_cast<double2 *>(dst) = v;
+            } else if (tm * kSimtTile + wm + 8 * i + fr < M) {
+                const uint32_t col = tn * CN + wn + 8 * j + 2 * fk;
+                if ((N & 1) == 0 && col < N) {
+                    *reinterpret_cast<double2 *>(dst) = v;
+                } else {
+                    if (col < N)
+                        dst[0] = v.x;
+                    if (col + 1 < N)
+                        dst[1] = v.y;
+                }
+            }
+        }
 }
 
 int launch_simt_gemm(int dtype, const void *a, const void *b, void *c, uint32_t m, uint32_t n, uint32_t k, float alpha,
                      cudaStream_t s)
 {
-    CLPK_REQUIRE(m % kSimtTile == 0 && n % kSimtTile == 0 && m > 0 && n > 0, "M and N must be multiples of %d", kSimtTile);
-    CLPK_REQUIRE(k % kSimtBK == 0 && k > 0, "K must be a multiple of %d", kSimtBK);
+    CLPK_REQUIRE(m > 0 && n > 0 && k > 0, "M, N and K must be positive");
+    const uint32_t k_unit = dtype == CLPK_DT_F32 ? 4 : 2;            // elements per 16 bytes: operand rows stay aligned
+    CLPK_REQUIRE(k % k_unit == 0, "K = %u: a row of A and B must be a multiple of 16 bytes", k);
     CLPK_REQUIRE(((uintptr_t)a % 16) == 0 && ((uintptr_t)b % 16) == 0 && ((uintptr_t)c % 16) == 0, "operands must be 16-byte aligned");
-    uint64_t tiles = (uint64_t)(m / kSimtTile) * (n / kSimtTile);
+    const uint32_t tile_n = dtype == CLPK_DT_F32 ? kSimtTile : 64;
+    const uint64_t tiles = (uint64_t)((m + kSimtTile - 1) / kSimtTile) * ((n + tile_n - 1) / tile_n);
     CLPK_REQUIRE(tiles <= 0x3FFFFFFFull, "too many tiles");
+    // whole tiles and whole k blocks take the kernel without the bounds checks
+    const bool ragged = m % kSimtTile != 0 || n % tile_n != 0 || k % kSimtBK != 0;
     if (dtype == CLPK_DT_F32) {
-        CLPK_CUDA(cudaFuncSetAttribute(sgemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSgemmSmemBytes));
-        sgemm_kernel<<<(unsigned)tiles, kSgemmThreads, kSgemmSmemBytes, s>>>(
-            static_cast<const float *>(a), static_cast<const float *>(b), static_cast<float *>(c), m, n, k, alpha);
+        auto kernel = ragged ? sgemm_kernel<true> : sgemm_kernel<false>;
+        CLPK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSgemmSmemBytes));
+        kernel<<<(unsigned)tiles, kSgemmThreads, kSgemmSmemBytes, s>>>(static_cast<const float *>(a), static_cast<const float *>(b),
+                                                                      static_cast<float *>(c), m, n, k, alpha);
         CLPK_LAUNCH_CHECK("sgemm");
     } else {
         // 128 x 64 CTA tiles: 34.2-34.5 TFLOPS at 4096^3 / 8192^3 against 31.9-32.1 with 128 x 128 tiles of 8 warps
-        CLPK_CUDA(cudaFuncSetAttribute(dgemm_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Dgemm<64>::smem_bytes));
-        dgemm_kernel<64><<<(unsigned)(2 * tiles), Dgemm<64>::threads, Dgemm<64>::smem_bytes, s>>>(
+        auto kernel = ragged ? dgemm_kernel<64, true> : dgemm_kernel<64, false>;
+        CLPK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Dgemm<64>::smem_bytes));
+        kernel<<<(unsigned)tiles, Dgemm<64>::threads, Dgemm<64>::smem_bytes, s>>>(
             static_cast<const double *>(a), static_cast<const double *>(b), static_cast<double *>(c), m, n, k, (double)alpha);
         CLPK_LAUNCH_CHECK("dgemm");
     }

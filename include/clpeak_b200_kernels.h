@@ -406,7 +406,7 @@ CLPK_API int clpk_dmma_peak(const double *d_a, const double *d_b, uint32_t n_mma
  *   dtype            A / B elements                  accumulate   C element
  *   CLPK_DT_F32      fp32, CUDA cores (FFMA)         fp32         fp32   the reference's "fp32" row
  *   CLPK_DT_F64      fp64, mma.sync.m8n8k4 (DMMA)    fp64         fp64   the reference's "fp64" row
- *                    (src/cuda/cuda_blas.cpp:567-581); M, N multiples of 128, K of 16
+ *                    (src/cuda/cuda_blas.cpp:567-581); any M, N > 0, K a multiple of 4 (fp32) or 2 (fp64)
  *   CLPK_DT_BF16     bf16                            fp32         bf16
  *   CLPK_DT_F16      fp16                            fp32         bf16
  *   CLPK_DT_TF32     fp32 words (19 bits read)       fp32         fp32

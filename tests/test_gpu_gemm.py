@@ -387,20 +387,25 @@ def run_simt_gemm(K, cuda, dtype, m, n, k, alpha=1.0):
             K.clpk_convert_f32(q.data_ptr(), f.data_ptr(), rows * k, N.DT_F64, stream_ptr())
             f = q
         ops.append(f)
-    c = cuda.full((m * n,), float("nan"), dtype=tdt, device="cuda")
+    pad = 1024                                                 # canary after C: nothing may be written there
+    c = cuda.full((m * n + pad,), float("nan"), dtype=tdt, device="cuda")
     st = dev_empty(1, cuda.int32)
     args = N.GemmArgs(dtype=dtype, m=m, n=n, k=k, d_a=ops[0].data_ptr(), d_b=ops[1].data_ptr(), d_c=c.data_ptr(),
                       d_sfa=None, d_sfb=None, alpha=alpha, d_workspace=None, workspace_bytes=0, d_status=st.data_ptr())
     K.clpk_gemm(C.byref(args), stream_ptr())
     sync()
     assert int(to_np(st)[0]) == 0
-    return to_np(ops[0]), to_np(ops[1]), to_np(c)
+    c_all = to_np(c)
+    assert np.isnan(c_all[m * n:]).all(), "the kernel wrote beyond C"
+    return to_np(ops[0]), to_np(ops[1]), c_all[:m * n]
 
 
 @pytest.mark.parametrize("dtype", [N.DT_F32, N.DT_F64])
-@pytest.mark.parametrize("m,n,k", [(128, 128, 16), (256, 384, 64), (384, 128, 1040), (2048, 2048, 512), (4096, 4096, 4096)])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 16), (256, 384, 64), (384, 128, 1040), (2048, 2048, 512), (4096, 4096, 4096),
+                                   (1, 1, 4), (100, 72, 20), (129, 131, 36), (300, 202, 1044), (64, 257, 16), (1000, 1001, 260)])
 def test_simt_gemm_against_the_oracle(K, orc, cuda, dtype, m, n, k):
-    """Every element of the small cases, samples of the large one, against the oracle's fp64 dot product.
+    """Every element of the small cases, samples of the large one, against the oracle's fp64 dot product; whole
+    tiles and shapes that are not (M, N not multiples of the tile, K not of the k block, N odd).
     Tolerance: K sequential roundings of the accumulator, K * u * sum|a||b| with u = 2^-23 (fp32; one extra
     bit over the unit roundoff for the host's own accumulation) or 2^-51 (fp64)."""
     a, b, c = run_simt_gemm(K, cuda, dtype, m, n, k)
@@ -411,7 +416,7 @@ def test_simt_gemm_against_the_oracle(K, orc, cuda, dtype, m, n, k):
         s_abs = np.abs(a.reshape(m, k)).astype(np.float64) @ np.abs(b.reshape(n, k)).astype(np.float64).T
         assert np.all(np.abs(c.reshape(m, n).astype(np.float64) - want) <= k * u * s_abs + 1e-300)
     rng = np.random.default_rng(4)
-    samples = list(zip(rng.integers(0, m, 150), rng.integers(0, n, 150))) + [(0, 0), (m - 1, n - 1), (127, 0), (0, 127)]
+    samples = list(zip(rng.integers(0, m, 150), rng.integers(0, n, 150))) + [(0, 0), (m - 1, n - 1), (min(127, m - 1), 0), (0, min(127, n - 1))]
     worst = 0.0
     for i, j in samples:
         want, s_abs = orc.gemm_element(dtype, a, b, k, int(i), int(j))
@@ -425,7 +430,7 @@ def test_simt_gemm_alpha_and_argument_checks(K, orc, cuda, dtype):
     _, _, c2 = run_simt_gemm(K, cuda, dtype, 128, 256, 64, alpha=0.5)
     assert np.array_equal(c2, c1 * 0.5)                        # a power of two scales exactly
     d = dev_empty(64, cuda.float64)
-    for m, n, k in ((100, 128, 16), (128, 128, 8), (128, 64, 16)):
+    for m, n, k in ((0, 128, 16), (128, 128, 0), (128, 128, 17), (128, 64, 1)):      # empty, or rows not a multiple of 16 bytes
         args = N.GemmArgs(dtype=dtype, m=m, n=n, k=k, d_a=d.data_ptr(), d_b=d.data_ptr(), d_c=d.data_ptr(), alpha=1.0,
                           d_status=d.data_ptr())
         with pytest.raises(N.ClpkError) as e:
