@@ -625,14 +625,16 @@ static_assert(sizeof(NvGemmSmem) <= 512, "NvGemmSmem");
 // One CTA moves 128 rows x 32 words through shared memory: coalesced 128-byte reads along a
 // row, coalesced 512-byte writes of whole blocks (a byte-per-thread scatter took 64 us per
 // 16 MiB operand, 7 % of a 16384^3 NVFP4 GEMM; this takes a tenth of that).
-__global__ void __launch_bounds__(256) pack_scales_kernel(uint32_t *__restrict__ out, const uint32_t *__restrict__ in,
+// Rows at and beyond `rows` (the operand padded up to whole tiles) get zero factors: their elements arrive
+// as zeros from the operand's tensor map, and zero times any finite factor is zero.
+__global__ void __launch_bounds__(256) pack_scales_kernel(uint32_t *__restrict__ out, const uint32_t *__restrict__ in, uint32_t rows,
                                                           uint32_t words_per_row, uint32_t kblocks, int is_b, uint32_t words)
 {
     __shared__ uint32_t tile[128][33];
     const uint32_t row0 = blockIdx.y * 128, w0 = blockIdx.x * 32;
     for (uint32_t i = threadIdx.x; i < 128 * 32; i += 256) {
         const uint32_t r = i >> 5, c = i & 31;
-        tile[r][c] = (w0 + c < words_per_row) ? in[(uint64_t)(row0 + r) * words_per_row + w0 + c] : 0u;
+        tile[r][c] = (w0 + c < words_per_row && row0 + r < rows) ? in[(uint64_t)(row0 + r) * words_per_row + w0 + c] : 0u;
     }
     __syncthreads();
     for (uint32_t i = threadIdx.x; i < 32 * 128; i += 256) {
@@ -669,7 +671,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
     const uint32_t rank = cluster_ctarank();
     const uint32_t cluster_id = blockIdx.x >> 1;
     const uint32_t n_clusters = gridDim.x >> 1;
-    const uint32_t tiles_m = p.m / kTileMN, tiles_n = p.n / TN;
+    const uint32_t tiles_m = (p.m + kTileMN - 1) / kTileMN, tiles_n = (p.n + TN - 1) / TN;
     const uint32_t n_tiles = tiles_m * tiles_n;
 
     if (threadIdx.x == 0) {
@@ -1093,14 +1095,18 @@ int clpk_gemm_last_clock(unsigned long long *h_cycles, unsigned long long *h_ns,
     return CLPK_OK;
 }
 
+// rows of a block-scaled operand rounded up to whole 256-row tiles
+static inline uint32_t padded_rows(uint32_t rows) { return (rows + 255u) / 256u * 256u; }
+
 int clpk_gemm_workspace_bytes(int dtype, uint32_t m, uint32_t n, uint32_t k, size_t *bytes)
 {
     CLPK_REQUIRE(bytes, "bytes is NULL");
     *bytes = 0;
+    const size_t rows = (size_t)padded_rows(m) + padded_rows(n);      // scale blocks cover whole tiles
     if (dtype == CLPK_DT_NVF4)
-        *bytes = ((size_t)m + n) * (k / 16);
+        *bytes = rows * (k / 16);
     if (dtype == CLPK_DT_MXF4)              // packed into 4-byte words of which each instruction uses two bytes
-        *bytes = ((size_t)m + n) * (k / 32);
+        *bytes = rows * (k / 32);
     return CLPK_OK;
 }
 
@@ -1123,19 +1129,19 @@ static uint32_t fp4_tile_n(uint32_t m, uint32_t n, uint32_t k)
 static int pack_scales(const clpk_gemm_args_t *a, cudaStream_t s)
 {
     const uint32_t words = a->dtype == CLPK_DT_MXF4 ? 2 : 4;   // 32-bit scale words per row per 256 elements of K
-    const size_t sfa_bytes = (size_t)a->m * (a->k / 256) * words * 4, sfb_bytes = (size_t)a->n * (a->k / 256) * words * 4;
+    const size_t sfa_bytes = (size_t)padded_rows(a->m) * (a->k / 256) * words * 4, sfb_bytes = (size_t)padded_rows(a->n) * (a->k / 256) * words * 4;
     CLPK_REQUIRE(a->d_sfa && a->d_sfb, "block-scaled FP4 needs d_sfa and d_sfb");
     CLPK_REQUIRE(a->d_workspace && a->workspace_bytes >= sfa_bytes + sfb_bytes && ((uintptr_t)a->d_workspace % 16) == 0,
                  "block-scaled FP4 needs a 16-byte aligned workspace of clpk_gemm_workspace_bytes() bytes");
     CLPK_REQUIRE(((uintptr_t)a->d_sfa % 4) == 0 && ((uintptr_t)a->d_sfb % 4) == 0, "scale arrays must be 4-byte aligned");
     uint8_t *wsa = static_cast<uint8_t *>(a->d_workspace), *wsb = wsa + sfa_bytes;
     const uint32_t words_per_row = a->k / 256 * words, kblocks = a->k / 256;
-    const dim3 ga((words_per_row + 31) / 32, a->m / 128), gb((words_per_row + 31) / 32, a->n / 128);
-    pack_scales_kernel<<<ga, 256, 0, s>>>(reinterpret_cast<uint32_t *>(wsa), static_cast<const uint32_t *>(a->d_sfa),
+    const dim3 ga((words_per_row + 31) / 32, padded_rows(a->m) / 128), gb((words_per_row + 31) / 32, padded_rows(a->n) / 128);
+    pack_scales_kernel<<<ga, 256, 0, s>>>(reinterpret_cast<uint32_t *>(wsa), static_cast<const uint32_t *>(a->d_sfa), a->m,
                                           words_per_row, kblocks, 0, words);
     // B's blocks: per 256 columns [k block][instruction][column half] for the 256-wide tile, per 128 columns
     // [k block][instruction] (A's order) for the 128-wide one
-    pack_scales_kernel<<<gb, 256, 0, s>>>(reinterpret_cast<uint32_t *>(wsb), static_cast<const uint32_t *>(a->d_sfb),
+    pack_scales_kernel<<<gb, 256, 0, s>>>(reinterpret_cast<uint32_t *>(wsb), static_cast<const uint32_t *>(a->d_sfb), a->n,
                                           words_per_row, kblocks, fp4_tile_n(a->m, a->n, a->k) == 256 ? 1 : 0, words);
     CLPK_LAUNCH_CHECK("pack_scales");
     return CLPK_OK;
@@ -1148,8 +1154,8 @@ int clpk_gemm_pack_scales(const clpk_gemm_args_t *a, void *stream)
         return rc;
     CLPK_REQUIRE(a, "args is NULL");
     CLPK_REQUIRE(a->dtype == CLPK_DT_NVF4 || a->dtype == CLPK_DT_MXF4, "only the block-scaled FP4 kinds have scales to pack");
-    CLPK_REQUIRE(a->m % 256 == 0 && a->n % 256 == 0 && a->m > 0 && a->n > 0 && a->k > 0 && a->k % 256 == 0,
-                 "M, N multiples of 256 and K a multiple of 256 (got %u, %u, %u)", a->m, a->n, a->k);
+    CLPK_REQUIRE(a->m > 0 && a->n > 0 && a->k > 0 && a->k % 256 == 0, "M, N positive and K a positive multiple of 256 (got %u, %u, %u)",
+                 a->m, a->n, a->k);
     return pack_scales(a, as_stream(stream));
 }
 
@@ -1168,11 +1174,11 @@ int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
     }
     CLPK_REQUIRE(a->m > 0 && a->n > 0 && a->k > 0, "M, N and K must be positive");
     const bool block_scaled = a->dtype == CLPK_DT_NVF4 || a->dtype == CLPK_DT_MXF4;
-    // The dense kinds take ragged shapes: TMA fills what a box reads beyond the operands with zeros and clips what
-    // a box would store beyond C, so a partial tile costs a whole one but needs no code.  The block-scaled kinds
-    // keep whole tiles (their scale factors are repacked per 128 rows and 256 elements of K).
-    CLPK_REQUIRE(!block_scaled || (a->m % 256 == 0 && a->n % 256 == 0 && a->k % 256 == 0),
-                 "block-scaled FP4 needs M, N and K to be multiples of 256 (got %u, %u, %u)", a->m, a->n, a->k);
+    // Ragged shapes: TMA fills what a box reads beyond the operands with zeros and clips what a box would store
+    // beyond C, so a partial tile costs a whole one but needs no code.  The block-scaled kinds keep K in whole
+    // stages of 256 elements (four instructions' scale factors travel as one block); their scale blocks are
+    // packed for whole tiles, with zero factors for the rows beyond M and N.
+    CLPK_REQUIRE(!block_scaled || a->k % 256 == 0, "block-scaled FP4 needs K to be a multiple of 256 (got %u)", a->k);
     CLPK_REQUIRE(((uintptr_t)a->d_a % 16) == 0 && ((uintptr_t)a->d_b % 16) == 0 && ((uintptr_t)a->d_c % 16) == 0,
                  "operands must be 16-byte aligned");
     uint32_t elem_bits;
@@ -1228,7 +1234,7 @@ int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
     if (block_scaled) {
         const bool mx = a->dtype == CLPK_DT_MXF4;
         const uint32_t words = mx ? 2 : 4;                      // 32-bit scale words per row per 256 elements of K
-        const size_t sfa_bytes = (size_t)a->m * (a->k / 256) * words * 4, sfb_bytes = (size_t)a->n * (a->k / 256) * words * 4;
+        const size_t sfa_bytes = (size_t)padded_rows(a->m) * (a->k / 256) * words * 4, sfb_bytes = (size_t)padded_rows(a->n) * (a->k / 256) * words * 4;
         CLPK_REQUIRE((a->d_sfa != nullptr) == (a->d_sfb != nullptr), "d_sfa and d_sfb: give both, or neither when the workspace is already packed");
         CLPK_REQUIRE(a->d_workspace && a->workspace_bytes >= sfa_bytes + sfb_bytes && ((uintptr_t)a->d_workspace % 16) == 0,
                      "block-scaled FP4 needs a 16-byte aligned workspace of clpk_gemm_workspace_bytes() bytes");
@@ -1250,7 +1256,7 @@ int clpk_gemm(const clpk_gemm_args_t *a, void *stream)
         rc = make_output_map(&tc, a->d_c, a->m, a->n, a->dtype);
         if (rc != CLPK_OK)
             return rc;
-        const uint32_t n_tiles = (a->m / kTileMN) * (a->n / tn);
+        const uint32_t n_tiles = ((a->m + kTileMN - 1) / kTileMN) * ((a->n + tn - 1) / tn);
         if (tn == 128) {
             rc = make_operand_map(&tb, a->d_b, a->n, row_bytes, 64);       // each CTA stages 64 rows of B per stage
             if (rc != CLPK_OK)

@@ -416,9 +416,10 @@ CLPK_API int clpk_dmma_peak(const double *d_a, const double *d_b, uint32_t n_mma
  *   CLPK_DT_I8       int8                            int32        int32 (alpha ignored)
  *   CLPK_DT_MXF4     e2m1 + ue8m0 per 32             fp32         bf16
  *   CLPK_DT_NVF4     e2m1 + ue4m3 per 16             fp32         bf16
- * Dense tcgen05 kinds: any M, N, K > 0 such that a row of A / B and a row of C are multiples of
- * 16 bytes (partial tiles are computed whole and clipped; whole 512 x 256 tiles and K a multiple
- * of 128 bytes waste nothing).  FP4 kinds: M, N and K multiples of 256.
+ * tcgen05 kinds: any M, N, K > 0 such that a row of A / B and a row of C are multiples of 16
+ * bytes (partial tiles are computed whole and clipped; whole 512 x 256 tiles and K a multiple
+ * of 128 bytes waste nothing).  FP4 kinds: K a multiple of 256; the workspace holds scale
+ * blocks for M and N rounded up to multiples of 256.
  * FP4 kinds: d_a/d_b are packed e2m1 (K/2 bytes per row); d_sfa/d_sfb are the
  * scale bytes row-major [rows][K/16] (NVF4) or [rows][K/32] (MXF4) as written by
  * clpk_quantize_fp4; the call repacks them into the tensor-core tile order in

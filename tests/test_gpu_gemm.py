@@ -196,10 +196,11 @@ def make_nvfp4_operand(K, cuda, rows, k, seed, dtype=N.DT_NVF4):
 def run_nvfp4(K, cuda, m, n, k, dtype=N.DT_NVF4):
     a, sfa, tsa, fa = make_nvfp4_operand(K, cuda, m, k, 40, dtype)
     b, sfb, tsb, fb = make_nvfp4_operand(K, cuda, n, k, 41, dtype)
-    c = cuda.full((m * n,), 0x7FC0, dtype=cuda.int16, device="cuda")
+    c = cuda.full((m * n + 2048,), 0x7FC0, dtype=cuda.int16, device="cuda")     # the tail is a canary: nothing is written beyond C
     need = C.c_size_t(0)
     K.clpk_gemm_workspace_bytes(dtype, m, n, k, C.byref(need))
-    assert need.value == (m + n) * (k // (16 if dtype == N.DT_NVF4 else 32))
+    pad = lambda rows: (rows + 255) // 256 * 256                # scale blocks cover whole 256-row tiles
+    assert need.value == (pad(m) + pad(n)) * (k // (16 if dtype == N.DT_NVF4 else 32))
     ws = dev_empty(need.value, cuda.uint8)
     st = dev_empty(1, cuda.int32)
     alpha = float(np.float32(tsa) * np.float32(tsb))
@@ -209,17 +210,21 @@ def run_nvfp4(K, cuda, m, n, k, dtype=N.DT_NVF4):
     K.clpk_gemm(C.byref(args), stream_ptr())
     sync()
     assert int(to_np(st)[0]) == 0
-    return dict(a=to_np(a), b=to_np(b), sfa=to_np(sfa), sfb=to_np(sfb), c=to_np(c).view(np.uint16), alpha=alpha,
-                fa=fa, fb=fb)
+    c_all = to_np(c).view(np.uint16)
+    assert np.all(c_all[m * n:] == 0x7FC0), "the kernel wrote beyond C"
+    return dict(a=to_np(a), b=to_np(b), sfa=to_np(sfa), sfb=to_np(sfb), c=c_all[:m * n], alpha=alpha, fa=fa, fb=fb)
 
 
 @pytest.mark.parametrize("dtype", [N.DT_NVF4, N.DT_MXF4])
-@pytest.mark.parametrize("m,n,k", [(256, 256, 256), (256, 512, 1024), (768, 256, 512), (2048, 2048, 2048)])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 256), (256, 512, 1024), (768, 256, 512), (2048, 2048, 2048),
+                                   (200, 328, 256), (1000, 1016, 512), (264, 8, 768), (1, 136, 256)])
 def test_gemm_nvfp4(K, orc, cuda, m, n, k, dtype):
+    """Whole tiles and shapes that are not (the scale blocks are packed for whole tiles, with zero factors for the
+    rows beyond M and N)."""
     r = run_nvfp4(K, cuda, m, n, k, dtype)
     assert not np.any(r["c"] == 0x7FC0)
     rng = np.random.default_rng(5)
-    samples = list(zip(rng.integers(0, m, 120), rng.integers(0, n, 120))) + [(0, 0), (m - 1, n - 1), (127, 128), (128, 127)]
+    samples = list(zip(rng.integers(0, m, 120), rng.integers(0, n, 120))) + [(0, 0), (m - 1, n - 1), (min(127, m - 1), min(128, n - 1)), (min(128, m - 1), min(127, n - 1))]
     worst = 0.0
     for (i, j) in samples:
         want, s = orc.gemm_element(dtype, r["a"], r["b"], k, int(i), int(j), r["sfa"], r["sfb"])
@@ -252,7 +257,7 @@ def test_gemm_fp4_config_sizes_sampled(K, orc, cuda, dtype, m):
 
 
 @pytest.mark.parametrize("dtype", [N.DT_NVF4, N.DT_MXF4])
-@pytest.mark.parametrize("m,n,k", [(256, 256, 256), (256, 768, 1024), (1024, 512, 2304), (4096, 4096, 4096)])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 256), (256, 768, 1024), (1024, 512, 2304), (4096, 4096, 4096), (520, 392, 512)])
 def test_gemm_fp4_both_tile_shapes_give_the_same_bits(K, orc, cuda, dtype, m, n, k):
     """The 256 x 128 two-accumulator tile (the epilogue of one tile overlaps the main loop of the next) against
     the 256 x 256 single-accumulator tile: every element of C is one cluster's sum over K in the same order
@@ -327,7 +332,11 @@ def test_gemm_nvfp4_argument_checks(K, cuda):
     with pytest.raises(N.ClpkError) as e:
         K.clpk_gemm(C.byref(args), None)                 # K must be a multiple of 256
     assert e.value.code == N.ERR_BAD_ARG
-    args.k = 256
+    args.k, args.n = 256, 260
+    with pytest.raises(N.ClpkError) as e:
+        K.clpk_gemm(C.byref(args), None)                 # a row of C (bf16) must be a multiple of 16 bytes
+    assert e.value.code == N.ERR_BAD_ARG
+    args.n = 256
     with pytest.raises(N.ClpkError) as e:
         K.clpk_gemm(C.byref(args), None)                 # workspace too small
     assert e.value.code == N.ERR_BAD_ARG
