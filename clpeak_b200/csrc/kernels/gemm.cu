@@ -186,71 +186,82 @@ __device__ __forceinline__ void dense_tile_coords(uint32_t tile, uint32_t tiles_
     nb = first_n + within % width;
 }
 
-// Epilogue of one warp for one tile: the warp's 32 rows (TMEM lanes) x 128 columns of each of
-// `row_blocks` row blocks, moved in boxes of 128 bytes per row (64 bf16 or 32 fp32/int32
-// columns): tcgen05.ld -> convert -> the warp's own 4 KiB staging box in shared memory, written
-// in the 128-byte swizzle so that the 32 lanes (one row each) spread over the banks -> one TMA
-// store per box, which writes whole lines of C and clips rows beyond M.  (A thread-per-row
-// store straight to global memory costs 32 partial-sector transactions per instruction and held
-// the drain of a 256 x 256 CTA tile at 8 us.)  `empty_bar` (in the leader CTA) is arrived on
-// as soon as the tile's last tcgen05.ld has landed: the next tile may then overwrite tensor
+// Epilogue of one warp for one tile of the dense kernel: the warp's 32 rows (TMEM lanes) x 128 columns of each
+// of the two row blocks, moved in boxes of 128 bytes per row (64 bf16 or 32 fp32/int32 columns): tcgen05.ld ->
+// convert -> the warp's own 4 KiB staging box in shared memory, written in the 128-byte swizzle so that the 32
+// lanes (one row each) spread over the banks -> one TMA store per box, which writes whole lines of C and clips
+// rows and columns beyond M and N.  (A thread-per-row store straight to global memory costs 32 partial-sector
+// transactions per instruction and held the drain of a 256 x 256 CTA tile at 8 us.)  `empty_bar` (in the leader
+// CTA) is arrived on as soon as the tile's last tcgen05.ld has landed: the next tile may then overwrite tensor
 // memory while the tail of the stores is still in flight.
 //   taddr0   : tensor-memory address of this warp's lanes, column 0 of its 128 columns, row block 0
 //   row0/col0: C coordinates of the same element
+// A warp's share of a row block (128 columns) is read with four tcgen05.ld in flight and one wait (64 columns at
+// a time with a wait each held tensor memory about 1000 cycles longer per tile).  The main loop cannot
+// start the next tile before tensor memory is free (both row blocks fill all 512 columns), so the time the
+// accumulators take to leave is exposed once per tile: measured with 4 clusters at a pinned 1.84 GHz and K from
+// 1024 to 16384, a stage costs 1020-1030 cycles (the 1024 of its eight instructions) and a tile 5900 more with
+// the narrow reads, 4900 with these; 256 KiB of accumulators per CTA leave at about 50 bytes per cycle.
 template <int DT>
-__device__ __forceinline__ void drain_warp_tile(uint32_t taddr0, uint32_t row_blocks, uint32_t row0, uint32_t col0,
-                                                uint8_t *box, const CUtensorMap *tmap_c, float alpha, uint64_t *empty_bar,
-                                                int lane)
+__device__ __forceinline__ void drain_warp_tile_wide(uint32_t taddr0, uint32_t row0, uint32_t col0, uint8_t *box,
+                                                     const CUtensorMap *tmap_c, float alpha, uint64_t *empty_bar, int lane)
 {
-    constexpr uint32_t kColsPerBox = 128 / OutBytes<DT>::value;
-    constexpr uint32_t kBoxes = 128 / kColsPerBox;                  // per row block per warp
+    constexpr bool kNarrow = OutBytes<DT>::value == 2;              // two boxes of 64 columns, else four of 32
+    constexpr uint32_t kBoxes = kNarrow ? 2 : 4;
     uint8_t *my_row = box + lane * 128;
     const uint32_t sw = (uint32_t)(lane & 7);
-    const uint32_t n_boxes = row_blocks * kBoxes;
 #pragma unroll 1
-    for (uint32_t hb = 0; hb < n_boxes; hb++) {
-        const uint32_t h = hb / kBoxes, c = (hb % kBoxes) * kColsPerBox;
-        const uint32_t taddr = taddr0 + h * 256 + c;
-        uint32_t w[32];                                          // 128 bytes of output
-        if constexpr (OutBytes<DT>::value == 2) {
-            uint32_t r0[32], r1[32];
-            tmem_ld_32x32b_x32(taddr, r0);
-            tmem_ld_32x32b_x32(taddr + 32, r1);
-            tmem_ld_wait();
+    for (uint32_t h = 0; h < 2; h++) {
+        uint32_t r[4][32];
 #pragma unroll
-            for (int i = 0; i < 16; i++) {
-                __nv_bfloat162 v0 = __floats2bfloat162_rn(__uint_as_float(r0[2 * i]) * alpha, __uint_as_float(r0[2 * i + 1]) * alpha);
-                __nv_bfloat162 v1 = __floats2bfloat162_rn(__uint_as_float(r1[2 * i]) * alpha, __uint_as_float(r1[2 * i + 1]) * alpha);
-                w[i] = *reinterpret_cast<uint32_t *>(&v0);
-                w[16 + i] = *reinterpret_cast<uint32_t *>(&v1);
-            }
-        } else {
-            tmem_ld_32x32b_x32(taddr, w);
-            tmem_ld_wait();
-            if constexpr (DT == CLPK_DT_TF32) {
-#pragma unroll
-                for (int i = 0; i < 32; i++)
-                    w[i] = __float_as_uint(__uint_as_float(w[i]) * alpha);
-            }
-        }
-        if (hb == n_boxes - 1) {
+        for (int q = 0; q < 4; q++)
+            tmem_ld_32x32b_x32(taddr0 + h * 256 + 32 * q, r[q]);
+        tmem_ld_wait();
+        if (h == 1) {
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0)
                 mbar_arrive_cluster(empty_bar, 0);
         }
-        // the previous box must have been read out of shared memory by its store
-        if (lane == 0)
-            bulk_wait_read<0>();
-        __syncwarp();
+        if constexpr (kNarrow) {
+            // pack in place: box b's 32 words take the place of r[b]
 #pragma unroll
-        for (uint32_t j = 0; j < 8; j++)
-            *reinterpret_cast<uint4 *>(my_row + ((j ^ sw) << 4)) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-            tma_store_2d(tmap_c, box, (int32_t)(col0 + c), (int32_t)(row0 + h * 256));
-            bulk_commit();
+            for (int b = 0; b < 2; b++) {
+                uint32_t w[32];
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    __nv_bfloat162 v0 = __floats2bfloat162_rn(__uint_as_float(r[2 * b][2 * i]) * alpha, __uint_as_float(r[2 * b][2 * i + 1]) * alpha);
+                    __nv_bfloat162 v1 = __floats2bfloat162_rn(__uint_as_float(r[2 * b + 1][2 * i]) * alpha, __uint_as_float(r[2 * b + 1][2 * i + 1]) * alpha);
+                    w[i] = *reinterpret_cast<uint32_t *>(&v0);
+                    w[16 + i] = *reinterpret_cast<uint32_t *>(&v1);
+                }
+#pragma unroll
+                for (int i = 0; i < 32; i++)
+                    r[b][i] = w[i];
+            }
+        } else if constexpr (DT == CLPK_DT_TF32) {
+#pragma unroll
+            for (int q = 0; q < 4; q++)
+#pragma unroll
+                for (int i = 0; i < 32; i++)
+                    r[q][i] = __float_as_uint(__uint_as_float(r[q][i]) * alpha);
+        }
+#pragma unroll
+        for (uint32_t b = 0; b < kBoxes; b++) {
+            // the previous box must have been read out of shared memory by its store
+            if (lane == 0)
+                bulk_wait_read<0>();
+            __syncwarp();
+#pragma unroll
+            for (uint32_t j = 0; j < 8; j++)
+                *reinterpret_cast<uint4 *>(my_row + ((j ^ sw) << 4)) =
+                    make_uint4(r[b][4 * j], r[b][4 * j + 1], r[b][4 * j + 2], r[b][4 * j + 3]);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_2d(tmap_c, box, (int32_t)(col0 + b * (128 / kBoxes)), (int32_t)(row0 + h * 256));
+                bulk_commit();
+            }
         }
     }
 }
@@ -500,8 +511,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
                 break;
             }
             tc_fence_after_sync();
-            drain_warp_tile<DT>(tmem + col_half * 128 + ((q * 32) << 16), 2, mb * kDenseTileM + rank * 128 + q * 32,
-                                nb * kTileMN + col_half * 128, box, &tmap_c, p.alpha, &sh->tmem_empty, lane);
+            drain_warp_tile_wide<DT>(tmem + col_half * 128 + ((q * 32) << 16), mb * kDenseTileM + rank * 128 + q * 32,
+                                     nb * kTileMN + col_half * 128, box, &tmap_c, p.alpha, &sh->tmem_empty, lane);
         }
         // The staging box must have been read before this CTA's shared memory goes away; the writes themselves
         // complete like any other store before the grid is reported finished, so they are not waited for here
