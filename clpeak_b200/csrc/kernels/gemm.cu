@@ -196,72 +196,120 @@ __device__ __forceinline__ void dense_tile_coords(uint32_t tile, uint32_t tiles_
 // memory while the tail of the stores is still in flight.
 //   taddr0   : tensor-memory address of this warp's lanes, column 0 of its 128 columns, row block 0
 //   row0/col0: C coordinates of the same element
-// A warp's share of a row block (128 columns) is read with four tcgen05.ld in flight and one wait (64 columns at
-// a time with a wait each held tensor memory about 1000 cycles longer per tile).  The main loop cannot
-// start the next tile before tensor memory is free (both row blocks fill all 512 columns), so the time the
-// accumulators take to leave is exposed once per tile: measured with 4 clusters at a pinned 1.84 GHz and K from
-// 1024 to 16384, a stage costs 1020-1030 cycles (the 1024 of its eight instructions) and a tile 5900 more with
-// the narrow reads, 4900 with these; 256 KiB of accumulators per CTA leave at about 50 bytes per cycle.
+// What a tile's hand-over costs was traced with clock64 stamps on 4 clusters at a fixed 1.84 GHz (K from 1024 to
+// 16384: a stage costs its 1024 cycles, a tile a constant on top).  The main loop cannot start the next tile
+// before tensor memory is free (both row blocks fill all 512 columns), so everything between the tile's last
+// instruction retiring and the arrive on `empty_bar` is exposed once per tile.  In the first version of this
+// epilogue that was 5 200 cycles, of which the tcgen05.ld themselves were 700 (a probe reads tensor memory at
+// 245 bytes per cycle with eight warps): the rest was two staging boxes stored before row block 1 was read (the
+// second box waits until TMA has read the first out of shared memory, 800-1400 cycles behind the operand loads),
+// and an mbarrier.arrive.release.cluster that took 1 650 cycles to retire because a release waits for the warp's
+// earlier shared-memory and bulk stores.  Now every column is read and converted before anything is stored and
+// the arrive is relaxed (the hand-over carries no memory): 2 200 cycles, 8192^3 fp8 3.9 % and NVFP4 5.5 % fewer.
+
+// one staging box out: wait until the previous store has read the box, fill it, hand it to TMA
+__device__ __forceinline__ void store_staged_box(const uint32_t (&w)[32], uint8_t *box, const CUtensorMap *tmap_c, uint32_t col,
+                                                 uint32_t row, int lane)
+{
+    uint8_t *my_row = box + lane * 128;
+    const uint32_t sw = (uint32_t)(lane & 7);
+    if (lane == 0)
+        bulk_wait_read<0>();
+    __syncwarp();
+#pragma unroll
+    for (uint32_t j = 0; j < 8; j++)
+        *reinterpret_cast<uint4 *>(my_row + ((j ^ sw) << 4)) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+        tma_store_2d(tmap_c, box, (int32_t)col, (int32_t)row);
+        bulk_commit();
+    }
+}
+
+__device__ __forceinline__ void pack_bf16x64(uint32_t (&w)[32], const uint32_t (&r0)[32], const uint32_t (&r1)[32], float alpha)
+{
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        __nv_bfloat162 v0 = __floats2bfloat162_rn(__uint_as_float(r0[2 * i]) * alpha, __uint_as_float(r0[2 * i + 1]) * alpha);
+        __nv_bfloat162 v1 = __floats2bfloat162_rn(__uint_as_float(r1[2 * i]) * alpha, __uint_as_float(r1[2 * i + 1]) * alpha);
+        w[i] = *reinterpret_cast<uint32_t *>(&v0);
+        w[16 + i] = *reinterpret_cast<uint32_t *>(&v1);
+    }
+}
+
 template <int DT>
 __device__ __forceinline__ void drain_warp_tile_wide(uint32_t taddr0, uint32_t row0, uint32_t col0, uint8_t *box,
                                                      const CUtensorMap *tmap_c, float alpha, uint64_t *empty_bar, int lane)
 {
-    constexpr bool kNarrow = OutBytes<DT>::value == 2;              // two boxes of 64 columns, else four of 32
-    constexpr uint32_t kBoxes = kNarrow ? 2 : 4;
-    uint8_t *my_row = box + lane * 128;
-    const uint32_t sw = (uint32_t)(lane & 7);
+    // The hand-over carries no memory (the reads have completed: tcgen05.wait::ld), so the arrive needs no release:
+    // with it the instruction took 1 650 cycles to retire here -- it waits for the warp's earlier shared-memory and
+    // bulk stores -- against 400 without.
+    auto release = [&]() {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0)
+            mbar_arrive_cluster_relaxed(empty_bar, 0);
+    };
+    if constexpr (OutBytes<DT>::value == 2) {
+        // 16-bit outputs: every column of the warp's lanes is read and packed (128 registers) before anything is
+        // written out, so that tensor memory is held for the reads alone: row block 0 with four tcgen05.ld in
+        // flight, row block 1 in two rounds of two (the register file holds no more).
+        uint32_t w0[32], w1[32], w2[32], w3[32];
+        {
+            uint32_t r0[32], r1[32], r2[32], r3[32];
+            tmem_ld_32x32b_x32(taddr0, r0);
+            tmem_ld_32x32b_x32(taddr0 + 32, r1);
+            tmem_ld_32x32b_x32(taddr0 + 64, r2);
+            tmem_ld_32x32b_x32(taddr0 + 96, r3);
+            tmem_ld_wait();
+            pack_bf16x64(w0, r0, r1, alpha);
+            pack_bf16x64(w1, r2, r3, alpha);
+        }
+        {
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32b_x32(taddr0 + 256, r0);
+            tmem_ld_32x32b_x32(taddr0 + 256 + 32, r1);
+            tmem_ld_wait();
+            pack_bf16x64(w2, r0, r1, alpha);
+        }
+        {
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32b_x32(taddr0 + 256 + 64, r0);
+            tmem_ld_32x32b_x32(taddr0 + 256 + 96, r1);
+            tmem_ld_wait();
+            release();
+            pack_bf16x64(w3, r0, r1, alpha);
+        }
+        store_staged_box(w0, box, tmap_c, col0, row0, lane);
+        store_staged_box(w1, box, tmap_c, col0 + 64, row0, lane);
+        store_staged_box(w2, box, tmap_c, col0, row0 + 256, lane);
+        store_staged_box(w3, box, tmap_c, col0 + 64, row0 + 256, lane);
+    } else {
+        // 32-bit outputs: a row block's 128 columns per round, four boxes of 32 columns
 #pragma unroll 1
-    for (uint32_t h = 0; h < 2; h++) {
-        uint32_t r[4][32];
+        for (uint32_t h = 0; h < 2; h++) {
+            uint32_t r0[32], r1[32], r2[32], r3[32];
+            tmem_ld_32x32b_x32(taddr0 + h * 256, r0);
+            tmem_ld_32x32b_x32(taddr0 + h * 256 + 32, r1);
+            tmem_ld_32x32b_x32(taddr0 + h * 256 + 64, r2);
+            tmem_ld_32x32b_x32(taddr0 + h * 256 + 96, r3);
+            tmem_ld_wait();
+            if (h == 1)
+                release();
+            if constexpr (DT == CLPK_DT_TF32) {
 #pragma unroll
-        for (int q = 0; q < 4; q++)
-            tmem_ld_32x32b_x32(taddr0 + h * 256 + 32 * q, r[q]);
-        tmem_ld_wait();
-        if (h == 1) {
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0)
-                mbar_arrive_cluster(empty_bar, 0);
-        }
-        if constexpr (kNarrow) {
-            // pack in place: box b's 32 words take the place of r[b]
-#pragma unroll
-            for (int b = 0; b < 2; b++) {
-                uint32_t w[32];
-#pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    __nv_bfloat162 v0 = __floats2bfloat162_rn(__uint_as_float(r[2 * b][2 * i]) * alpha, __uint_as_float(r[2 * b][2 * i + 1]) * alpha);
-                    __nv_bfloat162 v1 = __floats2bfloat162_rn(__uint_as_float(r[2 * b + 1][2 * i]) * alpha, __uint_as_float(r[2 * b + 1][2 * i + 1]) * alpha);
-                    w[i] = *reinterpret_cast<uint32_t *>(&v0);
-                    w[16 + i] = *reinterpret_cast<uint32_t *>(&v1);
+                for (int i = 0; i < 32; i++) {
+                    r0[i] = __float_as_uint(__uint_as_float(r0[i]) * alpha);
+                    r1[i] = __float_as_uint(__uint_as_float(r1[i]) * alpha);
+                    r2[i] = __float_as_uint(__uint_as_float(r2[i]) * alpha);
+                    r3[i] = __float_as_uint(__uint_as_float(r3[i]) * alpha);
                 }
-#pragma unroll
-                for (int i = 0; i < 32; i++)
-                    r[b][i] = w[i];
             }
-        } else if constexpr (DT == CLPK_DT_TF32) {
-#pragma unroll
-            for (int q = 0; q < 4; q++)
-#pragma unroll
-                for (int i = 0; i < 32; i++)
-                    r[q][i] = __float_as_uint(__uint_as_float(r[q][i]) * alpha);
-        }
-#pragma unroll
-        for (uint32_t b = 0; b < kBoxes; b++) {
-            // the previous box must have been read out of shared memory by its store
-            if (lane == 0)
-                bulk_wait_read<0>();
-            __syncwarp();
-#pragma unroll
-            for (uint32_t j = 0; j < 8; j++)
-                *reinterpret_cast<uint4 *>(my_row + ((j ^ sw) << 4)) =
-                    make_uint4(r[b][4 * j], r[b][4 * j + 1], r[b][4 * j + 2], r[b][4 * j + 3]);
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-                tma_store_2d(tmap_c, box, (int32_t)(col0 + b * (128 / kBoxes)), (int32_t)(row0 + h * 256));
-                bulk_commit();
-            }
+            store_staged_box(r0, box, tmap_c, col0, row0 + h * 256, lane);
+            store_staged_box(r1, box, tmap_c, col0 + 32, row0 + h * 256, lane);
+            store_staged_box(r2, box, tmap_c, col0 + 64, row0 + h * 256, lane);
+            store_staged_box(r3, box, tmap_c, col0 + 96, row0 + h * 256, lane);
         }
     }
 }
@@ -290,7 +338,7 @@ __device__ __forceinline__ void drain_warp_tile_early(uint32_t taddr0, uint32_t 
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0)
-                mbar_arrive_cluster(empty_bar, 0);
+                mbar_arrive_cluster_relaxed(empty_bar, 0);      // see drain_warp_tile_wide
         }
 #pragma unroll
         for (int i = 0; i < 16; i++) {
