@@ -597,17 +597,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
 //    (r % 32) * 16 + (r / 32) * 4 + j for row r's j-th factor.  One
 //    tcgen05.cp.cta_group::2.32x128b.warpx4 per block copies it from shared to
 //    tensor memory in both CTAs (4 columns, replicated in the four lane quarters).
-//  * Twelve such copies are needed per stage.  They are issued by four dedicated warps
-//    (10-13 of the leader CTA, three copies each), which run ahead of the MMA warp by up
-//    to the pipeline depth and hand over through an mbarrier (tcgen05.commit), so that
-//    they never sit in front of a stage's MMAs.  Writing the factors through registers
-//    (tcgen05.st from both CTAs) was tried and is slower: the per-stage cross-CTA
-//    mbarrier arrive costs about a microsecond.
-//  * Two producer warps per CTA, each with its own barriers: one loads the A and B
-//    tiles (full / empty), one the scale factors (sf_full; their shared-memory area is
-//    free again at sf_ready of the previous round, before that round's MMAs have even
-//    run), so the copies to tensor memory start when the 6 KiB of factors have landed
-//    instead of after the 64 KiB of tiles.
+//  * Twelve such copies are needed per stage (six for MXFP4).  The MMA warp issues them itself, in front of the
+//    stage's four instructions: tcgen05.cp and tcgen05.mma of one thread run in the order they were issued, so no
+//    barrier sits between a stage's factors reaching tensor memory and its multiplies.  (Four dedicated copy warps
+//    handing over through an mbarrier were the first design: a stage's copies could start only when the previous
+//    round's instructions on that stage had retired -- its tensor-memory columns -- and then queued behind the four
+//    stages of instructions issued meanwhile, so the pipe ran dry once per ring: 585 cycles per 512-cycle stage.
+//    With the copies in line MXFP4 runs at 513, NVFP4 at 552: seventeen tcgen05 instructions per stage from one
+//    elected lane at about 32 cycles each.)  Writing the factors through registers (tcgen05.st from both CTAs) was
+//    tried and is slower: the per-stage cross-CTA mbarrier arrive costs about a microsecond.
+//  * Two producer warps per CTA: one loads the A and B tiles (full / empty), one the scale factors (sf_full); both
+//    reuse a stage when its instructions have retired (empty).
 //  * Tensor memory (256-wide tile): accumulator in columns [0,256), then one 48-column scale area
 //    per pipeline stage (16 columns A, 32 columns B).  No room is left for a second
 //    accumulator, so a tile's epilogue is not overlapped with the next main loop; the
@@ -636,8 +636,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
 //    retired MMAs, raster group widths from 4 to 32.
 
 constexpr int kNvMaxStages = 6;
-constexpr int kNvCopyThreads = 4;
-constexpr int kNvGemmThreads = 32 * (3 + kEpilogueWarps + kNvCopyThreads);    // operand producer, MMA, 8 epilogue, 4 scale-copy warps, scale producer
+constexpr int kNvGemmThreads = 32 * (3 + kEpilogueWarps);                   // operand producer, MMA, 8 epilogue warps, scale producer
 constexpr uint32_t kNvSfCol = 256;                             // first scale column: after the accumulator(s)
 
 // TN = width of the cluster tile in columns of C.
@@ -670,7 +669,6 @@ struct NvGemmSmem {
     uint64_t full[kNvMaxStages];     // operand tiles of both CTAs landed (leader's barrier)
     uint64_t sf_full[kNvMaxStages];  // scale factors of both CTAs landed (leader's barrier)
     uint64_t empty[kNvMaxStages];    // the stage's MMAs retired (both CTAs)
-    uint64_t sf_ready[kNvMaxStages]; // the stage's scale factors are in tensor memory (both CTAs)
     uint64_t tmem_full[2];           // per accumulator
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
@@ -738,7 +736,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
             mbar_init(&sh->full[s], 1);
             mbar_init(&sh->sf_full[s], 1);
             mbar_init(&sh->empty[s], 1);
-            mbar_init(&sh->sf_ready[s], kNvCopyThreads);
         }
         for (int acc = 0; acc < 2; acc++) {
             mbar_init(&sh->tmem_full[acc], 1);
@@ -760,7 +757,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
     const uint32_t tmem = sh->tmem_base;
     join_previous_launch(p);
     const unsigned long long clk0 = clock64(), ns0 = globaltimer_ns();
-    constexpr int kScaleProducerWarp = 2 + kEpilogueWarps + kNvCopyThreads;
+    constexpr int kScaleProducerWarp = 2 + kEpilogueWarps;
 
     if (warp == 0) {
         // ---------------- operand producer (both CTAs): A and B tiles ----------------
@@ -801,8 +798,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
         }
     } else if (warp == kScaleProducerWarp) {
         // ---------------- scale-factor producer (both CTAs) ----------------
-        // The stage's scale area in shared memory is free again once the previous round's
-        // copies to tensor memory have completed, which is what sf_ready says.
+        // The stage's scale area in shared memory (and its tensor-memory columns) are free again when the previous
+        // round's instructions on the stage have retired: the copies run in front of them in the same queue.
         const uint32_t sf_full0 = leader_addr(&sh->sf_full[0]);
         uint32_t it = 0;
         bool ok = true;
@@ -813,7 +810,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
             const uint32_t sfb_block0 = nb * p.k_blocks * BS::b_blocks;
             for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
                 const uint32_t s = it % kNvStages, round = it / kNvStages;
-                if (round > 0 && !warp_wait(&sh->sf_ready[s], (round - 1) & 1)) {
+                if (round > 0 && !warp_wait(&sh->empty[s], (round - 1) & 1)) {
                     if (lane == 0)
                         atomicCAS(p.status, 0u, 0x216u);
                     ok = false;
@@ -855,7 +852,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
                 for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
                     const uint32_t s = it % kNvStages, round = it / kNvStages;
                     // the scale factors usually arrive first (6 KiB against 64): wait for them, then the tiles
-                    const bool landed = mbar_wait(&sh->sf_ready[s], round & 1) && mbar_wait(&sh->full[s], round & 1);
+                    const bool landed = mbar_wait(&sh->sf_full[s], round & 1) && mbar_wait(&sh->full[s], round & 1);
                     if (!__all_sync(0xffffffffu, landed ? 1 : 0)) {
                         if (lane == 0)
                             atomicCAS(p.status, 0u, 0x213u);
@@ -868,6 +865,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
                     const uint64_t ad = make_smem_desc(base, 16, 1024, kSwizzle128B);
                     const uint64_t bd = make_smem_desc(base + kHalfTileBytes, 16, 1024, kSwizzle128B);
                     if (elect_one()) {
+                        // the stage's scale factors go to tensor memory in front of its instructions, in the same queue:
+                        // 512-byte blocks, A's (4 columns each, from column 0), then B's (from column 16)
+                        const uint32_t sf_s = base + BS::tile_bytes;
+#pragma unroll
+                        for (uint32_t blk = 0; blk < BS::blocks; blk++) {
+                            const uint32_t col = blk < BS::a_blocks ? 4 * blk : 16 + 4 * (blk - BS::a_blocks);
+                            tmem_cp_32x128b_warpx4<2>(sfa_t + col, make_smem_desc(sf_s + blk * 512, 16, 128, kSwizzleNone));
+                        }
 #pragma unroll
                         for (uint32_t kk = 0; kk < 4; kk++) {
                             if constexpr (MX)
@@ -884,40 +889,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNvGemmThreads)
                 if (ok && elect_one())
                     tc_commit_pair(&sh->tmem_full[acc], 3);
                 __syncwarp();
-            }
-        }
-    } else if (warp >= 2 + kEpilogueWarps) {
-        // ---------------- scale-factor copy warps (leader CTA) ----------------
-        const uint32_t me = (uint32_t)(warp - (2 + kEpilogueWarps));
-        if (rank == 0) {
-            uint32_t it = 0;
-            bool ok = true;
-            for (uint32_t tile = cluster_id; tile < n_tiles && ok; tile += n_clusters) {
-                for (uint32_t kb = 0; kb < p.k_blocks; kb++, it++) {
-                    const uint32_t s = it % kNvStages, round = it / kNvStages;
-                    // the factors have landed, and the MMAs that read this stage's tensor-memory
-                    // columns in the previous round have retired
-                    if (!warp_wait(&sh->sf_full[s], round & 1) ||
-                        (round > 0 && !warp_wait(&sh->empty[s], (round - 1) & 1))) {
-                        if (lane == 0)
-                            atomicCAS(p.status, 0u, 0x215u);
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after_sync();
-                    const uint32_t sf_s = smem_u32(smem + (size_t)s * kNvStageBytes) + BS::tile_bytes;
-                    const uint32_t sf_t = tmem + kNvSfCol + s * kNvSfColsPerStage;
-                    if (elect_one()) {
-                        // 512-byte blocks of the stage: A's (4 columns each, from column 0), then B's (from column 16)
-                        for (uint32_t blk = me; blk < BS::blocks; blk += kNvCopyThreads) {
-                            const uint32_t col = blk < BS::a_blocks ? 4 * blk : 16 + 4 * (blk - BS::a_blocks);
-                            tmem_cp_32x128b_warpx4<2>(sf_t + col, make_smem_desc(sf_s + blk * 512, 16, 128, kSwizzleNone));
-                        }
-                        // arrives on sf_ready[s] in both CTAs when the copies above have completed in both
-                        tc_commit_pair(&sh->sf_ready[s], 3);
-                    }
-                    __syncwarp();
-                }
             }
         }
     } else {
