@@ -618,22 +618,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
 //    elements) has two factors per row per instruction, so one 32-bit word serves
 //    two instructions: the instruction descriptor's scale-factor id picks bytes 0-1
 //    or 2-3.  Half the blocks (2 of A + 4 of B per stage), half the copies.
-//  * What bounds it, with cycles counted at the clock CTA 0 really had (clock64 and
-//    %globaltimer around the whole kernel, clpk_gemm_last_clock): a fit over 4096^3,
-//    8192^3 and 16384^3 gives 669 cycles per 512-cycle stage, 1130 per tile and 9000 per
-//    launch -- the time goes in the main loop, not at the tile hand-over.  Releasing the
-//    accumulator before the epilogue has read it (timing only) changes nothing; the
-//    128-wide tile, which hides the epilogue, is 35 % slower; two N = 128 instructions per
-//    K step on the 256-wide tile cost 7 %.  A stage moves 38 KiB into shared memory (TMA)
-//    and 38 KiB out of it (32 KiB operands to the tensor core, 6 KiB scale factors to
-//    tensor memory): 76 KiB per 669 cycles = 116 bytes per cycle through a data pipe that
-//    takes one 128-byte wavefront per cycle (ncu: the reads alone fill 42 % of it over the
-//    whole launch).  A 256 x 256 x 256 FP4 stage needs 64 KiB of operand traffic per 512
-//    tensor-core cycles before its scale factors, so this shape is bound by the
-//    shared-memory data pipe at about 80 % of the tensor peak.  Tried and measured without
-//    effect: an L2 prefetch cursor ahead of the loads (slower), parked mbarrier waits, one
-//    polling lane per epilogue warp, letting the copies queue behind issued rather than
-//    retired MMAs, raster group widths from 4 to 32.
+//  * What it costs, in CTA 0's own cycles (clock64 and %globaltimer around the whole kernel,
+//    clpk_gemm_last_clock) on 4 clusters at a fixed 1.84 GHz with K from 1024 to 16384: a stage 552 cycles
+//    (NVFP4; MXFP4 513) against the 512 of its four instructions -- each scale copy takes about 3 cycles of the
+//    pipe -- and a tile about 1 600 more for the hand-over of tensor memory (see drain_warp_tile_wide).  The
+//    128-wide tile hides the hand-over but reads A twice as often and is 35 % slower; two N = 128 instructions per K
+//    step on the 256-wide tile cost 7 %.  Without effect: an L2 prefetch cursor ahead of the loads (slower), parked
+//    mbarrier waits, one polling lane per epilogue warp, raster group widths from 4 to 32, four stages instead of
+//    five (3 %), C stored with the L2 evict-first policy.
 
 constexpr int kNvMaxStages = 6;
 constexpr int kNvGemmThreads = 32 * (3 + kEpilogueWarps);                   // operand producer, MMA, 8 epilogue warps, scale producer
