@@ -229,6 +229,18 @@ __device__ __forceinline__ void store_staged_box(const uint32_t (&w)[32], uint8_
 
 __device__ __forceinline__ void pack_bf16x64(uint32_t (&w)[32], const uint32_t (&r0)[32], const uint32_t (&r1)[32], float alpha)
 {
+    // The conversion sits between the reads and the release of tensor memory; alpha = 1 (every dense row of the
+    // benchmark) skips the 64 multiplies, which are two thirds of its instructions.  x * 1.0f is x, bit for bit.
+    if (alpha == 1.0f) {
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            __nv_bfloat162 v0 = __floats2bfloat162_rn(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
+            __nv_bfloat162 v1 = __floats2bfloat162_rn(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]));
+            w[i] = *reinterpret_cast<uint32_t *>(&v0);
+            w[16 + i] = *reinterpret_cast<uint32_t *>(&v1);
+        }
+        return;
+    }
 #pragma unroll
     for (int i = 0; i < 16; i++) {
         __nv_bfloat162 v0 = __floats2bfloat162_rn(__uint_as_float(r0[2 * i]) * alpha, __uint_as_float(r0[2 * i + 1]) * alpha);
