@@ -612,8 +612,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
 //  * Twelve such copies are needed per stage (six for MXFP4).  The MMA warp issues them itself, in front of the
 //    stage's four instructions: tcgen05.cp and tcgen05.mma of one thread run in the order they were issued, so no
 //    barrier sits between a stage's factors reaching tensor memory and its multiplies.  (Four dedicated copy warps
-//    handing over through an mbarrier were the first design: a stage's copies could start only when the previous
-//    round's instructions on that stage had retired -- its tensor-memory columns -- and then queued behind the four
+//    handing over through an mbarrier were the first design: a stage's copies could start only when the ring's
+//    previous pass over that stage had retired -- its tensor-memory columns -- and then queued behind the four
 //    stages of instructions issued meanwhile, so the pipe ran dry once per ring: 585 cycles per 512-cycle stage.
 //    With the copies in line MXFP4 runs at 513, NVFP4 at 552: seventeen tcgen05 instructions per stage from one
 //    elected lane at about 32 cycles each.)  Writing the factors through registers (tcgen05.st from both CTAs) was
