@@ -615,8 +615,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
 //    handing over through an mbarrier were the first design: a stage's copies could start only when the ring's
 //    previous pass over that stage had retired -- its tensor-memory columns -- and then queued behind the four
 //    stages of instructions issued meanwhile, so the pipe ran dry once per ring: 585 cycles per 512-cycle stage.
-//    With the copies in line MXFP4 runs at 513, NVFP4 at 552: seventeen tcgen05 instructions per stage from one
-//    elected lane at about 32 cycles each.)  Writing the factors through registers (tcgen05.st from both CTAs) was
+//    With the copies in line MXFP4 runs at 513 and NVFP4 at 552: a copy takes about 3 cycles of the pipe, and
+//    issuing a stage's seventeen instructions takes the elected lane 304 cycles, eleven 234.)  Writing the factors
+//    through registers (tcgen05.st from both CTAs) was
 //    tried and is slower: the per-stage cross-CTA mbarrier arrive costs about a microsecond.
 //  * Two producer warps per CTA: one loads the A and B tiles (full / empty), one the scale factors (sf_full); both
 //    reuse a stage when its instructions have retired (empty).
