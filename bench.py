@@ -728,7 +728,7 @@ def check_gemm_samples(torch, N, dt, m, A, B, Cc, sfs, alpha, row_bytes, n_sampl
     from oracle import binding as orc            # checker only
     rng = np.random.default_rng(77)
     ii, jj = rng.integers(0, m, n_samples), rng.integers(0, m, n_samples)
-    sf_row = m // 16 if sfs[0] is not None else 0
+    sf_row = m // (32 if dt == N.DT_MXF4 else 16) if sfs[0] is not None else 0        # scale bytes per row
     worst = 0.0
     c16 = Cc.view(torch.int16)
     for i, j in zip(ii.tolist(), jj.tolist()):
@@ -1018,6 +1018,50 @@ def measure_rows(K, N, torch, stream, time_once, world=1, clocked=None, all_rank
             x = y = sx = sy = lib = lib_out = None
             del A, B, Cc, sfs, ws
             torch.cuda.empty_cache()
+
+    # MXFP4 (e2m1 with one ue8m0 factor per 32): the reference's cuBLASLt "mxf4_e2m1" row.  Timed and checked like
+    # the rows above, without a library side (torch's block-scaled entry point takes another scale layout).
+    for m in (8192, 16384):
+        try:
+            dt = N.DT_MXF4
+            A = torch.empty(m * m // 2, dtype=torch.uint8, device="cuda")
+            B = torch.empty(m * m // 2, dtype=torch.uint8, device="cuda")
+            Cc = torch.empty(m * m, dtype=torch.int16, device="cuda")
+            tmp = torch.empty(m * m, dtype=torch.float32, device="cuda")
+            sfs = [torch.empty(m * m // 32, dtype=torch.uint8, device="cuda") for _ in range(2)]
+            for buf, sfbuf, seed in ((A, sfs[0], 40), (B, sfs[1], 41)):
+                K.clpk_fill_f32(tmp.data_ptr(), m * m, seed, N.DIST_NORMAL, 0.0, 0.02, stream)
+                K.clpk_quantize_fp4(buf.data_ptr(), sfbuf.data_ptr(), tmp.data_ptr(), m, m, dt, 1.0, stream)
+            del tmp
+            ws_bytes = C.c_size_t(0)
+            K.clpk_gemm_workspace_bytes(dt, m, m, m, C.byref(ws_bytes))
+            ws = torch.empty(max(ws_bytes.value, 16), dtype=torch.uint8, device="cuda")
+            ga = N.GemmArgs(dtype=dt, m=m, n=m, k=m, d_a=A.data_ptr(), d_b=B.data_ptr(), d_c=Cc.data_ptr(),
+                            d_sfa=sfs[0].data_ptr(), d_sfb=sfs[1].data_ptr(), alpha=1.0, d_workspace=ws.data_ptr(),
+                            workspace_bytes=ws_bytes.value, d_status=status.data_ptr())
+            K.clpk_gemm_pack_scales(C.byref(ga), stream)
+            ga.d_sfa = None
+            ga.d_sfb = None
+            mine = lambda: K.clpk_gemm(C.byref(ga), stream)
+            flop = 2.0 * m * m * m
+            torch.cuda.synchronize()
+            time.sleep(3.0)                          # the rows above end in 2 s loops at the power cap
+            ms_rounds = [time_once(mine, reps=5) for _ in range(3)]
+            ms = median(ms_rounds)
+            Cc.fill_(0x7FC0)
+            mine()
+            torch.cuda.synchronize()
+            ok, worst = check_gemm_samples(torch, N, dt, m, A, B, Cc, sfs, 1.0, m // 2)
+            rows[f"gemm_mxf4_e2m1_{m}"] = {
+                "TFLOPS": flop / ms / 1e9, "ms": ms, "ms_rounds": ms_rounds, "frac_of_spec": flop / ms / 1e9 / SPEC["fp4_tflops"],
+                "status": int(status.item()), "box_TFLOPS": world * flop / ms / 1e9, "timing": "median of 3 bursts of 5 launches after 3 s idle",
+                "checked": all_ranks_ok(bool(ok) and int(status.item()) == 0),
+                "check": {"samples": 64, "worst_error_over_tolerance": worst, "replicas": world}}
+            del A, B, Cc, sfs, ws
+        except Exception as e:
+            rows[f"gemm_mxf4_e2m1_{m}"] = {"error": repr(e)[:200]}
+            all_ranks_ok(False)                      # keep the ranks' collectives in step
+        torch.cuda.empty_cache()
     return rows
 
 
